@@ -1,0 +1,102 @@
+/*
+ * tab_b200 — C ABI of the B200 (sm_100a) implementation of TAB's ternary/binary inference hot path.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the given CUDA stream and
+ * returns immediately (no host synchronisation).  Return value: 0 on success, a negative TAB_E_* code
+ * otherwise; nothing is thrown across this boundary.  None of the *_launch functions allocates or
+ * frees device memory: scratch is a caller-provided workspace.
+ *
+ * Data formats (identical to the reference CUDA backend):
+ *   x    float32, N·H·W·C elements in N,H,W,C order                       (TAB_GEMM.cu:184,231)
+ *   ths  float32[N], one threshold per image / per filter                   (TAB_GPU.cpp:23,49)
+ *   qx   int64  [N][H][W][PC][bits], PC = ceil(C/64); channel c is bit c%64 (LSB first) of word c/64;
+ *        bits == 2: plane 0 = sign (1 means -1), plane 1 = magnitude (1 means non-zero);
+ *        bits == 1: the single plane holds 1 for -1 and 0 for +1           (TAB_GEMM.cu:184-206,231-245)
+ *   btn  int32  [N], popcount of the magnitude plane of every n            (TAB_GEMM.cu:150-160)
+ *   y    float32, physical order [N][OH][OW][KN] (the reference relabels this buffer as
+ *        shape {N,KN,OH,OW} without permuting it)                           (TAB_GEMM.cu:53,509,526)
+ */
+#ifndef TAB_B200_H_
+#define TAB_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same object as cudaStream_t; declared here so that C callers need no CUDA headers. */
+typedef struct CUstream_st* tab_stream_t;
+
+enum {
+    TAB_OK = 0,
+    TAB_E_BAD_ARGUMENT = -1,   /* a size, type or bitwidth is out of range */
+    TAB_E_NULL_POINTER = -2,   /* a required pointer is NULL */
+    TAB_E_WORKSPACE = -3,      /* workspace smaller than tab_conv2d_workspace_bytes() or misaligned */
+    TAB_E_CUDA = -4,           /* the CUDA runtime reported an error; see tab_last_cuda_error() */
+    TAB_E_TOO_LARGE = -5,      /* a size exceeds what an entry point supports */
+    TAB_E_ALIGNMENT = -6       /* a pointer is not aligned to its element type */
+};
+
+/* Human-readable text for a TAB_E_* code (static storage). */
+const char* tab_error_string(int code);
+/* cudaError_t value of the most recent CUDA failure seen by this library on the calling thread. */
+int tab_last_cuda_error(void);
+/* Library version: major*10000 + minor*100 + patch. */
+int tab_version(void);
+
+/*
+ * Threshold-quantise and bit-pack (replaces QuanWithCuda_TAB, TAB_GEMM.cu:250-322, and its kernels
+ * TerOnlyKernel :163-208, BinOnlyKernel :211-247, BTN_Weight :150-160).
+ * bitwidth == 1 -> binary {+1,-1} (bit = x < ths[n]); anything else -> ternary {+1,0,-1}
+ * (x > ths[n] -> +1, else x < -ths[n] -> -1, else 0).
+ * qx receives N·H·W·PC·bits words; btn receives N counts (zero for bitwidth 1).  btn may be NULL, in
+ * which case the counts are not produced.  btn is cleared by this call; it need not be pre-zeroed.
+ */
+int tab_quantize_launch(const float* x, const float* ths, int64_t* qx, int32_t* btn,
+                        int bitwidth, int N, int H, int W, int C, tab_stream_t stream);
+
+/*
+ * Bytes of scratch tab_conv2d_launch needs for these sizes (the bit-packed activations).
+ * Returns 0 for invalid arguments.
+ */
+size_t tab_conv2d_workspace_bytes(int type, int N, int H, int W, int C);
+
+/*
+ * Quantise activations, then convolve with pre-quantised weights as an implicit-im2col popcount GEMM
+ * (replaces ConvWithCuda_TAB, TAB_GEMM.cu:325-527: TerOnly/BinOnlyKernel, PadKernel TAB_GEMM.cuh:73-89,
+ * Img2RowKernel :92-115, GEMMWithCuda :22-66 and TNN/TBN/BTN/BNNGEMM TAB_GEMM.cu:25-147).
+ * type: 0 TNN, 1 TBN, 2 BTN, 3 BNN.  qw is the tab_quantize_launch output of the weights
+ * [KN][KH][KW][C] at bitwidth 2 for types 0,2 and bitwidth 1 for types 1,3.  btn (int32[KN]) is read
+ * for type 2 only and may be NULL otherwise.  OH = (H + 2·p1 − KH + 1) / s1, OW likewise (integer
+ * division, TAB_GEMM.cu:354-357).  y receives N·OH·OW·KN floats.  workspace must be 256-byte aligned.
+ */
+int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                      float* y, void* workspace, size_t workspace_bytes, int type,
+                      int p1, int p2, int s1, int s2,
+                      int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
+
+/*
+ * Same convolution on activations that are already bit-packed (the qx layout above with bits = 2 for
+ * types 0,1 and bits = 1 for types 2,3).  This is the GEMM stage of tab_conv2d_launch on its own
+ * (GEMMWithCuda, TAB_GEMM.cuh:22-66, with padding and im2row folded in); it needs no workspace.
+ */
+int tab_conv2d_packed_launch(const int64_t* qx, const int64_t* qw, const int32_t* btn, float* y,
+                             int type, int p1, int p2, int s1, int s2,
+                             int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
+
+/*
+ * Register-only micro-benchmark of the integer pipes used by the convolution, for roofline
+ * denominators: runs `iters` rounds on a grid that fills the device and writes elapsed-independent
+ * checksums to `sink` (at least tab_pipe_probe_sink_bytes() bytes).  kind: 0 = 32-bit POPC,
+ * 1 = LOP3.  *ops_out receives the number of lane-level instructions of that kind issued; the caller
+ * times the call with CUDA events.  Has no counterpart in the reference.
+ */
+size_t tab_pipe_probe_sink_bytes(void);
+int tab_pipe_probe_launch(int kind, int iters, void* sink, double* ops_out, tab_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TAB_B200_H_ */

@@ -1,0 +1,115 @@
+// extern "C" entry points declared in include/tab_b200.h: argument validation, then kernel dispatch.
+// No entry point in this file allocates or frees device memory, and none synchronises the host.
+#include "tab_kernels.cuh"
+
+namespace tab {
+
+static thread_local int g_last_cuda_error = 0;
+
+int record_cuda_error(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return TAB_E_CUDA;
+}
+
+void conv_set_csa(bool on);
+
+static bool dims_ok(int N, int H, int W, int C) { return N >= 0 && H >= 0 && W >= 0 && C >= 1; }
+
+}  // namespace tab
+
+using namespace tab;
+
+extern "C" {
+
+const char* tab_error_string(int code) {
+    switch (code) {
+        case TAB_OK: return "success";
+        case TAB_E_BAD_ARGUMENT: return "bad argument (size, type or bitwidth out of range)";
+        case TAB_E_NULL_POINTER: return "required pointer is NULL";
+        case TAB_E_WORKSPACE: return "workspace too small or not 256-byte aligned";
+        case TAB_E_CUDA: return "CUDA runtime error (see tab_last_cuda_error)";
+        case TAB_E_TOO_LARGE: return "problem size exceeds the supported range";
+        case TAB_E_ALIGNMENT: return "pointer not aligned to its element type";
+        default: return "unknown error code";
+    }
+}
+
+int tab_last_cuda_error(void) { return g_last_cuda_error; }
+
+int tab_version(void) { return 100; }
+
+int tab_quantize_launch(const float* x, const float* ths, int64_t* qx, int32_t* btn,
+                        int bitwidth, int N, int H, int W, int C, tab_stream_t stream) {
+    if (!dims_ok(N, H, W, C) || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
+    if (N == 0) return TAB_OK;
+    if (reinterpret_cast<uintptr_t>(btn) & 3) return TAB_E_ALIGNMENT;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (btn) {
+        cudaError_t e = cudaMemsetAsync(btn, 0, sizeof(int32_t) * (size_t)N, s);
+        if (e != cudaSuccess) return record_cuda_error(e);
+    }
+    if ((long long)H * W == 0) return TAB_OK;
+    if (!x || !ths || !qx) return TAB_E_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) ||
+        (reinterpret_cast<uintptr_t>(qx) & 7))
+        return TAB_E_ALIGNMENT;
+    if ((long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
+    const int bits = (bitwidth == 1) ? 1 : 2;                      // TAB_GEMM.cu:267,309
+    return quantize_dispatch(x, ths, qx, bits == 2 ? btn : nullptr, bits, N, H, W, C, s);
+}
+
+size_t tab_conv2d_workspace_bytes(int type, int N, int H, int W, int C) {
+    if (type < 0 || type > 3 || !dims_ok(N, H, W, C)) return 0;
+    const size_t words = (size_t)N * H * W * packed_channels(C) * act_bits(type);
+    return (words * 8 + 255) / 256 * 256;
+}
+
+static int conv_args_ok(int type, int p1, int p2, int s1, int s2, int N, int H, int W, int C,
+                        int KN, int KH, int KW) {
+    if (type < 0 || type > 3) return TAB_E_BAD_ARGUMENT;
+    if (!dims_ok(N, H, W, C) || KN < 0 || KH < 1 || KW < 1 || p1 < 0 || p2 < 0 || s1 < 1 || s2 < 1)
+        return TAB_E_BAD_ARGUMENT;
+    return TAB_OK;
+}
+
+int tab_conv2d_packed_launch(const int64_t* qx, const int64_t* qw, const int32_t* btn, float* y,
+                             int type, int p1, int p2, int s1, int s2,
+                             int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
+    int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
+    if (rc != TAB_OK) return rc;
+    const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
+    if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
+    if (!qx || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
+    const uintptr_t qx_mask = act_bits(type) == 2 ? 15 : 7;        // 16-byte (sign, magnitude) pairs
+    if ((reinterpret_cast<uintptr_t>(qx) & qx_mask) || (reinterpret_cast<uintptr_t>(qw) & 7) ||
+        (reinterpret_cast<uintptr_t>(y) & 3) || (reinterpret_cast<uintptr_t>(btn) & 3))
+        return TAB_E_ALIGNMENT;
+    return conv_packed_dispatch(qx, qw, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                      float* y, void* workspace, size_t workspace_bytes, int type,
+                      int p1, int p2, int s1, int s2,
+                      int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
+    int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
+    if (rc != TAB_OK) return rc;
+    const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
+    if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
+    if (!x || !ths || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
+    const size_t need = tab_conv2d_workspace_bytes(type, N, H, W, C);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return TAB_E_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3)) return TAB_E_ALIGNMENT;
+    if ((long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    int64_t* qx = reinterpret_cast<int64_t*>(workspace);
+    rc = quantize_dispatch(x, ths, qx, nullptr, act_bits(type), N, H, W, C, s);   // TAB_GEMM.cu:419-426
+    if (rc != TAB_OK) return rc;
+    return tab_conv2d_packed_launch(qx, qw, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream);
+}
+
+/* Test/benchmark hook: 1 = carry-save popcount tree (default), 0 = one POPC per word. */
+void tab_debug_set_csa(int on) { conv_set_csa(on != 0); }
+
+}  // extern "C"

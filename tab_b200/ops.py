@@ -1,0 +1,126 @@
+"""``Quantize`` / ``Conv2d`` on torch CUDA tensors, calling the C ABI through ctypes.
+
+Argument order and meaning follow the reference binding (``TAB_GPU.cpp:34,53``); tensor checks follow
+its ``CHECK_INPUT`` macro (``TAB_GPU.cpp:7-9``): every tensor argument must be a contiguous CUDA tensor
+or a ``RuntimeError`` is raised.  Unlike the reference, dtypes are checked instead of converted (the
+reference takes ``data_ptr()`` of a converted temporary, ``TAB_GEMM.cu:279,341``) and CUDA failures
+raise instead of returning a partially written tensor (``TAB_GEMM.cu:292-321``).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+
+
+def _check_input(t: torch.Tensor, name: str, dtype: torch.dtype) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    if t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s" % (name, dtype))
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def conv_out_size(H, W, KH, KW, p1, p2, s1, s2):
+    """OH, OW as the reference computes them (``TAB_GEMM.cu:354-357``), clamped at 0."""
+    return max((H + 2 * p1 - KH + 1) // s1, 0), max((W + 2 * p2 - KW + 1) // s2, 0)
+
+
+def Quantize(X, thresholds, bitwidth, N, H, W, C):
+    """``TAB_Quantize`` (``TAB_GPU.cpp:53-58``): returns ``[QX, BTN_W]``.
+
+    ``QX`` int64 ``{N,H,W,ceil(C/64),bits}``; ``BTN_W`` int32 ``{N}`` (zeros when ``bitwidth == 1``).
+    """
+    _check_input(X, "X", torch.float32)
+    _check_input(thresholds, "thresholds", torch.float32)
+    N, H, W, C, bitwidth = int(N), int(H), int(W), int(C), int(bitwidth)
+    if min(N, H, W) < 0 or C < 1 or bitwidth < 1:
+        raise RuntimeError("Quantize: sizes must be non-negative, C >= 1 and bitwidth >= 1")
+    if X.numel() != N * H * W * C:
+        raise RuntimeError("X has %d elements, expected N*H*W*C = %d" % (X.numel(), N * H * W * C))
+    if thresholds.numel() != N:
+        raise RuntimeError("thresholds has %d elements, expected N = %d" % (thresholds.numel(), N))
+    bits = 1 if bitwidth == 1 else 2
+    PC = (C + 63) // 64
+    with torch.cuda.device(X.device):
+        QX = torch.empty((N, H, W, PC, bits), dtype=torch.int64, device=X.device)
+        BTN = torch.empty((N,), dtype=torch.int32, device=X.device)
+        rc = _cabi.lib().tab_quantize_launch(X.data_ptr(), thresholds.data_ptr(), QX.data_ptr(), BTN.data_ptr(),
+                                             bitwidth, N, H, W, C, _stream_ptr(X.device))
+    _cabi.check(rc, "tab_quantize_launch")
+    return [QX, BTN]
+
+
+def _conv_checks(conv_type, QW, btn, N, H, W, C, KN, KH, KW, p1, p2, s1, s2):
+    if conv_type not in (0, 1, 2, 3):
+        raise RuntimeError("type must be 0 (TNN), 1 (TBN), 2 (BTN) or 3 (BNN)")
+    if min(N, H, W, KN) < 0 or C < 1 or KH < 1 or KW < 1 or p1 < 0 or p2 < 0 or s1 < 1 or s2 < 1:
+        raise RuntimeError("Conv2d: invalid size, padding or stride")
+    wb = 1 if conv_type in (1, 3) else 2
+    need = KN * KH * KW * ((C + 63) // 64) * wb
+    if QW.numel() != need:
+        raise RuntimeError("QW has %d words, type %d needs KN*KH*KW*ceil(C/64)*%d = %d "
+                           "(quantise the weights at bitwidth %d)" % (QW.numel(), conv_type, wb, need, wb))
+    if conv_type == 2 and btn.numel() != KN:
+        raise RuntimeError("btn has %d elements, expected KN = %d" % (btn.numel(), KN))
+
+
+def Conv2d(X, QW, thresholds, btn, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW):
+    """``TAB_Conv2d`` (``TAB_GPU.cpp:34-42``): float32 tensor of shape ``{N,KN,OH,OW}`` whose buffer is in
+    ``[N][OH][OW][KN]`` order (``TAB_GEMM.cu:509,526``)."""
+    _check_input(X, "X", torch.float32)
+    _check_input(QW, "QW", torch.int64)
+    _check_input(thresholds, "thresholds", torch.float32)
+    _check_input(btn, "btn", torch.int32)
+    conv_type = int(type)
+    p1, p2, s1, s2 = int(padding1), int(padding2), int(stride1), int(stride2)
+    N, H, W, C, KN, KH, KW = (int(v) for v in (N, H, W, C, KN, KH, KW))
+    _conv_checks(conv_type, QW, btn, N, H, W, C, KN, KH, KW, p1, p2, s1, s2)
+    if X.numel() != N * H * W * C:
+        raise RuntimeError("X has %d elements, expected N*H*W*C = %d" % (X.numel(), N * H * W * C))
+    if thresholds.numel() != N:
+        raise RuntimeError("thresholds has %d elements, expected N = %d" % (thresholds.numel(), N))
+    OH, OW = conv_out_size(H, W, KH, KW, p1, p2, s1, s2)
+    l = _cabi.lib()
+    with torch.cuda.device(X.device):
+        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=X.device)
+        ws_bytes = l.tab_conv2d_workspace_bytes(conv_type, N, H, W, C)
+        ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=X.device)
+        rc = l.tab_conv2d_launch(X.data_ptr(), QW.data_ptr(), thresholds.data_ptr(), btn.data_ptr(), Y.data_ptr(),
+                                 ws.data_ptr(), ws.numel(), conv_type, p1, p2, s1, s2,
+                                 N, H, W, C, KN, KH, KW, _stream_ptr(X.device))
+    _cabi.check(rc, "tab_conv2d_launch")
+    return Y
+
+
+def conv2d_packed(QX, QW, btn, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW):
+    """The GEMM stage alone on already packed activations (``GEMMWithCuda``, ``TAB_GEMM.cuh:22-66``, with
+    the padding and im2row stages folded in)."""
+    _check_input(QX, "QX", torch.int64)
+    _check_input(QW, "QW", torch.int64)
+    _check_input(btn, "btn", torch.int32)
+    conv_type = int(type)
+    p1, p2, s1, s2 = int(padding1), int(padding2), int(stride1), int(stride2)
+    N, H, W, C, KN, KH, KW = (int(v) for v in (N, H, W, C, KN, KH, KW))
+    _conv_checks(conv_type, QW, btn, N, H, W, C, KN, KH, KW, p1, p2, s1, s2)
+    ab = 1 if conv_type in (2, 3) else 2
+    if QX.numel() != N * H * W * ((C + 63) // 64) * ab:
+        raise RuntimeError("QX has %d words, type %d needs %d" % (QX.numel(), conv_type, N * H * W * ((C + 63) // 64) * ab))
+    OH, OW = conv_out_size(H, W, KH, KW, p1, p2, s1, s2)
+    with torch.cuda.device(QX.device):
+        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=QX.device)
+        rc = _cabi.lib().tab_conv2d_packed_launch(QX.data_ptr(), QW.data_ptr(), btn.data_ptr(), Y.data_ptr(),
+                                                  conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+                                                  _stream_ptr(QX.device))
+    _cabi.check(rc, "tab_conv2d_packed_launch")
+    return Y
+
+
+# The reference's CPU module and README use these names for the same operators (TAB_CPU.cpp:637-638).
+TAB_Quantize = Quantize
+TAB_Conv2d = Conv2d
