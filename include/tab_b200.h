@@ -87,6 +87,16 @@ int tab_conv2d_packed_launch(const int64_t* qx, const int64_t* qw, const int32_t
                              int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
 
 /*
+ * Chaining helper: y += residual (skipped when residual is NULL), then ths[n] = scale * mean|y[n]| over
+ * the per_image floats of image n - the threshold the next layer's quantiser takes.  sums is scratch
+ * for N doubles (cleared by this call).  Convolution outputs are integer-valued, so the double sums are
+ * exact and the thresholds do not depend on scheduling.  The reference leaves residuals and thresholds
+ * to the caller (its notebook computes them with framework ops): no counterpart there.
+ */
+int tab_residual_threshold_launch(float* y, const float* residual, float* ths, double* sums,
+                                  float scale, int N, long long per_image, tab_stream_t stream);
+
+/*
  * Register-only micro-benchmark of the integer pipes used by the convolution, for roofline
  * denominators: runs `iters` rounds on a grid that fills the device and writes elapsed-independent
  * checksums to `sink` (at least tab_pipe_probe_sink_bytes() bytes).  kind: 0 = 32-bit POPC,

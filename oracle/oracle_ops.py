@@ -1,0 +1,32 @@
+"""The ``ops`` interface of ``tab_b200.chain`` / ``tab_b200.dp`` implemented with the CPU oracle, on numpy
+arrays (and a torch-CPU adapter for the gloo tests).  TEST INFRASTRUCTURE ONLY."""
+import numpy as np
+
+from . import c_oracle, tab_oracle as O
+
+
+class OracleOps:
+    @staticmethod
+    def Quantize(x, ths, bitwidth, N, H, W, C):
+        return list(c_oracle.quantize(x, ths, bitwidth, N, H, W, C))
+
+    @staticmethod
+    def Conv2d(x, qw, ths, btn, conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW):
+        return c_oracle.conv2d(np.asarray(x).reshape(-1), qw, ths, btn, conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
+
+    @staticmethod
+    def residual_threshold(y, residual=None, scale=0.7):
+        N = y.shape[0]
+        if residual is not None:
+            y += np.asarray(residual, dtype=np.float32).reshape(y.shape)
+        per = y.size // N
+        s = np.abs(y.astype(np.float64)).reshape(N, -1).sum(axis=1)
+        return (np.float64(np.float32(scale)) * (s / np.float64(per))).astype(np.float32)
+
+
+def torch_cpu_conv(x, qw, ths, btn, conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW):
+    """Oracle convolution on torch CPU tensors (stand-in "kernel" for the gloo data-parallel tests)."""
+    import torch
+    y = c_oracle.conv2d(x.numpy().reshape(-1), qw.numpy(), ths.numpy(), btn.numpy(), conv_type,
+                        p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
+    return torch.from_numpy(y)

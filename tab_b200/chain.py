@@ -1,0 +1,131 @@
+"""ResNet-18-shaped chain of TAB convolutions (the network-level workload of the benchmark).
+
+The reference defines no network: it exposes ``Quantize`` and ``Conv2d`` only, and leaves thresholds,
+residual additions and layer chaining to the caller.  This module writes that caller down once, so that
+the benchmark, the tests and the CPU oracle all run the very same sequence:
+
+  * input: fp32 NHWC activations ``[N,56,56,64]`` (the output of a ResNet-18 stem; the first
+    convolution and the final classifier are not part of the chain);
+  * four stages of two basic blocks; a block is ``conv3x3 -> conv3x3`` plus a shortcut, added
+    elementwise: the identity, or a ``conv1x1`` stride 2 pad 0 where the stage halves the resolution
+    and doubles the width (64 -> 128 -> 256 -> 512 channels, 56 -> 28 -> 14 -> 7 pixels);
+    16 3x3 convolutions and 3 1x1 convolutions in all;
+  * every convolution input is re-quantised with a per-image threshold ``0.7 * mean|x|``
+    (``Conv2d`` takes fp32 activations, TAB_GEMM.cu:419-426); there is no batch-norm and no other
+    non-linearity; ``Conv2d``'s output buffer ``[N][OH][OW][KN]`` is the next layer's NHWC input as is;
+  * weights: seeded N(0,1), quantised per filter at ``0.7 * mean|w|`` with the bitwidth the type needs.
+
+``forward`` is written against a small ``ops`` interface (``Conv2d``, ``residual_threshold``) so that
+the identical topology runs on the device operators of this package and, in the tests, on a CPU oracle.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+
+THRESHOLD_SCALE = 0.7
+
+
+@dataclass
+class ConvSpec:
+    name: str
+    C: int
+    KN: int
+    K: int
+    stride: int
+    pad: int
+
+
+@dataclass
+class BlockSpec:
+    conv_a: ConvSpec
+    conv_b: ConvSpec
+    shortcut: Optional[ConvSpec]     # None = identity
+
+
+def resnet18_blocks() -> List[BlockSpec]:
+    blocks = []
+    c_in = 64
+    for stage, c_out in enumerate([64, 128, 256, 512]):
+        for b in range(2):
+            down = (b == 0 and stage > 0)
+            s = 2 if down else 1
+            blocks.append(BlockSpec(
+                ConvSpec("s%db%d.a" % (stage + 1, b), c_in, c_out, 3, s, 1),
+                ConvSpec("s%db%d.b" % (stage + 1, b), c_out, c_out, 3, 1, 1),
+                ConvSpec("s%db%d.sc" % (stage + 1, b), c_in, c_out, 1, 2, 0) if down else None))
+            c_in = c_out
+    return blocks
+
+
+def conv_specs() -> List[ConvSpec]:
+    out = []
+    for b in resnet18_blocks():
+        out += [b.conv_a, b.conv_b] + ([b.shortcut] if b.shortcut else [])
+    return out
+
+
+def chain_binary_ops(N: int, H: int = 56, W: int = 56) -> int:
+    """2*M*KN*KH*KW*C summed over the 19 convolutions (one multiply and one add per tap)."""
+    total = 0
+    h, w = H, W
+    for b in resnet18_blocks():
+        oh, ow = (h + 2 - 3 + 1) // b.conv_a.stride, (w + 2 - 3 + 1) // b.conv_a.stride
+        total += 2 * N * oh * ow * b.conv_a.KN * 9 * b.conv_a.C
+        total += 2 * N * oh * ow * b.conv_b.KN * 9 * b.conv_b.C
+        if b.shortcut:
+            total += 2 * N * oh * ow * b.shortcut.KN * b.shortcut.C
+        h, w = oh, ow
+    return total
+
+
+def make_weights(seed: int, conv_type: int = 0):
+    """Seeded fp32 weights ``[KN,K,K,C]`` and per-filter thresholds for every convolution, as numpy arrays
+    keyed by layer name (seed + layer index per tensor)."""
+    out = {}
+    for i, cs in enumerate(conv_specs()):
+        rng = np.random.default_rng(seed + i)
+        w = rng.standard_normal((cs.KN, cs.K, cs.K, cs.C), dtype=np.float32)
+        t = (np.float32(THRESHOLD_SCALE) * np.abs(w).reshape(cs.KN, -1).mean(axis=1, dtype=np.float32)).astype(np.float32)
+        out[cs.name] = (w, t)
+    return out
+
+
+def weight_bitwidth(conv_type: int) -> int:
+    return 1 if conv_type in (1, 3) else 2
+
+
+def quantize_weights(weights, conv_type, quantize_fn, to_backend=lambda a: a):
+    """name -> (QW, BTN_W) using the backend's ``Quantize``."""
+    q = {}
+    specs = {cs.name: cs for cs in conv_specs()}
+    for name, (w, t) in weights.items():
+        cs = specs[name]
+        qw, btn = quantize_fn(to_backend(w), to_backend(t), weight_bitwidth(conv_type), cs.KN, cs.K, cs.K, cs.C)
+        q[name] = (qw, btn)
+    return q
+
+
+def forward(ops, x, ths, qweights, conv_type: int, N: int, H: int = 56, W: int = 56):
+    """Run the chain.  ``x``: fp32 activations with N*H*W*64 elements (NHWC); ``ths``: thresholds ``[N]``
+    for ``x``.  Returns ``(y, OH, OW, KN)`` where ``y`` holds N*OH*OW*KN floats in NHWC order.  ``x`` is
+    not modified; intermediate activations are updated in place by the residual additions."""
+    h, w = H, W
+    for b in resnet18_blocks():
+        a, bb, sc = b.conv_a, b.conv_b, b.shortcut
+        qa, ba = qweights[a.name]
+        y1 = ops.Conv2d(x, qa, ths, ba, conv_type, a.pad, a.pad, a.stride, a.stride, N, h, w, a.C, a.KN, a.K, a.K)
+        oh, ow = (h + 2 * a.pad - a.K + 1) // a.stride, (w + 2 * a.pad - a.K + 1) // a.stride
+        t1 = ops.residual_threshold(y1, None, THRESHOLD_SCALE)
+        qb, bbt = qweights[bb.name]
+        y2 = ops.Conv2d(y1, qb, t1, bbt, conv_type, bb.pad, bb.pad, bb.stride, bb.stride, N, oh, ow, bb.C, bb.KN, bb.K, bb.K)
+        if sc is None:
+            short = x
+        else:
+            qs, bs = qweights[sc.name]
+            short = ops.Conv2d(x, qs, ths, bs, conv_type, sc.pad, sc.pad, sc.stride, sc.stride, N, h, w, sc.C, sc.KN, sc.K, sc.K)
+        ths = ops.residual_threshold(y2, short, THRESHOLD_SCALE)      # y2 += short; thresholds of the sum
+        x, h, w = y2, oh, ow
+    return x, h, w, resnet18_blocks()[-1].conv_b.KN

@@ -1,0 +1,89 @@
+// PyTorch extension module TAB_CUDA: the reference's binding surface (TAB_GPU.cpp:34-65) over the C ABI
+// in include/tab_b200.h.  This is the only translation unit that includes torch headers; it holds no
+// arithmetic.  Exports Quantize / Conv2d (TAB_GPU.cpp:63-64) and the aliases TAB_Quantize / TAB_Conv2d
+// used by the reference's CPU module and README (TAB_CPU.cpp:637-638).
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <vector>
+#include "../../include/tab_b200.h"
+
+// Same checks and messages as the reference (TAB_GPU.cpp:7-9).
+#define CHECK_CUDA(x) TORCH_CHECK(x.device().is_cuda(), #x " must be a CUDA tensor")
+#define CHECK_CONTIGUOUS(x) TORCH_CHECK(x.is_contiguous(), #x " must be contiguous")
+#define CHECK_INPUT(x) CHECK_CUDA(x); CHECK_CONTIGUOUS(x)
+
+static void check_rc(int rc, const char* where) {
+    TORCH_CHECK(rc == TAB_OK, where, ": ", tab_error_string(rc), " (code ", rc, ", cudaError ", tab_last_cuda_error(), ")");
+}
+
+static tab_stream_t current_stream() {
+    return reinterpret_cast<tab_stream_t>(at::cuda::getCurrentCUDAStream().stream());
+}
+
+// Quantize the input to {+1,0,-1} (bitwidth != 1) or {+1,-1} (bitwidth == 1).  X: N,H,W,C float32;
+// thresholds: float32[N].  Returns {QX int64 {N,H,W,PC,bits}, BTN_W int32 {N}}  (TAB_GPU.cpp:53-58).
+std::vector<torch::Tensor> TAB_Quantize(torch::Tensor X, torch::Tensor thresholds, int bitwidth, int N, int H, int W, int C) {
+    CHECK_INPUT(X);
+    CHECK_INPUT(thresholds);
+    // The reference converts dtypes and keeps a pointer into the temporary (TAB_GEMM.cu:279-280); here
+    // the dtypes are required instead.
+    TORCH_CHECK(X.scalar_type() == torch::kFloat32, "X must have dtype torch.float32");
+    TORCH_CHECK(thresholds.scalar_type() == torch::kFloat32, "thresholds must have dtype torch.float32");
+    TORCH_CHECK(N >= 0 && H >= 0 && W >= 0 && C >= 1 && bitwidth >= 1, "Quantize: sizes must be non-negative, C >= 1 and bitwidth >= 1");
+    TORCH_CHECK(X.numel() == (int64_t)N * H * W * C, "X has ", X.numel(), " elements, expected N*H*W*C = ", (int64_t)N * H * W * C);
+    TORCH_CHECK(thresholds.numel() == N, "thresholds has ", thresholds.numel(), " elements, expected N = ", N);
+    const c10::cuda::CUDAGuard guard(X.device());
+    const int bits = bitwidth == 1 ? 1 : 2;
+    const int PC = (C + 63) / 64;
+    auto QX = torch::empty({N, H, W, PC, bits}, torch::device(X.device()).dtype(torch::kInt64));
+    auto BTN = torch::empty({N}, torch::device(X.device()).dtype(torch::kInt32));
+    check_rc(tab_quantize_launch(X.data_ptr<float>(), thresholds.data_ptr<float>(), QX.data_ptr<int64_t>(),
+                                 BTN.data_ptr<int32_t>(), bitwidth, N, H, W, C, current_stream()),
+             "tab_quantize_launch");
+    return {QX, BTN};
+}
+
+// Convolution of all TAB types: 0 TNN, 1 TBN, 2 BTN, 3 BNN (TAB_GPU.cpp:34-42).  Returns float32
+// {N,KN,OH,OW} whose buffer is in [N][OH][OW][KN] order (TAB_GEMM.cu:509,526).
+torch::Tensor TAB_Conv2d(torch::Tensor X, torch::Tensor QW, torch::Tensor thresholds, torch::Tensor btn, int type,
+                         int padding1, int padding2, int stride1, int stride2,
+                         int N, int H, int W, int C, int KN, int KH, int KW) {
+    CHECK_INPUT(X);
+    CHECK_INPUT(QW);
+    CHECK_INPUT(thresholds);
+    CHECK_INPUT(btn);
+    TORCH_CHECK(X.scalar_type() == torch::kFloat32, "X must have dtype torch.float32");
+    TORCH_CHECK(QW.scalar_type() == torch::kInt64, "QW must have dtype torch.int64");
+    TORCH_CHECK(thresholds.scalar_type() == torch::kFloat32, "thresholds must have dtype torch.float32");
+    TORCH_CHECK(btn.scalar_type() == torch::kInt32, "btn must have dtype torch.int32");
+    TORCH_CHECK(type >= 0 && type <= 3, "type must be 0 (TNN), 1 (TBN), 2 (BTN) or 3 (BNN)");
+    TORCH_CHECK(N >= 0 && H >= 0 && W >= 0 && KN >= 0 && C >= 1 && KH >= 1 && KW >= 1 && padding1 >= 0 && padding2 >= 0 &&
+                stride1 >= 1 && stride2 >= 1, "Conv2d: invalid size, padding or stride");
+    const int PC = (C + 63) / 64;
+    const int wb = (type == 1 || type == 3) ? 1 : 2;
+    const int64_t need = (int64_t)KN * KH * KW * PC * wb;
+    TORCH_CHECK(QW.numel() == need, "QW has ", QW.numel(), " words, type ", type, " needs KN*KH*KW*ceil(C/64)*", wb, " = ", need,
+                " (quantise the weights at bitwidth ", wb, ")");
+    TORCH_CHECK(type != 2 || btn.numel() == KN, "btn has ", btn.numel(), " elements, expected KN = ", KN);
+    TORCH_CHECK(X.numel() == (int64_t)N * H * W * C, "X has ", X.numel(), " elements, expected N*H*W*C = ", (int64_t)N * H * W * C);
+    TORCH_CHECK(thresholds.numel() == N, "thresholds has ", thresholds.numel(), " elements, expected N = ", N);
+    const c10::cuda::CUDAGuard guard(X.device());
+    const int64_t OH = std::max<int64_t>(((int64_t)H + 2 * padding1 - KH + 1) / stride1, 0);
+    const int64_t OW = std::max<int64_t>(((int64_t)W + 2 * padding2 - KW + 1) / stride2, 0);
+    auto Y = torch::empty({N, KN, OH, OW}, torch::device(X.device()).dtype(torch::kFloat32));
+    const size_t ws_bytes = tab_conv2d_workspace_bytes(type, N, H, W, C);
+    auto ws = torch::empty({(int64_t)std::max<size_t>(ws_bytes, 256)}, torch::device(X.device()).dtype(torch::kUInt8));
+    check_rc(tab_conv2d_launch(X.data_ptr<float>(), QW.data_ptr<int64_t>(), thresholds.data_ptr<float>(),
+                               btn.data_ptr<int32_t>(), Y.data_ptr<float>(), ws.data_ptr(), (size_t)ws.numel(), type,
+                               padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW, current_stream()),
+             "tab_conv2d_launch");
+    return Y;
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("Quantize", &TAB_Quantize, "Ternarization or binarization of fp32 data in NHWC format");
+    m.def("Conv2d", &TAB_Conv2d, "Conv2d of all TAB series CNNs (0 TNN, 1 TBN, 2 BTN, 3 BNN)");
+    m.def("TAB_Quantize", &TAB_Quantize, "Alias of Quantize");
+    m.def("TAB_Conv2d", &TAB_Conv2d, "Alias of Conv2d");
+}

@@ -124,3 +124,24 @@ def conv2d_packed(QX, QW, btn, type, padding1, padding2, stride1, stride2, N, H,
 # The reference's CPU module and README use these names for the same operators (TAB_CPU.cpp:637-638).
 TAB_Quantize = Quantize
 TAB_Conv2d = Conv2d
+
+
+def residual_threshold(Y, residual=None, scale=0.7):
+    """In place ``Y += residual`` (when given), then the per-image thresholds ``scale * mean|Y[n]|`` as a
+    float32 CUDA tensor ``{N}`` - the ``thresholds`` argument of the next ``Conv2d``.  N is ``Y.shape[0]``.
+    Not part of the reference's interface (its callers compute thresholds with framework ops)."""
+    _check_input(Y, "Y", torch.float32)
+    if residual is not None:
+        _check_input(residual, "residual", torch.float32)
+        if residual.numel() != Y.numel():
+            raise RuntimeError("residual has %d elements, expected %d" % (residual.numel(), Y.numel()))
+    N = int(Y.shape[0]) if Y.dim() > 0 else 1
+    per_image = Y.numel() // N if N else 0
+    with torch.cuda.device(Y.device):
+        ths = torch.empty((N,), dtype=torch.float32, device=Y.device)
+        sums = torch.empty((max(N, 1),), dtype=torch.float64, device=Y.device)
+        rc = _cabi.lib().tab_residual_threshold_launch(Y.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                                       ths.data_ptr(), sums.data_ptr(), float(scale), N, per_image,
+                                                       _stream_ptr(Y.device))
+    _cabi.check(rc, "tab_residual_threshold_launch")
+    return ths

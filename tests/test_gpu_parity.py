@@ -1,0 +1,313 @@
+"""Parity of the CUDA path, called through the C ABI, with the CPU oracle: bit-exact (integer-valued
+results; the comparison is array equality, tolerance 0)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import tab_b200 as TAB
+from tab_b200 import _cabi, chain
+from oracle import c_oracle, tab_oracle as O
+from oracle.oracle_ops import OracleOps
+from util import make_input
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+NAMES = ["tnn", "tbn", "btn", "bnn"]
+
+
+def dev_t(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def gpu_conv(cuda, x, qw, ths, btn, t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW):
+    y = TAB.Conv2d(dev_t(x, cuda), dev_t(qw, cuda), dev_t(ths, cuda), dev_t(btn, cuda), t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
+    return y.cpu().numpy()
+
+
+# ------------------------------------------------------------------------------------------ quantise
+
+@pytest.mark.parametrize("bw", [2, 1])
+@pytest.mark.parametrize("C", [3, 64, 65, 128, 200, 256])
+@pytest.mark.parametrize("N,H,W", [(1, 1, 1), (3, 5, 7), (16, 9, 4)])
+def test_quantize_matches_oracle(cuda, bw, C, N, H, W):
+    x, ths = make_input(C * 7 + N, N, H, W, C)
+    q, b = TAB.Quantize(dev_t(x, cuda), dev_t(ths, cuda), bw, N, H, W, C)
+    qo, bo = O.quantize(x, ths, bw, N, H, W, C)
+    assert q.dtype == torch.int64 and tuple(q.shape) == qo.shape and b.dtype == torch.int32
+    assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(b.cpu().numpy(), bo)
+
+
+def test_quantize_edge_values_golden(cuda):
+    g = np.load(os.path.join(GOLD, "quantize_edges.npz"))
+    x, ths = g["x"], g["ths"]
+    N, H, W, C = x.shape
+    for bw, qk, bk in ((2, "q2", "btn2"), (1, "q1", "btn1")):
+        q, b = TAB.Quantize(dev_t(x, cuda), dev_t(ths, cuda), bw, N, H, W, C)
+        assert np.array_equal(q.cpu().numpy(), g[qk]) and np.array_equal(b.cpu().numpy(), g[bk])
+    # the same edge values through the vectorised path (C = 128)
+    x2 = np.zeros((1, 2, 2, 128), np.float32)
+    x2[0, 0, 0, :8] = x[0, 0, 0, :8]
+    x2[0, 1, 1, 120:128] = x[0, 0, 0, :8]
+    t2 = np.array([0.5], np.float32)
+    for bw in (2, 1):
+        q, b = TAB.Quantize(dev_t(x2, cuda), dev_t(t2, cuda), bw, 1, 2, 2, 128)
+        qo, bo = O.quantize(x2, t2, bw, 1, 2, 2, 128)
+        assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(b.cpu().numpy(), bo)
+
+
+def test_quantize_empty_and_unaligned(cuda):
+    q, b = TAB.Quantize(torch.empty(0, device=cuda), torch.empty(0, device=cuda), 2, 0, 4, 4, 64)
+    assert tuple(q.shape) == (0, 4, 4, 1, 2) and tuple(b.shape) == (0,)
+    q, b = TAB.Quantize(torch.empty(0, device=cuda), torch.zeros(3, device=cuda), 2, 3, 0, 4, 64)
+    assert tuple(q.shape) == (3, 0, 4, 1, 2) and not b.cpu().numpy().any()
+    # input that starts 4 bytes past a 16-byte boundary: the scalar path must take over
+    N, H, W, C = 2, 3, 5, 64
+    x, ths = make_input(9, N, H, W, C)
+    buf = torch.zeros(x.size + 1, device=cuda)
+    buf[1:] = dev_t(x.reshape(-1), cuda)
+    q, b = TAB.Quantize(buf[1:], dev_t(ths, cuda), 2, N, H, W, C)
+    qo, bo = O.quantize(x, ths, 2, N, H, W, C)
+    assert np.array_equal(q.cpu().numpy(), qo) and np.array_equal(b.cpu().numpy(), bo)
+
+
+def test_notebook_facts_on_device(cuda):
+    w = torch.rand(64, 3, 3, 256, device=cuda)
+    t = 0.7 * w.reshape(64, -1).mean(dim=1)
+    q2, b2 = TAB.Quantize(w, t, 2, 64, 3, 3, 256)
+    q1, b1 = TAB.Quantize(w, t, 1, 64, 3, 3, 256)
+    assert tuple(q2.shape) == (64, 3, 3, 4, 2) and q2.dtype == torch.int64 and tuple(b2.shape) == (64,)
+    assert not q2[..., 0].any().item()
+    assert torch.equal(q1[..., 0], ~q2[..., 1])
+    assert not b1.any().item()
+
+
+@pytest.mark.parametrize("bw", [2, 1])
+def test_quantize_full_size_configuration(cuda, bw):
+    """N=256, 56x56x256 (822 MB): two images against the oracle, and the BTN_W counts against a popcount
+    of the device's own magnitude plane (a checksum over everything that was written)."""
+    N, H, W, C = 256, 56, 56, 256
+    g = torch.Generator(device=cuda)
+    g.manual_seed(1)
+    x = torch.randn(N, H, W, C, device=cuda, generator=g)
+    ths = (0.7 * x.abs().mean(dim=(1, 2, 3))).contiguous()
+    q, b = TAB.Quantize(x, ths, bw, N, H, W, C)
+    th = ths.cpu().numpy()
+    for n in (0, 131, N - 1):
+        qo, bo = c_oracle.quantize(x[n].cpu().numpy(), th[n:n + 1], bw, 1, H, W, C)
+        assert np.array_equal(q[n].cpu().numpy(), qo[0])
+        assert int(b[n].item()) == int(bo[0])
+    if bw == 2:
+        lut = torch.tensor([bin(i).count("1") for i in range(256)], dtype=torch.int32, device=cuda)
+        mag_bytes = q[..., 1].contiguous().view(torch.uint8).reshape(N, -1)
+        counts = lut[mag_bytes.long()].sum(dim=1, dtype=torch.int64)
+        assert torch.equal(counts, b.long())
+        assert not (q[..., 0] & ~q[..., 1]).any().item()      # a sign bit never without its magnitude bit
+    else:
+        assert not b.any().item()
+
+
+# ------------------------------------------------------------------------------------------ convolution
+
+def test_conv_cfg1_golden(cuda):
+    g = np.load(os.path.join(GOLD, "conv_cfg1_tnn.npz"))
+    p1, p2, s1, s2, N, H, W, C, KN, KH, KW = (int(v) for v in g["geom"])
+    qw, btn = TAB.Quantize(dev_t(g["w"], cuda), dev_t(g["wths"], cuda), 2, KN, KH, KW, C)
+    assert np.array_equal(qw.cpu().numpy(), g["qw"]) and np.array_equal(btn.cpu().numpy(), g["btn"])
+    y = TAB.Conv2d(dev_t(g["x"], cuda), qw, dev_t(g["ths"], cuda), btn, 0, p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
+    assert tuple(y.shape) == (1, 64, 32, 32) and y.dtype == torch.float32
+    assert np.array_equal(y.cpu().numpy(), g["y"].astype(np.float32))
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "conv_small_*.npz"))))
+def test_conv_small_golden(cuda, path):
+    g = np.load(path)
+    geom = [int(v) for v in g["geom"]]
+    for t, name in enumerate(NAMES):
+        y = gpu_conv(cuda, g["x"], g["qw_" + name], g["ths"], g["btn_" + name], t, *geom)
+        assert np.array_equal(y, g["y_" + name].astype(np.float32)), name
+
+
+@pytest.mark.parametrize("t", range(4))
+@pytest.mark.parametrize("K,p", [(1, 0), (1, 1), (3, 0), (3, 1)])
+@pytest.mark.parametrize("s", [1, 2])
+def test_conv_grid(cuda, t, K, p, s):
+    """types x {1x1,3x3} x stride x pad, over channel counts with and without a tail word and batch sizes."""
+    for C in (3, 64, 65, 128, 200, 256):
+        for N, H, W, KN in ((1, 6, 6, 4), (3, 9, 5, 70)):
+            x, ths = make_input(C + N, N, H, W, C)
+            w, wths = make_input(C + N + 1, KN, K, K, C)
+            qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, K, K, C)
+            y = gpu_conv(cuda, x, qw, ths, btn, t, p, p, s, s, N, H, W, C, KN, K, K)
+            yo = c_oracle.conv2d(x, qw, ths, btn, t, p, p, s, s, N, H, W, C, KN, K, K)
+            assert y.shape == yo.shape and np.array_equal(y, yo), (C, N, H, W, KN)
+
+
+@pytest.mark.parametrize("t", range(4))
+@pytest.mark.parametrize("geom", [
+    # p1 p2 s1 s2  N   H   W    C   KN KH KW
+    (2, 2, 1, 1, 2, 12, 12, 128, 130, 5, 5),
+    (3, 3, 2, 2, 1, 15, 13, 64, 20, 7, 7),
+    (1, 2, 3, 2, 2, 10, 7, 200, 6, 3, 5),       # non-square everything; stride does not divide
+    (0, 0, 1, 1, 1, 2, 2, 64, 8, 3, 3),         # kernel larger than image: empty output
+    (1, 1, 1, 1, 5, 13, 11, 64, 257, 3, 3),     # M and KN not multiples of the CTA tile
+    (0, 0, 1, 1, 2, 3, 3, 1024, 1024, 1, 1),    # KN = 1024 (impossible on the reference launch shape)
+    (1, 1, 1, 1, 1, 4, 4, 4608, 3, 3, 3),       # 72 words per tap
+])
+def test_conv_shapes(cuda, t, geom):
+    p1, p2, s1, s2, N, H, W, C, KN, KH, KW = geom
+    x, ths = make_input(31, N, H, W, C)
+    w, wths = make_input(32, KN, KH, KW, C)
+    qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, KH, KW, C)
+    y = gpu_conv(cuda, x, qw, ths, btn, t, *geom)
+    yo = c_oracle.conv2d(x, qw, ths, btn, t, *geom)
+    assert y.shape == yo.shape and np.array_equal(y, yo)
+    yd = O.conv2d_dense(x, qw, ths, t, *geom) if N * H * W * C * KN < 4e7 else yo
+    assert np.array_equal(y, yd)
+
+
+@pytest.mark.parametrize("t", range(4))
+def test_popcount_tree_equals_plain_popcount(cuda, t):
+    """The carry-save reduction and the one-POPC-per-word variant are separate code paths."""
+    N, H, W, C, KN = 4, 14, 14, 256, 96
+    x, ths = make_input(5, N, H, W, C)
+    w, wths = make_input(6, KN, 3, 3, C)
+    qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, 3, 3, C)
+    l = _cabi.lib()
+    try:
+        l.tab_debug_set_csa(0)
+        y0 = gpu_conv(cuda, x, qw, ths, btn, t, 1, 1, 1, 1, N, H, W, C, KN, 3, 3)
+    finally:
+        l.tab_debug_set_csa(1)
+    y1 = gpu_conv(cuda, x, qw, ths, btn, t, 1, 1, 1, 1, N, H, W, C, KN, 3, 3)
+    yo = c_oracle.conv2d(x, qw, ths, btn, t, 1, 1, 1, 1, N, H, W, C, KN, 3, 3)
+    assert np.array_equal(y0, yo) and np.array_equal(y1, yo)
+
+
+RESNET_LAYERS = [
+    # H   C   KN  K s p
+    (56, 64, 64, 3, 1, 1), (28, 128, 128, 3, 1, 1), (14, 256, 256, 3, 1, 1), (7, 512, 512, 3, 1, 1),
+    (56, 64, 128, 3, 2, 1), (28, 128, 256, 3, 2, 1), (14, 256, 512, 3, 2, 1),
+]
+
+
+@pytest.mark.parametrize("t", range(4))
+@pytest.mark.parametrize("layer", RESNET_LAYERS)
+def test_resnet_layers_full_batch_sampled_images(cuda, t, layer):
+    """The N=64 ResNet-18-shaped layers at full size on the device; the oracle checks images 0, 37 and 63
+    (every image is independent, so a sample of images is an exact check of those outputs)."""
+    H, C, KN, K, s, p = layer
+    N = 64
+    g = torch.Generator(device=cuda)
+    g.manual_seed(H * 1000 + C + t)
+    x = torch.randn(N, H, H, C, device=cuda, generator=g)
+    ths = (0.7 * x.abs().mean(dim=(1, 2, 3))).contiguous()
+    w, wths = make_input(H + C, KN, K, K, C)
+    qw, btn = TAB.Quantize(dev_t(w, cuda), dev_t(wths, cuda), O.weight_bits(t), KN, K, K, C)
+    y = TAB.Conv2d(x, qw, ths, btn, t, p, p, s, s, N, H, H, C, KN, K, K)
+    OH = (H + 2 * p - K + 1) // s
+    assert tuple(y.shape) == (N, KN, OH, OH)
+    yb = y.reshape(N, OH, OH, KN)
+    qwh, btnh, thh = qw.cpu().numpy(), btn.cpu().numpy(), ths.cpu().numpy()
+    for n in (0, 37, 63):
+        yo = c_oracle.conv2d(x[n].cpu().numpy(), qwh, thh[n:n + 1], btnh, t, p, p, s, s, 1, H, H, C, KN, K, K)
+        assert np.array_equal(yb[n].cpu().numpy().reshape(-1), yo.reshape(-1)), n
+    # sharding property: the first 8 images alone give the same answer as inside the full batch
+    y8 = TAB.Conv2d(x[:8].contiguous(), qw, ths[:8].contiguous(), btn, t, p, p, s, s, 8, H, H, C, KN, K, K)
+    assert torch.equal(y8.reshape(-1), y.reshape(-1)[:y8.numel()])
+
+
+@pytest.mark.parametrize("t", [3, 0])
+def test_large_1x1_configuration(cuda, t):
+    """N=128, 14x14x1024 -> 1024, 1x1 (M=25088, KN=1024, K=1024 bits), types BNN and TNN."""
+    N, H, C, KN = 128, 14, 1024, 1024
+    g = torch.Generator(device=cuda)
+    g.manual_seed(4 + t)
+    x = torch.randn(N, H, H, C, device=cuda, generator=g)
+    ths = (0.7 * x.abs().mean(dim=(1, 2, 3))).contiguous()
+    w, wths = make_input(77, KN, 1, 1, C)
+    qw, btn = TAB.Quantize(dev_t(w, cuda), dev_t(wths, cuda), O.weight_bits(t), KN, 1, 1, C)
+    y = TAB.Conv2d(x, qw, ths, btn, t, 0, 0, 1, 1, N, H, H, C, KN, 1, 1).reshape(N, -1)
+    qwh, btnh, thh = qw.cpu().numpy(), btn.cpu().numpy(), ths.cpu().numpy()
+    for n in (0, 64, 127):
+        yo = c_oracle.conv2d(x[n].cpu().numpy(), qwh, thh[n:n + 1], btnh, t, 0, 0, 1, 1, 1, H, H, C, KN, 1, 1)
+        assert np.array_equal(y[n].cpu().numpy(), yo.reshape(-1))
+
+
+def test_packed_entry_point_equals_fused_call(cuda):
+    N, H, W, C, KN = 3, 9, 8, 130, 33
+    x, ths = make_input(1, N, H, W, C)
+    w, wths = make_input(2, KN, 3, 3, C)
+    for t in range(4):
+        qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, 3, 3, C)
+        qx, _ = TAB.Quantize(dev_t(x, cuda), dev_t(ths, cuda), O.act_bits(t), N, H, W, C)
+        y = TAB.conv2d_packed(qx, dev_t(qw, cuda), dev_t(btn, cuda), t, 1, 1, 2, 1, N, H, W, C, KN, 3, 3)
+        yo = c_oracle.conv2d(x, qw, ths, btn, t, 1, 1, 2, 1, N, H, W, C, KN, 3, 3)
+        assert np.array_equal(y.cpu().numpy(), yo)
+
+
+# ------------------------------------------------------------------------------------------ chain
+
+def test_residual_threshold(cuda):
+    rng = np.random.default_rng(3)
+    for shape in ((3, 5, 4, 4), (2, 7, 3, 3), (4, 64, 7, 7)):
+        y = np.round(rng.standard_normal(shape) * 50).astype(np.float32)
+        r = np.round(rng.standard_normal(shape) * 50).astype(np.float32)
+        yd = dev_t(y, cuda)
+        t0 = TAB.ops.residual_threshold(yd, None, 0.7)
+        assert np.array_equal(t0.cpu().numpy(), OracleOps.residual_threshold(y.copy(), None, 0.7))
+        t1 = TAB.ops.residual_threshold(yd, dev_t(r, cuda), 0.7)
+        yo = y.copy()
+        to = OracleOps.residual_threshold(yo, r, 0.7)
+        assert np.array_equal(yd.cpu().numpy(), yo) and np.array_equal(t1.cpu().numpy(), to)
+
+
+@pytest.mark.parametrize("t", [0, 3])
+def test_chain_matches_oracle(cuda, t):
+    """The 19-convolution ResNet-18-shaped chain, N=3, integer-valued input so that every threshold is an
+    exact function of the data on both sides."""
+    N = 3
+    rng = np.random.default_rng(8)
+    x = np.round(rng.standard_normal((N, 56, 56, 64)) * 4).astype(np.float32)
+    weights = chain.make_weights(2000, t)
+    qo = chain.quantize_weights(weights, t, OracleOps.Quantize)
+    ths = OracleOps.residual_threshold(x.copy(), None, chain.THRESHOLD_SCALE)
+    yo, oh, ow, kn = chain.forward(OracleOps, x, ths, qo, t, N)
+    qd = chain.quantize_weights(weights, t, TAB.Quantize, lambda a: dev_t(a, cuda))
+    for k in qo:
+        assert np.array_equal(qd[k][0].cpu().numpy(), qo[k][0]) and np.array_equal(qd[k][1].cpu().numpy(), qo[k][1])
+    xd = dev_t(x, cuda)
+    thd = TAB.ops.residual_threshold(xd, None, chain.THRESHOLD_SCALE)
+    assert np.array_equal(thd.cpu().numpy(), ths)
+    yd, oh2, ow2, kn2 = chain.forward(TAB.ops, xd, thd, qd, t, N)
+    assert (oh, ow, kn) == (oh2, ow2, kn2) == (7, 7, 512)
+    assert np.array_equal(yd.cpu().numpy().reshape(-1), yo.reshape(-1))
+
+
+# ------------------------------------------------------------------------------------------ errors
+
+def test_error_behaviour(cuda):
+    x = torch.zeros(1, 4, 4, 64, device=cuda)
+    t = torch.zeros(1, device=cuda)
+    qw2 = torch.zeros(4, 3, 3, 1, 2, dtype=torch.int64, device=cuda)
+    qw1 = torch.zeros(4, 3, 3, 1, 1, dtype=torch.int64, device=cuda)
+    btn = torch.zeros(4, dtype=torch.int32, device=cuda)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        TAB.Conv2d(x.cpu(), qw2, t, btn, 0, 1, 1, 1, 1, 1, 4, 4, 64, 4, 3, 3)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        TAB.Conv2d(x.permute(0, 2, 1, 3), qw2, t, btn, 0, 1, 1, 1, 1, 1, 4, 4, 64, 4, 3, 3)
+    with pytest.raises(RuntimeError, match="bitwidth 2"):
+        TAB.Conv2d(x, qw1, t, btn, 0, 1, 1, 1, 1, 1, 4, 4, 64, 4, 3, 3)       # 1-bit weights given to TNN
+    with pytest.raises(RuntimeError, match="type must be"):
+        TAB.Conv2d(x, qw2, t, btn, 4, 1, 1, 1, 1, 1, 4, 4, 64, 4, 3, 3)
+    l = _cabi.lib()
+    y = torch.zeros(64, device=cuda)
+    ws = torch.zeros(64, dtype=torch.uint8, device=cuda)          # too small
+    rc = l.tab_conv2d_launch(x.data_ptr(), qw2.data_ptr(), t.data_ptr(), btn.data_ptr(), y.data_ptr(), ws.data_ptr(), 64,
+                             0, 1, 1, 1, 1, 1, 4, 4, 64, 4, 3, 3, None)
+    assert rc == -3
+    # after the rejected calls the device path still works
+    yy = TAB.Conv2d(x, qw2, t, btn, 0, 1, 1, 1, 1, 1, 4, 4, 64, 4, 3, 3)
+    assert not yy.any().item()
