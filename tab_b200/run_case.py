@@ -1,0 +1,71 @@
+"""Run one operator of the library on synthetic data and print its time (a small, fixed-size case for
+profilers and quick measurements).
+
+    python -m tab_b200.run_case conv     --type 0 --N 64 --H 56 --C 64 --KN 64 --K 3 --stride 1 --pad 1
+    python -m tab_b200.run_case packed   ...        # the popcount convolution alone on pre-packed activations
+    python -m tab_b200.run_case quantize --bitwidth 2 --N 256 --H 56 --C 256
+
+Prints one JSON line: milliseconds per call (CUDA events, after warm-up) and the derived TOPS or GB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import ops
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["conv", "packed", "quantize"])
+    ap.add_argument("--type", type=int, default=0)
+    ap.add_argument("--bitwidth", type=int, default=2)
+    ap.add_argument("--N", type=int, default=64)
+    ap.add_argument("--H", type=int, default=56)
+    ap.add_argument("--C", type=int, default=64)
+    ap.add_argument("--KN", type=int, default=64)
+    ap.add_argument("--K", type=int, default=3)
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--pad", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=2)
+    a = ap.parse_args()
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    N, H, W, C, KN, K, s, p, t = a.N, a.H, a.H, a.C, a.KN, a.K, a.stride, a.pad, a.type
+    x = torch.randn(N, H, W, C, device=dev)
+    ths = (0.7 * x.abs().mean(dim=(1, 2, 3))).contiguous()
+    if a.op == "quantize":
+        fn = lambda: ops.Quantize(x, ths, a.bitwidth, N, H, W, C)
+        bits = 1 if a.bitwidth == 1 else 2
+        work = 4 * N * H * W * C + 8 * N * H * W * ((C + 63) // 64) * bits + 8 * N
+        unit, scale = "GB/s", 1e6
+    else:
+        w = torch.randn(KN, K, K, C, device=dev)
+        wths = (0.7 * w.abs().mean(dim=(1, 2, 3))).contiguous()
+        qw, btn = ops.Quantize(w, wths, 1 if t in (1, 3) else 2, KN, K, K, C)
+        oh = (H + 2 * p - K + 1) // s
+        work = 2 * N * oh * oh * KN * K * K * C
+        unit, scale = "TOPS", 1e9
+        if a.op == "conv":
+            fn = lambda: ops.Conv2d(x, qw, ths, btn, t, p, p, s, s, N, H, W, C, KN, K, K)
+        else:
+            qx, _ = ops.Quantize(x, ths, 1 if t in (2, 3) else 2, N, H, W, C)
+            fn = lambda: ops.conv2d_packed(qx, qw, btn, t, p, p, s, s, N, H, W, C, KN, K, K)
+    for _ in range(a.warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.iters
+    print(json.dumps({"op": a.op, "args": vars(a), "ms": ms, "value": work / ms / scale, "unit": unit}))
+
+
+if __name__ == "__main__":
+    main()
