@@ -87,6 +87,34 @@ int tab_conv2d_packed_launch(const int64_t* qx, const int64_t* qw, const int32_t
                              int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
 
 /*
+ * tab_conv2d_launch without a workspace argument.  No counterpart in the reference (its host code calls
+ * cudaMalloc/cudaFree for scratch on every convolution, TAB_GEMM.cu:391-407,522-524).
+ *
+ * For callers that cannot allocate device memory: programs whose GPU memory belongs entirely to another
+ * component's pool, language bindings that can forward buffers they were given but not create new
+ * ones, and loops where an allocation's implicit device synchronisation is not acceptable.  The
+ * bit-packed activations go into a fixed array of TAB_STATIC_SCRATCH_BYTES that is part of the library
+ * image on every GPU that loads it (held until the process exits).  This function calls no cudaMalloc,
+ * cudaFree or other allocating routine.
+ *
+ * Limits and rules:
+ *   - N*H*W*ceil(C/64)*planes*8 bytes (planes = 2 for types 0,1; 1 for types 2,3) must not exceed
+ *     TAB_STATIC_SCRATCH_BYTES, else TAB_E_TOO_LARGE is returned and nothing is launched.
+ *   - The first call on each device looks up the array's device address (a one-time set-up under a lock);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Two calls whose kernels can overlap on the GPU
+ *     (different streams without an ordering between them, or different host threads) race on it and
+ *     give wrong results; serialise them on one stream or with events.
+ *   - The array keeps whatever the last call left; this function overwrites every word it later reads,
+ *     so no clearing is needed between calls.
+ * Arguments and results are otherwise exactly those of tab_conv2d_launch.
+ */
+#define TAB_STATIC_SCRATCH_BYTES (16u << 20)
+int tab_conv2d_static_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                             float* y, int type, int p1, int p2, int s1, int s2,
+                             int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
+
+/*
  * Chaining helper: y += residual (skipped when residual is NULL), then ths[n] = scale * mean|y[n]| over
  * the per_image floats of image n - the threshold the next layer's quantiser takes.  sums is scratch
  * for N doubles (cleared by this call).  Convolution outputs are integer-valued, so the double sums are

@@ -22,6 +22,7 @@ SYMBOLS = {
     "tab_conv2d_workspace_bytes": (_c.c_size_t, [_c.c_int] * 5),
     "tab_conv2d_launch": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_size_t] + [_c.c_int] * 12 + [_c.c_void_p]),
     "tab_conv2d_packed_launch": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int] * 12 + [_c.c_void_p]),
+    "tab_conv2d_static_launch": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 12 + [_c.c_void_p]),
     "tab_residual_threshold_launch": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_float, _c.c_int, _c.c_longlong, _c.c_void_p]),
     "tab_pipe_probe_sink_bytes": (_c.c_size_t, []),
     "tab_pipe_probe_launch": (_c.c_int, [_c.c_int, _c.c_int, _c.c_void_p, _c.POINTER(_c.c_double), _c.c_void_p]),

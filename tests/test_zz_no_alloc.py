@@ -1,0 +1,81 @@
+"""``tab_conv2d_static_launch``: the convolution for callers that cannot allocate device memory (their GPU
+memory is owned by another component's pool, or their binding can only forward buffers it was given, or
+an allocation's device synchronisation is not allowed where they call from).  Its scratch is a fixed
+array inside the library, so the test checks three things through the C ABI: the result equals
+``tab_conv2d_launch`` exactly (integer-valued outputs: tolerance 0), a second call right after the first
+is not disturbed by what the first left in the shared array, and a problem larger than the array is
+refused with TAB_E_TOO_LARGE instead of being launched.  The file name sorts last on purpose."""
+import numpy as np
+import pytest
+import torch
+
+from tab_b200 import _cabi
+from util import make_input
+
+pytestmark = pytest.mark.gpu
+
+STATIC_BYTES = 16 << 20
+
+
+def _quantize_weights(l, cuda, w, wths, t, KN, K, C):
+    wb = 1 if t in (1, 3) else 2
+    wd, td = torch.from_numpy(w).to(cuda), torch.from_numpy(wths).to(cuda)
+    qw = torch.empty(KN * K * K * ((C + 63) // 64) * wb, dtype=torch.int64, device=cuda)
+    btn = torch.empty(KN, dtype=torch.int32, device=cuda)
+    assert l.tab_quantize_launch(wd.data_ptr(), td.data_ptr(), qw.data_ptr(), btn.data_ptr(), wb, KN, K, K, C, None) == 0
+    return qw, btn
+
+
+def _both(l, cuda, t, geom, seed):
+    p1, p2, s1, s2, N, H, W, C, KN, KH, KW = geom
+    x, ths = make_input(seed, N, H, W, C)
+    w, wths = make_input(seed + 1, KN, KH, KW, C)
+    qw, btn = _quantize_weights(l, cuda, w, wths, t, KN, KH, C)
+    xd, td = torch.from_numpy(x).to(cuda), torch.from_numpy(ths).to(cuda)
+    OH, OW = (H + 2 * p1 - KH + 1) // s1, (W + 2 * p2 - KW + 1) // s2
+    y_ws = torch.full((N * OH * OW * KN,), -7.0, device=cuda)
+    y_st = torch.full((N * OH * OW * KN,), -9.0, device=cuda)
+    ws_bytes = l.tab_conv2d_workspace_bytes(t, N, H, W, C)
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=cuda)
+    stream = torch.cuda.current_stream(cuda).cuda_stream
+    rc = l.tab_conv2d_launch(xd.data_ptr(), qw.data_ptr(), td.data_ptr(), btn.data_ptr(), y_ws.data_ptr(), ws.data_ptr(),
+                             ws.numel(), t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream)
+    assert rc == 0
+    rc = l.tab_conv2d_static_launch(xd.data_ptr(), qw.data_ptr(), td.data_ptr(), btn.data_ptr(), y_st.data_ptr(),
+                                    t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream)
+    assert rc == 0, l.tab_error_string(rc)
+    torch.cuda.synchronize()
+    return y_ws.cpu().numpy(), y_st.cpu().numpy()
+
+
+def test_static_scratch_entry_point_matches_workspace_entry_point(cuda):
+    l = _cabi.lib()
+    # two calls in a row per type: a large problem, then a smaller one with different planes/strides that
+    # reuses the front of the same array while the rest still holds the first call's words
+    first = (1, 1, 1, 1, 8, 28, 28, 128, 96, 3, 3)
+    second = (0, 1, 2, 1, 3, 9, 7, 65, 10, 3, 3)
+    for t in range(4):
+        a_ws, a_st = _both(l, cuda, t, first, 10 + t)
+        b_ws, b_st = _both(l, cuda, (t + 2) % 4, second, 20 + t)
+        assert np.array_equal(a_ws, a_st), "type %d, first call" % t
+        assert np.array_equal(b_ws, b_st), "type %d, second call" % ((t + 2) % 4)
+        assert a_st.min() > -4609 and not np.all(a_st == -9.0)
+
+
+def test_static_scratch_limit_is_enforced(cuda):
+    l = _cabi.lib()
+    one = torch.zeros(1, device=cuda)
+    q = torch.zeros(2, dtype=torch.int64, device=cuda)
+    b = torch.zeros(1, dtype=torch.int32, device=cuda)
+    # N*H*W*PC*2*8 bytes just over the array: must be refused before anything is launched or read
+    N, H, W, C = 257, 64, 64, 64
+    assert N * H * W * 1 * 2 * 8 > STATIC_BYTES
+    rc = l.tab_conv2d_static_launch(one.data_ptr(), q.data_ptr(), one.data_ptr(), b.data_ptr(), one.data_ptr(),
+                                    0, 0, 0, 1, 1, N, H, W, C, 1, 1, 1, None)
+    assert rc == -5
+    assert b"exceeds" in l.tab_error_string(rc)
+    # exactly at the limit for the binary-activation layout is accepted by the size check (fails later only
+    # on the NULL pointers we pass, i.e. the limit itself did not trigger)
+    rc = l.tab_conv2d_static_launch(None, None, None, None, None, 3, 0, 0, 1, 1, 512, 64, 64, 64, 1, 1, 1, None)
+    assert rc == -2
+    torch.cuda.synchronize()
