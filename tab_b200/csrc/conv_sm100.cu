@@ -39,6 +39,11 @@ struct ConvParams {
     int N, H, W, PC, KN, KH, KW, OH, OW, p1, p2, s1, s2;
     int M, Kw, NUM;
     int qw16;                  // qw is 16-byte aligned
+    // Accumulation weights, passed as run-time values on purpose: "acc += w * popc" then stays an
+    // integer multiply-add (FMA pipe) instead of being strength-reduced into shifts/adds on the ALU pipe,
+    // which the LOP3 work already saturates.  wpos = {1,2,4,8,16}, wneg = {-2,-4,-8,-16,-32}.
+    int wpos[5];
+    int wneg[5];
 };
 
 template <int TYPE> struct Planes {
@@ -66,34 +71,42 @@ __device__ __forceinline__ void csa(uint32_t a, uint32_t b, uint32_t c, uint32_t
     carry = (a & b) | (c & (a | b));
 }
 
-// Sum of popcounts of NU 32-bit words, with carry-save compression first.
-template <int NU> __device__ __forceinline__ int popc_sum(const uint32_t (&x)[NU]);
-template <> __device__ __forceinline__ int popc_sum<2>(const uint32_t (&x)[2]) { return __popc(x[0]) + __popc(x[1]); }
-template <> __device__ __forceinline__ int popc_sum<4>(const uint32_t (&x)[4]) {
-    uint32_t s1, c1;
-    csa(x[0], x[1], x[2], s1, c1);
-    return __popc(s1) + __popc(x[3]) + 2 * __popc(c1);
+__device__ __forceinline__ void mad_acc(int& acc, int p, int w) {
+    asm("mad.lo.s32 %0, %1, %2, %0;" : "+r"(acc) : "r"(p), "r"(w));
 }
-template <> __device__ __forceinline__ int popc_sum<6>(const uint32_t (&x)[6]) {
-    uint32_t s1, c1, s2, c2;
-    csa(x[0], x[1], x[2], s1, c1);
-    csa(x[3], x[4], x[5], s2, c2);
-    return __popc(s1) + __popc(s2) + 2 * (__popc(c1) + __popc(c2));
-}
-template <> __device__ __forceinline__ int popc_sum<8>(const uint32_t (&x)[8]) {
-    uint32_t s1, c1, s2, c2, s3, c3, s4, c4;
-    csa(x[0], x[1], x[2], s1, c1);
-    csa(x[3], x[4], x[5], s2, c2);
-    csa(s1, s2, x[6], s3, c3);
-    csa(c1, c2, c3, s4, c4);
-    return __popc(s3) + __popc(x[7]) + 2 * __popc(s4) + 4 * __popc(c4);
-}
-// No compression: one POPC per word (kept for A/B measurements of the adder tree).
-template <int NU> __device__ __forceinline__ int popc_sum_plain(const uint32_t (&x)[NU]) {
-    int s = 0;
+
+// acc += sum_i w[LVL] * popc(x[i]) for N words of weight 2^LVL, after carry-save compression: triples
+// at a level go through a full adder (sum stays, carry moves one level up) until fewer than three
+// words remain at every level; only those survivors are POPC'ed.  N words cost about N/2 POPC.
+// cy holds C pending words of the next level.  Everything unrolls at compile time.
+template <int N, int C, int LVL> struct CsaTree {
+    static __device__ __forceinline__ void run(const uint32_t* x, const uint32_t* cy, int& acc, const int* w) {
+        if constexpr (N >= 3) {
+            constexpr int K = N / 3, R = N - 2 * K;
+            uint32_t same[R], cy2[C + K];
 #pragma unroll
-    for (int i = 0; i < NU; i++) s += __popc(x[i]);
-    return s;
+            for (int c = 0; c < C; c++) cy2[c] = cy[c];
+#pragma unroll
+            for (int k = 0; k < K; k++) csa(x[3 * k], x[3 * k + 1], x[3 * k + 2], same[k], cy2[C + k]);
+#pragma unroll
+            for (int r = 0; r < N - 3 * K; r++) same[K + r] = x[3 * K + r];
+            CsaTree<R, C + K, LVL>::run(same, cy2, acc, w);
+        } else {
+#pragma unroll
+            for (int i = 0; i < N; i++) mad_acc(acc, __popc(x[i]), w[LVL]);
+            if constexpr (C > 0) CsaTree<C, 0, LVL + 1>::run(cy, nullptr, acc, w);
+        }
+    }
+};
+
+// acc += w[0] * sum popc(x[i]); CSA selects the compressed or the one-POPC-per-word form.
+template <int NU, bool CSA> __device__ __forceinline__ void popc_accumulate(const uint32_t (&x)[NU], int& acc, const int* w) {
+    if constexpr (CSA) {
+        CsaTree<NU, 0, 0>::run(x, nullptr, acc, w);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NU; i++) mad_acc(acc, __popc(x[i]), w[0]);
+    }
 }
 
 // Read NW 64-bit words from shared memory (8-byte aligned; 16-byte loads when AL16).
@@ -117,7 +130,8 @@ template <int NW, bool AL16> __device__ __forceinline__ void lds_words(const uns
 // a_rows / b_rows point at this lane's first pixel / filter row, at the group's first word.
 template <int TYPE, int G, bool CSA>
 __device__ __forceinline__ void compute_group(const unsigned char* a_rows, const unsigned char* b_rows,
-                                              int (&acc)[RM][RN], int (&pcount)[RM], int kb, int fg) {
+                                              int (&acc)[RM][RN], int (&pcount)[RM], int kb, int fg,
+                                              const int* wpos, const int* wneg) {
     using P = Planes<TYPE>;
     constexpr int AB = P::AB, WB = P::WB, NU = 2 * G;
     // register image of the weights: [filter][word g][plane][lo,hi] as stored (planes interleaved per word)
@@ -150,7 +164,7 @@ __device__ __forceinline__ void compute_group(const unsigned char* a_rows, const
                         t[2 * g + h] = ma & mw;
                         u[2 * g + h] = (sa ^ sw) & t[2 * g + h];
                     }
-                acc[i][j] += (CSA ? popc_sum<NU>(t) : popc_sum_plain<NU>(t));
+                popc_accumulate<NU, CSA>(t, acc[i][j], wpos);
             } else if (TYPE == 1) {
 #pragma unroll
                 for (int g = 0; g < G; g++)
@@ -169,7 +183,7 @@ __device__ __forceinline__ void compute_group(const unsigned char* a_rows, const
 #pragma unroll
                     for (int h = 0; h < 2; h++) u[2 * g + h] = areg[2 * g + h] ^ wreg[j][2 * g + h];
             }
-            acc[i][j] -= 2 * (CSA ? popc_sum<NU>(u) : popc_sum_plain<NU>(u));
+            popc_accumulate<NU, CSA>(u, acc[i][j], wneg);
         }
     }
 }
@@ -286,19 +300,19 @@ conv_popc_kernel(const ConvParams p) {
         if (CSA) {
             const int ng = kc >> 2;
             for (int g = 0; g < ng; g++)
-                compute_group<TYPE, 4, true>(a_rows + g * 4 * AB * 8, b_rows + g * 4 * WB * 8, acc, pcount, g * 4, fg);
+                compute_group<TYPE, 4, true>(a_rows + g * 4 * AB * 8, b_rows + g * 4 * WB * 8, acc, pcount, g * 4, fg, p.wpos, p.wneg);
             const int kb = ng * 4;
             const unsigned char* ar = a_rows + kb * AB * 8;
             const unsigned char* br = b_rows + kb * WB * 8;
             switch (kc & 3) {
-                case 1: compute_group<TYPE, 1, true>(ar, br, acc, pcount, kb, fg); break;
-                case 2: compute_group<TYPE, 2, true>(ar, br, acc, pcount, kb, fg); break;
-                case 3: compute_group<TYPE, 3, true>(ar, br, acc, pcount, kb, fg); break;
+                case 1: compute_group<TYPE, 1, true>(ar, br, acc, pcount, kb, fg, p.wpos, p.wneg); break;
+                case 2: compute_group<TYPE, 2, true>(ar, br, acc, pcount, kb, fg, p.wpos, p.wneg); break;
+                case 3: compute_group<TYPE, 3, true>(ar, br, acc, pcount, kb, fg, p.wpos, p.wneg); break;
                 default: break;
             }
         } else {
             for (int k = 0; k < kc; k++)
-                compute_group<TYPE, 1, false>(a_rows + k * AB * 8, b_rows + k * WB * 8, acc, pcount, k, fg);
+                compute_group<TYPE, 1, false>(a_rows + k * AB * 8, b_rows + k * WB * 8, acc, pcount, k, fg, p.wpos, p.wneg);
         }
         __syncthreads();
     }
@@ -375,6 +389,7 @@ int conv_packed_dispatch(const int64_t* qx, const int64_t* qw, const int32_t* bt
         return TAB_E_TOO_LARGE;
     p.OH = (int)oh; p.OW = (int)ow; p.M = (int)M; p.Kw = (int)Kw; p.NUM = KH * KW * C;
     p.qw16 = (reinterpret_cast<uintptr_t>(qw) & 15) == 0;
+    for (int i = 0; i < 5; i++) { p.wpos[i] = 1 << i; p.wneg[i] = -(2 << i); }
     const bool csa = g_use_csa;
     switch (type) {
         case 0: return csa ? launch_conv<0, true>(p, stream) : launch_conv<0, false>(p, stream);

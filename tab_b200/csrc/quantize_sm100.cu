@@ -6,9 +6,11 @@
 // else x < -t -> (1, 1), else (0, 0); binary bit = (x < t); channel c is bit c%64 of word c/64.
 //
 // The kernel is HBM-bound: 4 bytes read per element, 2 or 1 bits written.  Fast path (C % 64 == 0,
-// 16-byte aligned input): a half-warp owns one 64-channel word; each lane issues UNROLL independent
-// 128-bit loads before it touches any of them, so a resident SM keeps >= 100 KB in flight; the 4-bit
-// predicate nibbles are merged with redux.sync (OR) and one lane stores the whole word group.
+// 32-byte aligned input): eight lanes own one 64-channel word; each lane issues QUNROLL independent
+// 256-bit loads before it touches any of them, so a resident SM keeps > 200 KB in flight; a lane turns
+// its 8 channels into one byte per plane with compares and predicated ORs and stores those bytes
+// itself - no shuffles, votes or redux (a first version merged nibbles with redux.sync and was bound
+// by that instruction's pipe at 37 % of DRAM bandwidth).
 // General path (any C, any alignment): one warp per word, two coalesced 32-bit loads per lane, the
 // two 32-bit halves come straight out of __ballot_sync.
 #include "tab_kernels.cuh"
@@ -16,70 +18,66 @@
 namespace tab {
 
 constexpr int QTHREADS = 256;
-constexpr int QUNROLL = 4;                                   // independent 128-bit loads per lane
-constexpr int QWORDS_PER_ITER = (QTHREADS / 16) * QUNROLL;   // 64 words = 16 KB of fp32 per CTA step
+constexpr int QUNROLL = 4;                                   // independent 256-bit loads per lane
+constexpr int QWORDS_PER_ITER = (QTHREADS / 8) * QUNROLL;    // 128 words = 32 KB of fp32 per CTA step
 
-__device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
-    float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
+struct f8 { float v[8]; };
+
+// 256-bit streaming load (sm_100): a lane reads 8 consecutive channels, a warp 1 KB contiguous.
+__device__ __forceinline__ f8 ld_stream_f8(const float* p) {
+    f8 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]),
+                   "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7]) : "l"(p));
+    return r;
 }
 
 // grid = (ctas_per_image, N).  words_per_image = H*W*PC with PC = C/64.
+// Eight lanes own one 64-channel word: lane b of the group quantises channels 8b..8b+7 and stores byte b
+// of the sign and of the magnitude word itself, so no cross-lane traffic is needed at all.
 template <int BITS>
 __global__ void __launch_bounds__(QTHREADS)
-quantize_c64_kernel(const float4* __restrict__ x, const float* __restrict__ ths,
+quantize_c64_kernel(const float* __restrict__ x, const float* __restrict__ ths,
                     uint64_t* __restrict__ qx, int* __restrict__ btn, long long words_per_image) {
     const int n = blockIdx.y;
     const float t = __ldg(ths + n);
     const float nt = -t;
-    const int lane16 = threadIdx.x & 15;
-    const int hw = threadIdx.x >> 4;                          // half-warp within the CTA: 0..15
-    const unsigned hmask = 0xFFFFu << (threadIdx.x & 16);     // my half-warp's lanes
-    const float4* xi = x + (long long)n * words_per_image * 16;
-    uint64_t* qi = qx + (long long)n * words_per_image * BITS;
+    const int byte = threadIdx.x & 7;
+    const int grp = threadIdx.x >> 3;                         // word slot within the CTA: 0..31
+    const float* xi = x + (long long)n * words_per_image * 64;
+    unsigned char* qi = reinterpret_cast<unsigned char*>(qx + (long long)n * words_per_image * BITS);
     int cnt = 0;
 
     for (long long w0 = (long long)blockIdx.x * QWORDS_PER_ITER; w0 < words_per_image;
          w0 += (long long)gridDim.x * QWORDS_PER_ITER) {
-        float4 v[QUNROLL];
+        f8 v[QUNROLL];
         long long w[QUNROLL];
 #pragma unroll
         for (int u = 0; u < QUNROLL; u++) {
-            w[u] = w0 + u * (QTHREADS / 16) + hw;
-            if (w[u] < words_per_image) v[u] = ld_stream_f4(xi + w[u] * 16 + lane16);
-            else v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            w[u] = w0 + u * (QTHREADS / 8) + grp;
+            if (w[u] < words_per_image) v[u] = ld_stream_f8(xi + w[u] * 64 + byte * 8);
         }
 #pragma unroll
         for (int u = 0; u < QUNROLL; u++) {
-            const int sh = (lane16 & 7) * 4;
+            if (w[u] >= words_per_image) continue;
             if (BITS == 2) {
-                const unsigned p0 = v[u].x > t, p1 = v[u].y > t, p2 = v[u].z > t, p3 = v[u].w > t;
-                const unsigned n0 = v[u].x < nt, n1 = v[u].y < nt, n2 = v[u].z < nt, n3 = v[u].w < nt;
-                const unsigned pos = p0 | (p1 << 1) | (p2 << 2) | (p3 << 3);
-                const unsigned neg = (n0 | (n1 << 1) | (n2 << 2) | (n3 << 3)) & ~pos;   // "+1" branch first
-                const unsigned s = neg << sh, m = (pos | neg) << sh;
-                const bool lo = lane16 < 8;
-                const unsigned s_lo = __reduce_or_sync(hmask, lo ? s : 0u);
-                const unsigned s_hi = __reduce_or_sync(hmask, lo ? 0u : s);
-                const unsigned m_lo = __reduce_or_sync(hmask, lo ? m : 0u);
-                const unsigned m_hi = __reduce_or_sync(hmask, lo ? 0u : m);
-                if (lane16 == 0 && w[u] < words_per_image) {
-                    uint4 o = make_uint4(s_lo, s_hi, m_lo, m_hi);
-                    *reinterpret_cast<uint4*>(qi + w[u] * 2) = o;
-                    cnt += __popc(m_lo) + __popc(m_hi);
+                unsigned pos = 0, neg = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    pos |= (v[u].v[i] > t) ? (1u << i) : 0u;
+                    neg |= (v[u].v[i] < nt) ? (1u << i) : 0u;
                 }
+                neg &= ~pos;                                   // the "+1" branch is tested first
+                const unsigned mag = pos | neg;
+                unsigned char* o = qi + w[u] * 16 + byte;
+                o[0] = (unsigned char)neg;                     // sign plane, byte `byte` of the word
+                o[8] = (unsigned char)mag;                     // magnitude plane
+                cnt += __popc(mag);
             } else {
-                const unsigned b0 = v[u].x < t, b1 = v[u].y < t, b2 = v[u].z < t, b3 = v[u].w < t;
-                const unsigned b = (b0 | (b1 << 1) | (b2 << 2) | (b3 << 3)) << sh;
-                const bool lo = lane16 < 8;
-                const unsigned b_lo = __reduce_or_sync(hmask, lo ? b : 0u);
-                const unsigned b_hi = __reduce_or_sync(hmask, lo ? 0u : b);
-                if (lane16 == 0 && w[u] < words_per_image) {
-                    uint2 o = make_uint2(b_lo, b_hi);
-                    *reinterpret_cast<uint2*>(qi + w[u]) = o;
-                }
+                unsigned b = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) b |= (v[u].v[i] < t) ? (1u << i) : 0u;
+                qi[w[u] * 8 + byte] = (unsigned char)b;
             }
         }
     }
@@ -160,8 +158,7 @@ int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* bt
         }
         return TAB_OK;
     }
-    const bool fast = (C % 64 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
-                      ((reinterpret_cast<uintptr_t>(qx) & 15) == 0);
+    const bool fast = (C % 64 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0);
     uint64_t* q = reinterpret_cast<uint64_t*>(qx);
     if (fast) {
         // enough CTAs to fill the device several times over, each looping a few steps
@@ -174,9 +171,8 @@ int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* bt
             if (per_image > steps) per_image = steps;
         }
         dim3 grid((unsigned)per_image, (unsigned)N);
-        const float4* x4 = reinterpret_cast<const float4*>(x);
-        if (bits == 2) quantize_c64_kernel<2><<<grid, QTHREADS, 0, stream>>>(x4, ths, q, btn, wpi);
-        else quantize_c64_kernel<1><<<grid, QTHREADS, 0, stream>>>(x4, ths, q, btn, wpi);
+        if (bits == 2) quantize_c64_kernel<2><<<grid, QTHREADS, 0, stream>>>(x, ths, q, btn, wpi);
+        else quantize_c64_kernel<1><<<grid, QTHREADS, 0, stream>>>(x, ths, q, btn, wpi);
     } else {
         long long steps = (wpi + (QTHREADS / 32) - 1) / (QTHREADS / 32);
         long long per_image = steps;
