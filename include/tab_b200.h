@@ -58,13 +58,24 @@ int tab_quantize_launch(const float* x, const float* ths, int64_t* qx, int32_t* 
                         int bitwidth, int N, int H, int W, int C, tab_stream_t stream);
 
 /*
- * Bytes of scratch tab_conv2d_launch needs for these sizes (the bit-packed activations).
+ * Bytes of scratch tab_conv2d_launch needs for these sizes, whichever compute path is selected (the
+ * quantised activations and, for the tensor-core path, the byte-expanded weights).
  * Returns 0 for invalid arguments.
  */
-size_t tab_conv2d_workspace_bytes(int type, int N, int H, int W, int C);
+size_t tab_conv2d_workspace_bytes(int type, int N, int H, int W, int C, int KN, int KH, int KW);
 
 /*
- * Quantise activations, then convolve with pre-quantised weights as an implicit-im2col popcount GEMM
+ * Compute path of tab_conv2d_launch (process-wide; results are identical bit for bit):
+ *   TAB_PATH_AUTO (default)  int8 tensor-core implicit GEMM (quantised values as bytes, s8 MMA)
+ *   TAB_PATH_POPCOUNT        bit-packed LOP3/POPC kernel - the reference's formulation (TAB_GEMM.cu:25-147);
+ *                            this is also what tab_conv2d_packed_launch always runs
+ * Returns the previous setting, or TAB_E_BAD_ARGUMENT.
+ */
+enum { TAB_PATH_AUTO = 0, TAB_PATH_POPCOUNT = 1 };
+int tab_conv2d_set_path(int path);
+
+/*
+ * Quantise activations, then convolve with pre-quantised weights as an implicit-im2col GEMM
  * (replaces ConvWithCuda_TAB, TAB_GEMM.cu:325-527: TerOnly/BinOnlyKernel, PadKernel TAB_GEMM.cuh:73-89,
  * Img2RowKernel :92-115, GEMMWithCuda :22-66 and TNN/TBN/BTN/BNNGEMM TAB_GEMM.cu:25-147).
  * type: 0 TNN, 1 TBN, 2 BTN, 3 BNN.  qw is the tab_quantize_launch output of the weights

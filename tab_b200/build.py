@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtab_b200.so")
-SOURCES = ["c_abi.cu", "quantize_sm100.cu", "conv_sm100.cu", "conv_static_sm100.cu", "chain_sm100.cu", "pipe_probe.cu"]
+SOURCES = ["c_abi.cu", "quantize_sm100.cu", "conv_sm100.cu", "conv_imma_sm100.cu", "conv_static_sm100.cu", "chain_sm100.cu", "pipe_probe.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

@@ -12,6 +12,11 @@ int record_cuda_error(cudaError_t e) {
 }
 
 void conv_set_csa(bool on);
+size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW);
+int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
+                       int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
+                       cudaStream_t stream);
+static int g_conv_path = TAB_PATH_AUTO;
 
 static bool dims_ok(int N, int H, int W, int C) { return N >= 0 && H >= 0 && W >= 0 && C >= 1; }
 
@@ -58,10 +63,22 @@ int tab_quantize_launch(const float* x, const float* ths, int64_t* qx, int32_t* 
     return quantize_dispatch(x, ths, qx, bits == 2 ? btn : nullptr, bits, N, H, W, C, s);
 }
 
-size_t tab_conv2d_workspace_bytes(int type, int N, int H, int W, int C) {
-    if (type < 0 || type > 3 || !dims_ok(N, H, W, C)) return 0;
+static size_t popc_workspace_bytes(int type, int N, int H, int W, int C) {
     const size_t words = (size_t)N * H * W * packed_channels(C) * act_bits(type);
     return (words * 8 + 255) / 256 * 256;
+}
+
+size_t tab_conv2d_workspace_bytes(int type, int N, int H, int W, int C, int KN, int KH, int KW) {
+    if (type < 0 || type > 3 || !dims_ok(N, H, W, C) || KN < 0 || KH < 1 || KW < 1) return 0;
+    const size_t a = popc_workspace_bytes(type, N, H, W, C), b = imma_workspace_bytes(N, H, W, C, KN, KH, KW);
+    return a > b ? a : b;
+}
+
+int tab_conv2d_set_path(int path) {
+    if (path != TAB_PATH_AUTO && path != TAB_PATH_POPCOUNT) return TAB_E_BAD_ARGUMENT;
+    const int prev = g_conv_path;
+    g_conv_path = path;
+    return prev;
 }
 
 static int conv_args_ok(int type, int p1, int p2, int s1, int s2, int N, int H, int W, int C,
@@ -97,12 +114,17 @@ int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
     if (!x || !ths || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
-    const size_t need = tab_conv2d_workspace_bytes(type, N, H, W, C);
+    const size_t need = tab_conv2d_workspace_bytes(type, N, H, W, C, KN, KH, KW);
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
         return TAB_E_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3)) return TAB_E_ALIGNMENT;
     if ((long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (g_conv_path == TAB_PATH_AUTO) {
+        if ((reinterpret_cast<uintptr_t>(qw) & 7) || (reinterpret_cast<uintptr_t>(y) & 3)) return TAB_E_ALIGNMENT;
+        rc = conv_imma_dispatch(x, qw, ths, y, workspace, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, s);
+        if (rc != TAB_E_TOO_LARGE) return rc;       // sizes beyond the tensor-core path: fall through
+    }
     int64_t* qx = reinterpret_cast<int64_t*>(workspace);
     rc = quantize_dispatch(x, ths, qx, nullptr, act_bits(type), N, H, W, C, s);   // TAB_GEMM.cu:419-426
     if (rc != TAB_OK) return rc;

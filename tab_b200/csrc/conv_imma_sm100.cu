@@ -1,0 +1,396 @@
+// TAB convolution on the integer tensor cores: quantised values {-1,0,+1} held as int8, implicit-im2col
+// GEMM with s8 x s8 -> s32 MMA.  Bit-exact with the popcount formulation: every product is in {-1,0,1}
+// and the int32 accumulation of at most KH*KW*C terms is exact, so y = sum a*w directly and none of the
+// per-type corrections of the popcount kernels (TAB_GEMM.cu:25-147: "- 2*cnt", btn[kn], NUM) is needed.
+//
+// Why this path exists next to conv_sm100.cu: on B200 a 1-bit MMA is not native (mma.sync ... b1 and.popc
+// is expanded by the compiler into byte operands + integer MMA: ncu shows 37 % IMMA pipe, 69 % ALU, 55 % LSU
+// for a register-only loop, 423 TOP/s), the POPC unit issues 16 lanes/clk/SM (about 145-290 TOP/s for
+// ternary data), while the s8 MMA sustains > 1100 TOP/s from registers.  Feeding the tensor cores with
+// expanded bytes is therefore the faster exact route for all four types.
+//
+// Stages (all on the caller's stream, scratch in the caller's workspace):
+//   1. quantize_int8_kernel   fp32 NHWC -> int8 NHWC with the channel dimension padded to a multiple of
+//                             64 (pad bytes 0): replaces TerOnly/BinOnlyKernel (TAB_GEMM.cu:163-247) for
+//                             this path; same compares, same thresholds.
+//   2. expand_weights_kernel  packed QW [KN][KH*KW*PC][wb] -> int8 [KN][KH*KW*PC][64]; channel tails -> 0.
+//   3. conv_imma_kernel       CTA tile TM pixels x TN filters, 4 warps, warp tile 64 x 64,
+//                             mma.sync.m16n8k32.s8; K walked in chunks of two 64-channel words (128 B per
+//                             row, XOR-swizzled so that ldmatrix is conflict-free), 2- or 3-stage cp.async ring;
+//                             the loader does padding (zero fill for ternary activations, +1 fill for
+//                             binary activations: a zero word means +1 there) and im2col by address.
+#include "tab_kernels.cuh"
+
+namespace tab {
+
+// ------------------------------------------------------------------------------------------------
+// 1. fp32 -> int8 {-1,0,+1}
+// ------------------------------------------------------------------------------------------------
+constexpr int Q8THREADS = 256;
+
+__device__ __forceinline__ int q_ternary(float v, float t, float nt) { return v > t ? 1 : (v < nt ? -1 : 0); }
+__device__ __forceinline__ int q_binary(float v, float t) { return v < t ? -1 : 1; }
+
+// grid = (chunks, N); one thread per 16 consecutive channels of a pixel (one 16-byte store).
+// groups_per_pixel = Cp/16; VEC: C % 16 == 0 and x 32-byte aligned -> two 256-bit loads per thread.
+template <int BITS, bool VEC>
+__global__ void __launch_bounds__(Q8THREADS)
+quantize_int8_kernel(const float* __restrict__ x, const float* __restrict__ ths, int8_t* __restrict__ q,
+                     long long pixels_per_image, int C, int Cp) {
+    const int n = blockIdx.y;
+    const float t = __ldg(ths + n), nt = -t;
+    const int gpp = Cp >> 4;
+    const long long groups = pixels_per_image * gpp;
+    const float* xi = x + (long long)n * pixels_per_image * C;
+    int8_t* qi = q + (long long)n * pixels_per_image * Cp;
+    for (long long g = (long long)blockIdx.x * Q8THREADS + threadIdx.x; g < groups; g += (long long)gridDim.x * Q8THREADS) {
+        const long long pix = g / gpp;
+        const int c0 = (int)(g - pix * gpp) << 4;
+        const float* src = xi + pix * C + c0;
+        float v[16];
+        if (VEC && c0 + 16 <= C) {
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+                asm volatile("ld.global.nc.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                             : "=f"(v[8 * h + 0]), "=f"(v[8 * h + 1]), "=f"(v[8 * h + 2]), "=f"(v[8 * h + 3]),
+                               "=f"(v[8 * h + 4]), "=f"(v[8 * h + 5]), "=f"(v[8 * h + 6]), "=f"(v[8 * h + 7])
+                             : "l"(src + 8 * h));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = (c0 + i < C) ? __ldg(src + i) : 0.f;
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            uint32_t r = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int i = 4 * w + b;
+                int qv = (BITS == 2) ? q_ternary(v[i], t, nt) : q_binary(v[i], t);
+                if (c0 + i >= C) qv = 0;                       // channel padding carries no value
+                r |= (uint32_t)(qv & 0xFF) << (8 * b);
+            }
+            o[w] = r;
+        }
+        *reinterpret_cast<uint4*>(qi + pix * Cp + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 2. packed weights -> int8
+// ------------------------------------------------------------------------------------------------
+// One thread per (filter, word k, 16-channel group).  words = KN*Kw.
+template <int WB>
+__global__ void expand_weights_kernel(const uint64_t* __restrict__ qw, int8_t* __restrict__ w8,
+                                      long long words, int PC, int C) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= words * 4) return;
+    const long long word = idx >> 2;
+    const int grp = (int)(idx & 3);
+    const int pc = (int)(word % PC);
+    const int cbase = pc * 64 + grp * 16;
+    uint32_t s16, m16;
+    if (WB == 2) {
+        s16 = (uint32_t)(qw[word * 2] >> (grp * 16)) & 0xFFFFu;
+        m16 = (uint32_t)(qw[word * 2 + 1] >> (grp * 16)) & 0xFFFFu;
+    } else {
+        s16 = (uint32_t)(qw[word] >> (grp * 16)) & 0xFFFFu;     // bit = 1 means -1
+        m16 = 0xFFFFu;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        uint32_t r = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int i = 4 * w + b;
+            int v = ((m16 >> i) & 1u) ? (((s16 >> i) & 1u) ? -1 : 1) : 0;
+            if (cbase + i >= C) v = 0;
+            r |= (uint32_t)(v & 0xFF) << (8 * b);
+        }
+        o[w] = r;
+    }
+    *reinterpret_cast<uint4*>(w8 + word * 64 + grp * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// 3. implicit-im2col s8 GEMM
+// ------------------------------------------------------------------------------------------------
+constexpr int ITHREADS = 128;                // 4 warps, each a 64 x 64 output tile
+constexpr int IKW = 2;                       // 64-channel words per K chunk (128 bytes per smem row)
+constexpr int IROW = IKW * 64;               // bytes per smem row
+
+struct ImmaParams {
+    const int8_t* qx;        // [N][H][W][Cp]
+    const int8_t* w8;        // [KN][Kw][64]
+    float* y;                // [M][KN]
+    int N, H, W, PC, KN, KH, KW, OH, OW, p1, p2, s1, s2;
+    int M, Kw;
+};
+
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src, bool valid) {
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void sts16(uint32_t dst, uint32_t v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(v));
+}
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void imma(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// smem byte offset of 16-byte unit `u` (0..7) of row `r`: XOR swizzle, conflict-free for 8 consecutive rows.
+__device__ __forceinline__ uint32_t swz(int r, int u) { return (uint32_t)(r * IROW + ((u ^ (r & 7)) << 4)); }
+
+// WM x WN warps (WM*WN == 4); CTA tile (64*WM) x (64*WN).  PADONE: out-of-image taps hold +1 (binary
+// activations) instead of 0.
+//
+// Loader: a 64-byte row-word is copied by four consecutive lanes (16 bytes each), so a warp reads eight
+// fully used 64-byte segments per cp.async instruction.  Each thread owns one (word-in-chunk, 16-byte unit)
+// pair and walks the rows r = tid/8 + 16 e; the per-row geometry (first tap's input coordinates and the
+// image offset) sits in shared memory, written once per CTA.
+template <int WM, int WN, int ISTAGES, bool PADONE>
+__global__ void __launch_bounds__(ITHREADS, 2)
+conv_imma_kernel(const ImmaParams p) {
+    constexpr int TMI = 64 * WM, TNI = 64 * WN;
+    constexpr int STAGE = (TMI + TNI) * IROW;
+    constexpr int RING = ISTAGES * STAGE;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
+    int4* rowinfo = reinterpret_cast<int4*>(smem + RING);        // {first-tap pixel index, tap mask lo, hi, row valid}
+
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.x * TMI;
+    const int n0 = blockIdx.y * TNI;
+    const int Cp = p.PC * 64;
+
+    // Per output pixel: pixel index of its first tap (may be negative: it is only used when the tap's bit
+    // in the validity mask is set) and a 64-bit mask with bit kh*KW+kw = "that tap lies inside the image".
+    for (int r = tid; r < TMI; r += ITHREADS) {
+        const int m = m0 + r;
+        const bool ok = m < p.M;
+        const int mm = ok ? m : 0;
+        const int ohw = p.OH * p.OW;
+        const int n = mm / ohw;
+        const int rr = mm - n * ohw;
+        const int oh = rr / p.OW;
+        const int ow = rr - oh * p.OW;
+        const int ih0 = oh * p.s1 - p.p1, iw0 = ow * p.s2 - p.p2;
+        unsigned long long mask = 0;
+        if (ok) {
+            for (int kh = 0; kh < p.KH; kh++)
+                for (int kw = 0; kw < p.KW; kw++)
+                    if ((unsigned)(ih0 + kh) < (unsigned)p.H && (unsigned)(iw0 + kw) < (unsigned)p.W)
+                        mask |= 1ULL << (kh * p.KW + kw);
+        }
+        rowinfo[r] = make_int4(n * p.H * p.W + ih0 * p.W + iw0, (int)(unsigned)mask, (int)(unsigned)(mask >> 32), ok ? 1 : 0);
+    }
+    __syncthreads();
+
+    // ---- loader state: this thread copies unit l_q of word l_wi of every chunk ----------------------------
+    const int l_unit = tid & 7, l_wi = l_unit >> 2, l_q = l_unit & 3;
+    const int l_row0 = tid >> 3;                                 // rows l_row0 + 16 e
+    int l_k = l_wi, l_kh, l_kw, l_pc;
+    {
+        const int tap = l_k / p.PC;
+        l_pc = l_k - tap * p.PC;
+        l_kh = tap / p.KW;
+        l_kw = tap - l_kh * p.KW;
+    }
+
+    auto load_chunk = [&](int stage) {
+        const uint32_t sA = sbase + stage * STAGE;
+        const uint32_t sB = sA + TMI * IROW;
+        const bool kvalid = l_k < p.Kw;
+        const int tap = l_kh * p.KW + l_kw;
+        const int tap_pix = l_kh * p.W + l_kw;
+        const int8_t* abase = p.qx + (long long)l_pc * 64 + l_q * 16;
+#pragma unroll 4
+        for (int e = 0; e < TMI / 16; e++) {
+            const int row = l_row0 + 16 * e;
+            const int4 ri = rowinfo[row];
+            const unsigned mword = tap < 32 ? (unsigned)ri.y : (unsigned)ri.z;
+            const bool inside = (mword >> (tap & 31)) & 1u;
+            const bool v = kvalid && inside;
+            const int8_t* src = v ? abase + (long long)(ri.x + tap_pix) * Cp : p.qx;
+            const uint32_t dst = sA + swz(row, l_unit);
+            if (PADONE && kvalid && !inside && ri.w) sts16(dst, 0x01010101u);
+            else cp16(dst, src, v);
+        }
+        const int8_t* bbase = p.w8 + ((long long)n0 * p.Kw + l_k) * 64 + l_q * 16;
+#pragma unroll 4
+        for (int e = 0; e < TNI / 16; e++) {
+            const int row = l_row0 + 16 * e;
+            const bool v = kvalid && (n0 + row) < p.KN;
+            const int8_t* src = v ? bbase + (long long)row * p.Kw * 64 : p.w8;
+            cp16(sB + swz(row, l_unit), src, v);
+        }
+        l_k += IKW;
+        l_pc += IKW;
+        while (l_pc >= p.PC) { l_pc -= p.PC; if (++l_kw == p.KW) { l_kw = 0; ++l_kh; } }
+        asm volatile("cp.async.commit_group;");
+    };
+
+    // ---- compute mapping ----------------------------------------------------------------------------
+    const int warp = tid >> 5, lane = tid & 31;
+    const int wm = warp % WM, wn = warp / WM;
+    // ldmatrix row/unit of this lane inside a 16-row (A) or 16-column (B) block
+    const int a_lrow = (lane & 7) + ((lane >> 3) & 1) * 8, a_lu = lane >> 4;
+    const int b_lrow = (lane & 7) + (lane >> 4) * 8, b_lu = (lane >> 3) & 1;
+    // row * IROW and (row & 7) are the same for every k-step: keep them, the unit index changes
+    uint32_t a_rowoff[4], b_rowoff[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        a_rowoff[i] = (uint32_t)((wm * 64 + i * 16 + a_lrow) * IROW);
+        b_rowoff[i] = (uint32_t)(TMI * IROW + (wn * 64 + i * 16 + b_lrow) * IROW);
+    }
+    const int a_x = a_lrow & 7, b_x = b_lrow & 7;               // (row & 7): 16-row blocks start at multiples of 16
+
+    int acc[4][8][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[i][j][e] = 0;
+
+    uint32_t af[2][4][4], bf[2][8][2];
+    auto load_frags = [&](uint32_t sA, int j, int buf) {
+#pragma unroll
+        for (int mi = 0; mi < 4; mi++)
+            ldsm4(sA + a_rowoff[mi] + (((2 * j + a_lu) ^ a_x) << 4), af[buf][mi][0], af[buf][mi][1], af[buf][mi][2], af[buf][mi][3]);
+#pragma unroll
+        for (int nj = 0; nj < 4; nj++)
+            ldsm4(sA + b_rowoff[nj] + (((2 * j + b_lu) ^ b_x) << 4), bf[buf][2 * nj][0], bf[buf][2 * nj][1],
+                  bf[buf][2 * nj + 1][0], bf[buf][2 * nj + 1][1]);
+    };
+
+    const int nchunks = (p.Kw + IKW - 1) / IKW;
+#pragma unroll
+    for (int s = 0; s < ISTAGES - 1; s++) {
+        if (s < nchunks) load_chunk(s); else asm volatile("cp.async.commit_group;");
+    }
+    for (int c = 0; c < nchunks; c++) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(ISTAGES - 2));
+        __syncthreads();
+        const uint32_t sA = sbase + (c % ISTAGES) * STAGE;
+        load_frags(sA, 0, 0);
+        if (c + ISTAGES - 1 < nchunks) load_chunk((c + ISTAGES - 1) % ISTAGES); else asm volatile("cp.async.commit_group;");
+#pragma unroll
+        for (int j = 0; j < IROW / 32; j++) {                   // k32 steps inside the chunk
+            if (j + 1 < IROW / 32) load_frags(sA, j + 1, (j + 1) & 1);   // next step's fragments first
+#pragma unroll
+            for (int mi = 0; mi < 4; mi++)
+#pragma unroll
+                for (int ni = 0; ni < 8; ni++) imma(acc[mi][ni], af[j & 1][mi], bf[j & 1][ni][0], bf[j & 1][ni][1]);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;");
+
+    // ---- epilogue: int32 -> float32, [M][KN] ---------------------------------------------------------
+    const int g = lane >> 2, t4 = lane & 3;
+    const bool pair_ok = (p.KN & 1) == 0;
+#pragma unroll
+    for (int mi = 0; mi < 4; mi++) {
+#pragma unroll
+        for (int hrow = 0; hrow < 2; hrow++) {
+            const int m = m0 + wm * 64 + mi * 16 + g + hrow * 8;
+            if (m >= p.M) continue;
+            float* yrow = p.y + (long long)m * p.KN;
+#pragma unroll
+            for (int ni = 0; ni < 8; ni++) {
+                const int n = n0 + wn * 64 + ni * 8 + 2 * t4;
+                const float v0 = (float)acc[mi][ni][2 * hrow], v1 = (float)acc[mi][ni][2 * hrow + 1];
+                if (pair_ok && n + 1 < p.KN) {
+                    *reinterpret_cast<float2*>(yrow + n) = make_float2(v0, v1);
+                } else {
+                    if (n < p.KN) yrow[n] = v0;
+                    if (n + 1 < p.KN) yrow[n + 1] = v1;
+                }
+            }
+        }
+    }
+}
+
+template <int WM, int WN, int ISTAGES, bool PADONE>
+static int launch_imma(const ImmaParams& p, cudaStream_t stream) {
+    constexpr int TMI = 64 * WM, TNI = 64 * WN;
+    constexpr int smem_bytes = ISTAGES * (TMI + TNI) * IROW + TMI * 16;
+    cudaError_t e = cudaFuncSetAttribute(conv_imma_kernel<WM, WN, ISTAGES, PADONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    dim3 grid((unsigned)((p.M + TMI - 1) / TMI), (unsigned)((p.KN + TNI - 1) / TNI));
+    conv_imma_kernel<WM, WN, ISTAGES, PADONE><<<grid, ITHREADS, smem_bytes, stream>>>(p);
+    return check_launch();
+}
+
+size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW) {
+    const size_t Cp = (size_t)packed_channels(C) * 64;
+    const size_t a = ((size_t)N * H * W * Cp + 255) / 256 * 256;
+    const size_t b = ((size_t)KN * KH * KW * Cp + 255) / 256 * 256;
+    return a + b;
+}
+
+// x fp32 -> y, all four types, scratch in `workspace` (imma_workspace_bytes).
+int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
+                       int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
+                       cudaStream_t stream) {
+    const int PC = packed_channels(C), Cp = PC * 64;
+    const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
+    if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
+    const long long M = (long long)N * oh * ow, Kw = (long long)KH * KW * PC;
+    if (M >= (1LL << 31) - 512 || Kw >= (1LL << 24) || (long long)N * H * W >= (1LL << 31) || (KN + 63) / 64 > 65535 || N > 65535 || KH * KW > 64)
+        return TAB_E_TOO_LARGE;
+    int8_t* qx8 = reinterpret_cast<int8_t*>(workspace);
+    int8_t* w8 = qx8 + ((size_t)N * H * W * Cp + 255) / 256 * 256;
+
+    // 1. activations
+    {
+        const long long pixels = (long long)H * W;
+        const long long groups = pixels * (Cp / 16);
+        long long per = (groups + Q8THREADS - 1) / Q8THREADS;
+        const long long cap = (148LL * 8 * 4 + N - 1) / N;
+        if (per > cap) per = cap;
+        if (per < 1) per = 1;
+        dim3 grid((unsigned)per, (unsigned)N);
+        const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)pixels * C) % 8 == 0);
+        const int ab = act_bits(type);
+        if (ab == 2) {
+            if (vec) quantize_int8_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
+            else quantize_int8_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
+        } else {
+            if (vec) quantize_int8_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
+            else quantize_int8_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
+        }
+        int rc = check_launch();
+        if (rc != TAB_OK) return rc;
+    }
+    // 2. weights
+    {
+        const long long words = (long long)KN * Kw;
+        const unsigned blocks = (unsigned)((words * 4 + 255) / 256);
+        const uint64_t* q = reinterpret_cast<const uint64_t*>(qw);
+        if (weight_bits(type) == 2) expand_weights_kernel<2><<<blocks, 256, 0, stream>>>(q, w8, words, PC, C);
+        else expand_weights_kernel<1><<<blocks, 256, 0, stream>>>(q, w8, words, PC, C);
+        int rc = check_launch();
+        if (rc != TAB_OK) return rc;
+    }
+    // 3. GEMM
+    ImmaParams p;
+    p.qx = qx8; p.w8 = w8; p.y = y;
+    p.N = N; p.H = H; p.W = W; p.PC = PC; p.KN = KN; p.KH = KH; p.KW = KW;
+    p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
+    p.M = (int)M; p.Kw = (int)Kw;
+    const bool padone = act_bits(type) == 1 && (p1 > 0 || p2 > 0);
+    // 256 x 64 tiles (two ring stages, so that two CTAs fit an SM) when there are at most 64 filters,
+    // 128 x 128 tiles with three stages otherwise
+    if (KN <= 64) return padone ? launch_imma<4, 1, 2, true>(p, stream) : launch_imma<4, 1, 2, false>(p, stream);
+    return padone ? launch_imma<2, 2, 3, true>(p, stream) : launch_imma<2, 2, 3, false>(p, stream);
+}
+
+}  // namespace tab

@@ -89,7 +89,7 @@ def Conv2d(X, QW, thresholds, btn, type, padding1, padding2, stride1, stride2, N
     l = _cabi.lib()
     with torch.cuda.device(X.device):
         Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=X.device)
-        ws_bytes = l.tab_conv2d_workspace_bytes(conv_type, N, H, W, C)
+        ws_bytes = l.tab_conv2d_workspace_bytes(conv_type, N, H, W, C, KN, KH, KW)
         ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=X.device)
         rc = l.tab_conv2d_launch(X.data_ptr(), QW.data_ptr(), thresholds.data_ptr(), btn.data_ptr(), Y.data_ptr(),
                                  ws.data_ptr(), ws.numel(), conv_type, p1, p2, s1, s2,

@@ -58,10 +58,13 @@ def test_argument_validation_without_a_device():
 
 def test_workspace_size():
     l = _cabi.lib()
-    # ternary activations: N*H*W*PC*2 words; binary: one plane; rounded up to 256 bytes
-    assert l.tab_conv2d_workspace_bytes(0, 2, 5, 5, 65) == (2 * 25 * 2 * 2 * 8 + 255) // 256 * 256
-    assert l.tab_conv2d_workspace_bytes(3, 2, 5, 5, 65) == (2 * 25 * 2 * 1 * 8 + 255) // 256 * 256
-    assert l.tab_conv2d_workspace_bytes(9, 2, 5, 5, 65) == 0
+    # the larger of: packed activations (N*H*W*PC*planes words) and byte activations + byte weights
+    # (N*H*W*PC*64 + KN*KH*KW*PC*64), each rounded up to 256 bytes
+    r = lambda b: (b + 255) // 256 * 256
+    assert l.tab_conv2d_workspace_bytes(0, 2, 5, 5, 65, 4, 3, 3) == max(r(2 * 25 * 2 * 2 * 8), r(2 * 25 * 128) + r(4 * 9 * 128))
+    assert l.tab_conv2d_workspace_bytes(3, 2, 5, 5, 65, 4, 3, 3) == r(2 * 25 * 128) + r(4 * 9 * 128)
+    assert l.tab_conv2d_workspace_bytes(9, 2, 5, 5, 65, 4, 3, 3) == 0
+    assert l.tab_conv2d_set_path(7) == -1
 
 
 def test_missing_library_fails_loudly(monkeypatch):

@@ -18,6 +18,15 @@ GOLD = os.path.join(os.path.dirname(__file__), "golden")
 NAMES = ["tnn", "tbn", "btn", "bnn"]
 
 
+@pytest.fixture(autouse=True, params=["tensor", "popcount"])
+def conv_path(request):
+    """Every test of this module runs once per compute path of tab_conv2d_launch."""
+    l = _cabi.lib()
+    prev = l.tab_conv2d_set_path(1 if request.param == "popcount" else 0)
+    yield request.param
+    l.tab_conv2d_set_path(prev)
+
+
 def dev_t(a, cuda):
     return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
 
@@ -169,8 +178,10 @@ def test_conv_shapes(cuda, t, geom):
 
 
 @pytest.mark.parametrize("t", range(4))
-def test_popcount_tree_equals_plain_popcount(cuda, t):
+def test_popcount_tree_equals_plain_popcount(cuda, t, conv_path):
     """The carry-save reduction and the one-POPC-per-word variant are separate code paths."""
+    if conv_path != "popcount":
+        pytest.skip("only meaningful on the popcount path")
     N, H, W, C, KN = 4, 14, 14, 256, 96
     x, ths = make_input(5, N, H, W, C)
     w, wths = make_input(6, KN, 3, 3, C)
