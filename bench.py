@@ -19,9 +19,10 @@ step (activation quantise, residual add, thresholds) counts as time but not as o
 ``value``   device-resident input, CUDA-event time of the K steps, L2 flushed between steps, max over ranks.
 ``e2e``     the same step through the TAB_CUDA extension module with the input in pinned host memory: the
             host-to-device copy of the shard and the device-to-host copy of the gathered output are timed.
-``roofline`` for the dominant kernel (the popcount convolution), timed alone per layer on pre-packed
-            activations; the denominator is the integer-pipe bound derived from POPC and LOP3 issue rates
-            measured in the same run by the library's register-only probe.
+``roofline`` for the dominant kernel (the s8 tensor-core GEMM of the convolution), timed alone per layer on
+            pre-quantised byte operands; denominator = 2 x the measured bf16 tensor peak.
+``roofline_popcount`` the bit-packed LOP3/POPC kernel on the same layers against the integer-pipe bound derived
+            from POPC and LOP3 issue rates measured in the same run by the library's register-only probe.
 ``cpu_baseline`` / ``--impl reference``: the reference's CPU algorithm (quantise, pad, im2row, its own
             compiled *GEMM_baseline functions when oracle/_ref exists, else the C port) on the host cores,
             on a bounded sample of images of the same workload.
@@ -262,11 +263,11 @@ def main():
     launches = [0]
 
     class CountingOps:
-        """tab_b200.ops with a kernel-launch counter (each Conv2d = quantise + conv kernels; each
-        residual_threshold = reduce + finalise kernels)."""
+        """tab_b200.ops with a kernel-launch counter (each Conv2d = quantise + weight-expand + GEMM kernels;
+        each residual_threshold = reduce + finalise kernels)."""
         @staticmethod
         def Conv2d(*a):
-            launches[0] += 2
+            launches[0] += 3
             return tab_ops.Conv2d(*a)
 
         @staticmethod
@@ -372,6 +373,7 @@ def main():
 
     popc_rate = probe(0)          # lane-level POPC per second, whole device
     lop3_rate = probe(1)
+    imma_sync_tops = probe(2) / 1e12   # s8 mma.sync from registers: the ceiling of the legacy MMA instruction
     # TNN per 32-bit word pair: 2 LOP3 to form t,u; f full adders (2 LOP3 each) per word and stream remove f POPC.
     # time(f) = max((2+4f)/lop3, 2(1-f)/popc); balanced f* gives the integer-pipe bound.
     f_star = (2 * lop3_rate - 2 * popc_rate) / (4 * popc_rate + 2 * lop3_rate)
@@ -381,7 +383,7 @@ def main():
     naive_popc_tops = popc_rate * 64 / 2 / 1e12
 
     layer_rows = []
-    conv_ms_sum, conv_ops_sum = 0.0, 0
+    sums = {"gemm_ms": 0.0, "popc_ms": 0.0, "call_ms": 0.0, "ops": 0}
     if not args.no_layer_table:
         h = H0
         jobs = []
@@ -392,47 +394,69 @@ def main():
             if b.shortcut is not None:
                 jobs.append((b.shortcut, h))
             h = oh_a
-        for cs, ih in jobs:
-            oh = (ih + 2 * cs.pad - cs.K + 1) // cs.stride
-            xin = torch.randn(n_local, ih, ih, cs.C, device=dev)
-            ths = tab_ops.residual_threshold(xin, None, 0.7)
-            qx, _ = tab_ops.Quantize(xin, ths, 2, n_local, ih, ih, cs.C)
-            qw, btn = qweights[cs.name]
-            yb = torch.empty(n_local * oh * oh * cs.KN, dtype=torch.float32, device=dev)
+
+        def time_launch(fn):
             times = []
             for i in range(6):
                 flush_buf.fill_(1)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                _cabi.check(lib.tab_conv2d_packed_launch(qx.data_ptr(), qw.data_ptr(), btn.data_ptr(), yb.data_ptr(), CONV_TYPE,
-                                                         cs.pad, cs.pad, cs.stride, cs.stride, n_local, ih, ih, cs.C, cs.KN, cs.K, cs.K,
-                                                         stream), "conv")
+                fn()
                 e1.record()
                 torch.cuda.synchronize()
                 if i >= 2:
                     times.append(e0.elapsed_time(e1))
-            ms = statistics.mean(times)
+            return statistics.mean(times)
+
+        for cs, ih in jobs:
+            oh = (ih + 2 * cs.pad - cs.K + 1) // cs.stride
+            xin = torch.randn(n_local, ih, ih, cs.C, device=dev)
+            ths = tab_ops.residual_threshold(xin, None, 0.7)
+            qw, btn = qweights[cs.name]
+            qx = tab_ops.Quantize(xin, ths, 2, n_local, ih, ih, cs.C)[0]
+            q8 = tab_ops.quantize_int8(xin, ths, 2, n_local, ih, ih, cs.C)
+            w8 = tab_ops.expand_weights(qw, 2, cs.KN, cs.K, cs.K, cs.C)
+            yb = torch.empty(n_local * oh * oh * cs.KN, dtype=torch.float32, device=dev)
+            geom = (cs.pad, cs.pad, cs.stride, cs.stride, n_local, ih, ih, cs.C, cs.KN, cs.K, cs.K)
+            ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_launch(q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "int8"))
+            ms_popc = time_launch(lambda: _cabi.check(lib.tab_conv2d_packed_launch(qx.data_ptr(), qw.data_ptr(), btn.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "popc"))
+            ms_call = time_launch(lambda: tab_ops.Conv2d(xin, qw, ths, btn, CONV_TYPE, *geom))
             lops = 2 * n_local * oh * oh * cs.KN * cs.K * cs.K * cs.C
-            conv_ms_sum += ms
-            conv_ops_sum += lops
-            layer_rows.append({"layer": cs.name, "in": [ih, ih, cs.C], "KN": cs.KN, "K": cs.K, "s": cs.stride, "ms": round(ms, 4),
-                               "tops": round(lops / ms / 1e9, 1)})
-    achieved = conv_ops_sum / (conv_ms_sum * 1e-3) / 1e12 if conv_ms_sum else None
+            sums["gemm_ms"] += ms_gemm; sums["popc_ms"] += ms_popc; sums["call_ms"] += ms_call; sums["ops"] += lops
+            layer_rows.append({"layer": cs.name, "in": [ih, ih, cs.C], "KN": cs.KN, "K": cs.K, "s": cs.stride,
+                               "gemm_ms": round(ms_gemm, 4), "gemm_tops": round(lops / ms_gemm / 1e9, 1),
+                               "popcount_kernel_tops": round(lops / ms_popc / 1e9, 1),
+                               "conv2d_call_ms": round(ms_call, 4), "conv2d_call_tops": round(lops / ms_call / 1e9, 1)})
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        bf16_peak, peak_src = float(peaks["bf16_tflops"]), "2 x MEASURED_PEAKS.json bf16_tflops (of measured; s8 runs at twice the bf16 rate)"
+    except Exception:
+        peaks = None
+        bf16_peak, peak_src = 1590.0, "2 x fallback 1.59 PFLOP/s bf16 (of fallback)"
+    tensor_peak = 2.0 * bf16_peak
+    achieved = sums["ops"] / (sums["gemm_ms"] * 1e-3) / 1e12 if sums["gemm_ms"] else None
     roofline = {
-        "kernel": "conv_popc_kernel<TNN> (implicit-im2col popcount GEMM), %d launches per step" % len(layer_rows),
-        "bound": "alu", "achieved": achieved, "peak": peak_tops, "unit": "TOP/s",
-        "frac": (achieved / peak_tops) if achieved else None, "traffic": None,
+        "kernel": "conv_imma_kernel (implicit-im2col s8 tensor-core GEMM), %d launches per step" % len(layer_rows),
+        "bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TOP/s",
+        "frac": (achieved / tensor_peak) if achieved else None, "traffic": None,
+        "peak_source": peak_src + "; ceiling of the s8 mma.sync instruction measured from registers in this run: %.0f TOP/s" % imma_sync_tops,
+        "frac_of_mma_sync_ceiling": (achieved / imma_sync_tops) if achieved else None,
+        "avg_launch_ms": sums["gemm_ms"] / max(len(layer_rows), 1),
+    }
+    popc_achieved = sums["ops"] / (sums["popc_ms"] * 1e-3) / 1e12 if sums["popc_ms"] else None
+    roofline_popcount = {
+        "kernel": "conv_popc_kernel<TNN> (bit-packed LOP3/POPC path, TAB_PATH_POPCOUNT), same layers",
+        "bound": "alu", "achieved": popc_achieved, "peak": peak_tops, "unit": "TOP/s",
+        "frac": (popc_achieved / peak_tops) if popc_achieved else None,
         "peak_source": "measured in this run: POPC %.3e/s, LOP3 %.3e/s (register-only probe); balanced carry-save bound "
                        "(f*=%.2f full adders per word); one-POPC-per-word bound would be %.1f TOP/s" % (popc_rate, lop3_rate, f_star, naive_popc_tops),
-        "avg_launch_ms": conv_ms_sum / max(len(layer_rows), 1),
     }
 
     # ---- TAB_Quantize alone at N=256, 56x56x256 (HBM-bound), against the measured copy bandwidth ---------
     quant = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    if peaks is not None and "hbm_gbs" in peaks:
         hbm_peak, hbm_src = float(peaks["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs (of measured)"
-    except Exception:
+    else:
         hbm_peak, hbm_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
     if world == 1:
         QN, QH, QW_, QC = 256, 56, 56, 256
@@ -465,7 +489,7 @@ def main():
     line = {
         "metric": "TAB_Conv2d binary-op TOPS", "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "u32 popcount (ternary bit-planes)", "data": "synthetic",
+        "vs_baseline": None, "dtype": "s8 (ternary values on the integer tensor cores, s32 accumulate; exact)", "data": "synthetic",
         "config": dict(workload_config(world), binary_ops_per_step=ops_per_step),
         "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(N * per_img_out * 4),
@@ -473,6 +497,7 @@ def main():
         "gpu_launches": gpu_launches,
         "clocks": clocks,
         "roofline": roofline,
+        "roofline_popcount": roofline_popcount,
         "quantize": quant,
         "layers": layer_rows,
     }

@@ -98,6 +98,24 @@ int tab_conv2d_packed_launch(const int64_t* qx, const int64_t* qw, const int32_t
                              int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
 
 /*
+ * The three stages of the tensor-core path of tab_conv2d_launch on their own, for callers that keep the
+ * byte-expanded weights between calls (weights are constant during inference) or already hold
+ * quantised activations.  Byte tensors hold the quantised values {-1,0,+1} as int8 with the channel
+ * dimension padded to Cp = 64*ceil(C/64) (padding bytes 0): activations [N][H][W][Cp], weights
+ * [KN][KH][KW][Cp].  All byte pointers must be 16-byte aligned.
+ *   tab_quantize_int8_launch   same compares as tab_quantize_launch (TAB_GEMM.cu:184-192, :231), byte output
+ *   tab_expand_weights_launch  tab_quantize_launch's packed weights (bitwidth 1 or 2) -> bytes
+ *   tab_conv2d_int8_launch     the GEMM stage (GEMMWithCuda, TAB_GEMM.cuh:22-66, with padding and im2row
+ *                              folded in); returns TAB_E_TOO_LARGE for KH*KW > 64 or N > 65535
+ */
+int tab_quantize_int8_launch(const float* x, const float* ths, int8_t* qx8, int bitwidth,
+                             int N, int H, int W, int C, tab_stream_t stream);
+int tab_expand_weights_launch(const int64_t* qw, int8_t* w8, int bitwidth, int KN, int KH, int KW, int C,
+                              tab_stream_t stream);
+int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
+                           int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
+
+/*
  * tab_conv2d_launch without a workspace argument.  No counterpart in the reference (its host code calls
  * cudaMalloc/cudaFree for scratch on every convolution, TAB_GEMM.cu:391-407,522-524).
  *
@@ -139,8 +157,9 @@ int tab_residual_threshold_launch(float* y, const float* residual, float* ths, d
  * Register-only micro-benchmark of the integer pipes used by the convolution, for roofline
  * denominators: runs `iters` rounds on a grid that fills the device and writes elapsed-independent
  * checksums to `sink` (at least tab_pipe_probe_sink_bytes() bytes).  kind: 0 = 32-bit POPC,
- * 1 = LOP3.  *ops_out receives the number of lane-level instructions of that kind issued; the caller
- * times the call with CUDA events.  Has no counterpart in the reference.
+ * 1 = LOP3, 2 = s8 mma.sync m16n8k32.  *ops_out receives the number of lane-level instructions of that
+ * kind issued (kind 2: multiply-adds * 2); the caller times the call with CUDA events.  Has no
+ * counterpart in the reference.
  */
 size_t tab_pipe_probe_sink_bytes(void);
 int tab_pipe_probe_launch(int kind, int iters, void* sink, double* ops_out, tab_stream_t stream);

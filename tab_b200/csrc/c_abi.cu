@@ -16,6 +16,10 @@ size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW);
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
                        cudaStream_t stream);
+int quantize_int8_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C, cudaStream_t stream);
+int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream);
+int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary_act, int p1, int p2, int s1, int s2,
+                       int N, int H, int W, int C, int KN, int KH, int KW, cudaStream_t stream);
 static int g_conv_path = TAB_PATH_AUTO;
 
 static bool dims_ok(int N, int H, int W, int C) { return N >= 0 && H >= 0 && W >= 0 && C >= 1; }
@@ -129,6 +133,37 @@ int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const
     rc = quantize_dispatch(x, ths, qx, nullptr, act_bits(type), N, H, W, C, s);   // TAB_GEMM.cu:419-426
     if (rc != TAB_OK) return rc;
     return tab_conv2d_packed_launch(qx, qw, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream);
+}
+
+int tab_quantize_int8_launch(const float* x, const float* ths, int8_t* qx8, int bitwidth,
+                             int N, int H, int W, int C, tab_stream_t stream) {
+    if (!dims_ok(N, H, W, C) || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
+    if ((long long)N * H * W == 0) return TAB_OK;
+    if (!x || !ths || !qx8) return TAB_E_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) || (reinterpret_cast<uintptr_t>(qx8) & 15))
+        return TAB_E_ALIGNMENT;
+    return quantize_int8_dispatch(x, ths, qx8, bitwidth == 1 ? 1 : 2, N, H, W, C, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int tab_expand_weights_launch(const int64_t* qw, int8_t* w8, int bitwidth, int KN, int KH, int KW, int C, tab_stream_t stream) {
+    if (KN < 0 || KH < 1 || KW < 1 || C < 1 || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
+    if (KN == 0) return TAB_OK;
+    if (!qw || !w8) return TAB_E_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(qw) & 7) || (reinterpret_cast<uintptr_t>(w8) & 15)) return TAB_E_ALIGNMENT;
+    return expand_weights_dispatch(qw, w8, bitwidth == 1 ? 1 : 2, KN, KH, KW, C, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
+                           int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
+    int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
+    if (rc != TAB_OK) return rc;
+    const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
+    if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
+    if (!qx8 || !w8 || !y) return TAB_E_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(qx8) & 15) || (reinterpret_cast<uintptr_t>(w8) & 15) || (reinterpret_cast<uintptr_t>(y) & 3))
+        return TAB_E_ALIGNMENT;
+    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+                              reinterpret_cast<cudaStream_t>(stream));
 }
 
 /* Test/benchmark hook: 1 = carry-save popcount tree (default), 0 = one POPC per word. */

@@ -336,61 +336,86 @@ size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW) 
     return a + b;
 }
 
-// x fp32 -> y, all four types, scratch in `workspace` (imma_workspace_bytes).
-int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
+static int imma_limits(int N, int H, int W, int C, int KN, int KH, int KW, long long oh, long long ow) {
+    const long long M = (long long)N * oh * ow, Kw = (long long)KH * KW * packed_channels(C);
+    if (M >= (1LL << 31) - 512 || Kw >= (1LL << 24) || (long long)N * H * W >= (1LL << 31) ||
+        (KN + 63) / 64 > 65535 || N > 65535 || KH * KW > 64)
+        return TAB_E_TOO_LARGE;
+    return TAB_OK;
+}
+
+int quantize_int8_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
+                           cudaStream_t stream) {
+    const int Cp = packed_channels(C) * 64;
+    const long long pixels = (long long)H * W;
+    if (N == 0 || pixels == 0) return TAB_OK;
+    if (N > 65535) return TAB_E_TOO_LARGE;
+    const long long groups = pixels * (Cp / 16);
+    long long per = (groups + Q8THREADS - 1) / Q8THREADS;
+    const long long cap = (148LL * 8 * 4 + N - 1) / N;
+    if (per > cap) per = cap;
+    if (per < 1) per = 1;
+    dim3 grid((unsigned)per, (unsigned)N);
+    const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && ((pixels * C) % 8 == 0);
+    if (bits == 2) {
+        if (vec) quantize_int8_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
+        else quantize_int8_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
+    } else {
+        if (vec) quantize_int8_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
+        else quantize_int8_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
+    }
+    return check_launch();
+}
+
+int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream) {
+    const int PC = packed_channels(C);
+    const long long words = (long long)KN * KH * KW * PC;
+    if (words == 0) return TAB_OK;
+    if (words * 4 >= (1LL << 31) * 256) return TAB_E_TOO_LARGE;
+    const unsigned blocks = (unsigned)((words * 4 + 255) / 256);
+    const uint64_t* q = reinterpret_cast<const uint64_t*>(qw);
+    if (wbits == 2) expand_weights_kernel<2><<<blocks, 256, 0, stream>>>(q, w8, words, PC, C);
+    else expand_weights_kernel<1><<<blocks, 256, 0, stream>>>(q, w8, words, PC, C);
+    return check_launch();
+}
+
+// GEMM stage alone on byte operands.  binary_act: activations are {-1,+1} (out-of-image taps count as +1).
+int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary_act,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
                        cudaStream_t stream) {
-    const int PC = packed_channels(C), Cp = PC * 64;
+    const int PC = packed_channels(C);
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
-    const long long M = (long long)N * oh * ow, Kw = (long long)KH * KW * PC;
-    if (M >= (1LL << 31) - 512 || Kw >= (1LL << 24) || (long long)N * H * W >= (1LL << 31) || (KN + 63) / 64 > 65535 || N > 65535 || KH * KW > 64)
-        return TAB_E_TOO_LARGE;
-    int8_t* qx8 = reinterpret_cast<int8_t*>(workspace);
-    int8_t* w8 = qx8 + ((size_t)N * H * W * Cp + 255) / 256 * 256;
-
-    // 1. activations
-    {
-        const long long pixels = (long long)H * W;
-        const long long groups = pixels * (Cp / 16);
-        long long per = (groups + Q8THREADS - 1) / Q8THREADS;
-        const long long cap = (148LL * 8 * 4 + N - 1) / N;
-        if (per > cap) per = cap;
-        if (per < 1) per = 1;
-        dim3 grid((unsigned)per, (unsigned)N);
-        const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)pixels * C) % 8 == 0);
-        const int ab = act_bits(type);
-        if (ab == 2) {
-            if (vec) quantize_int8_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
-            else quantize_int8_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
-        } else {
-            if (vec) quantize_int8_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
-            else quantize_int8_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, pixels, C, Cp);
-        }
-        int rc = check_launch();
-        if (rc != TAB_OK) return rc;
-    }
-    // 2. weights
-    {
-        const long long words = (long long)KN * Kw;
-        const unsigned blocks = (unsigned)((words * 4 + 255) / 256);
-        const uint64_t* q = reinterpret_cast<const uint64_t*>(qw);
-        if (weight_bits(type) == 2) expand_weights_kernel<2><<<blocks, 256, 0, stream>>>(q, w8, words, PC, C);
-        else expand_weights_kernel<1><<<blocks, 256, 0, stream>>>(q, w8, words, PC, C);
-        int rc = check_launch();
-        if (rc != TAB_OK) return rc;
-    }
-    // 3. GEMM
+    int rc = imma_limits(N, H, W, C, KN, KH, KW, oh, ow);
+    if (rc != TAB_OK) return rc;
     ImmaParams p;
     p.qx = qx8; p.w8 = w8; p.y = y;
     p.N = N; p.H = H; p.W = W; p.PC = PC; p.KN = KN; p.KH = KH; p.KW = KW;
     p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
-    p.M = (int)M; p.Kw = (int)Kw;
-    const bool padone = act_bits(type) == 1 && (p1 > 0 || p2 > 0);
+    p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * PC;
+    const bool padone = binary_act && (p1 > 0 || p2 > 0);
     // 256 x 64 tiles (two ring stages, so that two CTAs fit an SM) when there are at most 64 filters,
     // 128 x 128 tiles with three stages otherwise
     if (KN <= 64) return padone ? launch_imma<4, 1, 2, true>(p, stream) : launch_imma<4, 1, 2, false>(p, stream);
     return padone ? launch_imma<2, 2, 3, true>(p, stream) : launch_imma<2, 2, 3, false>(p, stream);
+}
+
+// x fp32 -> y, all four types, scratch in `workspace` (imma_workspace_bytes).
+int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
+                       int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
+                       cudaStream_t stream) {
+    const int Cp = packed_channels(C) * 64;
+    const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
+    if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
+    int rc = imma_limits(N, H, W, C, KN, KH, KW, oh, ow);
+    if (rc != TAB_OK) return rc;
+    int8_t* qx8 = reinterpret_cast<int8_t*>(workspace);
+    int8_t* w8 = qx8 + ((size_t)N * H * W * Cp + 255) / 256 * 256;
+    rc = quantize_int8_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, stream);
+    if (rc != TAB_OK) return rc;
+    rc = expand_weights_dispatch(qw, w8, weight_bits(type), KN, KH, KW, C, stream);
+    if (rc != TAB_OK) return rc;
+    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream);
 }
 
 }  // namespace tab

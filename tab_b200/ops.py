@@ -145,3 +145,48 @@ def residual_threshold(Y, residual=None, scale=0.7):
                                                        _stream_ptr(Y.device))
     _cabi.check(rc, "tab_residual_threshold_launch")
     return ths
+
+
+# ---- stages of the tensor-core path (byte operands), for callers that cache expanded weights -------------
+
+def quantize_int8(X, thresholds, bitwidth, N, H, W, C):
+    """fp32 NHWC -> int8 ``{N,H,W,Cp}`` holding the quantised values, ``Cp = 64*ceil(C/64)`` (padding 0)."""
+    _check_input(X, "X", torch.float32)
+    _check_input(thresholds, "thresholds", torch.float32)
+    Cp = (int(C) + 63) // 64 * 64
+    with torch.cuda.device(X.device):
+        q = torch.empty((N, H, W, Cp), dtype=torch.int8, device=X.device)
+        rc = _cabi.lib().tab_quantize_int8_launch(X.data_ptr(), thresholds.data_ptr(), q.data_ptr(), int(bitwidth),
+                                                  N, H, W, C, _stream_ptr(X.device))
+    _cabi.check(rc, "tab_quantize_int8_launch")
+    return q
+
+
+def expand_weights(QW, bitwidth, KN, KH, KW, C):
+    """Packed weights (``Quantize`` output) -> int8 ``{KN,KH,KW,Cp}``."""
+    _check_input(QW, "QW", torch.int64)
+    Cp = (int(C) + 63) // 64 * 64
+    bits = 1 if int(bitwidth) == 1 else 2
+    if QW.numel() != KN * KH * KW * (Cp // 64) * bits:
+        raise RuntimeError("QW has %d words, expected %d" % (QW.numel(), KN * KH * KW * (Cp // 64) * bits))
+    with torch.cuda.device(QW.device):
+        w8 = torch.empty((KN, KH, KW, Cp), dtype=torch.int8, device=QW.device)
+        rc = _cabi.lib().tab_expand_weights_launch(QW.data_ptr(), w8.data_ptr(), bits, KN, KH, KW, C, _stream_ptr(QW.device))
+    _cabi.check(rc, "tab_expand_weights_launch")
+    return w8
+
+
+def conv2d_int8(QX8, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW):
+    """The GEMM stage on byte operands; same output as ``Conv2d``."""
+    _check_input(QX8, "QX8", torch.int8)
+    _check_input(W8, "W8", torch.int8)
+    Cp = (int(C) + 63) // 64 * 64
+    if QX8.numel() != N * H * W * Cp or W8.numel() != KN * KH * KW * Cp:
+        raise RuntimeError("byte operands must be [N,H,W,Cp] and [KN,KH,KW,Cp] with Cp = %d" % Cp)
+    OH, OW = conv_out_size(H, W, KH, KW, int(padding1), int(padding2), int(stride1), int(stride2))
+    with torch.cuda.device(QX8.device):
+        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=QX8.device)
+        rc = _cabi.lib().tab_conv2d_int8_launch(QX8.data_ptr(), W8.data_ptr(), Y.data_ptr(), int(type), int(padding1), int(padding2),
+                                                int(stride1), int(stride2), N, H, W, C, KN, KH, KW, _stream_ptr(QX8.device))
+    _cabi.check(rc, "tab_conv2d_int8_launch")
+    return Y

@@ -259,6 +259,40 @@ def test_packed_entry_point_equals_fused_call(cuda):
         assert np.array_equal(y.cpu().numpy(), yo)
 
 
+def test_int8_stage_entry_points(cuda):
+    """quantize_int8 / expand_weights / conv2d_int8 against the de-quantised oracle planes and the fused call."""
+    N, H, W, C, KN, K = 3, 9, 8, 130, 70, 3
+    x, ths = make_input(1, N, H, W, C)
+    w, wths = make_input(2, KN, K, K, C)
+    Cp = 192
+    for t in range(4):
+        ab, wb = O.act_bits(t), O.weight_bits(t)
+        qx, _ = O.quantize(x, ths, ab, N, H, W, C)
+        qw, btn = O.quantize(w, wths, wb, KN, K, K, C)
+        q8 = TAB.ops.quantize_int8(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C)
+        w8 = TAB.ops.expand_weights(dev_t(qw, cuda), wb, KN, K, K, C)
+        assert tuple(q8.shape) == (N, H, W, Cp) and tuple(w8.shape) == (KN, K, K, Cp)
+        exp_a = np.zeros((N, H, W, Cp), np.int8)
+        exp_a[..., :C] = O.dequantize(qx, C).astype(np.int8)
+        exp_w = np.zeros((KN, K, K, Cp), np.int8)
+        exp_w[..., :C] = O.dequantize(qw, C).astype(np.int8)
+        assert np.array_equal(q8.cpu().numpy(), exp_a) and np.array_equal(w8.cpu().numpy(), exp_w)
+        y = TAB.ops.conv2d_int8(q8, w8, t, 1, 1, 2, 1, N, H, W, C, KN, K, K)
+        yo = c_oracle.conv2d(x, qw, ths, btn, t, 1, 1, 2, 1, N, H, W, C, KN, K, K)
+        assert np.array_equal(y.cpu().numpy(), yo)
+
+
+def test_kernels_larger_than_the_tensor_path_limit_fall_back(cuda):
+    """9x9 kernels (81 taps) exceed the tensor-core loader's 64-tap mask: the call must still be exact."""
+    N, H, W, C, KN, K = 1, 12, 12, 64, 8, 9
+    x, ths = make_input(3, N, H, W, C)
+    w, wths = make_input(4, KN, K, K, C)
+    for t in (0, 3):
+        qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, K, K, C)
+        y = gpu_conv(cuda, x, qw, ths, btn, t, 4, 4, 1, 1, N, H, W, C, KN, K, K)
+        assert np.array_equal(y, c_oracle.conv2d(x, qw, ths, btn, t, 4, 4, 1, 1, N, H, W, C, KN, K, K))
+
+
 # ------------------------------------------------------------------------------------------ chain
 
 def test_residual_threshold(cuda):
