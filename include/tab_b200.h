@@ -89,6 +89,24 @@ int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const
                       int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
 
 /*
+ * tab_conv2d_launch with two optional fusions for chained layers (no counterpart in the reference, whose
+ * callers add residuals and compute the next thresholds with framework ops):
+ *   residual  float32 [N][OH][OW][KN] or NULL: y = conv(x) + residual
+ *   abs_sums  double [N] or NULL: receives sum |y[n]| per image (cleared by this call); pass it to
+ *             tab_threshold_from_sums_launch to obtain scale*mean|y| as the next layer's thresholds.
+ * On the tensor-core path both happen in the GEMM epilogue (no extra pass over y); otherwise one extra
+ * pass is made.  Sums are exact (and independent of scheduling) for integer-valued data.
+ */
+int tab_conv2d_fused_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                            float* y, void* workspace, size_t workspace_bytes, int type,
+                            int p1, int p2, int s1, int s2,
+                            int N, int H, int W, int C, int KN, int KH, int KW,
+                            const float* residual, double* abs_sums, tab_stream_t stream);
+/* ths[n] = scale * sums[n] / per_image. */
+int tab_threshold_from_sums_launch(const double* sums, float* ths, float scale, int N, long long per_image,
+                                   tab_stream_t stream);
+
+/*
  * Same convolution on activations that are already bit-packed (the qx layout above with bits = 2 for
  * types 0,1 and bits = 1 for types 2,3).  This is the GEMM stage of tab_conv2d_launch on its own
  * (GEMMWithCuda, TAB_GEMM.cuh:22-66, with padding and im2row folded in); it needs no workspace.

@@ -24,6 +24,19 @@ class OracleOps:
         return (np.float64(np.float32(scale)) * (s / np.float64(per))).astype(np.float32)
 
 
+class OracleOpsFused(OracleOps):
+    """Same results through the fused interface (composition of the two oracle steps)."""
+
+    @staticmethod
+    def Conv2dFused(x, qw, ths, btn, conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, residual=None, threshold_scale=None):
+        y = OracleOps.Conv2d(x, qw, ths, btn, conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
+        if threshold_scale is None:
+            if residual is not None:
+                y += np.asarray(residual, dtype=np.float32).reshape(y.shape)
+            return y, None
+        return y, OracleOps.residual_threshold(y, residual, threshold_scale)
+
+
 def torch_cpu_conv(x, qw, ths, btn, conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW):
     """Oracle convolution on torch CPU tensors (stand-in "kernel" for the gloo data-parallel tests)."""
     import torch

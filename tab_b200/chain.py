@@ -111,21 +111,32 @@ def quantize_weights(weights, conv_type, quantize_fn, to_backend=lambda a: a):
 def forward(ops, x, ths, qweights, conv_type: int, N: int, H: int = 56, W: int = 56):
     """Run the chain.  ``x``: fp32 activations with N*H*W*64 elements (NHWC); ``ths``: thresholds ``[N]``
     for ``x``.  Returns ``(y, OH, OW, KN)`` where ``y`` holds N*OH*OW*KN floats in NHWC order.  ``x`` is
-    not modified; intermediate activations are updated in place by the residual additions."""
+    not modified.
+
+    ``ops`` provides ``Conv2d(...)`` and ``residual_threshold(Y, residual, scale)``; if it also provides
+    ``Conv2dFused(..., residual, threshold_scale) -> (Y, next_thresholds)`` the residual addition and the
+    threshold statistics ride in the convolution's epilogue instead of separate passes (same results)."""
+    fused = getattr(ops, "Conv2dFused", None)
     h, w = H, W
     for b in resnet18_blocks():
         a, bb, sc = b.conv_a, b.conv_b, b.shortcut
         qa, ba = qweights[a.name]
-        y1 = ops.Conv2d(x, qa, ths, ba, conv_type, a.pad, a.pad, a.stride, a.stride, N, h, w, a.C, a.KN, a.K, a.K)
-        oh, ow = (h + 2 * a.pad - a.K + 1) // a.stride, (w + 2 * a.pad - a.K + 1) // a.stride
-        t1 = ops.residual_threshold(y1, None, THRESHOLD_SCALE)
         qb, bbt = qweights[bb.name]
-        y2 = ops.Conv2d(y1, qb, t1, bbt, conv_type, bb.pad, bb.pad, bb.stride, bb.stride, N, oh, ow, bb.C, bb.KN, bb.K, bb.K)
+        oh, ow = (h + 2 * a.pad - a.K + 1) // a.stride, (w + 2 * a.pad - a.K + 1) // a.stride
+        ga = (a.pad, a.pad, a.stride, a.stride, N, h, w, a.C, a.KN, a.K, a.K)
+        gb = (bb.pad, bb.pad, bb.stride, bb.stride, N, oh, ow, bb.C, bb.KN, bb.K, bb.K)
         if sc is None:
             short = x
         else:
             qs, bs = qweights[sc.name]
             short = ops.Conv2d(x, qs, ths, bs, conv_type, sc.pad, sc.pad, sc.stride, sc.stride, N, h, w, sc.C, sc.KN, sc.K, sc.K)
-        ths = ops.residual_threshold(y2, short, THRESHOLD_SCALE)      # y2 += short; thresholds of the sum
+        if fused is not None:
+            y1, t1 = fused(x, qa, ths, ba, conv_type, *ga, None, THRESHOLD_SCALE)
+            y2, ths = fused(y1, qb, t1, bbt, conv_type, *gb, short, THRESHOLD_SCALE)   # y2 = conv + shortcut
+        else:
+            y1 = ops.Conv2d(x, qa, ths, ba, conv_type, *ga)
+            t1 = ops.residual_threshold(y1, None, THRESHOLD_SCALE)
+            y2 = ops.Conv2d(y1, qb, t1, bbt, conv_type, *gb)
+            ths = ops.residual_threshold(y2, short, THRESHOLD_SCALE)      # y2 += short; thresholds of the sum
         x, h, w = y2, oh, ow
     return x, h, w, resnet18_blocks()[-1].conv_b.KN

@@ -15,11 +15,13 @@ void conv_set_csa(bool on);
 size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW);
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const float* residual, double* abs_sums);
+int residual_abs_sum_dispatch(float* y, const float* residual, double* sums, int N, long long per_image, cudaStream_t s);
 int quantize_int8_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C, cudaStream_t stream);
 int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream);
 int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary_act, int p1, int p2, int s1, int s2,
-                       int N, int H, int W, int C, int KN, int KH, int KW, cudaStream_t stream);
+                       int N, int H, int W, int C, int KN, int KH, int KW, cudaStream_t stream,
+                       const float* residual, double* abs_sums);
 static int g_conv_path = TAB_PATH_AUTO;
 
 static bool dims_ok(int N, int H, int W, int C) { return N >= 0 && H >= 0 && W >= 0 && C >= 1; }
@@ -109,30 +111,61 @@ int tab_conv2d_packed_launch(const int64_t* qx, const int64_t* qw, const int32_t
                                 reinterpret_cast<cudaStream_t>(stream));
 }
 
-int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
-                      float* y, void* workspace, size_t workspace_bytes, int type,
-                      int p1, int p2, int s1, int s2,
-                      int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
+static int conv2d_impl(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                       float* y, void* workspace, size_t workspace_bytes, int type,
+                       int p1, int p2, int s1, int s2,
+                       int N, int H, int W, int C, int KN, int KH, int KW,
+                       const float* residual, double* abs_sums, tab_stream_t stream) {
     int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
     if (rc != TAB_OK) return rc;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (abs_sums && N > 0) {
+        if (reinterpret_cast<uintptr_t>(abs_sums) & 7) return TAB_E_ALIGNMENT;
+        cudaError_t e = cudaMemsetAsync(abs_sums, 0, sizeof(double) * (size_t)N, s);
+        if (e != cudaSuccess) return record_cuda_error(e);
+    }
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
     if (!x || !ths || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
     const size_t need = tab_conv2d_workspace_bytes(type, N, H, W, C, KN, KH, KW);
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
         return TAB_E_WORKSPACE;
-    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3)) return TAB_E_ALIGNMENT;
+    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) ||
+        (reinterpret_cast<uintptr_t>(residual) & 3))
+        return TAB_E_ALIGNMENT;
     if ((long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
-    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (g_conv_path == TAB_PATH_AUTO) {
         if ((reinterpret_cast<uintptr_t>(qw) & 7) || (reinterpret_cast<uintptr_t>(y) & 3)) return TAB_E_ALIGNMENT;
-        rc = conv_imma_dispatch(x, qw, ths, y, workspace, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, s);
-        if (rc != TAB_E_TOO_LARGE) return rc;       // sizes beyond the tensor-core path: fall through
+        const bool r8 = residual && ((reinterpret_cast<uintptr_t>(residual) & 7) == 0) && ((reinterpret_cast<uintptr_t>(y) & 7) == 0);
+        if (!residual || r8) {
+            rc = conv_imma_dispatch(x, qw, ths, y, workspace, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, s, residual, abs_sums);
+            if (rc != TAB_E_TOO_LARGE) return rc;       // sizes beyond the tensor-core path: fall through
+        }
     }
     int64_t* qx = reinterpret_cast<int64_t*>(workspace);
     rc = quantize_dispatch(x, ths, qx, nullptr, act_bits(type), N, H, W, C, s);   // TAB_GEMM.cu:419-426
     if (rc != TAB_OK) return rc;
-    return tab_conv2d_packed_launch(qx, qw, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream);
+    rc = tab_conv2d_packed_launch(qx, qw, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream);
+    if (rc != TAB_OK || (!residual && !abs_sums)) return rc;
+    // the popcount kernel has no fused epilogue: one extra pass adds the residual and sums |y|
+    return residual_abs_sum_dispatch(y, residual, abs_sums, N, oh * ow * (long long)KN, s);
+}
+
+int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                      float* y, void* workspace, size_t workspace_bytes, int type,
+                      int p1, int p2, int s1, int s2,
+                      int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
+    return conv2d_impl(x, qw, ths, btn, y, workspace, workspace_bytes, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+                       nullptr, nullptr, stream);
+}
+
+int tab_conv2d_fused_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                            float* y, void* workspace, size_t workspace_bytes, int type,
+                            int p1, int p2, int s1, int s2,
+                            int N, int H, int W, int C, int KN, int KH, int KW,
+                            const float* residual, double* abs_sums, tab_stream_t stream) {
+    return conv2d_impl(x, qw, ths, btn, y, workspace, workspace_bytes, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+                       residual, abs_sums, stream);
 }
 
 int tab_quantize_int8_launch(const float* x, const float* ths, int8_t* qx8, int bitwidth,
@@ -163,7 +196,7 @@ int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int ty
     if ((reinterpret_cast<uintptr_t>(qx8) & 15) || (reinterpret_cast<uintptr_t>(w8) & 15) || (reinterpret_cast<uintptr_t>(y) & 3))
         return TAB_E_ALIGNMENT;
     return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
-                              reinterpret_cast<cudaStream_t>(stream));
+                              reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr);
 }
 
 /* Test/benchmark hook: 1 = carry-save popcount tree (default), 0 = one POPC per word. */

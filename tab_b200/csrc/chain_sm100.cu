@@ -48,7 +48,7 @@ residual_abs_sum_kernel(float* __restrict__ y, const float* __restrict__ r, doub
         double t = 0.0;
 #pragma unroll
         for (int i = 0; i < RTHREADS / 32; i++) t += wsum[i];
-        atomicAdd(sums + n, t);
+        if (sums) atomicAdd(sums + n, t);
     }
 }
 
@@ -60,7 +60,51 @@ __global__ void threshold_finalize_kernel(const double* __restrict__ sums, float
 
 }  // namespace tab
 
+namespace tab {
+
+// y += residual (optional), sums[n] += sum |y[n]| (sums may be null when only the addition is wanted).
+int residual_abs_sum_dispatch(float* y, const float* residual, double* sums, int N, long long per_image, cudaStream_t s) {
+    if (per_image <= 0 || N <= 0) return TAB_OK;
+    const bool vec = (per_image % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(residual) & 15) == 0);
+    const long long items = vec ? per_image / 4 : per_image;
+    long long per = (items + RTHREADS * 4 - 1) / (RTHREADS * 4);
+    const long long cap = (148LL * 8 * 2 + N - 1) / N;
+    if (per > cap) per = cap;
+    if (per < 1) per = 1;
+    for (int n0 = 0; n0 < N; n0 += 65535) {
+        const int nn = (N - n0 < 65535) ? N - n0 : 65535;
+        dim3 grid((unsigned)per, (unsigned)nn);
+        float* yy = y + (long long)n0 * per_image;
+        const float* rr = residual ? residual + (long long)n0 * per_image : nullptr;
+        double* ss = sums ? sums + n0 : nullptr;
+        if (vec) {
+            if (rr) residual_abs_sum_kernel<true, true><<<grid, RTHREADS, 0, s>>>(yy, rr, ss, per_image);
+            else residual_abs_sum_kernel<true, false><<<grid, RTHREADS, 0, s>>>(yy, rr, ss, per_image);
+        } else {
+            if (rr) residual_abs_sum_kernel<false, true><<<grid, RTHREADS, 0, s>>>(yy, rr, ss, per_image);
+            else residual_abs_sum_kernel<false, false><<<grid, RTHREADS, 0, s>>>(yy, rr, ss, per_image);
+        }
+        int rc = check_launch();
+        if (rc != TAB_OK) return rc;
+    }
+    return TAB_OK;
+}
+
+}  // namespace tab
+
 using namespace tab;
+
+extern "C" int tab_threshold_from_sums_launch(const double* sums, float* ths, float scale, int N, long long per_image,
+                                              tab_stream_t stream) {
+    if (N < 0 || per_image < 0) return TAB_E_BAD_ARGUMENT;
+    if (N == 0) return TAB_OK;
+    if (!sums || !ths) return TAB_E_NULL_POINTER;
+    threshold_finalize_kernel<<<(N + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        sums, ths, scale, per_image > 0 ? (double)per_image : 1.0, N);
+    return check_launch();
+}
+
 
 extern "C" int tab_residual_threshold_launch(float* y, const float* residual, float* ths, double* sums,
                                              float scale, int N, long long per_image, tab_stream_t stream) {
@@ -73,31 +117,8 @@ extern "C" int tab_residual_threshold_launch(float* y, const float* residual, fl
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(double) * (size_t)N, s);
     if (e != cudaSuccess) return record_cuda_error(e);
-    if (per_image > 0) {
-        const bool vec = (per_image % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0) &&
-                         ((reinterpret_cast<uintptr_t>(residual) & 15) == 0);
-        const long long items = vec ? per_image / 4 : per_image;
-        long long per = (items + RTHREADS * 4 - 1) / (RTHREADS * 4);
-        const long long cap = (148LL * 8 * 2 + N - 1) / N;
-        if (per > cap) per = cap;
-        if (per < 1) per = 1;
-        for (int n0 = 0; n0 < N; n0 += 65535) {
-            const int nn = (N - n0 < 65535) ? N - n0 : 65535;
-            dim3 grid((unsigned)per, (unsigned)nn);
-            float* yy = y + (long long)n0 * per_image;
-            const float* rr = residual ? residual + (long long)n0 * per_image : nullptr;
-            double* ss = sums + n0;
-            if (vec) {
-                if (rr) residual_abs_sum_kernel<true, true><<<grid, RTHREADS, 0, s>>>(yy, rr, ss, per_image);
-                else residual_abs_sum_kernel<true, false><<<grid, RTHREADS, 0, s>>>(yy, rr, ss, per_image);
-            } else {
-                if (rr) residual_abs_sum_kernel<false, true><<<grid, RTHREADS, 0, s>>>(yy, rr, ss, per_image);
-                else residual_abs_sum_kernel<false, false><<<grid, RTHREADS, 0, s>>>(yy, rr, ss, per_image);
-            }
-            int rc = check_launch();
-            if (rc != TAB_OK) return rc;
-        }
-    }
+    int rc = residual_abs_sum_dispatch(y, residual, sums, N, per_image, s);
+    if (rc != TAB_OK) return rc;
     threshold_finalize_kernel<<<(N + 255) / 256, 256, 0, s>>>(sums, ths, scale, per_image > 0 ? (double)per_image : 1.0, N);
     return check_launch();
 }

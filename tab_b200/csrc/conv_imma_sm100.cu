@@ -124,6 +124,8 @@ struct ImmaParams {
     const int8_t* qx;        // [N][H][W][Cp]
     const int8_t* w8;        // [KN][Kw][64]
     float* y;                // [M][KN]
+    const float* residual;   // [M][KN] added to the result, or null
+    double* abs_sums;        // [N]: += sum |y| per image, or null
     int N, H, W, PC, KN, KH, KW, OH, OW, p1, p2, s1, s2;
     int M, Kw;
 };
@@ -155,7 +157,7 @@ __device__ __forceinline__ uint32_t swz(int r, int u) { return (uint32_t)(r * IR
 // fully used 64-byte segments per cp.async instruction.  Each thread owns one (word-in-chunk, 16-byte unit)
 // pair and walks the rows r = tid/8 + 16 e; the per-row geometry (first tap's input coordinates and the
 // image offset) sits in shared memory, written once per CTA.
-template <int WM, int WN, int ISTAGES, bool PADONE>
+template <int WM, int WN, int ISTAGES, bool PADONE, bool FUSED>
 __global__ void __launch_bounds__(ITHREADS, 2)
 conv_imma_kernel(const ImmaParams p) {
     constexpr int TMI = 64 * WM, TNI = 64 * WN;
@@ -294,39 +296,99 @@ conv_imma_kernel(const ImmaParams p) {
     asm volatile("cp.async.wait_group 0;");
 
     // ---- epilogue: int32 -> float32, [M][KN] ---------------------------------------------------------
+    // FUSED adds the residual and accumulates sum |y| per image: a warp's 64 rows touch at most three
+    // images when an image has >= 32 output pixels, so each lane keeps three partial sums, the warp
+    // reduces them with shuffles and lane 0 issues at most three double atomics; smaller images fall
+    // back to one atomic per row.
     const int g = lane >> 2, t4 = lane & 3;
     const bool pair_ok = (p.KN & 1) == 0;
+    const int ohw = p.OH * p.OW;
+    const int wrow0 = m0 + wm * 64;
+    const int wimg0 = FUSED ? wrow0 / ohw : 0;
+    const bool few = ohw >= 32;
+    const int wb1 = (wimg0 + 1) * ohw, wb2 = wb1 + ohw;          // first rows of the warp's 2nd and 3rd image
+    float part[3] = {0.f, 0.f, 0.f};                             // per lane: <= 8 rows x 16 values, exact in fp32 for integer data
 #pragma unroll
     for (int mi = 0; mi < 4; mi++) {
 #pragma unroll
         for (int hrow = 0; hrow < 2; hrow++) {
-            const int m = m0 + wm * 64 + mi * 16 + g + hrow * 8;
+            const int m = wrow0 + mi * 16 + g + hrow * 8;
             if (m >= p.M) continue;
-            float* yrow = p.y + (long long)m * p.KN;
+            float* __restrict__ yrow = p.y + (long long)m * p.KN;
+            const float* __restrict__ rrow = (FUSED && p.residual) ? p.residual + (long long)m * p.KN : nullptr;
+            // all residual loads of the row first (they must not wait behind the stores)
+            float2 res[8];
 #pragma unroll
             for (int ni = 0; ni < 8; ni++) {
                 const int n = n0 + wn * 64 + ni * 8 + 2 * t4;
-                const float v0 = (float)acc[mi][ni][2 * hrow], v1 = (float)acc[mi][ni][2 * hrow + 1];
+                res[ni] = make_float2(0.f, 0.f);
+                if (FUSED && rrow) {
+                    if (pair_ok && n + 1 < p.KN) res[ni] = __ldg(reinterpret_cast<const float2*>(rrow + n));
+                    else {
+                        if (n < p.KN) res[ni].x = __ldg(rrow + n);
+                        if (n + 1 < p.KN) res[ni].y = __ldg(rrow + n + 1);
+                    }
+                }
+            }
+            float rsum = 0.f;
+#pragma unroll
+            for (int ni = 0; ni < 8; ni++) {
+                const int n = n0 + wn * 64 + ni * 8 + 2 * t4;
+                const float v0 = (float)acc[mi][ni][2 * hrow] + res[ni].x, v1 = (float)acc[mi][ni][2 * hrow + 1] + res[ni].y;
                 if (pair_ok && n + 1 < p.KN) {
                     *reinterpret_cast<float2*>(yrow + n) = make_float2(v0, v1);
+                    if (FUSED) rsum += fabsf(v0) + fabsf(v1);
                 } else {
-                    if (n < p.KN) yrow[n] = v0;
-                    if (n + 1 < p.KN) yrow[n + 1] = v1;
+                    if (n < p.KN) { yrow[n] = v0; if (FUSED) rsum += fabsf(v0); }
+                    if (n + 1 < p.KN) { yrow[n + 1] = v1; if (FUSED) rsum += fabsf(v1); }
+                }
+            }
+            if (FUSED && p.abs_sums) {
+                if (few) {
+                    const int d = (m >= wb1) + (m >= wb2);
+                    part[0] += d == 0 ? rsum : 0.f;
+                    part[1] += d == 1 ? rsum : 0.f;
+                    part[2] += d == 2 ? rsum : 0.f;
+                } else {
+                    atomicAdd(p.abs_sums + m / ohw, (double)rsum);
                 }
             }
         }
     }
+    if (FUSED && p.abs_sums && few) {
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            double d = (double)part[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
+            if (lane == 0 && d != 0.0 && wimg0 + i < p.N) atomicAdd(p.abs_sums + wimg0 + i, d);
+        }
+    }
+}
+
+template <int WM, int WN, int ISTAGES, bool PADONE, bool FUSED>
+static int launch_imma_f(const ImmaParams& p, cudaStream_t stream) {
+    constexpr int TMI = 64 * WM, TNI = 64 * WN;
+    constexpr int smem_bytes = ISTAGES * (TMI + TNI) * IROW + TMI * 16;
+    // once per device and instantiation (kept out of the steady-state launch path, e.g. stream capture)
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        e = cudaFuncSetAttribute(conv_imma_kernel<WM, WN, ISTAGES, PADONE, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    dim3 grid((unsigned)((p.M + TMI - 1) / TMI), (unsigned)((p.KN + TNI - 1) / TNI));
+    conv_imma_kernel<WM, WN, ISTAGES, PADONE, FUSED><<<grid, ITHREADS, smem_bytes, stream>>>(p);
+    return check_launch();
 }
 
 template <int WM, int WN, int ISTAGES, bool PADONE>
 static int launch_imma(const ImmaParams& p, cudaStream_t stream) {
-    constexpr int TMI = 64 * WM, TNI = 64 * WN;
-    constexpr int smem_bytes = ISTAGES * (TMI + TNI) * IROW + TMI * 16;
-    cudaError_t e = cudaFuncSetAttribute(conv_imma_kernel<WM, WN, ISTAGES, PADONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) return record_cuda_error(e);
-    dim3 grid((unsigned)((p.M + TMI - 1) / TMI), (unsigned)((p.KN + TNI - 1) / TNI));
-    conv_imma_kernel<WM, WN, ISTAGES, PADONE><<<grid, ITHREADS, smem_bytes, stream>>>(p);
-    return check_launch();
+    return (p.residual || p.abs_sums) ? launch_imma_f<WM, WN, ISTAGES, PADONE, true>(p, stream)
+                                      : launch_imma_f<WM, WN, ISTAGES, PADONE, false>(p, stream);
 }
 
 size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW) {
@@ -382,14 +444,14 @@ int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, in
 // GEMM stage alone on byte operands.  binary_act: activations are {-1,+1} (out-of-image taps count as +1).
 int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary_act,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const float* residual, double* abs_sums) {
     const int PC = packed_channels(C);
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
     int rc = imma_limits(N, H, W, C, KN, KH, KW, oh, ow);
     if (rc != TAB_OK) return rc;
     ImmaParams p;
-    p.qx = qx8; p.w8 = w8; p.y = y;
+    p.qx = qx8; p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
     p.N = N; p.H = H; p.W = W; p.PC = PC; p.KN = KN; p.KH = KH; p.KW = KW;
     p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
     p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * PC;
@@ -403,7 +465,7 @@ int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary
 // x fp32 -> y, all four types, scratch in `workspace` (imma_workspace_bytes).
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const float* residual, double* abs_sums) {
     const int Cp = packed_channels(C) * 64;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
@@ -415,7 +477,7 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
     if (rc != TAB_OK) return rc;
     rc = expand_weights_dispatch(qw, w8, weight_bits(type), KN, KH, KW, C, stream);
     if (rc != TAB_OK) return rc;
-    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream);
+    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream, residual, abs_sums);
 }
 
 }  // namespace tab

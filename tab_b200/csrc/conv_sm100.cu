@@ -348,7 +348,7 @@ template <int TYPE, bool CSA>
 static int launch_conv(const ConvParams& p, cudaStream_t stream) {
     using P = Planes<TYPE>;
     const int smem_bytes = STAGES * P::STAGE_BYTES;
-    static thread_local bool configured[16] = {};
+    static bool configured[16] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return record_cuda_error(e);

@@ -81,7 +81,56 @@ torch::Tensor TAB_Conv2d(torch::Tensor X, torch::Tensor QW, torch::Tensor thresh
     return Y;
 }
 
+// Extension beyond the reference's surface: Conv2d with the residual addition and the statistics for the next
+// layer's thresholds fused into the convolution.  residual may be an undefined tensor (None); threshold_scale
+// <= 0 skips the thresholds.  Returns {Y, next_thresholds (empty when skipped)}.
+std::vector<torch::Tensor> TAB_Conv2dFused(torch::Tensor X, torch::Tensor QW, torch::Tensor thresholds, torch::Tensor btn, int type,
+                                           int padding1, int padding2, int stride1, int stride2,
+                                           int N, int H, int W, int C, int KN, int KH, int KW,
+                                           c10::optional<torch::Tensor> residual, double threshold_scale) {
+    CHECK_INPUT(X);
+    CHECK_INPUT(QW);
+    CHECK_INPUT(thresholds);
+    CHECK_INPUT(btn);
+    TORCH_CHECK(X.scalar_type() == torch::kFloat32 && thresholds.scalar_type() == torch::kFloat32, "X and thresholds must be float32");
+    TORCH_CHECK(QW.scalar_type() == torch::kInt64 && btn.scalar_type() == torch::kInt32, "QW must be int64 and btn int32");
+    TORCH_CHECK(type >= 0 && type <= 3, "type must be 0 (TNN), 1 (TBN), 2 (BTN) or 3 (BNN)");
+    TORCH_CHECK(N >= 0 && H >= 0 && W >= 0 && KN >= 0 && C >= 1 && KH >= 1 && KW >= 1 && padding1 >= 0 && padding2 >= 0 &&
+                stride1 >= 1 && stride2 >= 1, "Conv2d: invalid size, padding or stride");
+    const int PC = (C + 63) / 64;
+    const int wb = (type == 1 || type == 3) ? 1 : 2;
+    TORCH_CHECK(QW.numel() == (int64_t)KN * KH * KW * PC * wb, "QW does not match KN*KH*KW*ceil(C/64)*", wb);
+    TORCH_CHECK(X.numel() == (int64_t)N * H * W * C && thresholds.numel() == N, "X / thresholds do not match N*H*W*C / N");
+    const c10::cuda::CUDAGuard guard(X.device());
+    const int64_t OH = std::max<int64_t>(((int64_t)H + 2 * padding1 - KH + 1) / stride1, 0);
+    const int64_t OW = std::max<int64_t>(((int64_t)W + 2 * padding2 - KW + 1) / stride2, 0);
+    const float* rptr = nullptr;
+    if (residual.has_value() && residual->defined()) {
+        CHECK_INPUT((*residual));
+        TORCH_CHECK(residual->scalar_type() == torch::kFloat32 && residual->numel() == (int64_t)N * KN * OH * OW, "residual must be float32 with N*KN*OH*OW elements");
+        rptr = residual->data_ptr<float>();
+    }
+    auto Y = torch::empty({N, KN, OH, OW}, torch::device(X.device()).dtype(torch::kFloat32));
+    const size_t ws_bytes = tab_conv2d_workspace_bytes(type, N, H, W, C, KN, KH, KW);
+    auto ws = torch::empty({(int64_t)std::max<size_t>(ws_bytes, 256)}, torch::device(X.device()).dtype(torch::kUInt8));
+    torch::Tensor sums, next;
+    if (threshold_scale > 0) sums = torch::empty({std::max(N, 1)}, torch::device(X.device()).dtype(torch::kFloat64));
+    check_rc(tab_conv2d_fused_launch(X.data_ptr<float>(), QW.data_ptr<int64_t>(), thresholds.data_ptr<float>(), btn.data_ptr<int32_t>(),
+                                     Y.data_ptr<float>(), ws.data_ptr(), (size_t)ws.numel(), type, padding1, padding2, stride1, stride2,
+                                     N, H, W, C, KN, KH, KW, rptr, sums.defined() ? sums.data_ptr<double>() : nullptr, current_stream()),
+             "tab_conv2d_fused_launch");
+    if (sums.defined()) {
+        next = torch::empty({N}, torch::device(X.device()).dtype(torch::kFloat32));
+        check_rc(tab_threshold_from_sums_launch(sums.data_ptr<double>(), next.data_ptr<float>(), (float)threshold_scale, N,
+                                                (long long)KN * OH * OW, current_stream()), "tab_threshold_from_sums_launch");
+    } else {
+        next = torch::empty({0}, torch::device(X.device()).dtype(torch::kFloat32));
+    }
+    return {Y, next};
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("Conv2dFused", &TAB_Conv2dFused, "Conv2d + residual + next-layer thresholds (extension)");
     m.def("Quantize", &TAB_Quantize, "Ternarization or binarization of fp32 data in NHWC format");
     m.def("Conv2d", &TAB_Conv2d, "Conv2d of all TAB series CNNs (0 TNN, 1 TBN, 2 BTN, 3 BNN)");
     m.def("TAB_Quantize", &TAB_Quantize, "Alias of Quantize");

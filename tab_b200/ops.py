@@ -190,3 +190,42 @@ def conv2d_int8(QX8, W8, type, padding1, padding2, stride1, stride2, N, H, W, C,
                                                 int(stride1), int(stride2), N, H, W, C, KN, KH, KW, _stream_ptr(QX8.device))
     _cabi.check(rc, "tab_conv2d_int8_launch")
     return Y
+
+
+def Conv2dFused(X, QW, thresholds, btn, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW,
+                residual=None, threshold_scale=None):
+    """``Conv2d`` with the two chaining fusions of ``tab_conv2d_fused_launch``: ``Y = conv(X) + residual`` and,
+    when ``threshold_scale`` is given, the next layer's thresholds ``threshold_scale * mean|Y[n]|``.
+    Returns ``(Y, next_thresholds_or_None)``.  Not part of the reference's interface."""
+    _check_input(X, "X", torch.float32)
+    _check_input(QW, "QW", torch.int64)
+    _check_input(thresholds, "thresholds", torch.float32)
+    _check_input(btn, "btn", torch.int32)
+    conv_type = int(type)
+    p1, p2, s1, s2 = int(padding1), int(padding2), int(stride1), int(stride2)
+    N, H, W, C, KN, KH, KW = (int(v) for v in (N, H, W, C, KN, KH, KW))
+    _conv_checks(conv_type, QW, btn, N, H, W, C, KN, KH, KW, p1, p2, s1, s2)
+    if X.numel() != N * H * W * C or thresholds.numel() != N:
+        raise RuntimeError("X / thresholds do not match N*H*W*C / N")
+    OH, OW = conv_out_size(H, W, KH, KW, p1, p2, s1, s2)
+    if residual is not None:
+        _check_input(residual, "residual", torch.float32)
+        if residual.numel() != N * KN * OH * OW:
+            raise RuntimeError("residual has %d elements, expected %d" % (residual.numel(), N * KN * OH * OW))
+    l = _cabi.lib()
+    with torch.cuda.device(X.device):
+        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=X.device)
+        ws = torch.empty((max(l.tab_conv2d_workspace_bytes(conv_type, N, H, W, C, KN, KH, KW), 256),), dtype=torch.uint8, device=X.device)
+        sums = torch.empty((max(N, 1),), dtype=torch.float64, device=X.device) if threshold_scale is not None else None
+        st = _stream_ptr(X.device)
+        rc = l.tab_conv2d_fused_launch(X.data_ptr(), QW.data_ptr(), thresholds.data_ptr(), btn.data_ptr(), Y.data_ptr(),
+                                       ws.data_ptr(), ws.numel(), conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+                                       residual.data_ptr() if residual is not None else None,
+                                       sums.data_ptr() if sums is not None else None, st)
+        _cabi.check(rc, "tab_conv2d_fused_launch")
+        nxt = None
+        if sums is not None:
+            nxt = torch.empty((N,), dtype=torch.float32, device=X.device)
+            rc = l.tab_threshold_from_sums_launch(sums.data_ptr(), nxt.data_ptr(), float(threshold_scale), N, KN * OH * OW, st)
+            _cabi.check(rc, "tab_threshold_from_sums_launch")
+    return Y, nxt

@@ -28,6 +28,14 @@ def test_module_surface_and_results(cuda):
         assert y.dtype == torch.float32 and tuple(y.shape) == (N, KN, H, W) and y.is_cuda
         yo = c_oracle.conv2d(x, qo, ths, bo, t, 1, 1, 1, 1, N, H, W, C, KN, K, K)
         assert np.array_equal(y.cpu().numpy(), yo)
+    # extension: fused residual + thresholds
+    qw, btn = TAB.Quantize(torch.from_numpy(w).to(cuda), torch.from_numpy(wths).to(cuda), 2, KN, K, K, C)
+    r = torch.round(torch.randn(N, KN, H, W, device=cuda) * 9)
+    y, nxt = TAB.Conv2dFused(xd, qw, td, btn, 0, 1, 1, 1, 1, N, H, W, C, KN, K, K, r, 0.7)
+    y_ref = TAB.Conv2d(xd, qw, td, btn, 0, 1, 1, 1, 1, N, H, W, C, KN, K, K) + r
+    assert torch.equal(y, y_ref) and tuple(nxt.shape) == (N,)
+    exp = (np.float64(np.float32(0.7)) * (y_ref.abs().double().reshape(N, -1).sum(1).cpu().numpy() / (KN * H * W))).astype(np.float32)
+    assert np.array_equal(nxt.cpu().numpy(), exp)
     with pytest.raises(RuntimeError, match="X must be a CUDA tensor"):
         TAB.Quantize(torch.from_numpy(x), td, 2, N, H, W, C)
     with pytest.raises(RuntimeError, match="X must be contiguous"):

@@ -309,6 +309,30 @@ def test_residual_threshold(cuda):
         assert np.array_equal(yd.cpu().numpy(), yo) and np.array_equal(t1.cpu().numpy(), to)
 
 
+def test_fused_conv_matches_unfused(cuda):
+    """tab_conv2d_fused_launch: residual and per-image |y| statistics in the epilogue == separate passes."""
+    rng = np.random.default_rng(11)
+    for geom in ((1, 1, 1, 1, 5, 7, 7, 128, 130, 3, 3), (0, 0, 2, 2, 3, 14, 14, 64, 33, 1, 1), (1, 1, 1, 1, 2, 56, 56, 64, 64, 3, 3)):
+        p1, p2, s1, s2, N, H, W, C, KN, KH, KW = geom
+        x, ths = make_input(5, N, H, W, C)
+        w, wths = make_input(6, KN, KH, KW, C)
+        OH, OW = (H + 2 * p1 - KH + 1) // s1, (W + 2 * p2 - KW + 1) // s2
+        r = np.round(rng.standard_normal((N, KN, OH, OW)) * 20).astype(np.float32)
+        for t in range(4):
+            qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, KH, KW, C)
+            args = (dev_t(x, cuda), dev_t(qw, cuda), dev_t(ths, cuda), dev_t(btn, cuda), t, *geom)
+            yo = c_oracle.conv2d(x, qw, ths, btn, t, *geom)
+            y0, n0 = TAB.Conv2dFused(*args, None, None)
+            assert n0 is None and np.array_equal(y0.cpu().numpy(), yo)
+            y1, t1 = TAB.Conv2dFused(*args, None, 0.7)
+            assert np.array_equal(y1.cpu().numpy(), yo)
+            assert np.array_equal(t1.cpu().numpy(), OracleOps.residual_threshold(yo.copy(), None, 0.7))
+            y2, t2 = TAB.Conv2dFused(*args, dev_t(r, cuda), 0.7)
+            yr = yo.copy()
+            tr = OracleOps.residual_threshold(yr, r, 0.7)
+            assert np.array_equal(y2.cpu().numpy(), yr) and np.array_equal(t2.cpu().numpy(), tr)
+
+
 @pytest.mark.parametrize("t", [0, 3])
 def test_chain_matches_oracle(cuda, t):
     """The 19-convolution ResNet-18-shaped chain, N=3, integer-valued input so that every threshold is an
@@ -326,9 +350,15 @@ def test_chain_matches_oracle(cuda, t):
     xd = dev_t(x, cuda)
     thd = TAB.ops.residual_threshold(xd, None, chain.THRESHOLD_SCALE)
     assert np.array_equal(thd.cpu().numpy(), ths)
-    yd, oh2, ow2, kn2 = chain.forward(TAB.ops, xd, thd, qd, t, N)
+    yd, oh2, ow2, kn2 = chain.forward(TAB.ops, xd, thd, qd, t, N)        # fused epilogues
     assert (oh, ow, kn) == (oh2, ow2, kn2) == (7, 7, 512)
     assert np.array_equal(yd.cpu().numpy().reshape(-1), yo.reshape(-1))
+
+    class Unfused:
+        Conv2d = staticmethod(TAB.ops.Conv2d)
+        residual_threshold = staticmethod(TAB.ops.residual_threshold)
+    yu, _, _, _ = chain.forward(Unfused, xd, thd, qd, t, N)              # separate passes
+    assert np.array_equal(yu.cpu().numpy().reshape(-1), yo.reshape(-1))
 
 
 # ------------------------------------------------------------------------------------------ errors
