@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtab_b200.so")
-SOURCES = ["c_abi.cu", "quantize_sm100.cu", "conv_sm100.cu", "conv_imma_sm100.cu", "conv_static_sm100.cu", "chain_sm100.cu", "pipe_probe.cu"]
+SOURCES = ["c_abi.cu", "quantize_sm100.cu", "conv_sm100.cu", "conv_imma_sm100.cu", "conv_umma_sm100.cu", "conv_static_sm100.cu", "chain_sm100.cu", "pipe_probe.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
@@ -32,7 +32,8 @@ def _stale(target, deps):
 def build_library(force=False, verbose=False):
     """nvcc -> tab_b200/libtab_b200.so.  Returns the ptxas resource report."""
     srcs = [os.path.join(CSRC, s) for s in SOURCES]
-    deps = srcs + [os.path.join(CSRC, "tab_kernels.cuh"), os.path.join(ROOT, "include", "tab_b200.h"), __file__]
+    deps = srcs + [os.path.join(CSRC, "tab_kernels.cuh"), os.path.join(CSRC, "conv_int8.cuh"),
+                   os.path.join(ROOT, "include", "tab_b200.h"), __file__]
     log = os.path.join(HERE, "libtab_b200.ptxas.txt")
     if not force and not _stale(LIB, deps):
         return open(log).read() if os.path.exists(log) else ""

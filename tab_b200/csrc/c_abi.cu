@@ -12,6 +12,8 @@ int record_cuda_error(cudaError_t e) {
 }
 
 void conv_set_csa(bool on);
+void imma_set_variant(int v);
+int umma_status_read_and_clear();
 size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW);
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
@@ -198,6 +200,12 @@ int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int ty
     return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
                               reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr);
 }
+
+/* Test/benchmark hook: GEMM variant of the tensor-core path: 0 = default, 1 = mma.sync + im2col staging,
+   2 = mma.sync (patch or im2col staging), 3 = tcgen05. */
+void tab_debug_set_imma_variant(int v) { imma_set_variant(v); }
+/* Test hook: code of the last expired wait in the tcgen05 kernel on this device (0 = none); clears it. */
+int tab_debug_umma_status(void) { return umma_status_read_and_clear(); }
 
 /* Test/benchmark hook: 1 = carry-save popcount tree (default), 0 = one POPC per word. */
 void tab_debug_set_csa(int on) { conv_set_csa(on != 0); }

@@ -20,6 +20,7 @@
 //                             the loader does padding (zero fill for ternary activations, +1 fill for
 //                             binary activations: a zero word means +1 there) and im2col by address.
 #include "tab_kernels.cuh"
+#include "conv_int8.cuh"
 
 namespace tab {
 
@@ -117,26 +118,8 @@ __global__ void expand_weights_kernel(const uint64_t* __restrict__ qw, int8_t* _
 // 3. implicit-im2col s8 GEMM
 // ------------------------------------------------------------------------------------------------
 constexpr int ITHREADS = 128;                // 4 warps, each a 64 x 64 output tile
-constexpr int IKW = 2;                       // 64-channel words per K chunk (128 bytes per smem row)
-constexpr int IROW = IKW * 64;               // bytes per smem row
+constexpr int PATCH_SMEM_BUDGET = 110 * 1024; // dynamic shared memory of the patch variant: two CTAs per SM
 
-struct ImmaParams {
-    const int8_t* qx;        // [N][H][W][Cp]
-    const int8_t* w8;        // [KN][Kw][64]
-    float* y;                // [M][KN]
-    const float* residual;   // [M][KN] added to the result, or null
-    double* abs_sums;        // [N]: += sum |y| per image, or null
-    int N, H, W, PC, KN, KH, KW, OH, OW, p1, p2, s1, s2;
-    int M, Kw;
-};
-
-__device__ __forceinline__ void cp16(uint32_t dst, const void* src, bool valid) {
-    const int sz = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz));
-}
-__device__ __forceinline__ void sts16(uint32_t dst, uint32_t v) {
-    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(v));
-}
 __device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -147,8 +130,80 @@ __device__ __forceinline__ void imma(int (&c)[4], const uint32_t (&a)[4], uint32
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// smem byte offset of 16-byte unit `u` (0..7) of row `r`: XOR swizzle, conflict-free for 8 consecutive rows.
-__device__ __forceinline__ uint32_t swz(int r, int u) { return (uint32_t)(r * IROW + ((u ^ (r & 7)) << 4)); }
+
+// Epilogue shared by the GEMM kernels: int32 -> float32, [M][KN].
+// FUSED adds the residual and accumulates sum |y| per image: a warp's 64 rows touch at most three
+// images when an image has >= 32 output pixels, so each lane keeps three partial sums, the warp
+// reduces them with shuffles and lane 0 issues at most three double atomics; smaller images fall
+// back to one atomic per row.
+template <bool FUSED>
+__device__ __forceinline__ void imma_epilogue(const ImmaParams& p, const int (&acc)[4][8][4], int m0, int n0,
+                                              int wm, int wn, int lane) {
+    const int g = lane >> 2, t4 = lane & 3;
+    const bool pair_ok = (p.KN & 1) == 0;
+    const int ohw = p.OH * p.OW;
+    const int wrow0 = m0 + wm * 64;
+    const int wimg0 = FUSED ? wrow0 / ohw : 0;
+    const bool few = ohw >= 32;
+    const int wb1 = (wimg0 + 1) * ohw, wb2 = wb1 + ohw;          // first rows of the warp's 2nd and 3rd image
+    float part[3] = {0.f, 0.f, 0.f};                             // per lane: <= 8 rows x 16 values, exact in fp32 for integer data
+#pragma unroll
+    for (int mi = 0; mi < 4; mi++) {
+#pragma unroll
+        for (int hrow = 0; hrow < 2; hrow++) {
+            const int m = wrow0 + mi * 16 + g + hrow * 8;
+            if (m >= p.M) continue;
+            float* __restrict__ yrow = p.y + (long long)m * p.KN;
+            const float* __restrict__ rrow = (FUSED && p.residual) ? p.residual + (long long)m * p.KN : nullptr;
+            // all residual loads of the row first (they must not wait behind the stores)
+            float2 res[8];
+#pragma unroll
+            for (int ni = 0; ni < 8; ni++) {
+                const int n = n0 + wn * 64 + ni * 8 + 2 * t4;
+                res[ni] = make_float2(0.f, 0.f);
+                if (FUSED && rrow) {
+                    if (pair_ok && n + 1 < p.KN) res[ni] = __ldg(reinterpret_cast<const float2*>(rrow + n));
+                    else {
+                        if (n < p.KN) res[ni].x = __ldg(rrow + n);
+                        if (n + 1 < p.KN) res[ni].y = __ldg(rrow + n + 1);
+                    }
+                }
+            }
+            float rsum = 0.f;
+#pragma unroll
+            for (int ni = 0; ni < 8; ni++) {
+                const int n = n0 + wn * 64 + ni * 8 + 2 * t4;
+                const float v0 = (float)acc[mi][ni][2 * hrow] + res[ni].x, v1 = (float)acc[mi][ni][2 * hrow + 1] + res[ni].y;
+                if (pair_ok && n + 1 < p.KN) {
+                    *reinterpret_cast<float2*>(yrow + n) = make_float2(v0, v1);
+                    if (FUSED) rsum += fabsf(v0) + fabsf(v1);
+                } else {
+                    if (n < p.KN) { yrow[n] = v0; if (FUSED) rsum += fabsf(v0); }
+                    if (n + 1 < p.KN) { yrow[n + 1] = v1; if (FUSED) rsum += fabsf(v1); }
+                }
+            }
+            if (FUSED && p.abs_sums) {
+                if (few) {
+                    const int d = (m >= wb1) + (m >= wb2);
+                    part[0] += d == 0 ? rsum : 0.f;
+                    part[1] += d == 1 ? rsum : 0.f;
+                    part[2] += d == 2 ? rsum : 0.f;
+                } else {
+                    atomicAdd(p.abs_sums + m / ohw, (double)rsum);
+                }
+            }
+        }
+    }
+    if (FUSED && p.abs_sums && few) {
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            double d = (double)part[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
+            if (lane == 0 && d != 0.0 && wimg0 + i < p.N) atomicAdd(p.abs_sums + wimg0 + i, d);
+        }
+    }
+}
 
 // WM x WN warps (WM*WN == 4); CTA tile (64*WM) x (64*WN).  PADONE: out-of-image taps hold +1 (binary
 // activations) instead of 0.
@@ -295,75 +350,221 @@ conv_imma_kernel(const ImmaParams p) {
     }
     asm volatile("cp.async.wait_group 0;");
 
-    // ---- epilogue: int32 -> float32, [M][KN] ---------------------------------------------------------
-    // FUSED adds the residual and accumulates sum |y| per image: a warp's 64 rows touch at most three
-    // images when an image has >= 32 output pixels, so each lane keeps three partial sums, the warp
-    // reduces them with shuffles and lane 0 issues at most three double atomics; smaller images fall
-    // back to one atomic per row.
-    const int g = lane >> 2, t4 = lane & 3;
-    const bool pair_ok = (p.KN & 1) == 0;
+    imma_epilogue<FUSED>(p, acc, m0, n0, wm, wn, lane);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Patch variant: the A operand is not staged as an im2col tile (which copies every input pixel once
+// per tap) but as the patch of input pixels the CTA's output rows touch, one 64-byte row per pixel and
+// per 64-channel word; ldmatrix gathers the im2col rows from it by address.  For a 3x3 kernel this cuts
+// the activation copies (and the loader's instructions, which dominated the im2col variant) about 6x.
+//
+// Pixels are indexed on the zero-padded input grid, L = (n*PH + ph)*PW + pw.  Output row m with first tap
+// L0(m) = (n*PH + oh*s1)*PW + ow*s2 reads tap (kh,kw) at L0(m) + kh*PW + kw, so the patch of a tile is the
+// contiguous range [L0(first row), L0(last row) + (KH-1)*PW + KW-1]; padding pixels are filled with 0
+// (or +1 for binary activations).  K order: 64-channel word (outer), tap (inner); two taps per ring
+// stage of B.  pmax = largest patch over all tiles (computed on the host).
+template <int WM, int WN, bool PADONE, bool FUSED>
+__global__ void __launch_bounds__(ITHREADS, 2)
+conv_imma_patch_kernel(const ImmaParams p, const int pmax) {
+    constexpr int TMI = 64 * WM, TNI = 64 * WN, ISTAGES = 3;
+    constexpr int BSTAGE = TNI * IROW;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t sPatch = sbase + ISTAGES * BSTAGE;            // [2][pmax][64 B]
+    int* patch_src = reinterpret_cast<int*>(smem + ISTAGES * BSTAGE + 2 * pmax * 64);   // [pmax]
+
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.x * TMI;
+    const int n0 = blockIdx.y * TNI;
+    const int Cp = p.PC * 64;
+    const int PH = p.H + 2 * p.p1, PW = p.W + 2 * p.p2;
     const int ohw = p.OH * p.OW;
-    const int wrow0 = m0 + wm * 64;
-    const int wimg0 = FUSED ? wrow0 / ohw : 0;
-    const bool few = ohw >= 32;
-    const int wb1 = (wimg0 + 1) * ohw, wb2 = wb1 + ohw;          // first rows of the warp's 2nd and 3rd image
-    float part[3] = {0.f, 0.f, 0.f};                             // per lane: <= 8 rows x 16 values, exact in fp32 for integer data
+    const int T = p.KH * p.KW, CT = (T + 1) >> 1;                // taps, ring stages per channel word
+
+    auto first_tap = [&](int m) {
+        const int n = m / ohw;
+        const int r = m - n * ohw;
+        const int oh = r / p.OW;
+        const int ow = r - oh * p.OW;
+        return (n * PH + oh * p.s1) * PW + ow * p.s2;
+    };
+    const int m_last = min(m0 + TMI, p.M) - 1;
+    const int Lmin = first_tap(m0);
+    const int P = min(first_tap(m_last) + (p.KH - 1) * PW + p.KW - Lmin, pmax);
+
+    // source pixel (index into [N][H][W]) of every patch pixel, -1 for padding
+    for (int i = tid; i < P; i += ITHREADS) {
+        const int L = Lmin + i;
+        const int n = L / (PH * PW);
+        const int r = L - n * PH * PW;
+        const int ph = r / PW;
+        const int pw = r - ph * PW;
+        const int ih = ph - p.p1, iw = pw - p.p2;
+        const bool inside = ((unsigned)ih < (unsigned)p.H) && ((unsigned)iw < (unsigned)p.W) && n < p.N;
+        patch_src[i] = inside ? (n * p.H + ih) * p.W + iw : -1;
+    }
+    __syncthreads();
+
+    // ---- loaders ----------------------------------------------------------------------------------------
+    const int l_unit = tid & 7, l_wi = l_unit >> 2, l_q = l_unit & 3, l_row0 = tid >> 3;
+    auto load_b = [&](int c, int stage) {                        // ring stage: taps 2ct, 2ct+1 of word cc
+        const int cc = c / CT, ct = c - cc * CT;
+        const int tap = 2 * ct + l_wi;
+        const bool kvalid = tap < T;
+        const uint32_t sB = sbase + stage * BSTAGE;
+        const int8_t* bbase = p.w8 + ((long long)n0 * p.Kw + (long long)tap * p.PC + cc) * 64 + l_q * 16;
+#pragma unroll 4
+        for (int e = 0; e < TNI / 16; e++) {
+            const int row = l_row0 + 16 * e;
+            const bool v = kvalid && (n0 + row) < p.KN;
+            const int8_t* src = v ? bbase + (long long)row * p.Kw * 64 : p.w8;
+            cp16(sB + swz(row, l_unit), src, v);
+        }
+    };
+    auto load_patch = [&](int cc) {                              // all pixels of the patch, 64-channel word cc
+        const uint32_t buf = sPatch + (cc & 1) * pmax * 64;
+        const int8_t* abase = p.qx + (long long)cc * 64 + (tid & 3) * 16;
+        for (int i = tid; i < P * 4; i += ITHREADS) {
+            const int pix = i >> 2;
+            const int sp = patch_src[pix];
+            const uint32_t dst = buf + pix * 64 + ((((tid & 3) ^ (pix >> 1)) & 3) << 4);
+            if (PADONE && sp < 0) sts16(dst, 0x01010101u);
+            else cp16(dst, sp >= 0 ? abase + (long long)sp * Cp : p.qx, sp >= 0);
+        }
+    };
+
+    // ---- compute mapping ----------------------------------------------------------------------------------
+    const int warp = tid >> 5, lane = tid & 31;
+    const int wm = warp % WM, wn = warp / WM;
+    const int a_lrow = (lane & 7) + ((lane >> 3) & 1) * 8, a_lu = lane >> 4;
+    const int b_lrow = (lane & 7) + (lane >> 4) * 8, b_lu = (lane >> 3) & 1;
+    int a_rel[4];                                                // patch index of this lane's ldmatrix rows, tap (0,0)
+    uint32_t b_rowoff[4];
 #pragma unroll
-    for (int mi = 0; mi < 4; mi++) {
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + wm * 64 + i * 16 + a_lrow;
+        a_rel[i] = (m < p.M) ? first_tap(m) - Lmin : 0;
+        b_rowoff[i] = (uint32_t)((wn * 64 + i * 16 + b_lrow) * IROW);
+    }
+    const int b_x = b_lrow & 7;
+
+    int acc[4][8][4];
 #pragma unroll
-        for (int hrow = 0; hrow < 2; hrow++) {
-            const int m = wrow0 + mi * 16 + g + hrow * 8;
-            if (m >= p.M) continue;
-            float* __restrict__ yrow = p.y + (long long)m * p.KN;
-            const float* __restrict__ rrow = (FUSED && p.residual) ? p.residual + (long long)m * p.KN : nullptr;
-            // all residual loads of the row first (they must not wait behind the stores)
-            float2 res[8];
+    for (int i = 0; i < 4; i++)
 #pragma unroll
-            for (int ni = 0; ni < 8; ni++) {
-                const int n = n0 + wn * 64 + ni * 8 + 2 * t4;
-                res[ni] = make_float2(0.f, 0.f);
-                if (FUSED && rrow) {
-                    if (pair_ok && n + 1 < p.KN) res[ni] = __ldg(reinterpret_cast<const float2*>(rrow + n));
-                    else {
-                        if (n < p.KN) res[ni].x = __ldg(rrow + n);
-                        if (n + 1 < p.KN) res[ni].y = __ldg(rrow + n + 1);
-                    }
-                }
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[i][j][e] = 0;
+
+    uint32_t af[2][4][4], bf[2][8][2];
+    // fragments of k32 step j (0..3) of a stage: tap = first tap of the stage + j/2, half j%2 of the 64-byte word
+    auto load_frags = [&](uint32_t sB, uint32_t pbuf, int toff0, int toff1, int j, int buf) {
+        const int toff = (j >> 1) ? toff1 : toff0;
+#pragma unroll
+        for (int mi = 0; mi < 4; mi++) {
+            const int pix = a_rel[mi] + toff;
+            const uint32_t addr = pbuf + pix * 64 + ((((2 * (j & 1) + a_lu) ^ (pix >> 1)) & 3) << 4);
+            ldsm4(addr, af[buf][mi][0], af[buf][mi][1], af[buf][mi][2], af[buf][mi][3]);
+        }
+#pragma unroll
+        for (int nj = 0; nj < 4; nj++)
+            ldsm4(sB + b_rowoff[nj] + (((2 * j + b_lu) ^ b_x) << 4), bf[buf][2 * nj][0], bf[buf][2 * nj][1],
+                  bf[buf][2 * nj + 1][0], bf[buf][2 * nj + 1][1]);
+    };
+
+    const int nchunks = p.PC * CT;
+#pragma unroll
+    for (int s = 0; s < ISTAGES - 1; s++) {
+        if (s < nchunks) {
+            if (s % CT == 0) load_patch(s / CT);                 // CT >= 2: only s == 0 here
+            load_b(s, s);
+        }
+        asm volatile("cp.async.commit_group;");
+    }
+    for (int c = 0; c < nchunks; c++) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(ISTAGES - 2));
+        __syncthreads();
+        const int cc = c / CT, ct = c - cc * CT;
+        const uint32_t sB = sbase + (c % ISTAGES) * BSTAGE;
+        const uint32_t pbuf = sPatch + (cc & 1) * pmax * 64;
+        const int tap0 = 2 * ct, tap1 = min(2 * ct + 1, T - 1);
+        const int kh0 = tap0 / p.KW, kh1 = tap1 / p.KW;
+        const int toff0 = kh0 * PW + (tap0 - kh0 * p.KW), toff1 = kh1 * PW + (tap1 - kh1 * p.KW);
+        const int nsteps = (2 * ct + 1 < T) ? 4 : 2;              // an odd tap count leaves the last stage half empty
+        load_frags(sB, pbuf, toff0, toff1, 0, 0);
+        {
+            const int cn = c + ISTAGES - 1;
+            if (cn < nchunks) {
+                if (cn % CT == 0) load_patch(cn / CT);
+                load_b(cn, cn % ISTAGES);
             }
-            float rsum = 0.f;
+            asm volatile("cp.async.commit_group;");
+        }
 #pragma unroll
-            for (int ni = 0; ni < 8; ni++) {
-                const int n = n0 + wn * 64 + ni * 8 + 2 * t4;
-                const float v0 = (float)acc[mi][ni][2 * hrow] + res[ni].x, v1 = (float)acc[mi][ni][2 * hrow + 1] + res[ni].y;
-                if (pair_ok && n + 1 < p.KN) {
-                    *reinterpret_cast<float2*>(yrow + n) = make_float2(v0, v1);
-                    if (FUSED) rsum += fabsf(v0) + fabsf(v1);
-                } else {
-                    if (n < p.KN) { yrow[n] = v0; if (FUSED) rsum += fabsf(v0); }
-                    if (n + 1 < p.KN) { yrow[n + 1] = v1; if (FUSED) rsum += fabsf(v1); }
-                }
-            }
-            if (FUSED && p.abs_sums) {
-                if (few) {
-                    const int d = (m >= wb1) + (m >= wb2);
-                    part[0] += d == 0 ? rsum : 0.f;
-                    part[1] += d == 1 ? rsum : 0.f;
-                    part[2] += d == 2 ? rsum : 0.f;
-                } else {
-                    atomicAdd(p.abs_sums + m / ohw, (double)rsum);
-                }
+        for (int j = 0; j < 4; j++) {
+            if (j < nsteps) {
+                if (j + 1 < nsteps) load_frags(sB, pbuf, toff0, toff1, j + 1, (j + 1) & 1);
+#pragma unroll
+                for (int mi = 0; mi < 4; mi++)
+#pragma unroll
+                    for (int ni = 0; ni < 8; ni++) imma(acc[mi][ni], af[j & 1][mi], bf[j & 1][ni][0], bf[j & 1][ni][1]);
             }
         }
     }
-    if (FUSED && p.abs_sums && few) {
-#pragma unroll
-        for (int i = 0; i < 3; i++) {
-            double d = (double)part[i];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
-            if (lane == 0 && d != 0.0 && wimg0 + i < p.N) atomicAdd(p.abs_sums + wimg0 + i, d);
-        }
+    asm volatile("cp.async.wait_group 0;");
+    imma_epilogue<FUSED>(p, acc, m0, n0, wm, wn, lane);
+}
+
+// Largest patch (in pixels) over all tiles of TMI output rows; 0 when pixel indices would not fit an int.
+static int patch_pixels_max(int TMI, int N, int H, int W, int OH, int OW, int KH, int KW, int p1, int p2, int s1, int s2) {
+    const long long PH = H + 2LL * p1, PW = W + 2LL * p2;
+    if ((long long)N * PH * PW >= (1LL << 31)) return 0;
+    const long long M = (long long)N * OH * OW, ohw = (long long)OH * OW;
+    auto first_tap = [&](long long m) {
+        const long long n = m / ohw, r = m - n * ohw, oh = r / OW, ow = r - oh * OW;
+        return (n * PH + oh * s1) * PW + ow * s2;
+    };
+    // the pattern of tile starts repeats with period lcm(TMI, ohw) rows: scanning one period is exact
+    long long period = ohw;
+    {
+        long long a = TMI, b = ohw;
+        while (b) { const long long t = a % b; a = b; b = t; }
+        period = (long long)TMI / a * ohw;
     }
+    const long long scan = period < M ? period : M;
+    long long best = 0;
+    for (long long m0 = 0; m0 < scan; m0 += TMI) {
+        const long long ml = (m0 + TMI < M ? m0 + TMI : M) - 1;
+        const long long P = first_tap(ml) + (KH - 1) * PW + KW - first_tap(m0);
+        if (P > best) best = P;
+    }
+    // the last (partial) tile of the whole problem is never larger than a full one starting at the same row
+    return best < (1LL << 24) ? (int)best : 0;
+}
+
+template <int WM, int WN, bool PADONE, bool FUSED>
+static int launch_patch_f(const ImmaParams& p, int pmax, cudaStream_t stream) {
+    constexpr int TMI = 64 * WM, TNI = 64 * WN;
+    const int smem_bytes = 3 * TNI * IROW + 2 * pmax * 64 + pmax * 4;
+    static int configured[64] = {};                               // largest size configured so far, per device
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev < 0 || dev >= 64 || configured[dev] < smem_bytes) {
+        e = cudaFuncSetAttribute(conv_imma_patch_kernel<WM, WN, PADONE, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, PATCH_SMEM_BUDGET);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (dev >= 0 && dev < 64) configured[dev] = PATCH_SMEM_BUDGET;
+    }
+    dim3 grid((unsigned)((p.M + TMI - 1) / TMI), (unsigned)((p.KN + TNI - 1) / TNI));
+    conv_imma_patch_kernel<WM, WN, PADONE, FUSED><<<grid, ITHREADS, smem_bytes, stream>>>(p, pmax);
+    return check_launch();
+}
+
+template <int WM, int WN, bool PADONE>
+static int launch_patch(const ImmaParams& p, int pmax, cudaStream_t stream) {
+    return (p.residual || p.abs_sums) ? launch_patch_f<WM, WN, PADONE, true>(p, pmax, stream)
+                                      : launch_patch_f<WM, WN, PADONE, false>(p, pmax, stream);
 }
 
 template <int WM, int WN, int ISTAGES, bool PADONE, bool FUSED>
@@ -390,6 +591,11 @@ static int launch_imma(const ImmaParams& p, cudaStream_t stream) {
     return (p.residual || p.abs_sums) ? launch_imma_f<WM, WN, ISTAGES, PADONE, true>(p, stream)
                                       : launch_imma_f<WM, WN, ISTAGES, PADONE, false>(p, stream);
 }
+
+int conv_umma_dispatch(const ImmaParams& p, bool padone, int alt, cudaStream_t stream);
+
+// 0 = default choice, 1 = mma.sync with im2col staging, 2 = mma.sync (patch or im2col), 3 = tcgen05 (for A/B tests)
+static int g_imma_variant = 0;
 
 size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW) {
     const size_t Cp = (size_t)packed_channels(C) * 64;
@@ -456,11 +662,25 @@ int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary
     p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
     p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * PC;
     const bool padone = binary_act && (p1 > 0 || p2 > 0);
-    // 256 x 64 tiles (two ring stages, so that two CTAs fit an SM) when there are at most 64 filters,
-    // 128 x 128 tiles with three stages otherwise
-    if (KN <= 64) return padone ? launch_imma<4, 1, 2, true>(p, stream) : launch_imma<4, 1, 2, false>(p, stream);
+    // 256 x 64 tiles when there are at most 64 filters, 128 x 128 tiles otherwise.  The patch variant is used
+    // when the kernel has at least 3 taps, the largest patch fits the shared-memory budget and it copies at
+    // most half of what the im2col variant would; else the im2col variant (1x1 kernels, large strides).
+    if (g_imma_variant == 3 || g_imma_variant == 4) return conv_umma_dispatch(p, padone, g_imma_variant == 4, stream);
+    const bool narrow = KN <= 64;
+    const int TMI = narrow ? 256 : 128, TNI = narrow ? 64 : 128, T = KH * KW;
+    if (T >= 3 && g_imma_variant != 1) {
+        const int pmax = patch_pixels_max(TMI, N, H, W, (int)oh, (int)ow, KH, KW, p1, p2, s1, s2);
+        const long long need = 3LL * TNI * IROW + 2LL * pmax * 64 + 4LL * pmax;
+        if (pmax > 0 && need <= PATCH_SMEM_BUDGET && 2LL * pmax <= (long long)TMI * T) {
+            if (narrow) return padone ? launch_patch<4, 1, true>(p, pmax, stream) : launch_patch<4, 1, false>(p, pmax, stream);
+            return padone ? launch_patch<2, 2, true>(p, pmax, stream) : launch_patch<2, 2, false>(p, pmax, stream);
+        }
+    }
+    if (narrow) return padone ? launch_imma<4, 1, 2, true>(p, stream) : launch_imma<4, 1, 2, false>(p, stream);
     return padone ? launch_imma<2, 2, 3, true>(p, stream) : launch_imma<2, 2, 3, false>(p, stream);
 }
+
+void imma_set_variant(int v) { g_imma_variant = v; }
 
 // x fp32 -> y, all four types, scratch in `workspace` (imma_workspace_bytes).
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,

@@ -1,0 +1,346 @@
+// TAB convolution GEMM stage on the 5th-generation tensor cores: tcgen05.mma kind::i8 with the s32
+// accumulator in tensor memory (TMEM).  Same operands and the same results as conv_imma_sm100.cu (quantised
+// values {-1,0,+1} as int8, exact int32 accumulation); replaces ldmatrix + mma.sync, whose issue rate capped
+// that kernel at about half of the legacy instruction's own ceiling.
+//
+// One CTA = 256 threads = a 128 x TN output tile (TN = 64, 128 or 256 filters):
+//   * all eight warps are loaders: the implicit-im2col gather of the activation rows and the weight rows go
+//     to a ring of shared-memory stages with cp.async (16-byte units, zero fill / +1 fill for padding taps,
+//     exactly as in the mma.sync kernel).  A stage holds 128 bytes of K per row in the K-major, 128-byte
+//     swizzled layout the MMA's shared-memory descriptors expect: row r at r*128, 16-byte unit u at
+//     ((u ^ (r & 7)) << 4), stage base 1024-byte aligned.
+//   * once every thread's copies of a stage have landed (cp.async.wait_group, fence.proxy.async,
+//     __syncthreads) thread 0 issues four tcgen05.mma (K = 32 bytes each) for the stage and one
+//     tcgen05.commit that arrives on the stage's mbarrier when they have finished reading it;
+//     the loaders wait on that mbarrier before they overwrite the stage, two iterations later.
+//   * epilogue: tcgen05.ld brings the 128 x TN accumulator from TMEM to registers (warp w reads TMEM lanes
+//     32*(w%4).., columns (w/4)*TN/2..), converts to float, optionally adds the residual and accumulates
+//     per-image sums of |y|, and stores rows of [M][KN].
+// Every wait on an mbarrier is bounded: on expiry the kernel records a code in *status, stops waiting,
+// still frees its TMEM columns and returns.
+#include "tab_kernels.cuh"
+#include "conv_int8.cuh"
+
+namespace tab {
+
+constexpr int UTHREADS = 256;
+constexpr int UTM = 128;                     // rows (output pixels) per CTA = M of one MMA
+constexpr uint32_t UMMA_WAIT_LIMIT = 1u << 20;
+
+__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
+    for (uint32_t i = 0; i < UMMA_WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    const uint32_t lo = (smem_addr & 0x3FFFFu) >> 4;                       // start address, LBO unused (0)
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);            // SBO, descriptor version 1, SWIZZLE_128B
+    return ((uint64_t)hi << 32) | lo;
+}
+// Instruction descriptor: D s32, A/B signed 8-bit, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(UTM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// MT blocks of 128 rows per CTA (one accumulator of TNI TMEM columns each, all sharing the weight tile);
+// S ring stages; MMAs of a stage are issued D = S - 2 iterations after its copies were issued.
+template <int MT, int TNI, int S, bool PADONE, bool FUSED>
+__global__ void __launch_bounds__(UTHREADS, 1)
+conv_umma_kernel(const ImmaParams p, int* __restrict__ status) {
+    constexpr int TMI = UTM * MT;
+    constexpr int STAGE = (TMI + TNI) * IROW;
+    constexpr int D = (S >= 4) ? S - 2 : 1;
+    constexpr int TCOLS = MT * TNI;                              // TMEM columns (a power of two >= 32)
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sbase = (raw + 1023u) & ~1023u;                         // swizzle atoms need 1024-byte alignment
+    unsigned char* smem = smem_raw + (sbase - raw);
+    int4* rowinfo = reinterpret_cast<int4*>(smem + S * STAGE);             // {first-tap pixel, tap mask lo, hi, row valid}
+    const uint32_t mbar0 = sbase + S * STAGE + TMI * 16;                   // S stage barriers (8 bytes each)
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S * STAGE + TMI * 16 + S * 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * TMI;
+    const int n0 = blockIdx.y * TNI;
+    const int Cp = p.PC * 64;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) mbar_init(mbar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(sbase + S * STAGE + TMI * 16 + S * 8), "r"((uint32_t)TCOLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int r = tid; r < TMI; r += UTHREADS) {
+        const int m = m0 + r;
+        const bool ok = m < p.M;
+        const int mm = ok ? m : 0;
+        const int ohw = p.OH * p.OW;
+        const int n = mm / ohw;
+        const int rr = mm - n * ohw;
+        const int oh = rr / p.OW;
+        const int ow = rr - oh * p.OW;
+        const int ih0 = oh * p.s1 - p.p1, iw0 = ow * p.s2 - p.p2;
+        unsigned long long mask = 0;
+        if (ok) {
+            for (int kh = 0; kh < p.KH; kh++)
+                for (int kw = 0; kw < p.KW; kw++)
+                    if ((unsigned)(ih0 + kh) < (unsigned)p.H && (unsigned)(iw0 + kw) < (unsigned)p.W)
+                        mask |= 1ULL << (kh * p.KW + kw);
+        }
+        rowinfo[r] = make_int4(n * p.H * p.W + ih0 * p.W + iw0, (int)(unsigned)mask, (int)(unsigned)(mask >> 32), ok ? 1 : 0);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    // ---- loader: this thread copies unit l_q of word l_wi of every chunk, rows l_row0 + 32 e ---------------
+    const int l_unit = tid & 7, l_wi = l_unit >> 2, l_q = l_unit & 3, l_row0 = tid >> 3;
+    int l_k = l_wi, l_kh, l_kw, l_pc;
+    {
+        const int tap = l_k / p.PC;
+        l_pc = l_k - tap * p.PC;
+        l_kh = tap / p.KW;
+        l_kw = tap - l_kh * p.KW;
+    }
+    auto load_chunk = [&](int stage) {
+        const uint32_t sA = sbase + stage * STAGE;
+        const uint32_t sB = sA + TMI * IROW;
+        const bool kvalid = l_k < p.Kw;
+        const int tap = l_kh * p.KW + l_kw;
+        const int tap_pix = l_kh * p.W + l_kw;
+        const int8_t* abase = p.qx + (long long)l_pc * 64 + l_q * 16;
+#pragma unroll
+        for (int e = 0; e < TMI / 32; e++) {
+            const int row = l_row0 + 32 * e;
+            const int4 ri = rowinfo[row];
+            const unsigned mword = tap < 32 ? (unsigned)ri.y : (unsigned)ri.z;
+            const bool inside = (mword >> (tap & 31)) & 1u;
+            const bool v = kvalid && inside;
+            const int8_t* src = v ? abase + (long long)(ri.x + tap_pix) * Cp : p.qx;
+            const uint32_t dst = sA + swz(row, l_unit);
+            if (PADONE && kvalid && !inside && ri.w) sts16(dst, 0x01010101u);
+            else cp16(dst, src, v);
+        }
+        const int8_t* bbase = p.w8 + ((long long)n0 * p.Kw + l_k) * 64 + l_q * 16;
+#pragma unroll
+        for (int e = 0; e < TNI / 32; e++) {
+            const int row = l_row0 + 32 * e;
+            const bool v = kvalid && (n0 + row) < p.KN;
+            const int8_t* src = v ? bbase + (long long)row * p.Kw * 64 : p.w8;
+            cp16(sB + swz(row, l_unit), src, v);
+        }
+        l_k += IKW;
+        l_pc += IKW;
+        while (l_pc >= p.PC) { l_pc -= p.PC; if (++l_kw == p.KW) { l_kw = 0; ++l_kh; } }
+    };
+
+    constexpr uint32_t IDESC = umma_idesc(TNI);
+    const int nchunks = (p.Kw + IKW - 1) / IKW;
+    bool dead = false;                                          // a bounded wait expired: stop waiting, finish the protocol
+    for (int c = 0; c < nchunks + D; c++) {
+        if (c < nchunks) {
+            const int stage = c % S;
+            if (c >= S && !dead) {
+                // the MMAs that read this stage (chunk c - S) were committed two iterations ago
+                if (!mbar_wait(mbar0 + 8 * stage, (uint32_t)((c / S) - 1) & 1u)) { dead = true; if (status) atomicExch(status, 1); }
+            }
+            load_chunk(stage);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int r = c - D;
+        if (r >= 0) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(D) : "memory");     // chunk r's copies of this thread have landed
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // make them visible to the tensor core
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            if (tid == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sA = sbase + (r % S) * STAGE;
+                const uint64_t db = umma_desc(sA + TMI * IROW);
+#pragma unroll
+                for (int k = 0; k < IROW / 32; k++) {            // 32 bytes of K per MMA: advance the start address by 2 units
+#pragma unroll
+                    for (int mb = 0; mb < MT; mb++)
+                        umma_i8(tmem_base + mb * TNI, umma_desc(sA + mb * UTM * IROW) + 2 * k, db + 2 * k, IDESC,
+                                (r > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(mbar0 + 8 * (r % S));
+            }
+        }
+    }
+    // all MMAs are committed; the last commit covers every earlier one
+    {
+        const int last = nchunks - 1;
+        if (!dead && !mbar_wait(mbar0 + 8 * (last % S), (uint32_t)(last / S) & 1u)) { dead = true; if (status) atomicExch(status, 2); }
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // ---- epilogue: TMEM -> registers -> float [M][KN] --------------------------------------------------------
+    const int wq = warp & 3, wh = warp >> 2;                    // TMEM lane quarter, column half
+    const int ohw = p.OH * p.OW;
+    const bool few = ohw >= 16;                                 // 32 rows then touch at most three images
+    const bool vec4 = (p.KN & 3) == 0;
+#pragma unroll 1
+    for (int mb = 0; mb < MT; mb++) {
+        const int wrow0 = m0 + mb * UTM + wq * 32;
+        const int m = wrow0 + lane;
+        const bool row_ok = m < p.M;
+        const int wimg0 = FUSED ? wrow0 / ohw : 0;
+        const int wb1 = (wimg0 + 1) * ohw, wb2 = wb1 + ohw;
+        float rsum = 0.f;
+        float* __restrict__ yrow = p.y + (long long)(row_ok ? m : 0) * p.KN;
+        const float* __restrict__ rrow = (FUSED && p.residual) ? p.residual + (long long)(row_ok ? m : 0) * p.KN : nullptr;
+#pragma unroll 1
+        for (int cb = 0; cb < TNI / 2; cb += 32) {
+            const int col = wh * (TNI / 2) + cb;
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(mb * TNI + col), v);
+            if (!row_ok) continue;
+            const int nbase = n0 + col;
+            if (vec4 && nbase + 32 <= p.KN) {
+                float4 res[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    res[q] = (FUSED && rrow) ? __ldg(reinterpret_cast<const float4*>(rrow + nbase) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    float4 o;
+                    o.x = (float)(int)v[4 * q + 0] + res[q].x; o.y = (float)(int)v[4 * q + 1] + res[q].y;
+                    o.z = (float)(int)v[4 * q + 2] + res[q].z; o.w = (float)(int)v[4 * q + 3] + res[q].w;
+                    reinterpret_cast<float4*>(yrow + nbase)[q] = o;
+                    if (FUSED) rsum += (fabsf(o.x) + fabsf(o.y)) + (fabsf(o.z) + fabsf(o.w));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (nbase + i < p.KN) {
+                        float o = (float)(int)v[i];
+                        if (FUSED && rrow) o += __ldg(rrow + nbase + i);
+                        yrow[nbase + i] = o;
+                        if (FUSED) rsum += fabsf(o);
+                    }
+                }
+            }
+        }
+        if (FUSED && p.abs_sums) {
+            if (few) {
+                const int d = (m >= wb1) + (m >= wb2);
+#pragma unroll
+                for (int i = 0; i < 3; i++) {
+                    double t = (row_ok && d == i) ? (double)rsum : 0.0;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+                    if (lane == 0 && t != 0.0 && wimg0 + i < p.N) atomicAdd(p.abs_sums + wimg0 + i, t);
+                }
+            } else if (row_ok) {
+                atomicAdd(p.abs_sums + m / ohw, (double)rsum);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TCOLS) : "memory");
+    }
+}
+
+template <int MT, int TNI, int S, bool PADONE, bool FUSED>
+static int launch_umma_f(const ImmaParams& p, int* status, cudaStream_t stream) {
+    constexpr int TMI = UTM * MT;
+    constexpr int smem_bytes = S * (TMI + TNI) * IROW + TMI * 16 + S * 8 + 16 + 1024;
+    static_assert(smem_bytes <= 227 * 1024, "ring does not fit shared memory");
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        e = cudaFuncSetAttribute(conv_umma_kernel<MT, TNI, S, PADONE, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    dim3 grid((unsigned)((p.M + TMI - 1) / TMI), (unsigned)((p.KN + TNI - 1) / TNI));
+    conv_umma_kernel<MT, TNI, S, PADONE, FUSED><<<grid, UTHREADS, smem_bytes, stream>>>(p, status);
+    return check_launch();
+}
+
+template <int MT, int TNI, int S>
+static int launch_umma(const ImmaParams& p, bool padone, int* status, cudaStream_t stream) {
+    const bool fused = p.residual || p.abs_sums;
+    if (padone) return fused ? launch_umma_f<MT, TNI, S, true, true>(p, status, stream) : launch_umma_f<MT, TNI, S, true, false>(p, status, stream);
+    return fused ? launch_umma_f<MT, TNI, S, false, true>(p, status, stream) : launch_umma_f<MT, TNI, S, false, false>(p, status, stream);
+}
+
+// Where an expired wait is recorded (0 = never).  In host code the name is only a symbol handle; the device
+// address is looked up once per device.
+static __device__ int g_umma_status;
+static int* g_umma_status_addr[64] = {};
+
+static int* umma_status_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!g_umma_status_addr[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_umma_status) != cudaSuccess) return nullptr;
+        g_umma_status_addr[dev] = static_cast<int*>(ptr);
+    }
+    return g_umma_status_addr[dev];
+}
+
+// Reads (and clears) the record of expired waits on the current device; synchronises the device.
+int umma_status_read_and_clear() {
+    int v = -1, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_umma_status, sizeof(int)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(g_umma_status, &zero, sizeof(int));
+    return v;
+}
+
+// GEMM stage on the tcgen05 tensor cores; same contract as the mma.sync dispatch.
+int conv_umma_dispatch(const ImmaParams& p, bool padone, int alt, cudaStream_t stream) {
+    int* status = umma_status_ptr();
+    if (alt) {
+        if (p.KN <= 64) return launch_umma<4, 64, 3>(p, padone, status, stream);    // 512 x 64,  3 x 72 KB
+        if (p.KN <= 128) return launch_umma<2, 128, 4>(p, padone, status, stream);  // 256 x 128, 4 x 48 KB
+        return launch_umma<2, 256, 3>(p, padone, status, stream);                   // 256 x 256, 3 x 64 KB
+    }
+    if (p.KN <= 64) return launch_umma<2, 64, 5>(p, padone, status, stream);        // 256 x 64,  5 x 40 KB
+    if (p.KN <= 128) return launch_umma<1, 128, 6>(p, padone, status, stream);      // 128 x 128, 6 x 32 KB
+    return launch_umma<1, 256, 4>(p, padone, status, stream);                       // 128 x 256, 4 x 48 KB
+}
+
+}  // namespace tab

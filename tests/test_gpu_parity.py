@@ -18,12 +18,16 @@ GOLD = os.path.join(os.path.dirname(__file__), "golden")
 NAMES = ["tnn", "tbn", "btn", "bnn"]
 
 
-@pytest.fixture(autouse=True, params=["tensor", "popcount"])
+@pytest.fixture(autouse=True, params=["tensor", "tensor-im2col", "popcount"])
 def conv_path(request):
-    """Every test of this module runs once per compute path of tab_conv2d_launch."""
+    """Every test of this module runs once per compute path of tab_conv2d_launch: the tensor-core GEMM with
+    its own choice of operand staging (patch or im2col), the same forced to im2col staging, and the popcount
+    kernel."""
     l = _cabi.lib()
     prev = l.tab_conv2d_set_path(1 if request.param == "popcount" else 0)
+    l.tab_debug_set_imma_variant(1 if request.param == "tensor-im2col" else 0)
     yield request.param
+    l.tab_debug_set_imma_variant(0)
     l.tab_conv2d_set_path(prev)
 
 
