@@ -333,14 +333,17 @@ int umma_status_read_and_clear() {
 // GEMM stage on the tcgen05 tensor cores; same contract as the mma.sync dispatch.
 int conv_umma_dispatch(const ImmaParams& p, bool padone, int alt, cudaStream_t stream) {
     int* status = umma_status_ptr();
-    if (alt) {
-        if (p.KN <= 64) return launch_umma<4, 64, 3>(p, padone, status, stream);    // 512 x 64,  3 x 72 KB
-        if (p.KN <= 128) return launch_umma<2, 128, 4>(p, padone, status, stream);  // 256 x 128, 4 x 48 KB
-        return launch_umma<2, 256, 3>(p, padone, status, stream);                   // 256 x 256, 3 x 64 KB
+    // Tile shapes by filter count (measured on B200, 3x3 ResNet-18-shaped layers, batch 256): the loader is the
+    // limit, so the shape with the fewest copied bytes per multiply-add that still keeps >= 3 ring stages wins.
+    if (alt) {                                                                      // A/B alternative shapes
+        if (p.KN <= 64) return launch_umma<1, 64, 8>(p, padone, status, stream);    // 128 x 64,  8 x 25 KB
+        if (p.KN <= 128) return launch_umma<1, 128, 6>(p, padone, status, stream);  // 128 x 128, 6 x 33 KB
+        return launch_umma<2, 256, 3>(p, padone, status, stream);                   // 256 x 256, 3 x 65 KB
     }
-    if (p.KN <= 64) return launch_umma<2, 64, 5>(p, padone, status, stream);        // 256 x 64,  5 x 40 KB
-    if (p.KN <= 128) return launch_umma<1, 128, 6>(p, padone, status, stream);      // 128 x 128, 6 x 32 KB
-    return launch_umma<1, 256, 4>(p, padone, status, stream);                       // 128 x 256, 4 x 48 KB
+    if (p.KN <= 64) return launch_umma<2, 64, 5>(p, padone, status, stream);        // 256 x 64,  5 x 41 KB
+    if (p.KN <= 128) return launch_umma<2, 128, 4>(p, padone, status, stream);      // 256 x 128, 4 x 49 KB
+    if (p.KN <= 256) return launch_umma<1, 256, 4>(p, padone, status, stream);      // 128 x 256, 4 x 49 KB
+    return launch_umma<2, 256, 3>(p, padone, status, stream);                       // 256 x 256, 3 x 65 KB
 }
 
 }  // namespace tab
