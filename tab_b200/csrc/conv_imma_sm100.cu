@@ -667,8 +667,8 @@ int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary
     // most half of what the im2col variant would; else the im2col variant (1x1 kernels, large strides).
     // more than 64 filters: tcgen05 kernel; up to 64 filters the mma.sync kernel with patch staging is still ahead
     // (very short K - fewer than four ring stages - does not amortise the tcgen05 kernel's set-up)
-    if (g_imma_variant == 3 || g_imma_variant == 4 || (g_imma_variant == 0 && KN > 64 && p.Kw >= 8))
-        return conv_umma_dispatch(p, padone, g_imma_variant == 4, stream);
+    if (g_imma_variant == 3 || g_imma_variant == 4 || g_imma_variant == 5 || (g_imma_variant == 0 && KN > 64 && p.Kw >= 8))
+        return conv_umma_dispatch(p, padone, g_imma_variant == 4 ? 1 : (g_imma_variant == 5 ? 2 : 0), stream);
     const bool narrow = KN <= 64;
     const int TMI = narrow ? 256 : 128, TNI = narrow ? 64 : 128, T = KH * KW;
     if (T >= 3 && g_imma_variant != 1) {

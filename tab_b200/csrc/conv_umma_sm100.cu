@@ -26,6 +26,7 @@ namespace tab {
 constexpr int UTHREADS = 256;
 constexpr int UTM = 128;                     // rows (output pixels) per CTA = M of one MMA
 constexpr uint32_t UMMA_WAIT_LIMIT = 1u << 20;
+constexpr int UMMA_SMEM_MAX = 227 * 1024;    // dynamic shared memory the tcgen05 kernels may ask for (one CTA per SM)
 
 __device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count) : "memory");
@@ -306,6 +307,254 @@ static int launch_umma(const ImmaParams& p, bool padone, int* status, cudaStream
     return fused ? launch_umma_f<MT, TNI, S, false, true>(p, status, stream) : launch_umma_f<MT, TNI, S, false, false>(p, status, stream);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Patch variant (stride 1): instead of an im2col tile per tap, the CTA stages the patch of input pixels
+// once per pair of 64-channel words and points the MMA's A descriptor into it.
+//
+// Output positions are enumerated on the zero-padded input grid: virtual row R = (n*PH + oh)*PW + ow' with
+// ow' in [0, PW).  For stride 1 the first tap of R is input pixel R itself and tap (kh, kw) is pixel
+// R + kh*PW + kw, so the 128 rows of an MMA for any tap are 128 consecutive patch pixels: a K-major,
+// 128-byte-swizzled operand that starts (kh*PW + kw) rows further into the same shared-memory patch.
+// (The hardware applies the 128-byte swizzle to absolute shared-memory address bits, so a descriptor may
+// start at any 128-byte row of a 1024-byte aligned buffer; measured: results stay exact with the
+// descriptor's base-offset field left 0.)  Rows with ow' >= OW or oh >= OH are computed and dropped
+// (7 % of the rows at 56x56, 13 % at 28x28).  A 3x3 layer copies each activation byte about 1.2 times
+// instead of 9, which is what the copy-bound im2col kernel needed.
+//
+// Ring: one stage = the weights of one tap for the current word pair, [TN][128 B].  The patch of the next
+// word pair goes into the second patch buffer while the current one is multiplied.
+template <int MT, int TNI, int SB, bool PADONE, bool FUSED>
+__global__ void __launch_bounds__(UTHREADS, (MT * TNI <= 256) ? 2 : 1)
+conv_umma_patch_kernel(const ImmaParams p, int* __restrict__ status, const int prow, const int npb) {
+    constexpr int TMI = UTM * MT;
+    constexpr int BSTAGE = TNI * IROW;
+    constexpr int DB = SB - 2;
+    constexpr int TCOLS = MT * TNI;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sbase = (raw + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (sbase - raw);
+    const uint32_t sPatch = sbase;                                         // [npb][prow][128 B], prow % 8 == 0
+    const uint32_t sRing = sbase + npb * prow * IROW;                      // [SB][TNI][128 B]
+    const int tail = npb * prow * IROW + SB * BSTAGE;
+    int* patch_src = reinterpret_cast<int*>(smem + tail);                  // [prow]
+    const uint32_t mbar0 = sbase + tail + prow * 4;                        // SB stage barriers, then 2 patch barriers
+    const uint32_t mbarP = mbar0 + 8 * SB;
+    const uint32_t tslot = mbarP + 16;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + tail + prow * 4 + 8 * SB + 16);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.y * TNI;
+    const int Cp = p.PC * 64;
+    const int PH = p.H + 2 * p.p1, PW = p.W + 2 * p.p2, PHW = PH * PW;
+    const int T = p.KH * p.KW, ncp = (p.PC + 1) >> 1;
+    const int R0 = blockIdx.x * TMI;                                       // first virtual row = first patch pixel
+    const int P = TMI + (p.KH - 1) * PW + p.KW - 1;                        // patch pixels in use (<= prow)
+
+    if (tid == 0) {
+        for (int s = 0; s < SB + 2; s++) mbar_init(mbar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(tslot), "r"((uint32_t)TCOLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int i = tid; i < P; i += UTHREADS) {                              // source pixel of every patch pixel, -1 = padding
+        const int L = R0 + i;
+        const int n = L / PHW;
+        const int r = L - n * PHW;
+        const int ph = r / PW;
+        const int pw = r - ph * PW;
+        const int ih = ph - p.p1, iw = pw - p.p2;
+        const bool inside = n < p.N && ((unsigned)ih < (unsigned)p.H) && ((unsigned)iw < (unsigned)p.W);
+        patch_src[i] = inside ? (n * p.H + ih) * p.W + iw : -1;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    // ---- loaders ------------------------------------------------------------------------------------------
+    const int l_unit = tid & 7, l_word = l_unit >> 2, l_q = l_unit & 3, l_row0 = tid >> 3;
+    auto load_patch = [&](int cp) {
+        const int word = 2 * cp + l_word;
+        if (word >= p.PC) return;                                          // odd word count: the upper half of the rows is never read
+        const uint32_t buf = sPatch + (cp & (npb - 1)) * prow * IROW;
+        const int8_t* abase = p.qx + (long long)word * 64 + l_q * 16;
+        for (int pix = l_row0; pix < P; pix += UTHREADS / 8) {
+            const int sp = patch_src[pix];
+            const uint32_t dst = buf + swz(pix, l_unit);
+            if (PADONE && sp < 0) sts16(dst, 0x01010101u);
+            else cp16(dst, sp >= 0 ? abase + (long long)sp * Cp : p.qx, sp >= 0);
+        }
+    };
+    auto load_b = [&](int c, int slot) {                                   // weights of tap (c % T), word pair (c / T)
+        const int cp = c / T, tap = c - cp * T;
+        const int word = 2 * cp + l_word;
+        if (word >= p.PC) return;
+        const uint32_t sB = sRing + slot * BSTAGE;
+        const int8_t* bbase = p.w8 + ((long long)n0 * p.Kw + (long long)tap * p.PC + word) * 64 + l_q * 16;
+#pragma unroll
+        for (int e = 0; e < TNI / 32; e++) {
+            const int row = l_row0 + 32 * e;
+            const bool v = (n0 + row) < p.KN;
+            cp16(sB + swz(row, l_unit), v ? bbase + (long long)row * p.Kw * 64 : p.w8, v);
+        }
+    };
+
+    constexpr uint32_t IDESC = umma_idesc(TNI);
+    const int nst = ncp * T;
+    bool dead = false;
+    for (int it = 0; it < nst + DB; it++) {
+        if (it < nst) {
+            const int slot = it % SB;
+            const int cp = it / T, tap = it - cp * T;
+            if (it >= SB && !dead) {
+                if (!mbar_wait(mbar0 + 8 * slot, (uint32_t)((it / SB) - 1) & 1u)) { dead = true; if (status) atomicExch(status, 3); }
+            }
+            if (tap == 0) {
+                if (cp >= npb && !dead) {                                  // the buffer's previous word pair must be fully multiplied
+                    if (!mbar_wait(mbarP + 8 * (cp & 1), (uint32_t)((cp / 2) - 1) & 1u)) { dead = true; if (status) atomicExch(status, 4); }
+                }
+                load_patch(cp);
+            }
+            load_b(it, slot);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int r = it - DB;
+        if (r >= 0) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(DB) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            if (tid == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int cp = r / T, tap = r - cp * T;
+                const int kh = tap / p.KW, kw = tap - kh * p.KW;
+                const uint32_t abuf = sPatch + (cp & (npb - 1)) * prow * IROW + (uint32_t)(kh * PW + kw) * IROW;
+                const uint64_t db = umma_desc(sRing + (r % SB) * BSTAGE);
+                const int ksteps = (2 * cp + 1 < p.PC) ? 4 : 2;            // one or two 64-channel words in this pair
+                for (int k = 0; k < ksteps; k++) {
+#pragma unroll
+                    for (int mb = 0; mb < MT; mb++)
+                        umma_i8(tmem_base + mb * TNI, umma_desc(abuf + mb * UTM * IROW) + 2 * k, db + 2 * k, IDESC,
+                                (r > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(mbar0 + 8 * (r % SB));
+                if (tap == T - 1) umma_commit(mbarP + 8 * (cp & 1));
+            }
+        }
+    }
+    {
+        const int last = nst - 1;
+        if (!dead && !mbar_wait(mbar0 + 8 * (last % SB), (uint32_t)(last / SB) & 1u)) { dead = true; if (status) atomicExch(status, 5); }
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // ---- epilogue: virtual row -> output pixel, TMEM -> float [M][KN] ------------------------------------------
+    const int wq = warp & 3, wh = warp >> 2;
+    const bool vec4 = (p.KN & 3) == 0;
+#pragma unroll 1
+    for (int mb = 0; mb < MT; mb++) {
+        const int R = R0 + mb * UTM + wq * 32 + lane;
+        const int n = R / PHW;
+        const int rr = R - n * PHW;
+        const int oh = rr / PW;
+        const int ow = rr - oh * PW;
+        const bool row_ok = n < p.N && oh < p.OH && ow < p.OW;
+        const long long m = ((long long)n * p.OH + oh) * p.OW + ow;
+        const int wimg0 = (R0 + mb * UTM + wq * 32) / PHW;                 // image of the warp's first row
+        float rsum = 0.f;
+        float* __restrict__ yrow = p.y + (row_ok ? m : 0) * p.KN;
+        const float* __restrict__ rrow = (FUSED && p.residual) ? p.residual + (row_ok ? m : 0) * p.KN : nullptr;
+#pragma unroll 1
+        for (int cb = 0; cb < TNI / 2; cb += 32) {
+            const int col = wh * (TNI / 2) + cb;
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(mb * TNI + col), v);
+            if (!row_ok) continue;
+            const int nbase = n0 + col;
+            if (vec4 && nbase + 32 <= p.KN) {
+                float4 res[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    res[q] = (FUSED && rrow) ? __ldg(reinterpret_cast<const float4*>(rrow + nbase) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    float4 o;
+                    o.x = (float)(int)v[4 * q + 0] + res[q].x; o.y = (float)(int)v[4 * q + 1] + res[q].y;
+                    o.z = (float)(int)v[4 * q + 2] + res[q].z; o.w = (float)(int)v[4 * q + 3] + res[q].w;
+                    reinterpret_cast<float4*>(yrow + nbase)[q] = o;
+                    if (FUSED) rsum += (fabsf(o.x) + fabsf(o.y)) + (fabsf(o.z) + fabsf(o.w));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (nbase + i < p.KN) {
+                        float o = (float)(int)v[i];
+                        if (FUSED && rrow) o += __ldg(rrow + nbase + i);
+                        yrow[nbase + i] = o;
+                        if (FUSED) rsum += fabsf(o);
+                    }
+                }
+            }
+        }
+        if (FUSED && p.abs_sums) {
+            const int d = n - wimg0;                                       // 32 consecutive grid positions: usually one image, rarely more
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                double t = (row_ok && d == i) ? (double)rsum : 0.0;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+                if (lane == 0 && t != 0.0 && wimg0 + i < p.N) atomicAdd(p.abs_sums + wimg0 + i, t);
+            }
+            if (row_ok && d > 2) atomicAdd(p.abs_sums + n, (double)rsum);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TCOLS) : "memory");
+    }
+}
+
+template <int MT, int TNI, int SB, bool PADONE, bool FUSED>
+static int launch_umma_patch_f(const ImmaParams& p, int* status, int prow, int npb, cudaStream_t stream) {
+    constexpr int TMI = UTM * MT;
+    const int smem_bytes = npb * prow * IROW + SB * TNI * IROW + prow * 4 + 8 * (SB + 2) + 16 + 1024;
+    static int configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev < 0 || dev >= 64 || configured[dev] < smem_bytes) {
+        e = cudaFuncSetAttribute(conv_umma_patch_kernel<MT, TNI, SB, PADONE, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (dev >= 0 && dev < 64) configured[dev] = UMMA_SMEM_MAX;
+    }
+    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2;
+    const long long Mv = (long long)(p.N - 1) * PH * PW + (long long)(p.OH - 1) * PW + p.OW;   // last useful virtual row + 1
+    dim3 grid((unsigned)((Mv + TMI - 1) / TMI), (unsigned)((p.KN + TNI - 1) / TNI));
+    conv_umma_patch_kernel<MT, TNI, SB, PADONE, FUSED><<<grid, UTHREADS, smem_bytes, stream>>>(p, status, prow, npb);
+    return check_launch();
+}
+
+// Returns TAB_E_TOO_LARGE when this shape does not fit the patch variant (the caller then uses another kernel).
+template <int MT, int TNI, int SB>
+static int launch_umma_patch(const ImmaParams& p, bool padone, int* status, cudaStream_t stream) {
+    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2;
+    // at least SB taps: a patch buffer is only reused after commits that are issued SB - 2 iterations later
+    if (p.s1 != 1 || p.s2 != 1 || p.KH * p.KW < SB || (long long)p.N * PH * PW >= (1LL << 31) - 4096) return TAB_E_TOO_LARGE;
+    const int prow = (int)((UTM * MT + (p.KH - 1) * PW + p.KW - 1 + 7) / 8 * 8);
+    const int npb = p.PC > 2 ? 2 : 1;
+    const long long smem_bytes = (long long)npb * prow * IROW + (long long)SB * TNI * IROW + prow * 4LL + 8 * (SB + 2) + 16 + 1024;
+    if (smem_bytes > UMMA_SMEM_MAX) return TAB_E_TOO_LARGE;
+    const bool fused = p.residual || p.abs_sums;
+    if (padone) return fused ? launch_umma_patch_f<MT, TNI, SB, true, true>(p, status, prow, npb, stream)
+                             : launch_umma_patch_f<MT, TNI, SB, true, false>(p, status, prow, npb, stream);
+    return fused ? launch_umma_patch_f<MT, TNI, SB, false, true>(p, status, prow, npb, stream)
+                 : launch_umma_patch_f<MT, TNI, SB, false, false>(p, status, prow, npb, stream);
+}
+
 // Where an expired wait is recorded (0 = never).  In host code the name is only a symbol handle; the device
 // address is looked up once per device.
 static __device__ int g_umma_status;
@@ -333,6 +582,19 @@ int umma_status_read_and_clear() {
 // GEMM stage on the tcgen05 tensor cores; same contract as the mma.sync dispatch.
 int conv_umma_dispatch(const ImmaParams& p, bool padone, int alt, cudaStream_t stream) {
     int* status = umma_status_ptr();
+    // Patch staging needs stride 1 and pays for the rows it computes on the padded grid and drops: it is used when
+    // at least 70 % of the grid positions are real outputs (56x56: 93 %, 28x28: 87 %, 14x14: 77 %, 7x7: 60 %).
+    const double useful = (double)p.OH * p.OW / ((double)(p.H + 2 * p.p1) * (p.W + 2 * p.p2));
+    if (alt == 2 || (alt == 0 && p.s1 == 1 && p.s2 == 1 && useful >= 0.7)) {
+        int rc;
+        // up to 128 filters: shapes small enough for two CTAs per SM, so that one CTA's epilogue and set-up
+        // overlap the other's MMAs
+        if (p.KN <= 64) rc = launch_umma_patch<2, 64, 4>(p, padone, status, stream);        // 256 rows x 64
+        else if (p.KN <= 128) rc = launch_umma_patch<2, 128, 4>(p, padone, status, stream); // 256 rows x 128
+        else rc = launch_umma_patch<2, 256, 4>(p, padone, status, stream);                  // 256 rows x 256
+        if (rc != TAB_E_TOO_LARGE) return rc;
+        alt = 0;
+    }
     // Tile shapes by filter count (measured on B200, 3x3 ResNet-18-shaped layers, batch 256): the loader is the
     // limit, so the shape with the fewest copied bytes per multiply-add that still keeps >= 3 ring stages wins.
     if (alt) {                                                                      // A/B alternative shapes

@@ -31,8 +31,12 @@ def main():
     ap.add_argument("--pad", type=int, default=1)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--gemm-variant", type=int, default=0,
+                    help="tensor-core GEMM kernel: 0 library choice, 1 mma.sync+im2col, 2 mma.sync, 3/4 tcgen05 im2col shapes, 5 tcgen05 patch")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
+    from . import _cabi
+    _cabi.lib().tab_debug_set_imma_variant(a.gemm_variant)
     torch.manual_seed(0)
     N, H, W, C, KN, K, s, p, t = a.N, a.H, a.H, a.C, a.KN, a.K, a.stride, a.pad, a.type
     x = torch.randn(N, H, W, C, device=dev)
