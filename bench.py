@@ -19,8 +19,9 @@ step (activation quantise, residual add, thresholds) counts as time but not as o
 ``value``   device-resident input, CUDA-event time of the K steps, L2 flushed between steps, max over ranks.
 ``e2e``     the same step through the TAB_CUDA extension module with the input in pinned host memory: the
             host-to-device copy of the shard and the device-to-host copy of the gathered output are timed.
-``roofline`` for the dominant kernel (the s8 tensor-core GEMM of the convolution), timed alone per layer on
-            pre-quantised byte operands; denominator = 2 x the measured bf16 tensor peak.
+``roofline`` for the dominant kernels (the int8 tensor-core GEMM stage of the convolution: tcgen05 kind::i8,
+            mma.sync s8 for <= 64 filters), timed alone per layer on pre-quantised byte operands;
+            denominator = 2 x the measured bf16 tensor peak.
 ``roofline_popcount`` the bit-packed LOP3/POPC kernel on the same layers against the integer-pipe bound derived
             from POPC and LOP3 issue rates measured in the same run by the library's register-only probe.
 ``cpu_baseline`` / ``--impl reference``: the reference's CPU algorithm (quantise, pad, im2row, its own
@@ -501,9 +502,12 @@ def main():
     tensor_peak = 2.0 * bf16_peak
     achieved = sums["ops"] / (sums["gemm_ms"] * 1e-3) / 1e12 if sums["gemm_ms"] else None
     roofline = {
-        "kernel": "conv_imma_kernel (implicit-im2col s8 tensor-core GEMM), %d launches per step" % len(layer_rows),
+        "kernel": "int8 tensor-core GEMM stage of Conv2d (tcgen05.mma kind::i8 kernels; mma.sync s8 kernel for <= 64 filters and 1x1), %d launches per step" % len(layer_rows),
         "bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TOP/s",
-        "frac": (achieved / tensor_peak) if achieved else None, "traffic": None,
+        "frac": (achieved / tensor_peak) if achieved else None,
+        # DRAM bytes of the largest launch of the step (56x56x64->64, batch 256): ncu capture at batch 128 (25.8 MB read +
+        # 49.6 MB written, equal to the algorithmic byte activations + fp32 output) scaled by 2 (traffic is proportional to N)
+        "traffic": 150.7e6, "traffic_note": "largest launch (56x56x64->64 conv, N=256); ncu at N=128 scaled x2; algorithmic 154.1e6",
         "peak_source": peak_src + "; ceiling of the s8 mma.sync instruction measured from registers in this run: %.0f TOP/s" % imma_sync_tops,
         "frac_of_mma_sync_ceiling": (achieved / imma_sync_tops) if achieved else None,
         "avg_launch_ms": sums["gemm_ms"] / max(len(layer_rows), 1),

@@ -175,8 +175,8 @@ int tab_residual_threshold_launch(float* y, const float* residual, float* ths, d
  * Register-only micro-benchmark of the integer pipes used by the convolution, for roofline
  * denominators: runs `iters` rounds on a grid that fills the device and writes elapsed-independent
  * checksums to `sink` (at least tab_pipe_probe_sink_bytes() bytes).  kind: 0 = 32-bit POPC,
- * 1 = LOP3, 2 = s8 mma.sync m16n8k32.  *ops_out receives the number of lane-level instructions of that
- * kind issued (kind 2: multiply-adds * 2); the caller times the call with CUDA events.  Has no
+ * 1 = LOP3, 2 = s8 mma.sync m16n8k32, 3 / 4 = 1-bit mma.sync m16n8k256 and.popc / xor.popc.  *ops_out receives
+ * the number of lane-level instructions of that kind issued (kinds 2-4: multiply-adds * 2); the caller times the call with CUDA events.  Has no
  * counterpart in the reference.
  */
 size_t tab_pipe_probe_sink_bytes(void);

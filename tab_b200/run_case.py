@@ -19,7 +19,8 @@ from . import ops
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["conv", "packed", "quantize"])
+    ap.add_argument("op", choices=["conv", "packed", "quantize", "probe"])
+    ap.add_argument("--kind", type=int, default=0, help="probe: 0 POPC, 1 LOP3, 2 s8 mma.sync, 3 b1 mma and.popc, 4 b1 mma xor.popc")
     ap.add_argument("--type", type=int, default=0)
     ap.add_argument("--bitwidth", type=int, default=2)
     ap.add_argument("--N", type=int, default=64)
@@ -38,6 +39,23 @@ def main():
     from . import _cabi
     _cabi.lib().tab_debug_set_imma_variant(a.gemm_variant)
     torch.manual_seed(0)
+    if a.op == "probe":
+        import ctypes
+        l = _cabi.lib()
+        sink = torch.empty(l.tab_pipe_probe_sink_bytes(), dtype=torch.uint8, device=dev)
+        n_ops = ctypes.c_double(0)
+        best = None
+        for i in range(a.iters + a.warmup):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _cabi.check(l.tab_pipe_probe_launch(a.kind, 2048, sink.data_ptr(), ctypes.byref(n_ops), torch.cuda.current_stream().cuda_stream), "probe")
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= a.warmup:
+                ms = e0.elapsed_time(e1)
+                best = ms if best is None else min(best, ms)
+        print(json.dumps({"op": "probe", "kind": a.kind, "ms": best, "value": n_ops.value / best / 1e9, "unit": "Gop/s (lane instructions, or binary/int8 ops for the MMA kinds)"}))
+        return
     N, H, W, C, KN, K, s, p, t = a.N, a.H, a.H, a.C, a.KN, a.K, a.stride, a.pad, a.type
     x = torch.randn(N, H, W, C, device=dev)
     ths = (0.7 * x.abs().mean(dim=(1, 2, 3))).contiguous()
