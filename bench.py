@@ -18,7 +18,8 @@ step (activation quantise, residual add, thresholds) counts as time but not as o
 
 ``value``   device-resident input, CUDA-event time of the K steps, L2 flushed between steps, max over ranks.
 ``e2e``     the same step through the TAB_CUDA extension module with the input in pinned host memory: the
-            host-to-device copy of the shard and the device-to-host copy of the gathered output are timed.
+            host-to-device copy of the shard and the device-to-host copy of the gathered output are timed.  The shard
+            is processed in four chunks of images so that the copy of one chunk overlaps the forward of the previous.
 ``roofline`` for the dominant kernels (the int8 tensor-core GEMM stage of the convolution: tcgen05 kind::i8,
             mma.sync s8 for <= 64 filters), timed alone per layer on pre-quantised byte operands;
             denominator = 2 x the measured bf16 tensor peak.
@@ -337,29 +338,37 @@ def main():
     #      gaps; the library's launches take a stream and never allocate or synchronise, so they capture) ----
     graphs = {}
 
-    def make_graph(op_set, x_static):
+    def make_graph(op_set, x_static, nb=None):
+        nb = n_local if nb is None else nb
         try:
             side = torch.cuda.Stream(dev)
             side.wait_stream(torch.cuda.current_stream(dev))
             with torch.cuda.stream(side):
                 for _ in range(2):                       # first calls set kernel attributes: outside capture
                     ths = op_set.residual_threshold(x_static, None, chain.THRESHOLD_SCALE)
-                    chain.forward(op_set, x_static, ths, qweights, CONV_TYPE, n_local)
+                    chain.forward(op_set, x_static, ths, qweights, CONV_TYPE, nb)
             torch.cuda.current_stream(dev).wait_stream(side)
             torch.cuda.synchronize()
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr):
                 ths = op_set.residual_threshold(x_static, None, chain.THRESHOLD_SCALE)
-                y, _, _, _ = chain.forward(op_set, x_static, ths, qweights, CONV_TYPE, n_local)
+                y, _, _, _ = chain.forward(op_set, x_static, ths, qweights, CONV_TYPE, nb)
             return gr, y
         except Exception as exc:                          # report and fall back to eager launches
             sys.stderr.write("cuda graph capture failed (%s): timing eager launches\n" % exc)
             return None, None
 
-    x_static_e2e = torch.empty_like(x_dev)
+    # End-to-end step: the shard is processed in NCH chunks of images (every image is independent), so that the
+    # host-to-device copy of chunk i+1 overlaps the forward of chunk i: two input buffers / graphs in ping-pong,
+    # copies on their own streams.
+    NCH = 4 if n_local % 4 == 0 and n_local >= 16 else 1
+    nb_e2e = n_local // NCH
+    x_chunk = [torch.empty((nb_e2e, H0, W0, C0), dtype=torch.float32, device=dev) for _ in range(2 if NCH > 1 else 1)]
+    y_local = torch.empty(n_local * per_img_out, dtype=torch.float32, device=dev)
     graphs["dev"] = make_graph(CountingOps, x_dev)
-    graphs["e2e"] = make_graph(ModuleOps, x_static_e2e)
-    use_graph = graphs["dev"][0] is not None and graphs["e2e"][0] is not None
+    graphs["e2e"] = [make_graph(ModuleOps, xb, nb_e2e) for xb in x_chunk]
+    use_graph = graphs["dev"][0] is not None and all(g[0] is not None for g in graphs["e2e"])
+    h2d_stream = torch.cuda.Stream(dev)
     launches[0] = 0
     if use_graph:
         ths_ = CountingOps.residual_threshold(x_dev, None, chain.THRESHOLD_SCALE)      # count one forward's kernels
@@ -379,14 +388,26 @@ def main():
         return step_device(CountingOps, x_dev)
 
     def step_e2e_any():
-        if use_graph:
-            x_static_e2e.copy_(x_host, non_blocking=True)
-            graphs["e2e"][0].replay()
-            y = finish(graphs["e2e"][1])
-            if rank == 0:
-                y_host.copy_(y, non_blocking=True)
-            return y
-        return step_e2e()
+        if not use_graph:
+            return step_e2e()
+        main = torch.cuda.current_stream(dev)
+        h2d_stream.wait_stream(main)                 # the step starts where the caller's stream is
+        ev_in, ev_done = [], []
+        for i in range(NCH):
+            k = i % len(x_chunk)
+            with torch.cuda.stream(h2d_stream):
+                if i >= len(x_chunk):
+                    h2d_stream.wait_event(ev_done[i - len(x_chunk)])     # the buffer's previous chunk has been consumed
+                x_chunk[k].copy_(x_host[i * nb_e2e:(i + 1) * nb_e2e], non_blocking=True)
+                e = torch.cuda.Event(); e.record(h2d_stream); ev_in.append(e)
+            main.wait_event(ev_in[i])
+            graphs["e2e"][k][0].replay()
+            y_local[i * nb_e2e * per_img_out:(i + 1) * nb_e2e * per_img_out].copy_(graphs["e2e"][k][1].reshape(-1), non_blocking=True)
+            e = torch.cuda.Event(); e.record(main); ev_done.append(e)
+        y = finish(y_local)
+        if rank == 0:
+            y_host.copy_(y, non_blocking=True)
+        return y
 
     # ---- warm-up, then the timed region ---------------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
@@ -562,7 +583,7 @@ def main():
         "config": dict(workload_config(world), binary_ops_per_step=ops_per_step),
         "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(N * per_img_out * 4),
-                "api": "TAB_CUDA.Conv2d (extension module) + pinned-host copies; bytes are rank 0's"},
+                "api": "TAB_CUDA.Conv2d / Conv2dFused (extension module) + pinned-host copies, %d chunks of images pipelined; bytes are rank 0's" % NCH},
         "gpu_launches": gpu_launches, "cuda_graph": bool(use_graph),
         "clocks": clocks,
         "roofline": roofline,
