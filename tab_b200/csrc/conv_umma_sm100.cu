@@ -580,32 +580,70 @@ int umma_status_read_and_clear() {
 }
 
 // GEMM stage on the tcgen05 tensor cores; same contract as the mma.sync dispatch.
+//
+// Shape choice.  All variants are bound by their loaders, and measured per-CTA times follow
+//     time ~ 3.2 ns x (rows copied per K step) x (K steps)  +  a fixed set-up/epilogue cost,
+// where a "row" is 128 bytes of one operand row.  The candidates are scored with that model times the number of
+// waves the grid needs on the device's SMs, so that small problems (few output rows) get small tiles and fill the
+// machine, and large ones get the tiles with the fewest copies per multiply-add.
+struct UmmaChoice { int patch, mt, tn; };
+
 int conv_umma_dispatch(const ImmaParams& p, bool padone, int alt, cudaStream_t stream) {
     int* status = umma_status_ptr();
-    // Patch staging needs stride 1 and pays for the rows it computes on the padded grid and drops: it is used when
-    // at least 70 % of the grid positions are real outputs (56x56: 93 %, 28x28: 87 %, 14x14: 77 %, 7x7: 60 %).
-    const double useful = (double)p.OH * p.OW / ((double)(p.H + 2 * p.p1) * (p.W + 2 * p.p2));
-    if (alt == 2 || (alt == 0 && p.s1 == 1 && p.s2 == 1 && useful >= 0.7)) {
-        int rc;
-        // up to 128 filters: shapes small enough for two CTAs per SM, so that one CTA's epilogue and set-up
-        // overlap the other's MMAs
-        if (p.KN <= 64) rc = launch_umma_patch<2, 64, 4>(p, padone, status, stream);        // 256 rows x 64
-        else if (p.KN <= 128) rc = launch_umma_patch<2, 128, 4>(p, padone, status, stream); // 256 rows x 128
-        else rc = launch_umma_patch<2, 256, 4>(p, padone, status, stream);                  // 256 rows x 256
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2;
+    const int T = p.KH * p.KW;
+    const long long nchunks = (p.Kw + IKW - 1) / IKW, ncp = (p.PC + 1) / 2;
+    const long long Mv = (long long)(p.N - 1) * PH * PW + (long long)(p.OH - 1) * PW + p.OW;
+    const long long halo = (p.KH - 1) * PW + p.KW - 1;
+    const bool patch_ok = p.s1 == 1 && p.s2 == 1 && T >= 4 && (long long)p.N * PH * PW < (1LL << 31) - 4096;
+    const double fixed = 1200.0;                                 // set-up + epilogue of one CTA, in row units
+
+    static const UmmaChoice cands[] = {{0, 2, 256}, {0, 1, 256}, {0, 2, 128}, {0, 1, 128}, {0, 2, 64}, {0, 1, 64},
+                                       {1, 2, 256}, {1, 2, 128}, {1, 1, 128}, {1, 2, 64}};
+    UmmaChoice best = {0, 1, 64};
+    double best_cost = 1e300;
+    for (const UmmaChoice& c : cands) {
+        if (c.tn > 64 && c.tn / 2 >= p.KN) continue;             // a tile twice as wide as the filter count only wastes
+        if (alt == 1 && c.patch) continue;                       // A/B switches: im2col staging only / patch staging only
+        if (alt == 2 && !c.patch && patch_ok) continue;
+        const long long tm = 128LL * c.mt;
+        const long long ctas_n = (p.KN + c.tn - 1) / c.tn;
+        double cost;
+        if (c.patch) {
+            if (!patch_ok) continue;
+            const long long prow = (tm + halo + 7) / 8 * 8;
+            const int npb = p.PC > 2 ? 2 : 1;
+            const long long smem = npb * prow * IROW + 4LL * c.tn * IROW + prow * 4 + 8 * 6 + 16 + 1024;
+            if (smem > UMMA_SMEM_MAX) continue;
+            const long long ctas = ((Mv + tm - 1) / tm) * ctas_n;
+            const int per_sm = (c.mt * c.tn <= 256 && 2 * smem <= UMMA_SMEM_MAX) ? 2 : 1;
+            const double rows = (double)ncp * (double)(tm + halo + (long long)T * c.tn) + fixed;
+            const double waves = (double)((ctas + (long long)sms * per_sm - 1) / ((long long)sms * per_sm));
+            cost = waves * rows * (per_sm == 2 ? 1.6 : 1.0);     // two resident CTAs share the SM's copy rate
+        } else {
+            const long long ctas = ((p.M + tm - 1) / tm) * ctas_n;
+            const double rows = (double)nchunks * (double)(tm + c.tn) + fixed;
+            cost = (double)((ctas + sms - 1) / sms) * rows;
+        }
+        if (cost < best_cost) { best_cost = cost; best = c; }
+    }
+    if (best.patch) {
+        int rc = TAB_E_TOO_LARGE;
+        if (best.mt == 2 && best.tn == 256) rc = launch_umma_patch<2, 256, 4>(p, padone, status, stream);
+        else if (best.mt == 2 && best.tn == 128) rc = launch_umma_patch<2, 128, 4>(p, padone, status, stream);
+        else if (best.mt == 1 && best.tn == 128) rc = launch_umma_patch<1, 128, 4>(p, padone, status, stream);
+        else if (best.mt == 2 && best.tn == 64) rc = launch_umma_patch<2, 64, 4>(p, padone, status, stream);
         if (rc != TAB_E_TOO_LARGE) return rc;
-        alt = 0;
+        best = {0, 1, p.KN <= 64 ? 64 : (p.KN <= 128 ? 128 : 256)};
     }
-    // Tile shapes by filter count (measured on B200, 3x3 ResNet-18-shaped layers, batch 256): the loader is the
-    // limit, so the shape with the fewest copied bytes per multiply-add that still keeps >= 3 ring stages wins.
-    if (alt) {                                                                      // A/B alternative shapes
-        if (p.KN <= 64) return launch_umma<1, 64, 8>(p, padone, status, stream);    // 128 x 64,  8 x 25 KB
-        if (p.KN <= 128) return launch_umma<1, 128, 6>(p, padone, status, stream);  // 128 x 128, 6 x 33 KB
-        return launch_umma<2, 256, 3>(p, padone, status, stream);                   // 256 x 256, 3 x 65 KB
-    }
-    if (p.KN <= 64) return launch_umma<2, 64, 5>(p, padone, status, stream);        // 256 x 64,  5 x 41 KB
-    if (p.KN <= 128) return launch_umma<2, 128, 4>(p, padone, status, stream);      // 256 x 128, 4 x 49 KB
-    if (p.KN <= 256) return launch_umma<1, 256, 4>(p, padone, status, stream);      // 128 x 256, 4 x 49 KB
-    return launch_umma<2, 256, 3>(p, padone, status, stream);                       // 256 x 256, 3 x 65 KB
+    if (best.tn == 256) return best.mt == 2 ? launch_umma<2, 256, 3>(p, padone, status, stream)     // 256 x 256, 3 x 65 KB
+                                            : launch_umma<1, 256, 4>(p, padone, status, stream);    // 128 x 256, 4 x 49 KB
+    if (best.tn == 128) return best.mt == 2 ? launch_umma<2, 128, 4>(p, padone, status, stream)     // 256 x 128, 4 x 49 KB
+                                            : launch_umma<1, 128, 6>(p, padone, status, stream);    // 128 x 128, 6 x 33 KB
+    return best.mt == 2 ? launch_umma<2, 64, 5>(p, padone, status, stream)                          // 256 x 64,  5 x 41 KB
+                        : launch_umma<1, 64, 8>(p, padone, status, stream);                         // 128 x 64,  8 x 25 KB
 }
 
 }  // namespace tab
