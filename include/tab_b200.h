@@ -59,10 +59,12 @@ int tab_quantize_launch(const float* x, const float* ths, int64_t* qx, int32_t* 
 
 /*
  * Bytes of scratch tab_conv2d_launch needs for these sizes, whichever compute path is selected (the
- * quantised activations and, for the tensor-core path, the byte-expanded weights).
+ * quantised activations - in zero-padded form where the kernel wants them so - and, for the tensor-core path, the
+ * byte-expanded weights).  Same geometry arguments, in the same order, as tab_conv2d_launch.
  * Returns 0 for invalid arguments.
  */
-size_t tab_conv2d_workspace_bytes(int type, int N, int H, int W, int C, int KN, int KH, int KW);
+size_t tab_conv2d_workspace_bytes(int type, int p1, int p2, int s1, int s2,
+                                  int N, int H, int W, int C, int KN, int KH, int KW);
 
 /*
  * Compute path of tab_conv2d_launch (process-wide; results are identical bit for bit):

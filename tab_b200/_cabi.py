@@ -19,7 +19,7 @@ SYMBOLS = {
     "tab_version": (_c.c_int, []),
     "tab_quantize_launch": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                        _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
-    "tab_conv2d_workspace_bytes": (_c.c_size_t, [_c.c_int] * 8),
+    "tab_conv2d_workspace_bytes": (_c.c_size_t, [_c.c_int] * 12),
     "tab_conv2d_set_path": (_c.c_int, [_c.c_int]),
     "tab_conv2d_launch": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_size_t] + [_c.c_int] * 12 + [_c.c_void_p]),
     "tab_conv2d_fused_launch": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_size_t] + [_c.c_int] * 12 + [_c.c_void_p] * 3),

@@ -14,7 +14,7 @@ int record_cuda_error(cudaError_t e) {
 void conv_set_csa(bool on);
 void imma_set_variant(int v);
 int umma_status_read_and_clear();
-size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW);
+size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2);
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
                        cudaStream_t stream, const float* residual, double* abs_sums);
@@ -76,9 +76,9 @@ static size_t popc_workspace_bytes(int type, int N, int H, int W, int C) {
     return (words * 8 + 255) / 256 * 256;
 }
 
-size_t tab_conv2d_workspace_bytes(int type, int N, int H, int W, int C, int KN, int KH, int KW) {
-    if (type < 0 || type > 3 || !dims_ok(N, H, W, C) || KN < 0 || KH < 1 || KW < 1) return 0;
-    const size_t a = popc_workspace_bytes(type, N, H, W, C), b = imma_workspace_bytes(N, H, W, C, KN, KH, KW);
+size_t tab_conv2d_workspace_bytes(int type, int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW) {
+    if (type < 0 || type > 3 || !dims_ok(N, H, W, C) || KN < 0 || KH < 1 || KW < 1 || p1 < 0 || p2 < 0 || s1 < 1 || s2 < 1) return 0;
+    const size_t a = popc_workspace_bytes(type, N, H, W, C), b = imma_workspace_bytes(N, H, W, C, KN, KH, KW, p1, p2);
     return a > b ? a : b;
 }
 
@@ -129,7 +129,7 @@ static int conv2d_impl(const float* x, const int64_t* qw, const float* ths, cons
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
     if (!x || !ths || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
-    const size_t need = tab_conv2d_workspace_bytes(type, N, H, W, C, KN, KH, KW);
+    const size_t need = tab_conv2d_workspace_bytes(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
         return TAB_E_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) ||

@@ -77,6 +77,66 @@ quantize_int8_kernel(const float* __restrict__ x, const float* __restrict__ ths,
     }
 }
 
+// Same quantiser writing a zero-padded (or +1-padded, for binary activations) tensor [N][PH][PW][Cp]: the input
+// of the TMA-fed GEMM, which reads padding taps like any other pixel.  One thread per 16 channels of a PADDED
+// pixel; border pixels get the padding value in the real channels and 0 in the channel padding.
+template <int BITS, bool VEC>
+__global__ void __launch_bounds__(Q8THREADS)
+quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict__ ths, int8_t* __restrict__ q,
+                            int H, int W, int C, int Cp, int p1, int p2) {
+    const int n = blockIdx.y;
+    const float t = __ldg(ths + n), nt = -t;
+    const int gpp = Cp >> 4;
+    const int PH = H + 2 * p1, PW = W + 2 * p2;
+    const long long groups = (long long)PH * PW * gpp;
+    const float* xi = x + (long long)n * H * W * C;
+    int8_t* qi = q + (long long)n * PH * PW * Cp;
+    for (long long g = (long long)blockIdx.x * Q8THREADS + threadIdx.x; g < groups; g += (long long)gridDim.x * Q8THREADS) {
+        const long long pix = g / gpp;
+        const int c0 = (int)(g - pix * gpp) << 4;
+        const int ph = (int)(pix / PW), pw = (int)(pix - (long long)ph * PW);
+        const int ih = ph - p1, iw = pw - p2;
+        uint32_t o[4];
+        if ((unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) {
+            const float* src = xi + ((long long)ih * W + iw) * C + c0;
+            float v[16];
+            if (VEC && c0 + 16 <= C) {
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+                    asm volatile("ld.global.nc.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=f"(v[8 * h + 0]), "=f"(v[8 * h + 1]), "=f"(v[8 * h + 2]), "=f"(v[8 * h + 3]),
+                                   "=f"(v[8 * h + 4]), "=f"(v[8 * h + 5]), "=f"(v[8 * h + 6]), "=f"(v[8 * h + 7])
+                                 : "l"(src + 8 * h));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) v[i] = (c0 + i < C) ? __ldg(src + i) : 0.f;
+            }
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                uint32_t r = 0;
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    const int i = 4 * w + b;
+                    int qv = (BITS == 2) ? q_ternary(v[i], t, nt) : q_binary(v[i], t);
+                    if (c0 + i >= C) qv = 0;
+                    r |= (uint32_t)(qv & 0xFF) << (8 * b);
+                }
+                o[w] = r;
+            }
+        } else {
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                uint32_t r = 0;
+#pragma unroll
+                for (int b = 0; b < 4; b++)
+                    if (BITS == 1 && c0 + 4 * w + b < C) r |= 1u << (8 * b);     // binary activations pad with +1
+                o[w] = r;
+            }
+        }
+        *reinterpret_cast<uint4*>(qi + pix * Cp + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // 2. packed weights -> int8
 // ------------------------------------------------------------------------------------------------
@@ -593,13 +653,15 @@ static int launch_imma(const ImmaParams& p, cudaStream_t stream) {
 }
 
 int conv_umma_dispatch(const ImmaParams& p, bool padone, int alt, cudaStream_t stream);
+int conv_tma_dispatch(const ImmaParams& p, cudaStream_t stream);
 
 // 0 = default choice, 1 = mma.sync with im2col staging, 2 = mma.sync (patch or im2col), 3 = tcgen05 (for A/B tests)
 static int g_imma_variant = 0;
+static const bool g_tma_default = false;   // the TMA-fed kernel is opt-in (variant 6) until it has been measured ahead
 
-size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW) {
+size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2) {
     const size_t Cp = (size_t)packed_channels(C) * 64;
-    const size_t a = ((size_t)N * H * W * Cp + 255) / 256 * 256;
+    const size_t a = ((size_t)N * (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2) * Cp + 255) / 256 * 256;   // room for the padded form
     const size_t b = ((size_t)KN * KH * KW * Cp + 255) / 256 * 256;
     return a + b;
 }
@@ -695,10 +757,41 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
     int rc = imma_limits(N, H, W, C, KN, KH, KW, oh, ow);
     if (rc != TAB_OK) return rc;
     int8_t* qx8 = reinterpret_cast<int8_t*>(workspace);
-    int8_t* w8 = qx8 + ((size_t)N * H * W * Cp + 255) / 256 * 256;
-    rc = quantize_int8_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, stream);
-    if (rc != TAB_OK) return rc;
+    int8_t* w8 = qx8 + ((size_t)N * (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2) * Cp + 255) / 256 * 256;
     rc = expand_weights_dispatch(qw, w8, weight_bits(type), KN, KH, KW, C, stream);
+    if (rc != TAB_OK) return rc;
+    // TMA-fed tcgen05 kernel on padded activations: stride 1, at least 4 taps, most of the padded grid useful
+    {
+        const long long PH = H + 2LL * p1, PW = W + 2LL * p2;
+        const double useful = (double)oh * ow / ((double)PH * PW);
+        const bool want = g_imma_variant == 6 || (g_imma_variant == 0 && g_tma_default && useful >= 0.7 && KN > 64);
+        if (want && s1 == 1 && s2 == 1 && KH * KW >= 4 && N <= 65535 && N * PH * PW < (1LL << 31) - 4096) {
+            const long long groups = PH * PW * (Cp / 16);
+            long long per = (groups + Q8THREADS - 1) / Q8THREADS;
+            const long long cap = (148LL * 8 * 4 + N - 1) / N;
+            if (per > cap) per = cap;
+            if (per < 1) per = 1;
+            dim3 grid((unsigned)per, (unsigned)N);
+            const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)H * W * C) % 8 == 0);
+            if (act_bits(type) == 2) {
+                if (vec) quantize_int8_padded_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2);
+                else quantize_int8_padded_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2);
+            } else {
+                if (vec) quantize_int8_padded_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2);
+                else quantize_int8_padded_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2);
+            }
+            rc = check_launch();
+            if (rc != TAB_OK) return rc;
+            ImmaParams p;
+            p.qx = qx8; p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
+            p.N = N; p.H = H; p.W = W; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
+            p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
+            p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * p.PC;
+            rc = conv_tma_dispatch(p, stream);
+            if (rc != TAB_E_TOO_LARGE) return rc;     // shape not covered: continue with the unpadded form
+        }
+    }
+    rc = quantize_int8_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, stream);
     if (rc != TAB_OK) return rc;
     return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream, residual, abs_sums);
 }

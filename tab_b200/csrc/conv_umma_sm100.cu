@@ -18,6 +18,7 @@
 //     per-image sums of |y|, and stores rows of [M][KN].
 // Every wait on an mbarrier is bounded: on expiry the kernel records a code in *status, stops waiting,
 // still frees its TMEM columns and returns.
+#include <cuda.h>
 #include "tab_kernels.cuh"
 #include "conv_int8.cuh"
 
@@ -307,6 +308,73 @@ static int launch_umma(const ImmaParams& p, bool padone, int* status, cudaStream
     return fused ? launch_umma_f<MT, TNI, S, false, true>(p, status, stream) : launch_umma_f<MT, TNI, S, false, false>(p, status, stream);
 }
 
+// Epilogue of the kernels that enumerate output positions on the zero-padded input grid: virtual row -> output
+// pixel (rows outside the real output are dropped), TMEM -> registers -> float [M][KN], optional residual and
+// per-image sums of |y|.
+template <int MT, int TNI, bool FUSED>
+__device__ __forceinline__ void grid_epilogue(const ImmaParams& p, uint32_t tmem_base, int R0, int n0, int PW, int PHW,
+                                              int warp, int lane) {
+    const int wq = warp & 3, wh = warp >> 2;
+    const bool vec4 = (p.KN & 3) == 0;
+#pragma unroll 1
+    for (int mb = 0; mb < MT; mb++) {
+        const int R = R0 + mb * UTM + wq * 32 + lane;
+        const int n = R / PHW;
+        const int rr = R - n * PHW;
+        const int oh = rr / PW;
+        const int ow = rr - oh * PW;
+        const bool row_ok = n < p.N && oh < p.OH && ow < p.OW;
+        const long long m = ((long long)n * p.OH + oh) * p.OW + ow;
+        const int wimg0 = (R0 + mb * UTM + wq * 32) / PHW;                 // image of the warp's first row
+        float rsum = 0.f;
+        float* __restrict__ yrow = p.y + (row_ok ? m : 0) * p.KN;
+        const float* __restrict__ rrow = (FUSED && p.residual) ? p.residual + (row_ok ? m : 0) * p.KN : nullptr;
+#pragma unroll 1
+        for (int cb = 0; cb < TNI / 2; cb += 32) {
+            const int col = wh * (TNI / 2) + cb;
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(mb * TNI + col), v);
+            if (!row_ok) continue;
+            const int nbase = n0 + col;
+            if (vec4 && nbase + 32 <= p.KN) {
+                float4 res[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    res[q] = (FUSED && rrow) ? __ldg(reinterpret_cast<const float4*>(rrow + nbase) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    float4 o;
+                    o.x = (float)(int)v[4 * q + 0] + res[q].x; o.y = (float)(int)v[4 * q + 1] + res[q].y;
+                    o.z = (float)(int)v[4 * q + 2] + res[q].z; o.w = (float)(int)v[4 * q + 3] + res[q].w;
+                    reinterpret_cast<float4*>(yrow + nbase)[q] = o;
+                    if (FUSED) rsum += (fabsf(o.x) + fabsf(o.y)) + (fabsf(o.z) + fabsf(o.w));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (nbase + i < p.KN) {
+                        float o = (float)(int)v[i];
+                        if (FUSED && rrow) o += __ldg(rrow + nbase + i);
+                        yrow[nbase + i] = o;
+                        if (FUSED) rsum += fabsf(o);
+                    }
+                }
+            }
+        }
+        if (FUSED && p.abs_sums) {
+            const int d = n - wimg0;                                       // 32 consecutive grid positions: usually one image, rarely more
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                double t = (row_ok && d == i) ? (double)rsum : 0.0;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+                if (lane == 0 && t != 0.0 && wimg0 + i < p.N) atomicAdd(p.abs_sums + wimg0 + i, t);
+            }
+            if (row_ok && d > 2) atomicAdd(p.abs_sums + n, (double)rsum);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Patch variant (stride 1): instead of an im2col tile per tap, the CTA stages the patch of input pixels
 // once per pair of 64-channel words and points the MMA's A descriptor into it.
@@ -451,66 +519,7 @@ conv_umma_patch_kernel(const ImmaParams p, int* __restrict__ status, const int p
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // ---- epilogue: virtual row -> output pixel, TMEM -> float [M][KN] ------------------------------------------
-    const int wq = warp & 3, wh = warp >> 2;
-    const bool vec4 = (p.KN & 3) == 0;
-#pragma unroll 1
-    for (int mb = 0; mb < MT; mb++) {
-        const int R = R0 + mb * UTM + wq * 32 + lane;
-        const int n = R / PHW;
-        const int rr = R - n * PHW;
-        const int oh = rr / PW;
-        const int ow = rr - oh * PW;
-        const bool row_ok = n < p.N && oh < p.OH && ow < p.OW;
-        const long long m = ((long long)n * p.OH + oh) * p.OW + ow;
-        const int wimg0 = (R0 + mb * UTM + wq * 32) / PHW;                 // image of the warp's first row
-        float rsum = 0.f;
-        float* __restrict__ yrow = p.y + (row_ok ? m : 0) * p.KN;
-        const float* __restrict__ rrow = (FUSED && p.residual) ? p.residual + (row_ok ? m : 0) * p.KN : nullptr;
-#pragma unroll 1
-        for (int cb = 0; cb < TNI / 2; cb += 32) {
-            const int col = wh * (TNI / 2) + cb;
-            uint32_t v[32];
-            tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(mb * TNI + col), v);
-            if (!row_ok) continue;
-            const int nbase = n0 + col;
-            if (vec4 && nbase + 32 <= p.KN) {
-                float4 res[8];
-#pragma unroll
-                for (int q = 0; q < 8; q++)
-                    res[q] = (FUSED && rrow) ? __ldg(reinterpret_cast<const float4*>(rrow + nbase) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    float4 o;
-                    o.x = (float)(int)v[4 * q + 0] + res[q].x; o.y = (float)(int)v[4 * q + 1] + res[q].y;
-                    o.z = (float)(int)v[4 * q + 2] + res[q].z; o.w = (float)(int)v[4 * q + 3] + res[q].w;
-                    reinterpret_cast<float4*>(yrow + nbase)[q] = o;
-                    if (FUSED) rsum += (fabsf(o.x) + fabsf(o.y)) + (fabsf(o.z) + fabsf(o.w));
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    if (nbase + i < p.KN) {
-                        float o = (float)(int)v[i];
-                        if (FUSED && rrow) o += __ldg(rrow + nbase + i);
-                        yrow[nbase + i] = o;
-                        if (FUSED) rsum += fabsf(o);
-                    }
-                }
-            }
-        }
-        if (FUSED && p.abs_sums) {
-            const int d = n - wimg0;                                       // 32 consecutive grid positions: usually one image, rarely more
-#pragma unroll
-            for (int i = 0; i < 3; i++) {
-                double t = (row_ok && d == i) ? (double)rsum : 0.0;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
-                if (lane == 0 && t != 0.0 && wimg0 + i < p.N) atomicAdd(p.abs_sums + wimg0 + i, t);
-            }
-            if (row_ok && d > 2) atomicAdd(p.abs_sums + n, (double)rsum);
-        }
-    }
+    grid_epilogue<MT, TNI, FUSED>(p, tmem_base, R0, n0, PW, PHW, warp, lane);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
@@ -553,6 +562,212 @@ static int launch_umma_patch(const ImmaParams& p, bool padone, int* status, cuda
                              : launch_umma_patch_f<MT, TNI, SB, true, false>(p, status, prow, npb, stream);
     return fused ? launch_umma_patch_f<MT, TNI, SB, false, true>(p, status, prow, npb, stream)
                  : launch_umma_patch_f<MT, TNI, SB, false, false>(p, status, prow, npb, stream);
+}
+
+// ------------------------------------------------------------------------------------------------
+// TMA variant of the patch kernel (stride 1): both operands arrive by tensor-map bulk copies, so the copy side
+// costs one instruction per 16-32 KB instead of one cp.async per 16 bytes with per-row address arithmetic.
+//
+// The activations are quantised into a *padded* byte tensor [N*PH*PW][Cp] (border pixels hold the padding value:
+// 0 for ternary, +1 for binary activations).  On that tensor the patch of a tile is simply rows
+// [R0, R0 + prow) x 128 bytes - a plain 2-D box - and the weights of one tap for one pair of 64-channel words are
+// the box rows [n0, n0 + TN) x 128 bytes of the [KN][Kw*64] byte matrix.  The copies use the 128-byte swizzle, which is
+// the layout the MMA descriptors expect, and complete on "full" mbarriers (expect_tx); tcgen05.commit arrives on the
+// "empty" barriers.  One thread runs the whole producer/MMA loop; the other threads only wait for the final commit
+// and run the epilogue.  No multicast, one CTA per cluster.
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"(tmap), "r"(mbar), "r"(x), "r"(y) : "memory");
+}
+
+constexpr int TMA_BOX_ROWS = 128;            // rows per activation box (16 KB)
+
+template <int MT, int TNI, int SB, bool FUSED>
+__global__ void __launch_bounds__(UTHREADS, (MT * TNI <= 256) ? 2 : 1)
+conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const ImmaParams p, int* __restrict__ status, const int prow, const int npb) {
+    constexpr int BSTAGE = TNI * IROW;
+    constexpr int DB = SB - 2;
+    constexpr int TCOLS = MT * TNI;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sbase = (raw + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (sbase - raw);
+    const uint32_t sPatch = sbase;                                         // [npb][prow][128 B], prow % 128 == 0
+    const uint32_t sRing = sbase + npb * prow * IROW;                      // [SB][TNI][128 B]
+    const int tail = npb * prow * IROW + SB * BSTAGE;
+    const uint32_t fullB = sbase + tail, emptyB = fullB + 8 * SB;          // SB + SB stage barriers
+    const uint32_t fullP = emptyB + 8 * SB, emptyP = fullP + 16, doneB = emptyP + 16;
+    const uint32_t tslot = doneB + 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + tail + 16 * SB + 40);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.y * TNI;
+    const int PH = p.H + 2 * p.p1, PW = p.W + 2 * p.p2, PHW = PH * PW;
+    const int T = p.KH * p.KW, ncp = (p.PC + 1) >> 1;
+    const int R0 = blockIdx.x * (UTM * MT);
+
+    if (tid == 0) {
+        for (int s = 0; s < 2 * SB + 5; s++) mbar_init(fullB + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(tslot), "r"((uint32_t)TCOLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool dead = false;
+    if (tid == 0) {
+        constexpr uint32_t IDESC = umma_idesc(TNI);
+        const int nst = ncp * T;
+        const int nbox = prow / TMA_BOX_ROWS;
+        for (int it = 0; it < nst + DB && !dead; it++) {
+            if (it < nst) {
+                const int slot = it % SB;
+                const int cp = it / T, tap = it - cp * T;
+                if (it >= SB && !mbar_wait(emptyB + 8 * slot, (uint32_t)((it / SB) - 1) & 1u)) { dead = true; if (status) atomicExch(status, 6); break; }
+                if (tap == 0) {
+                    const int pb = cp & (npb - 1);
+                    if (cp >= npb && !mbar_wait(emptyP + 8 * pb, (uint32_t)((cp / npb) - 1) & 1u)) { dead = true; if (status) atomicExch(status, 7); break; }
+                    mbar_expect_tx(fullP + 8 * pb, (uint32_t)(nbox * TMA_BOX_ROWS * IROW));
+                    for (int b = 0; b < nbox; b++)
+                        tma_load_2d(sPatch + (pb * prow + b * TMA_BOX_ROWS) * IROW, &tmA, 2 * cp * 64, R0 + b * TMA_BOX_ROWS, fullP + 8 * pb);
+                }
+                mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
+                tma_load_2d(sRing + slot * BSTAGE, &tmB, (tap * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
+            }
+            const int r = it - DB;
+            if (r >= 0) {
+                const int slot = r % SB;
+                const int cp = r / T, tap = r - cp * T;
+                const int pb = cp & (npb - 1);
+                if (tap == 0 && !mbar_wait(fullP + 8 * pb, (uint32_t)(cp / npb) & 1u)) { dead = true; if (status) atomicExch(status, 8); break; }
+                if (!mbar_wait(fullB + 8 * slot, (uint32_t)(r / SB) & 1u)) { dead = true; if (status) atomicExch(status, 9); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int kh = tap / p.KW, kw = tap - kh * p.KW;
+                const uint32_t abuf = sPatch + (uint32_t)(pb * prow + kh * PW + kw) * IROW;
+                const uint64_t db = umma_desc(sRing + slot * BSTAGE);
+                const int ksteps = (2 * cp + 1 < p.PC) ? 4 : 2;
+                for (int k = 0; k < ksteps; k++) {
+#pragma unroll
+                    for (int mb = 0; mb < MT; mb++)
+                        umma_i8(tmem_base + mb * TNI, umma_desc(abuf + mb * UTM * IROW) + 2 * k, db + 2 * k, IDESC,
+                                (r > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(emptyB + 8 * slot);
+                if (tap == T - 1) umma_commit(emptyP + 8 * pb);
+            }
+        }
+        umma_commit(doneB);                                     // arrives when every MMA issued above has completed
+    }
+    __syncwarp();
+    // everybody (the issuing thread included) waits for the accumulators; back off between polls
+    {
+        bool ok = false;
+        for (uint32_t i = 0; i < (1u << 16) && !ok; i++) {
+            uint32_t t;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(t) : "r"(doneB), "r"(0u) : "memory");
+            ok = t != 0;
+            if (!ok) __nanosleep(200);
+        }
+        if (!ok && status) atomicExch(status, 10);
+    }
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    grid_epilogue<MT, TNI, FUSED>(p, tmem_base, R0, n0, PW, PHW, warp, lane);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TCOLS) : "memory");
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2-D byte tensor [rows][row_bytes] (row pitch = row_bytes), box = 128 bytes x box_rows, 128-byte swizzle.
+static bool make_map_2d(CUtensorMap* m, const void* base, unsigned long long row_bytes, unsigned long long rows, unsigned box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {128, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int MT, int TNI, int SB, bool FUSED>
+static int launch_umma_tma_f(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, int prow, int npb,
+                             cudaStream_t stream) {
+    constexpr int TMI = UTM * MT;
+    const int smem_bytes = npb * prow * IROW + SB * TNI * IROW + 16 * SB + 64 + 1024;
+    static int configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev < 0 || dev >= 64 || configured[dev] < smem_bytes) {
+        e = cudaFuncSetAttribute(conv_umma_tma_kernel<MT, TNI, SB, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (dev >= 0 && dev < 64) configured[dev] = UMMA_SMEM_MAX;
+    }
+    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2;
+    const long long Mv = (long long)(p.N - 1) * PH * PW + (long long)(p.OH - 1) * PW + p.OW;
+    dim3 grid((unsigned)((Mv + TMI - 1) / TMI), (unsigned)((p.KN + TNI - 1) / TNI));
+    conv_umma_tma_kernel<MT, TNI, SB, FUSED><<<grid, UTHREADS, smem_bytes, stream>>>(tmA, tmB, p, status, prow, npb);
+    return check_launch();
+}
+
+template <int MT, int TNI, int SB>
+static int launch_umma_tma(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, cudaStream_t stream) {
+    const long long PW = p.W + 2LL * p.p2;
+    const int prow = (int)((UTM * MT + (p.KH - 1) * PW + p.KW - 1 + TMA_BOX_ROWS - 1) / TMA_BOX_ROWS * TMA_BOX_ROWS);
+    const int npb = p.PC > 2 ? 2 : 1;
+    const long long smem_bytes = (long long)npb * prow * IROW + (long long)SB * TNI * IROW + 16 * SB + 64 + 1024;
+    if (smem_bytes > UMMA_SMEM_MAX || p.KH * p.KW < SB) return TAB_E_TOO_LARGE;
+    return (p.residual || p.abs_sums) ? launch_umma_tma_f<MT, TNI, SB, true>(tmA, tmB, p, status, prow, npb, stream)
+                                      : launch_umma_tma_f<MT, TNI, SB, false>(tmA, tmB, p, status, prow, npb, stream);
+}
+
+static int* umma_status_ptr();
+
+// GEMM stage of the TMA variant.  p.qx must be the PADDED byte activations [N*PH*PW][Cp]; stride 1 only.
+// shape: 0 = choose by filter count; returns TAB_E_TOO_LARGE when the shape does not fit (caller falls back).
+int conv_tma_dispatch(const ImmaParams& p, cudaStream_t stream) {
+    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2, rows = (long long)p.N * PH * PW;
+    if (p.s1 != 1 || p.s2 != 1 || rows >= (1LL << 31) - 4096 || !encode_tiled_fn()) return TAB_E_TOO_LARGE;
+    if ((reinterpret_cast<uintptr_t>(p.qx) & 15) || (reinterpret_cast<uintptr_t>(p.w8) & 15)) return TAB_E_TOO_LARGE;
+    alignas(64) CUtensorMap tmA, tmB;
+    const unsigned tn = p.KN <= 64 ? 64 : (p.KN <= 128 ? 128 : 256);
+    if (!make_map_2d(&tmA, p.qx, (unsigned long long)p.PC * 64, (unsigned long long)rows, TMA_BOX_ROWS)) return TAB_E_TOO_LARGE;
+    if (!make_map_2d(&tmB, p.w8, (unsigned long long)p.Kw * 64, (unsigned long long)p.KN, tn)) return TAB_E_TOO_LARGE;
+    int* status = umma_status_ptr();
+    if (tn == 64) return launch_umma_tma<2, 64, 4>(tmA, tmB, p, status, stream);
+    if (tn == 128) return launch_umma_tma<2, 128, 4>(tmA, tmB, p, status, stream);
+    return launch_umma_tma<2, 256, 4>(tmA, tmB, p, status, stream);
 }
 
 // Where an expired wait is recorded (0 = never).  In host code the name is only a symbol handle; the device

@@ -72,7 +72,7 @@ torch::Tensor TAB_Conv2d(torch::Tensor X, torch::Tensor QW, torch::Tensor thresh
     const int64_t OH = std::max<int64_t>(((int64_t)H + 2 * padding1 - KH + 1) / stride1, 0);
     const int64_t OW = std::max<int64_t>(((int64_t)W + 2 * padding2 - KW + 1) / stride2, 0);
     auto Y = torch::empty({N, KN, OH, OW}, torch::device(X.device()).dtype(torch::kFloat32));
-    const size_t ws_bytes = tab_conv2d_workspace_bytes(type, N, H, W, C, KN, KH, KW);
+    const size_t ws_bytes = tab_conv2d_workspace_bytes(type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW);
     auto ws = torch::empty({(int64_t)std::max<size_t>(ws_bytes, 256)}, torch::device(X.device()).dtype(torch::kUInt8));
     check_rc(tab_conv2d_launch(X.data_ptr<float>(), QW.data_ptr<int64_t>(), thresholds.data_ptr<float>(),
                                btn.data_ptr<int32_t>(), Y.data_ptr<float>(), ws.data_ptr(), (size_t)ws.numel(), type,
@@ -111,7 +111,7 @@ std::vector<torch::Tensor> TAB_Conv2dFused(torch::Tensor X, torch::Tensor QW, to
         rptr = residual->data_ptr<float>();
     }
     auto Y = torch::empty({N, KN, OH, OW}, torch::device(X.device()).dtype(torch::kFloat32));
-    const size_t ws_bytes = tab_conv2d_workspace_bytes(type, N, H, W, C, KN, KH, KW);
+    const size_t ws_bytes = tab_conv2d_workspace_bytes(type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW);
     auto ws = torch::empty({(int64_t)std::max<size_t>(ws_bytes, 256)}, torch::device(X.device()).dtype(torch::kUInt8));
     torch::Tensor sums, next;
     if (threshold_scale > 0) sums = torch::empty({std::max(N, 1)}, torch::device(X.device()).dtype(torch::kFloat64));

@@ -89,7 +89,7 @@ def Conv2d(X, QW, thresholds, btn, type, padding1, padding2, stride1, stride2, N
     l = _cabi.lib()
     with torch.cuda.device(X.device):
         Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=X.device)
-        ws_bytes = l.tab_conv2d_workspace_bytes(conv_type, N, H, W, C, KN, KH, KW)
+        ws_bytes = l.tab_conv2d_workspace_bytes(conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
         ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=X.device)
         rc = l.tab_conv2d_launch(X.data_ptr(), QW.data_ptr(), thresholds.data_ptr(), btn.data_ptr(), Y.data_ptr(),
                                  ws.data_ptr(), ws.numel(), conv_type, p1, p2, s1, s2,
@@ -215,7 +215,7 @@ def Conv2dFused(X, QW, thresholds, btn, type, padding1, padding2, stride1, strid
     l = _cabi.lib()
     with torch.cuda.device(X.device):
         Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=X.device)
-        ws = torch.empty((max(l.tab_conv2d_workspace_bytes(conv_type, N, H, W, C, KN, KH, KW), 256),), dtype=torch.uint8, device=X.device)
+        ws = torch.empty((max(l.tab_conv2d_workspace_bytes(conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW), 256),), dtype=torch.uint8, device=X.device)
         sums = torch.empty((max(N, 1),), dtype=torch.float64, device=X.device) if threshold_scale is not None else None
         st = _stream_ptr(X.device)
         rc = l.tab_conv2d_fused_launch(X.data_ptr(), QW.data_ptr(), thresholds.data_ptr(), btn.data_ptr(), Y.data_ptr(),

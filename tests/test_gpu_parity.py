@@ -18,16 +18,17 @@ GOLD = os.path.join(os.path.dirname(__file__), "golden")
 NAMES = ["tnn", "tbn", "btn", "bnn"]
 
 
-@pytest.fixture(autouse=True, params=["tensor", "tensor-tcgen05", "tensor-mma-sync", "tensor-im2col", "popcount"])
+@pytest.fixture(autouse=True, params=["tensor", "tensor-tcgen05", "tensor-tma", "tensor-mma-sync", "tensor-im2col", "popcount"])
 def conv_path(request):
     """Every test of this module runs once per compute path of tab_conv2d_launch: the tensor-core GEMM with the
-    library's own choice of kernel, the same forced to the tcgen05 kernel, to the mma.sync kernels (patch or
+    library's own choice of kernel, the same forced to the tcgen05 kernels (cp.async-fed; TMA-fed where the shape
+    allows), to the mma.sync kernels (patch or
     im2col staging), to mma.sync with im2col staging only, and the popcount kernel.  After each test the
     tcgen05 kernel's record of expired waits must be clean."""
     l = _cabi.lib()
     l.tab_debug_umma_status.restype = int
     prev = l.tab_conv2d_set_path(1 if request.param == "popcount" else 0)
-    l.tab_debug_set_imma_variant({"tensor-tcgen05": 3, "tensor-mma-sync": 2, "tensor-im2col": 1}.get(request.param, 0))
+    l.tab_debug_set_imma_variant({"tensor-tcgen05": 3, "tensor-tma": 6, "tensor-mma-sync": 2, "tensor-im2col": 1}.get(request.param, 0))
     yield request.param
     l.tab_debug_set_imma_variant(0)
     l.tab_conv2d_set_path(prev)

@@ -35,7 +35,7 @@ def _both(l, cuda, t, geom, seed):
     OH, OW = (H + 2 * p1 - KH + 1) // s1, (W + 2 * p2 - KW + 1) // s2
     y_ws = torch.full((N * OH * OW * KN,), -7.0, device=cuda)
     y_st = torch.full((N * OH * OW * KN,), -9.0, device=cuda)
-    ws_bytes = l.tab_conv2d_workspace_bytes(t, N, H, W, C, KN, KH, KW)
+    ws_bytes = l.tab_conv2d_workspace_bytes(t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
     ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=cuda)
     stream = torch.cuda.current_stream(cuda).cuda_stream
     rc = l.tab_conv2d_launch(xd.data_ptr(), qw.data_ptr(), td.data_ptr(), btn.data_ptr(), y_ws.data_ptr(), ws.data_ptr(),
