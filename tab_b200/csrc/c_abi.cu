@@ -211,3 +211,9 @@ int tab_debug_umma_status(void) { return umma_status_read_and_clear(); }
 void tab_debug_set_csa(int on) { conv_set_csa(on != 0); }
 
 }  // extern "C"
+
+#ifdef TAB_PERSIST_PROFILE
+namespace tab { int persist_profile_read(unsigned long long* out16); void persist_set_debug(int v); }
+extern "C" void tab_debug_persist_set(int v) { tab::persist_set_debug(v); }
+extern "C" int tab_debug_persist_profile(unsigned long long* out16) { return tab::persist_profile_read(out16); }
+#endif

@@ -653,11 +653,12 @@ static int launch_imma(const ImmaParams& p, cudaStream_t stream) {
 }
 
 int conv_umma_dispatch(const ImmaParams& p, bool padone, int alt, cudaStream_t stream);
-int conv_tma_dispatch(const ImmaParams& p, cudaStream_t stream);
+int conv_tma_dispatch(const ImmaParams& p, int mode, cudaStream_t stream);
+bool conv_tma_persist_fits(const ImmaParams& p);
 
 // 0 = default choice, 1 = mma.sync with im2col staging, 2 = mma.sync (patch or im2col), 3 = tcgen05 (for A/B tests)
 static int g_imma_variant = 0;
-static const bool g_tma_default = false;   // the TMA-fed kernel is opt-in (variant 6) until it has been measured ahead
+static const bool g_tma_default = true;   // persistent TMA-fed kernel where it applies (measured ahead of the others)
 
 size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2) {
     const size_t Cp = (size_t)packed_channels(C) * 64;
@@ -760,12 +761,20 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
     int8_t* w8 = qx8 + ((size_t)N * (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2) * Cp + 255) / 256 * 256;
     rc = expand_weights_dispatch(qw, w8, weight_bits(type), KN, KH, KW, C, stream);
     if (rc != TAB_OK) return rc;
-    // TMA-fed tcgen05 kernel on padded activations: stride 1, at least 4 taps, most of the padded grid useful
+    // Persistent TMA-fed tcgen05 kernel on zero-padded activations: stride 1, at least 4 taps (with fewer, the padded
+    // grid costs more than the patch saves), and at least 45 % of the padded grid useful.
     {
         const long long PH = H + 2LL * p1, PW = W + 2LL * p2;
         const double useful = (double)oh * ow / ((double)PH * PW);
-        const bool want = g_imma_variant == 6 || (g_imma_variant == 0 && g_tma_default && useful >= 0.7 && KN > 64);
-        if (want && s1 == 1 && s2 == 1 && KH * KW >= 4 && N <= 65535 && N * PH * PW < (1LL << 31) - 4096) {
+        ImmaParams p;
+        p.qx = qx8; p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
+        p.N = N; p.H = H; p.W = W; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
+        p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
+        p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * p.PC;
+        const bool shape = s1 == 1 && s2 == 1 && KH * KW >= 4 && N <= 65535 && N * PH * PW < (1LL << 31) - 4096;
+        const bool want = shape && (g_imma_variant == 6 || g_imma_variant == 7 ||
+                                    (g_imma_variant == 0 && g_tma_default && useful >= 0.45 && conv_tma_persist_fits(p)));
+        if (want) {
             const long long groups = PH * PW * (Cp / 16);
             long long per = (groups + Q8THREADS - 1) / Q8THREADS;
             const long long cap = (148LL * 8 * 4 + N - 1) / N;
@@ -782,13 +791,8 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
             }
             rc = check_launch();
             if (rc != TAB_OK) return rc;
-            ImmaParams p;
-            p.qx = qx8; p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
-            p.N = N; p.H = H; p.W = W; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
-            p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
-            p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * p.PC;
-            rc = conv_tma_dispatch(p, stream);
-            if (rc != TAB_E_TOO_LARGE) return rc;     // shape not covered: continue with the unpadded form
+            rc = conv_tma_dispatch(p, g_imma_variant == 7 ? 2 : (g_imma_variant == 6 ? 1 : 0), stream);
+            if (rc != TAB_E_TOO_LARGE) return rc;     // shape not covered after all: continue with the unpadded form
         }
     }
     rc = quantize_int8_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, stream);

@@ -21,6 +21,7 @@
 #include <cuda.h>
 #include "tab_kernels.cuh"
 #include "conv_int8.cuh"
+#include <mutex>
 
 namespace tab {
 
@@ -311,7 +312,8 @@ static int launch_umma(const ImmaParams& p, bool padone, int* status, cudaStream
 // Epilogue of the kernels that enumerate output positions on the zero-padded input grid: virtual row -> output
 // pixel (rows outside the real output are dropped), TMEM -> registers -> float [M][KN], optional residual and
 // per-image sums of |y|.
-template <int MT, int TNI, bool FUSED>
+// NWH warp groups of four warps split the TN columns between them (warp = 4*group + TMEM lane quarter).
+template <int MT, int TNI, bool FUSED, int NWH = 2>
 __device__ __forceinline__ void grid_epilogue(const ImmaParams& p, uint32_t tmem_base, int R0, int n0, int PW, int PHW,
                                               int warp, int lane) {
     const int wq = warp & 3, wh = warp >> 2;
@@ -330,8 +332,8 @@ __device__ __forceinline__ void grid_epilogue(const ImmaParams& p, uint32_t tmem
         float* __restrict__ yrow = p.y + (row_ok ? m : 0) * p.KN;
         const float* __restrict__ rrow = (FUSED && p.residual) ? p.residual + (row_ok ? m : 0) * p.KN : nullptr;
 #pragma unroll 1
-        for (int cb = 0; cb < TNI / 2; cb += 32) {
-            const int col = wh * (TNI / 2) + cb;
+        for (int cb = 0; cb < TNI / NWH; cb += 32) {
+            const int col = wh * (TNI / NWH) + cb;
             uint32_t v[32];
             tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(mb * TNI + col), v);
             if (!row_ok) continue;
@@ -690,6 +692,365 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
 }
 
+// Epilogue with coalesced stores for a warp that owns TMEM lane quarter wq.  tcgen05.ld hands lane r the 32 columns
+// of accumulator row r; written straight out, one store instruction would touch 32 different output rows.  The warp
+// instead passes each 32x32 block through a private 4 KB shared-memory buffer (16-byte chunks XOR-swizzled by row, so
+// both directions are conflict-free) and stores it transposed: eight lanes cover 128 contiguous bytes of one row,
+// one instruction writes four full lines.  The residual is read the same way, and |y| is summed in double.
+__device__ __forceinline__ void sts_v4(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ int4 lds_v4(uint32_t a) {
+    int4 r;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(a) : "memory");
+    return r;
+}
+
+// The warp handles row blocks mb0, mb0 + mbstep, ... and columns [c0, c1) of the tile.
+template <int MT, int TNI, bool FUSED>
+__device__ __forceinline__ void grid_epilogue_coalesced(const ImmaParams& p, uint32_t tmem_base, int R0, int n0, int PW, int PHW,
+                                                        int wq, int lane, uint32_t stage, int mb0, int mbstep, int c0, int c1) {
+    const bool vec4 = (p.KN & 3) == 0;
+    const int rsub = lane >> 3, chunk = lane & 7;
+#pragma unroll 1
+    for (int mb = mb0; mb < MT; mb += mbstep) {
+        const int Rw = R0 + mb * UTM + wq * 32;
+        const int R = Rw + lane;
+        const int n = R / PHW;
+        const int rr = R - n * PHW;
+        const int oh = rr / PW;
+        const int ow = rr - oh * PW;
+        const bool row_ok = n < p.N && oh < p.OH && ow < p.OW;
+        const int wimg0 = Rw / PHW;                                        // image of the warp's first row
+        const int m = row_ok ? (n * p.OH + oh) * p.OW + ow : -1;           // output row (M < 2^31 is checked on the host)
+        const int d = n - wimg0;
+        int mi[8], di[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            mi[i] = __shfl_sync(0xFFFFFFFFu, m, 4 * i + rsub);
+            di[i] = __shfl_sync(0xFFFFFFFFu, d, 4 * i + rsub);
+        }
+        double acc0 = 0.0, acc1 = 0.0, acc2 = 0.0;
+#pragma unroll 1
+        for (int cb = c0; cb < c1; cb += 32) {
+            const int nbase = n0 + cb;
+            if (nbase >= p.KN) break;                                      // uniform over the warp
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(mb * TNI + cb), v);
+            if (vec4 && nbase + 32 <= p.KN) {
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    sts_v4(stage + lane * 128 + ((q ^ (lane & 7)) << 4), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                __syncwarp();
+                int4 raw[8];
+                float4 res[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = 4 * i + rsub;
+                    raw[i] = lds_v4(stage + r * 128 + ((chunk ^ (r & 7)) << 4));
+                    res[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (FUSED && p.residual && mi[i] >= 0)
+                        res[i] = __ldg(reinterpret_cast<const float4*>(p.residual + (long long)mi[i] * p.KN + nbase) + chunk);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (mi[i] < 0) continue;
+                    float4 o;
+                    o.x = (float)raw[i].x + res[i].x; o.y = (float)raw[i].y + res[i].y;
+                    o.z = (float)raw[i].z + res[i].z; o.w = (float)raw[i].w + res[i].w;
+                    reinterpret_cast<float4*>(p.y + (long long)mi[i] * p.KN + nbase)[chunk] = o;
+                    if (FUSED) {
+                        const double sabs = (double)((fabsf(o.x) + fabsf(o.y)) + (fabsf(o.z) + fabsf(o.w)));
+                        if (di[i] == 0) acc0 += sabs;
+                        else if (di[i] == 1) acc1 += sabs;
+                        else if (di[i] == 2) acc2 += sabs;
+                        else if (p.abs_sums) atomicAdd(p.abs_sums + wimg0 + di[i], sabs);
+                    }
+                }
+                __syncwarp();
+            } else if (row_ok) {
+                float* yrow = p.y + (long long)m * p.KN;
+                const float* rrow = (FUSED && p.residual) ? p.residual + (long long)m * p.KN : nullptr;
+                float rsum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    if (nbase + i < p.KN) {
+                        float o = (float)(int)v[i];
+                        if (FUSED && rrow) o += __ldg(rrow + nbase + i);
+                        yrow[nbase + i] = o;
+                        if (FUSED) rsum += fabsf(o);
+                    }
+                }
+                if (FUSED) {
+                    if (d == 0) acc0 += (double)rsum;
+                    else if (d == 1) acc1 += (double)rsum;
+                    else if (d == 2) acc2 += (double)rsum;
+                    else if (p.abs_sums) atomicAdd(p.abs_sums + n, (double)rsum);
+                }
+            }
+        }
+        if (FUSED && p.abs_sums) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, o);
+                acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, o);
+                acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, o);
+            }
+            if (lane == 0) {
+                if (acc0 != 0.0 && wimg0 < p.N) atomicAdd(p.abs_sums + wimg0, acc0);
+                if (acc1 != 0.0 && wimg0 + 1 < p.N) atomicAdd(p.abs_sums + wimg0 + 1, acc1);
+                if (acc2 != 0.0 && wimg0 + 2 < p.N) atomicAdd(p.abs_sums + wimg0 + 2, acc2);
+            }
+        }
+    }
+}
+
+// Persistent, warp-specialised form of the TMA kernel: one CTA per SM walks over tiles; warp 0 (one thread) issues the
+// tensor-map copies and runs ahead across tile boundaries, warp 1 (one thread) issues the MMAs into one of two TMEM
+// accumulator buffers, warps 4-7 drain the other buffer (tcgen05.ld -> float -> global) - so copies, MMAs and the
+// epilogue of consecutive tiles overlap.  Counters g (ring stages), q (patch buffers) and a (accumulator buffers)
+// run across tiles; barrier parities follow from them.
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
+}
+
+#ifdef TAB_PERSIST_PROFILE
+// Build-time instrumentation (off in the shipped library): cycles CTA 0's role threads spend in each wait.
+__device__ unsigned long long g_persist_prof[16];
+#define PWAIT(slot, call) ([&]() { const long long _t = clock64(); const bool _r = (call); prof[slot] += clock64() - _t; return _r; }())
+#else
+#define PWAIT(slot, call) (call)
+#endif
+
+// Bounded wait by a whole warp; the result is the same in every lane.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t addr, uint32_t parity) {
+    return __all_sync(0xFFFFFFFFu, mbar_wait(addr, parity));
+}
+// True in exactly one lane of a converged warp.  Role loops are run by the whole warp with the issuing instructions
+// under this predicate, so that loop counters, addresses and descriptors stay warp-uniform values.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
+#ifdef TAB_PERSIST_PROFILE
+#define PDBG(bit) ((dbg & (bit)) != 0)
+#else
+#define PDBG(bit) false
+#endif
+
+// BRES: the filter block of the CTA (all taps, all channel pairs; needs KN <= TNI) is copied once and stays in shared
+// memory; otherwise it streams through a ring of SB stages, one stage per tap and channel pair.
+constexpr int PTHREADS = 384;                                              // warps 0-2 producers and MMA, 3 idle, 4-11 epilogue
+
+template <int MT, int TNI, int SB, bool BRES, bool FUSED>
+__global__ void __launch_bounds__(PTHREADS, 1)
+conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const ImmaParams p, int* __restrict__ status, const int prow, const int nst,
+                         const int tiles_m, const int tiles_n, const int dbg) {
+    constexpr int BSTAGE = TNI * IROW;
+    constexpr int ACOLS = MT * TNI;                                        // columns of one accumulator buffer
+    static_assert(2 * ACOLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
+    static_assert(SB <= 8, "eight ring barriers are laid out");
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sbase = (raw + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (sbase - raw);
+    const uint32_t sPatch = sbase;                                         // [2][prow][128 B]
+    const uint32_t sRing = sbase + 2 * prow * IROW;                        // [nst][TNI][128 B]
+    const int tail = 2 * prow * IROW + nst * BSTAGE;
+    const uint32_t fullB = sbase + tail, emptyB = fullB + 64;              // [8] each
+    const uint32_t fullP = emptyB + 64, emptyP = fullP + 16, accFull = emptyP + 16, accEmpty = accFull + 16;
+    const uint32_t tslot = accEmpty + 16;                                  // = fullB + 192
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + tail + 192);
+    const uint32_t sStage = sbase + tail + 256;                            // [8 epilogue warps][4 KB]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int PH = p.H + 2 * p.p1, PW = p.W + 2 * p.p2, PHW = PH * PW;
+    const int T = p.KH * p.KW, ncp = (p.PC + 1) >> 1;
+    const int ntiles = tiles_m * tiles_n;
+
+    if (tid == 0) {
+        for (int s = 0; s < 22; s++) mbar_init(fullB + 8 * s, 1);
+        mbar_init(accEmpty, 8); mbar_init(accEmpty + 8, 8);                // one arrival per epilogue warp
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(tslot), "r"((uint32_t)(2 * ACOLS)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+#ifdef TAB_PERSIST_PROFILE
+    long long prof[3] = {0, 0, 0};
+    const long long prof_t0 = clock64();
+#endif
+    // In every role the whole warp runs the loops and the waits and one elected lane issues the copies, MMAs and
+    // commits: loop counters, addresses and descriptors then stay warp-uniform values (a single-thread role was
+    // measured to spend 130-170 cycles per MMA on issue alone; this form 45-90).
+    if (warp == 0) {
+        // ---- patch producer: runs ahead of the MMAs by up to two patches (across tile boundaries) ----------------
+        const int nbox = prow / TMA_BOX_ROWS;
+        unsigned q = 0;
+        bool dead = false;
+        for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x) {
+            const int R0 = (t / tiles_n) * (UTM * MT);
+            for (int cp = 0; cp < ncp; cp++, q++) {
+                const unsigned pb = q & 1;
+                if (q >= 2 && !PWAIT(0, mbar_wait_warp(emptyP + 8 * pb, ((q >> 1) - 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 11); break; }
+                if (elect_one()) {
+                    if (PDBG(2)) mbar_arrive(fullP + 8 * pb);
+                    else {
+                        mbar_expect_tx(fullP + 8 * pb, (uint32_t)(nbox * TMA_BOX_ROWS * IROW));
+                        for (int b = 0; b < nbox; b++)
+                            tma_load_2d(sPatch + (pb * prow + b * TMA_BOX_ROWS) * IROW, &tmA, 2 * cp * 64, R0 + b * TMA_BOX_ROWS, fullP + 8 * pb);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 2) {
+        // ---- filter producer ---------------------------------------------------------------------------------------
+        if (BRES) {
+            if (elect_one()) {
+                mbar_expect_tx(fullB, (uint32_t)(nst * BSTAGE));
+                for (int cp = 0; cp < ncp; cp++)
+                    for (int tap = 0; tap < T; tap++)
+                        tma_load_2d(sRing + (cp * T + tap) * BSTAGE, &tmB, (tap * p.PC + 2 * cp) * 64, 0, fullB);
+            }
+            __syncwarp();
+        } else {
+            unsigned g = 0;
+            bool dead = false;
+            for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x) {
+                const int n0 = (t % tiles_n) * TNI;
+                for (int cp = 0; cp < ncp && !dead; cp++) {
+                    for (int tap = 0; tap < T; tap++, g++) {
+                        const unsigned slot = g % SB;
+                        if (g >= (unsigned)SB && !PWAIT(1, mbar_wait_warp(emptyB + 8 * slot, ((g / SB) - 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 12); break; }
+                        if (elect_one()) {
+                            if (PDBG(4)) mbar_arrive(fullB + 8 * slot);
+                            else {
+                                mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
+                                tma_load_2d(sRing + slot * BSTAGE, &tmB, (tap * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
+                            }
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA warp --------------------------------------------------------------------------------------------------
+        constexpr uint32_t IDESC = umma_idesc(TNI);
+        constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+        constexpr uint32_t MB_UNITS = (UTM * IROW) >> 4;                   // next 128-row block of the patch, in 16-byte units
+        unsigned g = 0, q = 0, a = 0;
+        bool dead = false;
+        if (BRES && !PWAIT(2, mbar_wait_warp(fullB, 0))) { dead = true; if (status && lane == 0) atomicExch(status, 15); }
+        for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
+            const unsigned buf = a & 1;
+            if (a >= 2 && !PWAIT(0, mbar_wait_warp(accEmpty + 8 * buf, ((a >> 1) - 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 13); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem_base + buf * ACOLS;
+            for (int cp = 0; cp < ncp && !dead; cp++, q++) {
+                const unsigned pb = q & 1;
+                if (!PWAIT(1, mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 14); break; }
+                const bool four = 2 * cp + 1 < p.PC;                       // both 64-channel words of the pair exist
+                uint32_t arow = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;   // descriptor address of the tap's first patch row
+                int kw = 0;
+                if (BRES) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (elect_one()) {
+                        for (int tap = 0; tap < T; tap++) {
+                            const uint64_t da = ((uint64_t)DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4));
+                            const uint64_t db = ((uint64_t)DESC_HI << 32) | ((sRing + (uint32_t)(cp * T + tap) * BSTAGE) >> 4);
+                            const uint32_t first = (cp > 0 || tap > 0) ? 1u : 0u;
+#pragma unroll
+                            for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS, db, IDESC, first);
+#pragma unroll
+                            for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 2, db + 2, IDESC, 1u);
+                            if (four) {
+#pragma unroll
+                                for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 4, db + 4, IDESC, 1u);
+#pragma unroll
+                                for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 6, db + 6, IDESC, 1u);
+                            }
+                            if (++kw == p.KW) { kw = 0; arow += (uint32_t)PW * (IROW >> 4); }
+                        }
+                        umma_commit(emptyP + 8 * pb);
+                        if (cp == ncp - 1) umma_commit(accFull + 8 * buf);
+                    }
+                    __syncwarp();
+                    continue;
+                }
+                for (int tap = 0; tap < T; tap++, g++) {
+                    const unsigned slot = g % SB;
+                    if (!PWAIT(2, mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 15); break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (elect_one()) {
+                        const uint64_t da = ((uint64_t)DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4));
+                        const uint64_t db = ((uint64_t)DESC_HI << 32) | ((sRing + slot * BSTAGE) >> 4);
+                        const uint32_t first = (cp > 0 || tap > 0) ? 1u : 0u;
+#pragma unroll
+                        for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS, db, IDESC, first);
+#pragma unroll
+                        for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 2, db + 2, IDESC, 1u);
+                        if (four) {
+#pragma unroll
+                            for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 4, db + 4, IDESC, 1u);
+#pragma unroll
+                            for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 6, db + 6, IDESC, 1u);
+                        }
+                        umma_commit(emptyB + 8 * slot);
+                        if (tap == T - 1) {
+                            umma_commit(emptyP + 8 * pb);
+                            if (cp == ncp - 1) umma_commit(accFull + 8 * buf);
+                        }
+                    }
+                    __syncwarp();
+                    if (++kw == p.KW) { kw = 0; arow += (uint32_t)PW * (IROW >> 4); }
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ---- epilogue warps (TMEM lane quarter = warp % 4) --------------------------------------------------------
+        unsigned a = 0;
+        bool dead = false;
+        for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
+            const unsigned buf = a & 1;
+            const int R0 = (t / tiles_n) * (UTM * MT), n0 = (t % tiles_n) * TNI;
+            if (!PWAIT(0, mbar_wait_warp(accFull + 8 * buf, (a >> 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 16); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // two warps per TMEM lane quarter: they split the row blocks of a two-block tile, else the columns
+            const int wg = (warp - 4) >> 2;
+            if (!PDBG(1)) {
+                if (MT == 2) grid_epilogue_coalesced<MT, TNI, FUSED>(p, tmem_base + buf * ACOLS, R0, n0, PW, PHW, warp & 3, lane, sStage + (warp - 4) * 4096, wg, 2, 0, TNI);
+                else grid_epilogue_coalesced<MT, TNI, FUSED>(p, tmem_base + buf * ACOLS, R0, n0, PW, PHW, warp & 3, lane, sStage + (warp - 4) * 4096, 0, 1, wg * (TNI / 2), (wg + 1) * (TNI / 2));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accEmpty + 8 * buf);
+        }
+    }
+#ifdef TAB_PERSIST_PROFILE
+    if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 1 || warp == 4 || warp == 2)) {
+        const int o = warp == 0 ? 0 : (warp == 1 ? 4 : (warp == 4 ? 8 : 12));
+        g_persist_prof[o] = clock64() - prof_t0;
+        g_persist_prof[o + 1] = prof[0]; g_persist_prof[o + 2] = prof[1]; g_persist_prof[o + 3] = prof[2];
+    }
+#endif
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)(2 * ACOLS)) : "memory");
+    }
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -709,15 +1070,36 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D byte tensor [rows][row_bytes] (row pitch = row_bytes), box = 128 bytes x box_rows, 128-byte swizzle.
+// Encoding a map costs tens of microseconds on the host, more than a small convolution takes on the device, and
+// callers reuse their buffers: the last few maps are kept, keyed by everything that goes into them.
+struct MapKey { const void* base; unsigned long long row_bytes, rows; unsigned box_rows; };
 static bool make_map_2d(CUtensorMap* m, const void* base, unsigned long long row_bytes, unsigned long long rows, unsigned box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
+    constexpr int NCACHE = 32;
+    static std::mutex mu;
+    static MapKey keys[NCACHE] = {};
+    static CUtensorMap maps[NCACHE];
+    static int used = 0, next = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; i++) {
+        if (keys[i].base == base && keys[i].row_bytes == row_bytes && keys[i].rows == rows && keys[i].box_rows == box_rows) {
+            *m = maps[i];
+            return true;
+        }
+    }
     const cuuint64_t dims[2] = {row_bytes, rows};
     const cuuint64_t strides[1] = {row_bytes};
     const cuuint32_t box[2] = {128, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    keys[next] = MapKey{base, row_bytes, rows, box_rows};
+    maps[next] = *m;
+    next = (next + 1) % NCACHE;
+    if (used < NCACHE) used++;
+    return true;
 }
 
 template <int MT, int TNI, int SB, bool FUSED>
@@ -752,19 +1134,111 @@ static int launch_umma_tma(const CUtensorMap& tmA, const CUtensorMap& tmB, const
                                       : launch_umma_tma_f<MT, TNI, SB, false>(tmA, tmB, p, status, prow, npb, stream);
 }
 
+static int g_persist_dbg = 0;
+void persist_set_debug(int v) { g_persist_dbg = v; }
+
+template <int MT, int TNI, int SB, bool BRES, bool FUSED>
+static int launch_umma_persist_f(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, int prow, int nst,
+                                 int smem_bytes, cudaStream_t stream) {
+    constexpr int TMI = UTM * MT;
+    static int configured[64] = {};
+    int dev = 0, sms = 148;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (dev < 0 || dev >= 64 || configured[dev] < smem_bytes) {
+        e = cudaFuncSetAttribute(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (dev >= 0 && dev < 64) configured[dev] = UMMA_SMEM_MAX;
+    }
+    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2;
+    const long long Mv = (long long)(p.N - 1) * PH * PW + (long long)(p.OH - 1) * PW + p.OW;
+    const long long tiles_m = (Mv + TMI - 1) / TMI, tiles_n = (p.KN + TNI - 1) / TNI;
+    if (tiles_m * tiles_n >= (1LL << 31)) return TAB_E_TOO_LARGE;
+    const long long ntiles = tiles_m * tiles_n;
+    const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
+    conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED><<<grid, PTHREADS, smem_bytes, stream>>>(tmA, tmB, p, status, prow, nst, (int)tiles_m,
+                                                                                             (int)tiles_n, g_persist_dbg);
+    return check_launch();
+}
+
+// Shared-memory need of the persistent kernel for a tile shape; resident (out) says whether the filter block stays
+// in shared memory.  0 = does not fit.
+static long long persist_smem(const ImmaParams& p, int mt, int tn, int sb, bool* resident) {
+    const long long PW = p.W + 2LL * p.p2;
+    const long long prow = (UTM * mt + (p.KH - 1) * PW + p.KW - 1 + TMA_BOX_ROWS - 1) / TMA_BOX_ROWS * TMA_BOX_ROWS;
+    const long long fixed = 2 * prow * IROW + 256 + 8 * 4096 + 1024;
+    const long long nres = (long long)p.KH * p.KW * ((p.PC + 1) / 2);     // stages of a resident filter block
+    if (p.KN <= tn && fixed + nres * tn * IROW <= UMMA_SMEM_MAX) { *resident = true; return fixed + nres * tn * IROW; }
+    *resident = false;
+    const long long need = fixed + (long long)sb * tn * IROW;
+    return need <= UMMA_SMEM_MAX ? need : 0;
+}
+
+template <int MT, int TNI, int SB>
+static int launch_umma_persist(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, cudaStream_t stream) {
+    const long long PW = p.W + 2LL * p.p2;
+    const int prow = (int)((UTM * MT + (p.KH - 1) * PW + p.KW - 1 + TMA_BOX_ROWS - 1) / TMA_BOX_ROWS * TMA_BOX_ROWS);
+    bool resident = false;
+    const long long smem_bytes = persist_smem(p, MT, TNI, SB, &resident);
+    if (!smem_bytes) return TAB_E_TOO_LARGE;
+    const bool fused = p.residual || p.abs_sums;
+    if (resident) {
+        const int nres = p.KH * p.KW * ((p.PC + 1) / 2);
+        return fused ? launch_umma_persist_f<MT, TNI, SB, true, true>(tmA, tmB, p, status, prow, nres, (int)smem_bytes, stream)
+                     : launch_umma_persist_f<MT, TNI, SB, true, false>(tmA, tmB, p, status, prow, nres, (int)smem_bytes, stream);
+    }
+    return fused ? launch_umma_persist_f<MT, TNI, SB, false, true>(tmA, tmB, p, status, prow, SB, (int)smem_bytes, stream)
+                 : launch_umma_persist_f<MT, TNI, SB, false, false>(tmA, tmB, p, status, prow, SB, (int)smem_bytes, stream);
+}
+
+// Tile of the persistent kernel for a problem: N tile by filter count; two row blocks per tile when the patch of a
+// wide image still fits.  false = no shape fits (wide images with many taps).
+static bool persist_plan(const ImmaParams& p, int* mt, int* tn) {
+    bool res;
+    *tn = p.KN <= 64 ? 64 : (p.KN <= 128 ? 128 : 256);
+    if (*tn == 256) { *mt = 1; return persist_smem(p, 1, 256, 4, &res) != 0; }
+    const int sb2 = *tn == 64 ? 6 : 4, sb1 = 6;
+    if (persist_smem(p, 2, *tn, sb2, &res)) { *mt = 2; return true; }
+    *mt = 1;
+    return persist_smem(p, 1, *tn, sb1, &res) != 0;
+}
+
+static bool tma_shape_ok(const ImmaParams& p) {
+    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2, rows = (long long)p.N * PH * PW;
+    return p.s1 == 1 && p.s2 == 1 && rows < (1LL << 31) - 4096;
+}
+
+// Whether conv_tma_dispatch(p, 0, ..) will take the problem (asked before the activations are laid out padded).
+bool conv_tma_persist_fits(const ImmaParams& p) {
+    int mt, tn;
+    return tma_shape_ok(p) && persist_plan(p, &mt, &tn);
+}
+
 static int* umma_status_ptr();
 
 // GEMM stage of the TMA variant.  p.qx must be the PADDED byte activations [N*PH*PW][Cp]; stride 1 only.
 // shape: 0 = choose by filter count; returns TAB_E_TOO_LARGE when the shape does not fit (caller falls back).
-int conv_tma_dispatch(const ImmaParams& p, cudaStream_t stream) {
+// mode 0: persistent kernel or TAB_E_TOO_LARGE; 1: persistent kernel, else the one-tile-per-CTA TMA kernel; 2: the latter only.
+// TAB_E_TOO_LARGE = shape not covered (the caller falls back to the kernels on unpadded activations).
+int conv_tma_dispatch(const ImmaParams& p, int mode, cudaStream_t stream) {
     const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2, rows = (long long)p.N * PH * PW;
-    if (p.s1 != 1 || p.s2 != 1 || rows >= (1LL << 31) - 4096 || !encode_tiled_fn()) return TAB_E_TOO_LARGE;
+    if (!tma_shape_ok(p) || !encode_tiled_fn()) return TAB_E_TOO_LARGE;
     if ((reinterpret_cast<uintptr_t>(p.qx) & 15) || (reinterpret_cast<uintptr_t>(p.w8) & 15)) return TAB_E_TOO_LARGE;
     alignas(64) CUtensorMap tmA, tmB;
     const unsigned tn = p.KN <= 64 ? 64 : (p.KN <= 128 ? 128 : 256);
     if (!make_map_2d(&tmA, p.qx, (unsigned long long)p.PC * 64, (unsigned long long)rows, TMA_BOX_ROWS)) return TAB_E_TOO_LARGE;
     if (!make_map_2d(&tmB, p.w8, (unsigned long long)p.Kw * 64, (unsigned long long)p.KN, tn)) return TAB_E_TOO_LARGE;
     int* status = umma_status_ptr();
+    if (mode != 2) {
+        int mt = 0, ptn = 0;
+        if (persist_plan(p, &mt, &ptn)) {
+            if (ptn == 64) return mt == 2 ? launch_umma_persist<2, 64, 6>(tmA, tmB, p, status, stream) : launch_umma_persist<1, 64, 6>(tmA, tmB, p, status, stream);
+            if (ptn == 128) return mt == 2 ? launch_umma_persist<2, 128, 4>(tmA, tmB, p, status, stream) : launch_umma_persist<1, 128, 6>(tmA, tmB, p, status, stream);
+            return launch_umma_persist<1, 256, 4>(tmA, tmB, p, status, stream);
+        }
+        if (mode == 0) return TAB_E_TOO_LARGE;
+    }
     if (tn == 64) return launch_umma_tma<2, 64, 4>(tmA, tmB, p, status, stream);
     if (tn == 128) return launch_umma_tma<2, 128, 4>(tmA, tmB, p, status, stream);
     return launch_umma_tma<2, 256, 4>(tmA, tmB, p, status, stream);
@@ -860,5 +1334,148 @@ int conv_umma_dispatch(const ImmaParams& p, bool padone, int alt, cudaStream_t s
     return best.mt == 2 ? launch_umma<2, 64, 5>(p, padone, status, stream)                          // 256 x 64,  5 x 41 KB
                         : launch_umma<1, 64, 8>(p, padone, status, stream);                         // 128 x 64,  8 x 25 KB
 }
+
+// Issue-rate probe for the tensor pipe: every CTA (one per SM) issues `iters` x 4 int8 MMAs of 128 x TN x 32 on
+// operands that already sit in shared memory (K-major, 128-byte swizzle, as the convolution kernels lay them out),
+// with no copies and no epilogue - the rate the GEMM kernels can at best reach for that instruction shape.
+// mode 0: back-to-back MMAs, one commit at the end.  mode 1: a commit after every group of 4 x NA MMAs (nobody
+// waits on it).  mode 2: the groups go through a ring of four slots with the full/empty handshake the convolution
+// kernels use (another thread plays the producer, without copying anything).
+template <int TNI, int NA>
+__global__ void __launch_bounds__(128, 1) umma_probe_kernel(uint32_t* __restrict__ sink, int iters, int* __restrict__ status,
+                                                            int shift_rows, int mode) {
+    constexpr int S = 4;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t sbase = (raw + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (sbase - raw);
+    const uint32_t sA = sbase + shift_rows * IROW, sB = sbase + (NA * UTM + 8) * IROW;
+    const int tail = (NA * UTM + 8) * IROW + TNI * IROW;
+    const uint32_t done = sbase + tail, dummy = done + 8, full = done + 16, empty = full + 8 * S, tslot = empty + 8 * S;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + tail + 16 + 16 * S);
+    for (int i = threadIdx.x; i < tail / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0x01ff0001u * (uint32_t)(i % 3);
+    constexpr int TCOLS = NA * TNI < 32 ? 32 : NA * TNI;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2 + 2 * S; i++) mbar_init(done + 8 * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(tslot), "r"((uint32_t)TCOLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 32 && mode == 2) {
+        for (unsigned g = 0; g < (unsigned)iters; g++) {
+            const unsigned slot = g % S;
+            if (g >= (unsigned)S && !mbar_wait(empty + 8 * slot, ((g / S) - 1) & 1u)) { if (status) atomicExch(status, 21); break; }
+            mbar_arrive(full + 8 * slot);
+        }
+    }
+    if (mode == 3) {
+        // mode 2 with both roles run by whole warps and the issuing instructions under elect_one()
+        const int warp = threadIdx.x >> 5;
+        if (warp == 1) {
+            for (unsigned g = 0; g < (unsigned)iters; g++) {
+                const unsigned slot = g % S;
+                if (g >= (unsigned)S && !mbar_wait(empty + 8 * slot, ((g / S) - 1) & 1u)) { if (status) atomicExch(status, 21); break; }
+                if (elect_one()) mbar_arrive(full + 8 * slot);
+                __syncwarp();
+            }
+        } else if (warp == 0) {
+            constexpr uint32_t IDESC = umma_idesc(TNI);
+            const uint64_t db = umma_desc(sB);
+            const long long t0 = clock64();
+            for (unsigned it = 0; it < (unsigned)iters; it++) {
+                const unsigned slot = it % S;
+                if (!mbar_wait(full + 8 * slot, (it / S) & 1u)) { if (status) atomicExch(status, 22); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (elect_one()) {
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+#pragma unroll
+                        for (int a = 0; a < NA; a++)
+                            umma_i8(tmem_base + a * TNI, umma_desc(sA + a * UTM * IROW) + 2 * k, db + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty + 8 * slot);
+                }
+                __syncwarp();
+            }
+            if (elect_one()) umma_commit(done);
+            __syncwarp();
+            const long long t1 = clock64();
+            if (!mbar_wait(done, 0) && status) atomicExch(status, 20);
+            const long long t2 = clock64();
+            if (threadIdx.x == 0) { sink[2 * blockIdx.x] = (uint32_t)(t1 - t0); sink[2 * blockIdx.x + 1] = (uint32_t)(t2 - t0); }
+        }
+    } else if (threadIdx.x == 0) {
+        constexpr uint32_t IDESC = umma_idesc(TNI);
+        const uint64_t db = umma_desc(sB);
+        const long long t0 = clock64();
+        for (unsigned it = 0; it < (unsigned)iters; it++) {
+            const unsigned slot = it % S;
+            if (mode == 2) {
+                if (!mbar_wait(full + 8 * slot, (it / S) & 1u)) { if (status) atomicExch(status, 22); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+#pragma unroll
+                for (int a = 0; a < NA; a++)
+                    umma_i8(tmem_base + a * TNI, umma_desc(sA + a * UTM * IROW) + 2 * k, db + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            }
+            if (mode == 1) umma_commit(dummy);
+            if (mode == 2) umma_commit(empty + 8 * slot);
+        }
+        umma_commit(done);
+        const long long t1 = clock64();
+        if (!mbar_wait(done, 0) && status) atomicExch(status, 20);
+        const long long t2 = clock64();
+        sink[2 * blockIdx.x] = (uint32_t)(t1 - t0);                         // cycles spent issuing
+        sink[2 * blockIdx.x + 1] = (uint32_t)(t2 - t0);                     // cycles until the last MMA retired
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TCOLS) : "memory");
+    }
+}
+
+template <int TNI, int NA>
+static int launch_umma_probe(uint32_t* sink, int iters, int blocks, int shift_rows, int mode, cudaStream_t stream) {
+    const int smem_bytes = (NA * UTM + 8) * IROW + TNI * IROW + 128 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(umma_probe_kernel<TNI, NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    umma_probe_kernel<TNI, NA><<<blocks, 128, smem_bytes, stream>>>(sink, iters, umma_status_ptr(), shift_rows, mode);
+    return check_launch();
+}
+
+// code = shape + 5 * shift + 40 * mode.  shape: 0 = N 64, 1 = N 128, 2 = N 256 (one A tile); 3 = N 64, 4 = N 128 with
+// two A tiles sharing each B slice.  shift (0..7): rows by which A starts into its 1024-byte swizzle group.
+// Returns the int8 operations of the whole launch through ops_out.
+int umma_probe_dispatch(int code, int iters, uint32_t* sink, int blocks, double* ops_out, cudaStream_t stream) {
+    const int mode = code / 40, shift_rows = (code % 40) / 5, shape = code % 5;
+    if (mode > 3) return TAB_E_BAD_ARGUMENT;
+    const int tn = (shape == 0 || shape == 3) ? 64 : ((shape == 1 || shape == 4) ? 128 : 256);
+    const int na = shape >= 3 ? 2 : 1;
+    if (ops_out) *ops_out = (double)blocks * iters * 4.0 * na * (128.0 * tn * 32 * 2);
+    switch (shape) {
+        case 0: return launch_umma_probe<64, 1>(sink, iters, blocks, shift_rows, mode, stream);
+        case 1: return launch_umma_probe<128, 1>(sink, iters, blocks, shift_rows, mode, stream);
+        case 2: return launch_umma_probe<256, 1>(sink, iters, blocks, shift_rows, mode, stream);
+        case 3: return launch_umma_probe<64, 2>(sink, iters, blocks, shift_rows, mode, stream);
+        case 4: return launch_umma_probe<128, 2>(sink, iters, blocks, shift_rows, mode, stream);
+    }
+    return TAB_E_BAD_ARGUMENT;
+}
+
+#ifdef TAB_PERSIST_PROFILE
+int persist_profile_read(unsigned long long* out16) {
+    return cudaMemcpyFromSymbol(out16, g_persist_prof, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 }  // namespace tab

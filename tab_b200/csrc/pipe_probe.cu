@@ -104,15 +104,18 @@ static int probe_blocks() {
 
 }  // namespace tab
 
+namespace tab { int umma_probe_dispatch(int shape, int iters, uint32_t* sink, int blocks, double* ops_out, cudaStream_t stream); }
+
 using namespace tab;
 
 extern "C" size_t tab_pipe_probe_sink_bytes(void) { return (size_t)probe_blocks() * PROBE_THREADS * 4; }
 
 extern "C" int tab_pipe_probe_launch(int kind, int iters, void* sink, double* ops_out, tab_stream_t stream) {
-    if (kind < 0 || kind > 4 || iters < 1) return TAB_E_BAD_ARGUMENT;
+    if (kind < 0 || kind > 164 || iters < 1) return TAB_E_BAD_ARGUMENT;
     if (!sink) return TAB_E_NULL_POINTER;
     const int blocks = probe_blocks();
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (kind >= 5) return umma_probe_dispatch(kind - 5, iters, (uint32_t*)sink, blocks / 8, ops_out, s);   // one CTA per SM
     if (kind == 0) pipe_probe_kernel<0><<<blocks, PROBE_THREADS, 0, s>>>((uint32_t*)sink, iters, 12345u);
     else if (kind == 1) pipe_probe_kernel<1><<<blocks, PROBE_THREADS, 0, s>>>((uint32_t*)sink, iters, 12345u);
     else if (kind == 2) imma_probe_kernel<<<blocks, PROBE_THREADS, 0, s>>>((uint32_t*)sink, iters, 12345u);
