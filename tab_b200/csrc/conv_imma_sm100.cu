@@ -80,14 +80,16 @@ quantize_int8_kernel(const float* __restrict__ x, const float* __restrict__ ths,
 // Same quantiser writing a zero-padded (or +1-padded, for binary activations) tensor [N][PH][PW][Cp]: the input
 // of the TMA-fed GEMM, which reads padding taps like any other pixel.  One thread per 16 channels of a PADDED
 // pixel; border pixels get the padding value in the real channels and 0 in the channel padding.
+// The quantised grid may subsample the input: its pixel (i, j) is input pixel (i*sy, j*sx) and it has Hq x Wq
+// pixels before padding (a strided 1x1 convolution only ever reads those pixels).
 template <int BITS, bool VEC>
 __global__ void __launch_bounds__(Q8THREADS)
 quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict__ ths, int8_t* __restrict__ q,
-                            int H, int W, int C, int Cp, int p1, int p2) {
+                            int H, int W, int C, int Cp, int p1, int p2, int Hq, int Wq, int sy, int sx) {
     const int n = blockIdx.y;
     const float t = __ldg(ths + n), nt = -t;
     const int gpp = Cp >> 4;
-    const int PH = H + 2 * p1, PW = W + 2 * p2;
+    const int PH = Hq + 2 * p1, PW = Wq + 2 * p2;
     const long long groups = (long long)PH * PW * gpp;
     const float* xi = x + (long long)n * H * W * C;
     int8_t* qi = q + (long long)n * PH * PW * Cp;
@@ -97,8 +99,8 @@ quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict
         const int ph = (int)(pix / PW), pw = (int)(pix - (long long)ph * PW);
         const int ih = ph - p1, iw = pw - p2;
         uint32_t o[4];
-        if ((unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) {
-            const float* src = xi + ((long long)ih * W + iw) * C + c0;
+        if ((unsigned)ih < (unsigned)Hq && (unsigned)iw < (unsigned)Wq) {
+            const float* src = xi + ((long long)ih * sy * W + (long long)iw * sx) * C + c0;
             float v[16];
             if (VEC && c0 + 16 <= C) {
 #pragma unroll
@@ -761,43 +763,58 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
     int8_t* w8 = qx8 + ((size_t)N * (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2) * Cp + 255) / 256 * 256;
     rc = expand_weights_dispatch(qw, w8, weight_bits(type), KN, KH, KW, C, stream);
     if (rc != TAB_OK) return rc;
-    // Persistent TMA-fed tcgen05 kernel on zero-padded activations: stride 1, at least 4 taps (with fewer, the padded
-    // grid costs more than the patch saves), and at least 45 % of the padded grid useful.
+    // A strided 1x1 convolution without padding reads only every s-th pixel: quantise just those, densely, and run
+    // it as a stride-1 convolution on the subsampled grid.
+    int Hq = H, Wq = W, sy = 1, sx = 1, S1 = s1, S2 = s2;
+    if (KH == 1 && KW == 1 && p1 == 0 && p2 == 0 && (s1 > 1 || s2 > 1)) { Hq = (int)oh; Wq = (int)ow; sy = s1; sx = s2; S1 = S2 = 1; }
+    const bool subsampled = sy > 1 || sx > 1;
+    auto quantize_padded = [&](int q1, int q2) -> int {
+        const long long PH = Hq + 2LL * q1, PW = Wq + 2LL * q2;
+        const long long groups = PH * PW * (Cp / 16);
+        long long per = (groups + Q8THREADS - 1) / Q8THREADS;
+        const long long cap = (148LL * 8 * 4 + N - 1) / N;
+        if (per > cap) per = cap;
+        if (per < 1) per = 1;
+        dim3 grid((unsigned)per, (unsigned)N);
+        const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)H * W * C) % 8 == 0);
+        if (act_bits(type) == 2) {
+            if (vec) quantize_int8_padded_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, q1, q2, Hq, Wq, sy, sx);
+            else quantize_int8_padded_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, q1, q2, Hq, Wq, sy, sx);
+        } else {
+            if (vec) quantize_int8_padded_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, q1, q2, Hq, Wq, sy, sx);
+            else quantize_int8_padded_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, q1, q2, Hq, Wq, sy, sx);
+        }
+        return check_launch();
+    };
+    // Persistent TMA-fed tcgen05 kernel on zero-padded activations: stride 1; at least 4 taps unless there is no
+    // padding at all (with fewer, the padded grid costs more than the patch saves); at least 45 % of the padded
+    // grid useful.
+    bool quantized = false;
     {
-        const long long PH = H + 2LL * p1, PW = W + 2LL * p2;
+        const long long PH = Hq + 2LL * p1, PW = Wq + 2LL * p2;
         const double useful = (double)oh * ow / ((double)PH * PW);
         ImmaParams p;
         p.qx = qx8; p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
-        p.N = N; p.H = H; p.W = W; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
-        p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
+        p.N = N; p.H = Hq; p.W = Wq; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
+        p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = S1; p.s2 = S2;
         p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * p.PC;
-        const bool shape = s1 == 1 && s2 == 1 && KH * KW >= 4 && N <= 65535 && N * PH * PW < (1LL << 31) - 4096;
+        const bool shape = S1 == 1 && S2 == 1 && (KH * KW >= 4 || (p1 == 0 && p2 == 0)) && N <= 65535 &&
+                           N * PH * PW < (1LL << 31) - 4096;
         const bool want = shape && (g_imma_variant == 6 || g_imma_variant == 7 ||
                                     (g_imma_variant == 0 && g_tma_default && useful >= 0.45 && conv_tma_persist_fits(p)));
         if (want) {
-            const long long groups = PH * PW * (Cp / 16);
-            long long per = (groups + Q8THREADS - 1) / Q8THREADS;
-            const long long cap = (148LL * 8 * 4 + N - 1) / N;
-            if (per > cap) per = cap;
-            if (per < 1) per = 1;
-            dim3 grid((unsigned)per, (unsigned)N);
-            const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)H * W * C) % 8 == 0);
-            if (act_bits(type) == 2) {
-                if (vec) quantize_int8_padded_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2);
-                else quantize_int8_padded_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2);
-            } else {
-                if (vec) quantize_int8_padded_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2);
-                else quantize_int8_padded_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2);
-            }
-            rc = check_launch();
+            rc = quantize_padded(p1, p2);
             if (rc != TAB_OK) return rc;
+            quantized = p1 == 0 && p2 == 0;           // without padding the layout is the one the other kernels read
             rc = conv_tma_dispatch(p, g_imma_variant == 7 ? 2 : (g_imma_variant == 6 ? 1 : 0), stream);
             if (rc != TAB_E_TOO_LARGE) return rc;     // shape not covered after all: continue with the unpadded form
         }
     }
-    rc = quantize_int8_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, stream);
-    if (rc != TAB_OK) return rc;
-    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream, residual, abs_sums);
+    if (!quantized) {
+        rc = subsampled ? quantize_padded(0, 0) : quantize_int8_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, stream);
+        if (rc != TAB_OK) return rc;
+    }
+    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, S1, S2, N, Hq, Wq, C, KN, KH, KW, stream, residual, abs_sums);
 }
 
 }  // namespace tab

@@ -173,6 +173,9 @@ def test_conv_grid(cuda, t, K, p, s):
     (1, 1, 1, 1, 5, 13, 11, 64, 257, 3, 3),     # M and KN not multiples of the CTA tile
     (0, 0, 1, 1, 2, 3, 3, 1024, 1024, 1, 1),    # KN = 1024 (impossible on the reference launch shape)
     (1, 1, 1, 1, 1, 4, 4, 4608, 3, 3, 3),       # 72 words per tap
+    (0, 0, 2, 3, 2, 11, 10, 128, 70, 1, 1),     # strided 1x1 without padding: only the pixels it reads are quantised
+    (0, 0, 2, 2, 3, 14, 14, 256, 512, 1, 1),
+    (0, 0, 1, 1, 2, 9, 9, 64, 64, 2, 2),        # 2x2 taps, no padding
 ])
 def test_conv_shapes(cuda, t, geom):
     p1, p2, s1, s2, N, H, W, C, KN, KH, KW = geom
