@@ -20,9 +20,12 @@ step (activation quantise, residual add, thresholds) counts as time but not as o
 ``e2e``     the same step through the TAB_CUDA extension module with the input in pinned host memory: the
             host-to-device copy of the shard and the device-to-host copy of the gathered output are timed.  The shard
             is processed in four chunks of images so that the copy of one chunk overlaps the forward of the previous.
-``roofline`` for the dominant kernels (the int8 tensor-core GEMM stage of the convolution: tcgen05 kind::i8,
-            mma.sync s8 for <= 64 filters), timed alone per layer on pre-quantised byte operands;
-            denominator = 2 x the measured bf16 tensor peak.
+``roofline`` for the dominant kernels (the int8 tensor-core GEMM stage of the convolution: the persistent TMA-fed
+            tcgen05 kind::i8 kernel, the cp.async-fed one for stride-2 3x3), timed alone per layer on pre-quantised byte
+            operands; denominator = the tcgen05 int8 rate measured in the same run by the library's issue probe
+            (MMAs from shared memory, no copies), which is above 2 x the measured bf16 peak.
+``roofline_hbm_layers`` the launches of that stage that are bound by their bytes rather than their MMAs, in GB/s
+            against the measured copy bandwidth.
 ``roofline_popcount`` the bit-packed LOP3/POPC kernel on the same layers against the integer-pipe bound derived
             from POPC and LOP3 issue rates measured in the same run by the library's register-only probe.
 ``cpu_baseline`` / ``--impl reference``: the reference's CPU algorithm (quantise, pad, im2row, its own
@@ -50,6 +53,8 @@ GLOBAL_BATCH = 256
 H0 = W0 = 56
 C0 = 64
 CONV_TYPE = 0
+# dram__bytes_read.sum + dram__bytes_write.sum of conv_umma_persist_kernel on the 56x56x64->64 layer at N=256 (one ncu capture)
+PERSIST_L1_TRAFFIC = None
 WEIGHT_SEED = 5000
 INPUT_SEED = 5
 
@@ -265,16 +270,17 @@ def main():
     launches = [0]
 
     class CountingOps:
-        """tab_b200.ops with a kernel-launch counter (each Conv2d = quantise + weight-expand + GEMM kernels;
-        each residual_threshold = reduce + finalise kernels)."""
+        """tab_b200.ops with a kernel-launch counter (each Conv2d or Conv2dFused = two kernels: quantise, with the weight
+        expansion and the clears folded in, and the GEMM, whose last CTA also finishes the next thresholds; each
+        residual_threshold = reduce + finalise kernels)."""
         @staticmethod
         def Conv2d(*a):
-            launches[0] += 3
+            launches[0] += 2
             return tab_ops.Conv2d(*a)
 
         @staticmethod
         def Conv2dFused(*a):
-            launches[0] += 4                     # quantise + weight-expand + GEMM(+residual,+stats) + thresholds
+            launches[0] += 2
             return tab_ops.Conv2dFused(*a)
 
         @staticmethod
@@ -334,7 +340,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- CUDA graph of one forward (the step is ~75 short launches: replaying a graph removes the launch
+    # ---- CUDA graph of one forward (the step is ~40 short launches: replaying a graph removes the launch
     #      gaps; the library's launches take a stream and never allocate or synchronise, so they capture) ----
     graphs = {}
 
@@ -450,7 +456,7 @@ def main():
         for i in range(4):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            _cabi.check(lib.tab_pipe_probe_launch(kind, 4096, sink.data_ptr(), ctypes.byref(n_ops), stream), "probe")
+            _cabi.check(lib.tab_pipe_probe_launch(kind, 4096 if kind < 5 else 1024, sink.data_ptr(), ctypes.byref(n_ops), stream), "probe")
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1)
@@ -470,7 +476,9 @@ def main():
     naive_popc_tops = popc_rate * 64 / 2 / 1e12
 
     layer_rows = []
-    sums = {"gemm_ms": 0.0, "popc_ms": 0.0, "call_ms": 0.0, "ops": 0}
+    sums = {"gemm_ms": 0.0, "popc_ms": 0.0, "call_ms": 0.0, "ops": 0, "hbm_ms": 0.0, "hbm_bytes": 0}
+    umma_tops = probe(7) / 1e12        # tcgen05.mma kind::i8 128x256x32 from shared memory, no copies: the tensor ceiling
+    hbm_peak_guess, tensor_peak_guess = 6.5e12, umma_tops * 1e12           # only to label a layer memory- or tensor-bound
     if not args.no_layer_table:
         h = H0
         jobs = []
@@ -501,37 +509,73 @@ def main():
             ths = tab_ops.residual_threshold(xin, None, 0.7)
             qw, btn = qweights[cs.name]
             qx = tab_ops.Quantize(xin, ths, 2, n_local, ih, ih, cs.C)[0]
-            q8 = tab_ops.quantize_int8(xin, ths, 2, n_local, ih, ih, cs.C)
             w8 = tab_ops.expand_weights(qw, 2, cs.KN, cs.K, cs.K, cs.C)
             yb = torch.empty(n_local * oh * oh * cs.KN, dtype=torch.float32, device=dev)
             geom = (cs.pad, cs.pad, cs.stride, cs.stride, n_local, ih, ih, cs.C, cs.KN, cs.K, cs.K)
-            ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_launch(q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "int8"))
+            # the GEMM stage alone, through the kernel tab_conv2d_launch picks for this layer
+            if cs.stride == 1:
+                q8 = tab_ops.quantize_int8_padded(xin, ths, 2, n_local, ih, ih, cs.C, cs.pad, cs.pad)
+                gemm_kernel = "persistent tcgen05 (TMA)"
+                ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_padded_launch(
+                    q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, cs.pad, cs.pad, n_local, ih, ih, cs.C, cs.KN, cs.K, cs.K, stream), "int8p"))
+                in_bytes = q8.numel()
+            elif cs.K == 1 and cs.pad == 0:
+                xs = xin[:, ::cs.stride, ::cs.stride, :].contiguous()      # the strided 1x1 reads only these pixels
+                q8 = tab_ops.quantize_int8_padded(xs, ths, 2, n_local, oh, oh, cs.C, 0, 0)
+                gemm_kernel = "persistent tcgen05 (TMA), subsampled input"
+                ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_padded_launch(
+                    q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, 0, 0, n_local, oh, oh, cs.C, cs.KN, 1, 1, stream), "int8p"))
+                in_bytes = q8.numel()
+            else:
+                q8 = tab_ops.quantize_int8(xin, ths, 2, n_local, ih, ih, cs.C)
+                gemm_kernel = "tcgen05 (cp.async im2col)"
+                ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_launch(q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "int8"))
+                in_bytes = q8.numel()
             ms_popc = time_launch(lambda: _cabi.check(lib.tab_conv2d_packed_launch(qx.data_ptr(), qw.data_ptr(), btn.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "popc"))
             ms_call = time_launch(lambda: tab_ops.Conv2d(xin, qw, ths, btn, CONV_TYPE, *geom))
             lops = 2 * n_local * oh * oh * cs.KN * cs.K * cs.K * cs.C
+            gemm_bytes = in_bytes + w8.numel() + 4 * yb.numel()             # byte activations + byte weights read, fp32 output written
             sums["gemm_ms"] += ms_gemm; sums["popc_ms"] += ms_popc; sums["call_ms"] += ms_call; sums["ops"] += lops
+            if gemm_bytes / hbm_peak_guess > lops / tensor_peak_guess:
+                sums["hbm_ms"] += ms_gemm; sums["hbm_bytes"] += gemm_bytes
             layer_rows.append({"layer": cs.name, "in": [ih, ih, cs.C], "KN": cs.KN, "K": cs.K, "s": cs.stride,
+                               "gemm_kernel": gemm_kernel,
                                "gemm_ms": round(ms_gemm, 4), "gemm_tops": round(lops / ms_gemm / 1e9, 1),
+                               "gemm_GBps": round(gemm_bytes / ms_gemm / 1e6, 1),
                                "popcount_kernel_tops": round(lops / ms_popc / 1e9, 1),
                                "conv2d_call_ms": round(ms_call, 4), "conv2d_call_tops": round(lops / ms_call / 1e9, 1)})
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        bf16_peak, peak_src = float(peaks["bf16_tflops"]), "2 x MEASURED_PEAKS.json bf16_tflops (of measured; s8 runs at twice the bf16 rate)"
+        bf16_peak, peak_src = float(peaks["bf16_tflops"]), "of measured"
     except Exception:
         peaks = None
-        bf16_peak, peak_src = 1590.0, "2 x fallback 1.59 PFLOP/s bf16 (of fallback)"
-    tensor_peak = 2.0 * bf16_peak
+        bf16_peak, peak_src = 1590.0, "of fallback"
+    tensor_peak = umma_tops                      # measured in this run; 2 x the measured bf16 figure is reported beside it
     achieved = sums["ops"] / (sums["gemm_ms"] * 1e-3) / 1e12 if sums["gemm_ms"] else None
     roofline = {
-        "kernel": "int8 tensor-core GEMM stage of Conv2d (tcgen05.mma kind::i8 kernels; mma.sync s8 kernel for <= 64 filters and 1x1), %d launches per step" % len(layer_rows),
+        "kernel": "int8 tensor-core GEMM stage of Conv2d: conv_umma_persist_kernel (persistent TMA-fed tcgen05.mma kind::i8) for the "
+                  "stride-1 and 1x1 layers, conv_umma_kernel (tcgen05, cp.async im2col) for the three stride-2 3x3 layers; %d launches per step" % len(layer_rows),
         "bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TOP/s",
         "frac": (achieved / tensor_peak) if achieved else None,
-        # DRAM bytes of the largest launch of the step (56x56x64->64, batch 256): ncu capture at batch 128 (25.8 MB read +
-        # 49.6 MB written, equal to the algorithmic byte activations + fp32 output) scaled by 2 (traffic is proportional to N)
-        "traffic": 150.7e6, "traffic_note": "largest launch (56x56x64->64 conv, N=256); ncu at N=128 scaled x2; algorithmic 154.1e6",
-        "peak_source": peak_src + "; ceiling of the s8 mma.sync instruction measured from registers in this run: %.0f TOP/s" % imma_sync_tops,
-        "frac_of_mma_sync_ceiling": (achieved / imma_sync_tops) if achieved else None,
+        # DRAM bytes of the largest launch of the step (56x56x64->64, batch 256), from the ncu capture summarised under profiles/
+        "traffic": PERSIST_L1_TRAFFIC, "traffic_note": "largest launch (56x56x64->64 conv, N=256), ncu dram bytes read+written; algorithmic %.1fe6 "
+                   "(padded byte activations + byte weights + fp32 output)" % ((256 * 58 * 58 * 64 + 64 * 9 * 64 + 4 * 256 * 56 * 56 * 64) / 1e6),
+        "peak_source": "measured in this run: tcgen05.mma kind::i8 128x256x32 issued back to back from shared memory on every SM (no copies, "
+                       "no epilogue); 2 x MEASURED_PEAKS.json bf16_tflops would be %.0f TOP/s (%s); s8 mma.sync ceiling measured in this run: %.0f TOP/s"
+                       % (2.0 * bf16_peak, peak_src, imma_sync_tops),
+        "frac_of_2x_bf16_measured": (achieved / (2.0 * bf16_peak)) if achieved else None,
         "avg_launch_ms": sums["gemm_ms"] / max(len(layer_rows), 1),
+    }
+    if peaks is not None and "hbm_gbs" in peaks:
+        hbm_peak, hbm_src = float(peaks["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs (of measured)"
+    else:
+        hbm_peak, hbm_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
+    hbm_achieved = sums["hbm_bytes"] / (sums["hbm_ms"] * 1e-3) / 1e9 if sums["hbm_ms"] else None
+    roofline_hbm_layers = {
+        "kernel": "the GEMM-stage launches whose byte traffic, not their MMAs, sets the floor (few filters per byte of output: the 56x56x64 layers and the 1x1 shortcuts)",
+        "bound": "hbm", "achieved": hbm_achieved, "peak": hbm_peak, "unit": "GB/s",
+        "frac": (hbm_achieved / hbm_peak) if hbm_achieved else None, "peak_source": hbm_src,
+        "bytes": "algorithmic: byte activations + byte weights read, fp32 output written",
     }
     popc_achieved = sums["ops"] / (sums["popc_ms"] * 1e-3) / 1e12 if sums["popc_ms"] else None
     roofline_popcount = {
@@ -544,10 +588,6 @@ def main():
 
     # ---- TAB_Quantize alone at N=256, 56x56x256 (HBM-bound), against the measured copy bandwidth ---------
     quant = {}
-    if peaks is not None and "hbm_gbs" in peaks:
-        hbm_peak, hbm_src = float(peaks["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs (of measured)"
-    else:
-        hbm_peak, hbm_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
     if world == 1:
         QN, QH, QW_, QC = 256, 56, 56, 256
         g2 = torch.Generator(device=dev)
@@ -587,6 +627,7 @@ def main():
         "gpu_launches": gpu_launches, "cuda_graph": bool(use_graph),
         "clocks": clocks,
         "roofline": roofline,
+        "roofline_hbm_layers": roofline_hbm_layers,
         "roofline_popcount": roofline_popcount,
         "quantize": quant,
         "layers": layer_rows,

@@ -104,6 +104,19 @@ int tab_conv2d_fused_launch(const float* x, const int64_t* qw, const float* ths,
                             int p1, int p2, int s1, int s2,
                             int N, int H, int W, int C, int KN, int KH, int KW,
                             const float* residual, double* abs_sums, tab_stream_t stream);
+/*
+ * tab_conv2d_fused_launch that also finishes the next layer's thresholds (no counterpart in the reference):
+ *   next_ths   float [N] or NULL: receives next_scale * abs_sums[n] / (KN*OH*OW), i.e. next_scale * mean|y[n]|;
+ *              needs abs_sums.  On the tensor-core path the GEMM kernel's last CTA writes it, so a chained layer
+ *              costs two launches (quantise with the weight expansion and the clears folded in, GEMM); on the
+ *              other paths it is tab_threshold_from_sums_launch after the sums.
+ */
+int tab_conv2d_chain_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                            float* y, void* workspace, size_t workspace_bytes, int type,
+                            int p1, int p2, int s1, int s2,
+                            int N, int H, int W, int C, int KN, int KH, int KW,
+                            const float* residual, double* abs_sums, float* next_ths, float next_scale,
+                            tab_stream_t stream);
 /* ths[n] = scale * sums[n] / per_image. */
 int tab_threshold_from_sums_launch(const double* sums, float* ths, float scale, int N, long long per_image,
                                    tab_stream_t stream);
@@ -134,6 +147,21 @@ int tab_expand_weights_launch(const int64_t* qw, int8_t* w8, int bitwidth, int K
                               tab_stream_t stream);
 int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
                            int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
+
+/*
+ * The same stages in the form tab_conv2d_launch itself uses for stride-1 convolutions: the quantiser writes the
+ * padding into the byte tensor, [N][H+2*p1][W+2*p2][Cp] with border pixels 0 (ternary activations) or +1 (binary
+ * activations, bitwidth 1) - the reference's padded im2row input (TAB_Utils.cu:23-63) in bytes - and the GEMM
+ * stage (the persistent TMA-fed tcgen05 kernel) reads padding taps like any other pixel.
+ *   tab_quantize_int8_padded_launch  N <= 65535
+ *   tab_conv2d_int8_padded_launch    stride 1 only; weights from tab_expand_weights_launch; returns
+ *                                    TAB_E_TOO_LARGE when the shape is not covered (N*(H+2*p1)*(W+2*p2) >= 2^31,
+ *                                    KH*KW > 64, N > 65535)
+ */
+int tab_quantize_int8_padded_launch(const float* x, const float* ths, int8_t* qx8p, int bitwidth,
+                                    int N, int H, int W, int C, int p1, int p2, tab_stream_t stream);
+int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y, int type, int p1, int p2,
+                                  int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
 
 /*
  * tab_conv2d_launch without a workspace argument.  No counterpart in the reference (its host code calls

@@ -17,13 +17,18 @@ int umma_status_read_and_clear();
 size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2);
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
-                       cudaStream_t stream, const float* residual, double* abs_sums);
+                       cudaStream_t stream, const float* residual, double* abs_sums, float* next_ths, float next_scale);
+struct FusedTail;
 int residual_abs_sum_dispatch(float* y, const float* residual, double* sums, int N, long long per_image, cudaStream_t s);
 int quantize_int8_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C, cudaStream_t stream);
+int quantize_int8_padded_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
+                                  int p1, int p2, int Hq, int Wq, int sy, int sx, cudaStream_t stream);
+int conv_int8_padded_dispatch(const int8_t* qx8p, const int8_t* w8, float* y, int p1, int p2, int N, int H, int W, int C,
+                              int KN, int KH, int KW, cudaStream_t stream, const float* residual, double* abs_sums);
 int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream);
 int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary_act, int p1, int p2, int s1, int s2,
                        int N, int H, int W, int C, int KN, int KH, int KW, cudaStream_t stream,
-                       const float* residual, double* abs_sums);
+                       const float* residual, double* abs_sums, const FusedTail* tail);
 static int g_conv_path = TAB_PATH_AUTO;
 
 static bool dims_ok(int N, int H, int W, int C) { return N >= 0 && H >= 0 && W >= 0 && C >= 1; }
@@ -117,17 +122,28 @@ static int conv2d_impl(const float* x, const int64_t* qw, const float* ths, cons
                        float* y, void* workspace, size_t workspace_bytes, int type,
                        int p1, int p2, int s1, int s2,
                        int N, int H, int W, int C, int KN, int KH, int KW,
-                       const float* residual, double* abs_sums, tab_stream_t stream) {
+                       const float* residual, double* abs_sums, float* next_ths, float next_scale, tab_stream_t stream) {
     int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
     if (rc != TAB_OK) return rc;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (abs_sums && N > 0) {
-        if (reinterpret_cast<uintptr_t>(abs_sums) & 7) return TAB_E_ALIGNMENT;
-        cudaError_t e = cudaMemsetAsync(abs_sums, 0, sizeof(double) * (size_t)N, s);
-        if (e != cudaSuccess) return record_cuda_error(e);
-    }
+    if (next_ths && !abs_sums) return TAB_E_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(abs_sums) & 7) || (reinterpret_cast<uintptr_t>(next_ths) & 3)) return TAB_E_ALIGNMENT;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
-    if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
+    // empty output, or any path but the tensor-core one: the sums are cleared and the thresholds finished by
+    // separate small launches (the tensor-core path folds both into its two kernels)
+    auto clear_sums = [&]() -> int {
+        if (!abs_sums || N <= 0) return TAB_OK;
+        cudaError_t e = cudaMemsetAsync(abs_sums, 0, sizeof(double) * (size_t)N, s);
+        return e == cudaSuccess ? TAB_OK : record_cuda_error(e);
+    };
+    auto finish_ths = [&]() -> int {
+        if (!next_ths || N <= 0) return TAB_OK;
+        return tab_threshold_from_sums_launch(abs_sums, next_ths, next_scale, N, (long long)KN * (oh > 0 ? oh : 0) * (ow > 0 ? ow : 0), stream);
+    };
+    if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) {
+        rc = clear_sums();
+        return rc != TAB_OK ? rc : finish_ths();
+    }
     if (!x || !ths || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
     const size_t need = tab_conv2d_workspace_bytes(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
@@ -140,17 +156,21 @@ static int conv2d_impl(const float* x, const int64_t* qw, const float* ths, cons
         if ((reinterpret_cast<uintptr_t>(qw) & 7) || (reinterpret_cast<uintptr_t>(y) & 3)) return TAB_E_ALIGNMENT;
         const bool r8 = residual && ((reinterpret_cast<uintptr_t>(residual) & 7) == 0) && ((reinterpret_cast<uintptr_t>(y) & 7) == 0);
         if (!residual || r8) {
-            rc = conv_imma_dispatch(x, qw, ths, y, workspace, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, s, residual, abs_sums);
+            rc = conv_imma_dispatch(x, qw, ths, y, workspace, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, s, residual, abs_sums,
+                                    next_ths, next_scale);
             if (rc != TAB_E_TOO_LARGE) return rc;       // sizes beyond the tensor-core path: fall through
         }
     }
+    rc = clear_sums();
+    if (rc != TAB_OK) return rc;
     int64_t* qx = reinterpret_cast<int64_t*>(workspace);
     rc = quantize_dispatch(x, ths, qx, nullptr, act_bits(type), N, H, W, C, s);   // TAB_GEMM.cu:419-426
     if (rc != TAB_OK) return rc;
     rc = tab_conv2d_packed_launch(qx, qw, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream);
     if (rc != TAB_OK || (!residual && !abs_sums)) return rc;
     // the popcount kernel has no fused epilogue: one extra pass adds the residual and sums |y|
-    return residual_abs_sum_dispatch(y, residual, abs_sums, N, oh * ow * (long long)KN, s);
+    rc = residual_abs_sum_dispatch(y, residual, abs_sums, N, oh * ow * (long long)KN, s);
+    return rc != TAB_OK ? rc : finish_ths();
 }
 
 int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
@@ -158,7 +178,7 @@ int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const
                       int p1, int p2, int s1, int s2,
                       int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
     return conv2d_impl(x, qw, ths, btn, y, workspace, workspace_bytes, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
-                       nullptr, nullptr, stream);
+                       nullptr, nullptr, nullptr, 0.f, stream);
 }
 
 int tab_conv2d_fused_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
@@ -167,7 +187,17 @@ int tab_conv2d_fused_launch(const float* x, const int64_t* qw, const float* ths,
                             int N, int H, int W, int C, int KN, int KH, int KW,
                             const float* residual, double* abs_sums, tab_stream_t stream) {
     return conv2d_impl(x, qw, ths, btn, y, workspace, workspace_bytes, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
-                       residual, abs_sums, stream);
+                       residual, abs_sums, nullptr, 0.f, stream);
+}
+
+int tab_conv2d_chain_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
+                            float* y, void* workspace, size_t workspace_bytes, int type,
+                            int p1, int p2, int s1, int s2,
+                            int N, int H, int W, int C, int KN, int KH, int KW,
+                            const float* residual, double* abs_sums, float* next_ths, float next_scale,
+                            tab_stream_t stream) {
+    return conv2d_impl(x, qw, ths, btn, y, workspace, workspace_bytes, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+                       residual, abs_sums, next_ths, next_scale, stream);
 }
 
 int tab_quantize_int8_launch(const float* x, const float* ths, int8_t* qx8, int bitwidth,
@@ -198,7 +228,31 @@ int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int ty
     if ((reinterpret_cast<uintptr_t>(qx8) & 15) || (reinterpret_cast<uintptr_t>(w8) & 15) || (reinterpret_cast<uintptr_t>(y) & 3))
         return TAB_E_ALIGNMENT;
     return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
-                              reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr);
+                              reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr);
+}
+
+int tab_quantize_int8_padded_launch(const float* x, const float* ths, int8_t* qx8p, int bitwidth,
+                                    int N, int H, int W, int C, int p1, int p2, tab_stream_t stream) {
+    if (!dims_ok(N, H, W, C) || bitwidth < 1 || p1 < 0 || p2 < 0) return TAB_E_BAD_ARGUMENT;
+    if ((long long)N * (H + 2LL * p1) * (W + 2LL * p2) == 0) return TAB_OK;
+    if (!x || !ths || !qx8p) return TAB_E_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) || (reinterpret_cast<uintptr_t>(qx8p) & 15))
+        return TAB_E_ALIGNMENT;
+    return quantize_int8_padded_dispatch(x, ths, qx8p, bitwidth == 1 ? 1 : 2, N, H, W, C, p1, p2, H, W, 1, 1,
+                                         reinterpret_cast<cudaStream_t>(stream));
+}
+
+int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y, int type, int p1, int p2,
+                                  int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
+    int rc = conv_args_ok(type, p1, p2, 1, 1, N, H, W, C, KN, KH, KW);
+    if (rc != TAB_OK) return rc;
+    const long long oh = (long long)H + 2LL * p1 - KH + 1, ow = (long long)W + 2LL * p2 - KW + 1;
+    if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
+    if (!qx8p || !w8 || !y) return TAB_E_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(qx8p) & 15) || (reinterpret_cast<uintptr_t>(w8) & 15) || (reinterpret_cast<uintptr_t>(y) & 3))
+        return TAB_E_ALIGNMENT;
+    return conv_int8_padded_dispatch(qx8p, w8, y, p1, p2, N, H, W, C, KN, KH, KW, reinterpret_cast<cudaStream_t>(stream),
+                                     nullptr, nullptr);
 }
 
 /* Test/benchmark hook: GEMM variant of the tensor-core path: 0 = default, 1 = mma.sync + im2col staging,

@@ -82,11 +82,67 @@ quantize_int8_kernel(const float* __restrict__ x, const float* __restrict__ ths,
 // pixel; border pixels get the padding value in the real channels and 0 in the channel padding.
 // The quantised grid may subsample the input: its pixel (i, j) is input pixel (i*sy, j*sx) and it has Hq x Wq
 // pixels before padding (a strided 1x1 convolution only ever reads those pixels).
+// One thread per (filter, word k, 16-channel group) of the packed weights: 16 bytes of {-1,0,+1}.
+template <int WB>
+__device__ __forceinline__ void expand_group(const uint64_t* __restrict__ qw, int8_t* __restrict__ w8, long long idx, int PC, int C) {
+    const long long word = idx >> 2;
+    const int grp = (int)(idx & 3);
+    const int pc = (int)(word % PC);
+    const int cbase = pc * 64 + grp * 16;
+    uint32_t s16, m16;
+    if (WB == 2) {
+        s16 = (uint32_t)(qw[word * 2] >> (grp * 16)) & 0xFFFFu;
+        m16 = (uint32_t)(qw[word * 2 + 1] >> (grp * 16)) & 0xFFFFu;
+    } else {
+        s16 = (uint32_t)(qw[word] >> (grp * 16)) & 0xFFFFu;     // bit = 1 means -1
+        m16 = 0xFFFFu;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        uint32_t r = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int i = 4 * w + b;
+            int v = ((m16 >> i) & 1u) ? (((s16 >> i) & 1u) ? -1 : 1) : 0;
+            if (cbase + i >= C) v = 0;
+            r |= (uint32_t)(v & 0xFF) << (8 * b);
+        }
+        o[w] = r;
+    }
+    *reinterpret_cast<uint4*>(w8 + word * 64 + grp * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Inside a convolution call the same launch also does the call's small set-up jobs, so that they cost no launch of
+// their own: all CTAs share the expansion of the packed weights to bytes, and the first CTA of every image clears
+// that image's |y| sum (and the first of all the completion counter) for the GEMM's epilogue.
+struct PrepExtras {
+    int images;                  // grid rows (= images)
+    double* zero_sums;           // [images] or null
+    unsigned* zero_counter;      // or null
+    const uint64_t* qw;          // packed weights, or null
+    int8_t* w8;
+    long long words;             // KN*KH*KW*PC
+    int wbits;
+};
+
 template <int BITS, bool VEC>
 __global__ void __launch_bounds__(Q8THREADS)
 quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict__ ths, int8_t* __restrict__ q,
-                            int H, int W, int C, int Cp, int p1, int p2, int Hq, int Wq, int sy, int sx) {
+                            int H, int W, int C, int Cp, int p1, int p2, int Hq, int Wq, int sy, int sx, const PrepExtras ex) {
     const int n = blockIdx.y;
+    if (ex.qw != nullptr) {                                                // the weights, spread over all CTAs of the launch
+        const int PC = Cp >> 6;
+        const long long stride = (long long)gridDim.x * gridDim.y * Q8THREADS;
+        for (long long idx = ((long long)blockIdx.y * gridDim.x + blockIdx.x) * Q8THREADS + threadIdx.x; idx < ex.words * 4; idx += stride) {
+            if (ex.wbits == 2) expand_group<2>(ex.qw, ex.w8, idx, PC, C);
+            else expand_group<1>(ex.qw, ex.w8, idx, PC, C);
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        if (ex.zero_sums) ex.zero_sums[n] = 0.0;
+        if (n == 0 && ex.zero_counter) *ex.zero_counter = 0u;
+    }
     const float t = __ldg(ths + n), nt = -t;
     const int gpp = Cp >> 4;
     const int PH = Hq + 2 * p1, PW = Wq + 2 * p2;
@@ -148,32 +204,7 @@ __global__ void expand_weights_kernel(const uint64_t* __restrict__ qw, int8_t* _
                                       long long words, int PC, int C) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= words * 4) return;
-    const long long word = idx >> 2;
-    const int grp = (int)(idx & 3);
-    const int pc = (int)(word % PC);
-    const int cbase = pc * 64 + grp * 16;
-    uint32_t s16, m16;
-    if (WB == 2) {
-        s16 = (uint32_t)(qw[word * 2] >> (grp * 16)) & 0xFFFFu;
-        m16 = (uint32_t)(qw[word * 2 + 1] >> (grp * 16)) & 0xFFFFu;
-    } else {
-        s16 = (uint32_t)(qw[word] >> (grp * 16)) & 0xFFFFu;     // bit = 1 means -1
-        m16 = 0xFFFFu;
-    }
-    uint32_t o[4];
-#pragma unroll
-    for (int w = 0; w < 4; w++) {
-        uint32_t r = 0;
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-            const int i = 4 * w + b;
-            int v = ((m16 >> i) & 1u) ? (((s16 >> i) & 1u) ? -1 : 1) : 0;
-            if (cbase + i >= C) v = 0;
-            r |= (uint32_t)(v & 0xFF) << (8 * b);
-        }
-        o[w] = r;
-    }
-    *reinterpret_cast<uint4*>(w8 + word * 64 + grp * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    expand_group<WB>(qw, w8, idx, PC, C);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -413,6 +444,7 @@ conv_imma_kernel(const ImmaParams p) {
     asm volatile("cp.async.wait_group 0;");
 
     imma_epilogue<FUSED>(p, acc, m0, n0, wm, wn, lane);
+    if (FUSED) fused_finish(p);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -576,6 +608,7 @@ conv_imma_patch_kernel(const ImmaParams p, const int pmax) {
     }
     asm volatile("cp.async.wait_group 0;");
     imma_epilogue<FUSED>(p, acc, m0, n0, wm, wn, lane);
+    if (FUSED) fused_finish(p);
 }
 
 // Largest patch (in pixels) over all tiles of TMI output rows; 0 when pixel indices would not fit an int.
@@ -666,7 +699,7 @@ size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, 
     const size_t Cp = (size_t)packed_channels(C) * 64;
     const size_t a = ((size_t)N * (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2) * Cp + 255) / 256 * 256;   // room for the padded form
     const size_t b = ((size_t)KN * KH * KW * Cp + 255) / 256 * 256;
-    return a + b;
+    return a + b + 256;                          // + completion counter of the fused tail
 }
 
 static int imma_limits(int N, int H, int W, int C, int KN, int KH, int KW, long long oh, long long ow) {
@@ -715,7 +748,7 @@ int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, in
 // GEMM stage alone on byte operands.  binary_act: activations are {-1,+1} (out-of-image taps count as +1).
 int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary_act,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
-                       cudaStream_t stream, const float* residual, double* abs_sums) {
+                       cudaStream_t stream, const float* residual, double* abs_sums, const FusedTail* tail) {
     const int PC = packed_channels(C);
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
@@ -726,6 +759,10 @@ int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary
     p.N = N; p.H = H; p.W = W; p.PC = PC; p.KN = KN; p.KH = KH; p.KW = KW;
     p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
     p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * PC;
+    if (tail && tail->ths_out && abs_sums) {
+        p.ths_out = tail->ths_out; p.ths_scale = tail->scale; p.done_counter = tail->counter;
+        p.per_image = (double)KN * (double)oh * (double)ow;
+    }
     const bool padone = binary_act && (p1 > 0 || p2 > 0);
     // 256 x 64 tiles when there are at most 64 filters, 128 x 128 tiles otherwise.  The patch variant is used
     // when the kernel has at least 3 taps, the largest patch fits the shared-memory budget and it copies at
@@ -751,40 +788,89 @@ int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary
 void imma_set_variant(int v) { g_imma_variant = v; }
 
 // x fp32 -> y, all four types, scratch in `workspace` (imma_workspace_bytes).
+static int quantize_prep_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
+                                  int p1, int p2, int Hq, int Wq, int sy, int sx, const PrepExtras& ex, cudaStream_t stream);
+
+// Quantise to the zero-padded byte tensor [N][Hq + 2*p1][Wq + 2*p2][Cp]; quantised pixel (i, j) is input pixel
+// (i*sy, j*sx).  Binary activations (bits 1) get +1 in the border.  N <= 65535.
+int quantize_int8_padded_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
+                                  int p1, int p2, int Hq, int Wq, int sy, int sx, cudaStream_t stream) {
+    PrepExtras none = {};
+    none.images = N;
+    return quantize_prep_dispatch(x, ths, qx8, bits, N, H, W, C, p1, p2, Hq, Wq, sy, sx, none, stream);
+}
+
+static int quantize_prep_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
+                                  int p1, int p2, int Hq, int Wq, int sy, int sx, const PrepExtras& ex, cudaStream_t stream) {
+    if (N >= 65535) return TAB_E_TOO_LARGE;
+    const int Cp = packed_channels(C) * 64;
+    const long long PH = Hq + 2LL * p1, PW = Wq + 2LL * p2;
+    const long long groups = PH * PW * (Cp / 16);
+    if (N == 0 || groups == 0) return TAB_OK;
+    long long per = (groups + Q8THREADS - 1) / Q8THREADS;
+    const long long cap = (148LL * 8 * 4 + N - 1) / N;
+    if (per > cap) per = cap;
+    if (per < 1) per = 1;
+    dim3 grid((unsigned)per, (unsigned)N);
+    const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)H * W * C) % 8 == 0);
+    if (bits == 2) {
+        if (vec) quantize_int8_padded_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2, Hq, Wq, sy, sx, ex);
+        else quantize_int8_padded_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2, Hq, Wq, sy, sx, ex);
+    } else {
+        if (vec) quantize_int8_padded_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2, Hq, Wq, sy, sx, ex);
+        else quantize_int8_padded_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2, Hq, Wq, sy, sx, ex);
+    }
+    return check_launch();
+}
+
+// GEMM stage on activations that already carry their padding (stride 1): the TMA-fed tcgen05 kernels.
+// TAB_E_TOO_LARGE when the shape is not covered.
+int conv_int8_padded_dispatch(const int8_t* qx8p, const int8_t* w8, float* y, int p1, int p2, int N, int H, int W, int C,
+                              int KN, int KH, int KW, cudaStream_t stream, const float* residual, double* abs_sums) {
+    const long long oh = (long long)H + 2LL * p1 - KH + 1, ow = (long long)W + 2LL * p2 - KW + 1;
+    if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
+    int rc = imma_limits(N, H, W, C, KN, KH, KW, oh, ow);
+    if (rc != TAB_OK) return rc;
+    const long long PH = H + 2LL * p1, PW = W + 2LL * p2;
+    if (N * PH * PW >= (1LL << 31) - 4096) return TAB_E_TOO_LARGE;
+    ImmaParams p;
+    p.qx = qx8p; p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
+    p.N = N; p.H = H; p.W = W; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
+    p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = 1; p.s2 = 1;
+    p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * p.PC;
+    return conv_tma_dispatch(p, g_imma_variant == 7 ? 2 : 1, stream);
+}
+
+// Scratch layout: padded byte activations | byte weights | 256 bytes holding the completion counter of the fused tail.
+// next_ths (optional, with abs_sums): the GEMM's last CTA writes next_scale * abs_sums[n] / (KN*OH*OW) there.
+// abs_sums is cleared by this call.  Three launches at most: quantise (+ weight expansion + clears), GEMM.
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
-                       cudaStream_t stream, const float* residual, double* abs_sums) {
+                       cudaStream_t stream, const float* residual, double* abs_sums, float* next_ths, float next_scale) {
     const int Cp = packed_channels(C) * 64;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
     int rc = imma_limits(N, H, W, C, KN, KH, KW, oh, ow);
     if (rc != TAB_OK) return rc;
+    if (N >= 65535) return TAB_E_TOO_LARGE;
     int8_t* qx8 = reinterpret_cast<int8_t*>(workspace);
     int8_t* w8 = qx8 + ((size_t)N * (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2) * Cp + 255) / 256 * 256;
-    rc = expand_weights_dispatch(qw, w8, weight_bits(type), KN, KH, KW, C, stream);
-    if (rc != TAB_OK) return rc;
+    unsigned* counter = reinterpret_cast<unsigned*>(w8 + ((size_t)KN * KH * KW * Cp + 255) / 256 * 256);
+    FusedTail tail = {};
+    if (next_ths && abs_sums) { tail.ths_out = next_ths; tail.scale = next_scale; tail.counter = counter; }
+    PrepExtras ex = {};
+    ex.images = N;
+    ex.zero_sums = abs_sums;
+    ex.zero_counter = tail.ths_out ? counter : nullptr;
+    ex.qw = reinterpret_cast<const uint64_t*>(qw); ex.w8 = w8;
+    ex.words = (long long)KN * KH * KW * packed_channels(C);
+    ex.wbits = weight_bits(type);
     // A strided 1x1 convolution without padding reads only every s-th pixel: quantise just those, densely, and run
     // it as a stride-1 convolution on the subsampled grid.
     int Hq = H, Wq = W, sy = 1, sx = 1, S1 = s1, S2 = s2;
     if (KH == 1 && KW == 1 && p1 == 0 && p2 == 0 && (s1 > 1 || s2 > 1)) { Hq = (int)oh; Wq = (int)ow; sy = s1; sx = s2; S1 = S2 = 1; }
-    const bool subsampled = sy > 1 || sx > 1;
     auto quantize_padded = [&](int q1, int q2) -> int {
-        const long long PH = Hq + 2LL * q1, PW = Wq + 2LL * q2;
-        const long long groups = PH * PW * (Cp / 16);
-        long long per = (groups + Q8THREADS - 1) / Q8THREADS;
-        const long long cap = (148LL * 8 * 4 + N - 1) / N;
-        if (per > cap) per = cap;
-        if (per < 1) per = 1;
-        dim3 grid((unsigned)per, (unsigned)N);
-        const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)H * W * C) % 8 == 0);
-        if (act_bits(type) == 2) {
-            if (vec) quantize_int8_padded_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, q1, q2, Hq, Wq, sy, sx);
-            else quantize_int8_padded_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, q1, q2, Hq, Wq, sy, sx);
-        } else {
-            if (vec) quantize_int8_padded_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, q1, q2, Hq, Wq, sy, sx);
-            else quantize_int8_padded_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, q1, q2, Hq, Wq, sy, sx);
-        }
-        return check_launch();
+        return quantize_prep_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, q1, q2, Hq, Wq, sy, sx, ex, stream);
     };
     // Persistent TMA-fed tcgen05 kernel on zero-padded activations: stride 1; at least 4 taps unless there is no
     // padding at all (with fewer, the padded grid costs more than the patch saves); at least 45 % of the padded
@@ -798,8 +884,11 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
         p.N = N; p.H = Hq; p.W = Wq; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
         p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = S1; p.s2 = S2;
         p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * p.PC;
-        const bool shape = S1 == 1 && S2 == 1 && (KH * KW >= 4 || (p1 == 0 && p2 == 0)) && N <= 65535 &&
-                           N * PH * PW < (1LL << 31) - 4096;
+        if (tail.ths_out) {
+            p.ths_out = tail.ths_out; p.ths_scale = tail.scale; p.done_counter = tail.counter;
+            p.per_image = (double)KN * (double)oh * (double)ow;
+        }
+        const bool shape = S1 == 1 && S2 == 1 && (KH * KW >= 4 || (p1 == 0 && p2 == 0)) && N * PH * PW < (1LL << 31) - 4096;
         const bool want = shape && (g_imma_variant == 6 || g_imma_variant == 7 ||
                                     (g_imma_variant == 0 && g_tma_default && useful >= 0.45 && conv_tma_persist_fits(p)));
         if (want) {
@@ -811,10 +900,10 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
         }
     }
     if (!quantized) {
-        rc = subsampled ? quantize_padded(0, 0) : quantize_int8_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, stream);
+        rc = quantize_padded(0, 0);
         if (rc != TAB_OK) return rc;
     }
-    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, S1, S2, N, Hq, Wq, C, KN, KH, KW, stream, residual, abs_sums);
+    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, S1, S2, N, Hq, Wq, C, KN, KH, KW, stream, residual, abs_sums, &tail);
 }
 
 }  // namespace tab

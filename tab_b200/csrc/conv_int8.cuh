@@ -17,7 +17,36 @@ struct ImmaParams {
     double* abs_sums;        // [N]: += sum |y| per image, or null
     int N, H, W, PC, KN, KH, KW, OH, OW, p1, p2, s1, s2;
     int M, Kw;
+    // Optional tail of a fused launch: the CTA that finishes last turns the sums into the next layer's thresholds,
+    // ths_out[n] = ths_scale * abs_sums[n] / per_image (null = leave that to the caller).
+    float* ths_out = nullptr;
+    float ths_scale = 0.f;
+    double per_image = 1.0;
+    unsigned* done_counter = nullptr;   // zero before the launch
 };
+
+// Host-side description of that tail.
+struct FusedTail { float* ths_out; float scale; unsigned* counter; };
+
+// Called by every thread of every CTA at the end of a fused kernel, after the CTA's last atomic on abs_sums.
+__device__ __forceinline__ void fused_finish(const ImmaParams& p) {
+    if (p.ths_out == nullptr) return;
+    __threadfence();
+    int mine = 0;
+    __syncthreads();                                                       // every thread's atomics are issued and fenced
+    if (threadIdx.x == 0) {
+        const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+        mine = (atomicAdd(p.done_counter, 1u) == total - 1u);
+    }
+    const int last = __syncthreads_or(mine);                               // no shared memory: the kernels use all of it
+    if (last) {
+        __threadfence();
+        for (int n = threadIdx.x; n < p.N; n += blockDim.x) {
+            const double sum = __ldcg(p.abs_sums + n);                     // the other CTAs' atomics live in L2
+            p.ths_out[n] = (float)((double)p.ths_scale * (sum / p.per_image));
+        }
+    }
+}
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void* src, bool valid) {
     const int sz = valid ? 16 : 0;

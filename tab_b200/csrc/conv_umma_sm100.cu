@@ -46,6 +46,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
     return false;
 }
 
+// One non-blocking probe of the phase with the given parity.
+__device__ __forceinline__ bool mbar_try(uint32_t addr, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    return ok != 0;
+}
+
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     const uint32_t lo = (smem_addr & 0x3FFFFu) >> 4;                       // start address, LBO unused (0)
@@ -59,8 +69,8 @@ __host__ __device__ constexpr uint32_t umma_idesc(int n) {
 __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\t"
                  "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t mbar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
@@ -281,6 +291,7 @@ conv_umma_kernel(const ImmaParams p, int* __restrict__ status) {
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TCOLS) : "memory");
     }
+    if (FUSED) fused_finish(p);
 }
 
 template <int MT, int TNI, int S, bool PADONE, bool FUSED>
@@ -527,6 +538,7 @@ conv_umma_patch_kernel(const ImmaParams p, int* __restrict__ status, const int p
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TCOLS) : "memory");
     }
+    if (FUSED) fused_finish(p);
 }
 
 template <int MT, int TNI, int SB, bool PADONE, bool FUSED>
@@ -690,6 +702,7 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TCOLS) : "memory");
     }
+    if (FUSED) fused_finish(p);
 }
 
 // Epilogue with coalesced stores for a warp that owns TMEM lane quarter wq.  tcgen05.ld hands lane r the 32 columns
@@ -1049,6 +1062,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)(2 * ACOLS)) : "memory");
     }
+    if (FUSED) fused_finish(p);
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
@@ -1375,7 +1389,48 @@ __global__ void __launch_bounds__(128, 1) umma_probe_kernel(uint32_t* __restrict
             mbar_arrive(full + 8 * slot);
         }
     }
-    if (mode == 3) {
+    if (mode == 4) {
+        // mode 3 with the next slot's barrier probed before the current group is issued (its latency hides behind the MMAs)
+        const int warp = threadIdx.x >> 5;
+        if (warp == 1) {
+            for (unsigned g = 0; g < (unsigned)iters; g++) {
+                const unsigned slot = g % S;
+                if (g >= (unsigned)S && !mbar_wait(empty + 8 * slot, ((g / S) - 1) & 1u)) { if (status) atomicExch(status, 21); break; }
+                __syncwarp();
+                if (elect_one()) mbar_arrive(full + 8 * slot);
+                __syncwarp();
+            }
+        } else if (warp == 0) {
+            constexpr uint32_t IDESC = umma_idesc(TNI);
+            const uint64_t db = umma_desc(sB);
+            const long long t0 = clock64();
+            bool ready = mbar_wait(full, 0);
+            for (unsigned it = 0; it < (unsigned)iters; it++) {
+                const unsigned slot = it % S;
+                if (!ready && !mbar_wait(full + 8 * slot, (it / S) & 1u)) { if (status) atomicExch(status, 22); break; }
+                const unsigned nslot = (it + 1) % S;
+                ready = mbar_try(full + 8 * nslot, ((it + 1) / S) & 1u);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (elect_one()) {
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+#pragma unroll
+                        for (int a = 0; a < NA; a++)
+                            umma_i8(tmem_base + a * TNI, umma_desc(sA + a * UTM * IROW) + 2 * k, db + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty + 8 * slot);
+                }
+                __syncwarp();
+            }
+            if (elect_one()) umma_commit(done);
+            __syncwarp();
+            const long long t1 = clock64();
+            if (!mbar_wait(done, 0) && status) atomicExch(status, 20);
+            const long long t2 = clock64();
+            if (threadIdx.x == 0) { sink[2 * blockIdx.x] = (uint32_t)(t1 - t0); sink[2 * blockIdx.x + 1] = (uint32_t)(t2 - t0); }
+        }
+    } else if (mode == 3) {
         // mode 2 with both roles run by whole warps and the issuing instructions under elect_one()
         const int warp = threadIdx.x >> 5;
         if (warp == 1) {
@@ -1458,7 +1513,7 @@ static int launch_umma_probe(uint32_t* sink, int iters, int blocks, int shift_ro
 // Returns the int8 operations of the whole launch through ops_out.
 int umma_probe_dispatch(int code, int iters, uint32_t* sink, int blocks, double* ops_out, cudaStream_t stream) {
     const int mode = code / 40, shift_rows = (code % 40) / 5, shape = code % 5;
-    if (mode > 3) return TAB_E_BAD_ARGUMENT;
+    if (mode > 4) return TAB_E_BAD_ARGUMENT;
     const int tn = (shape == 0 || shape == 3) ? 64 : ((shape == 1 || shape == 4) ? 128 : 256);
     const int na = shape >= 3 ? 2 : 1;
     if (ops_out) *ops_out = (double)blocks * iters * 4.0 * na * (128.0 * tn * 32 * 2);

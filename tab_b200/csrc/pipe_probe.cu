@@ -111,7 +111,7 @@ using namespace tab;
 extern "C" size_t tab_pipe_probe_sink_bytes(void) { return (size_t)probe_blocks() * PROBE_THREADS * 4; }
 
 extern "C" int tab_pipe_probe_launch(int kind, int iters, void* sink, double* ops_out, tab_stream_t stream) {
-    if (kind < 0 || kind > 164 || iters < 1) return TAB_E_BAD_ARGUMENT;
+    if (kind < 0 || kind > 204 || iters < 1) return TAB_E_BAD_ARGUMENT;
     if (!sink) return TAB_E_NULL_POINTER;
     const int blocks = probe_blocks();
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -114,18 +114,14 @@ std::vector<torch::Tensor> TAB_Conv2dFused(torch::Tensor X, torch::Tensor QW, to
     const size_t ws_bytes = tab_conv2d_workspace_bytes(type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW);
     auto ws = torch::empty({(int64_t)std::max<size_t>(ws_bytes, 256)}, torch::device(X.device()).dtype(torch::kUInt8));
     torch::Tensor sums, next;
-    if (threshold_scale > 0) sums = torch::empty({std::max(N, 1)}, torch::device(X.device()).dtype(torch::kFloat64));
-    check_rc(tab_conv2d_fused_launch(X.data_ptr<float>(), QW.data_ptr<int64_t>(), thresholds.data_ptr<float>(), btn.data_ptr<int32_t>(),
+    const bool want = threshold_scale > 0;
+    if (want) sums = torch::empty({std::max(N, 1)}, torch::device(X.device()).dtype(torch::kFloat64));
+    next = torch::empty({want ? N : 0}, torch::device(X.device()).dtype(torch::kFloat32));
+    check_rc(tab_conv2d_chain_launch(X.data_ptr<float>(), QW.data_ptr<int64_t>(), thresholds.data_ptr<float>(), btn.data_ptr<int32_t>(),
                                      Y.data_ptr<float>(), ws.data_ptr(), (size_t)ws.numel(), type, padding1, padding2, stride1, stride2,
-                                     N, H, W, C, KN, KH, KW, rptr, sums.defined() ? sums.data_ptr<double>() : nullptr, current_stream()),
-             "tab_conv2d_fused_launch");
-    if (sums.defined()) {
-        next = torch::empty({N}, torch::device(X.device()).dtype(torch::kFloat32));
-        check_rc(tab_threshold_from_sums_launch(sums.data_ptr<double>(), next.data_ptr<float>(), (float)threshold_scale, N,
-                                                (long long)KN * OH * OW, current_stream()), "tab_threshold_from_sums_launch");
-    } else {
-        next = torch::empty({0}, torch::device(X.device()).dtype(torch::kFloat32));
-    }
+                                     N, H, W, C, KN, KH, KW, rptr, want ? sums.data_ptr<double>() : nullptr,
+                                     (want && N > 0) ? next.data_ptr<float>() : nullptr, (float)threshold_scale, current_stream()),
+             "tab_conv2d_chain_launch");
     return {Y, next};
 }
 

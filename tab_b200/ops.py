@@ -192,9 +192,41 @@ def conv2d_int8(QX8, W8, type, padding1, padding2, stride1, stride2, N, H, W, C,
     return Y
 
 
+def quantize_int8_padded(X, thresholds, bitwidth, N, H, W, C, padding1, padding2):
+    """fp32 NHWC -> int8 ``{N,H+2*padding1,W+2*padding2,Cp}``: quantised values with the convolution's padding
+    written in (0 for ternary, +1 for binary activations in the real channels)."""
+    _check_input(X, "X", torch.float32)
+    _check_input(thresholds, "thresholds", torch.float32)
+    Cp = (int(C) + 63) // 64 * 64
+    with torch.cuda.device(X.device):
+        q = torch.empty((N, H + 2 * int(padding1), W + 2 * int(padding2), Cp), dtype=torch.int8, device=X.device)
+        rc = _cabi.lib().tab_quantize_int8_padded_launch(X.data_ptr(), thresholds.data_ptr(), q.data_ptr(), int(bitwidth),
+                                                         N, H, W, C, int(padding1), int(padding2), _stream_ptr(X.device))
+    _cabi.check(rc, "tab_quantize_int8_padded_launch")
+    return q
+
+
+def conv2d_int8_padded(QX8P, W8, type, padding1, padding2, N, H, W, C, KN, KH, KW):
+    """The stride-1 GEMM stage on padded byte activations (``quantize_int8_padded``); same output as ``Conv2d``.
+    Raises ``TabError`` (TAB_E_TOO_LARGE) for shapes the TMA-fed kernels do not cover."""
+    _check_input(QX8P, "QX8P", torch.int8)
+    _check_input(W8, "W8", torch.int8)
+    Cp = (int(C) + 63) // 64 * 64
+    p1, p2 = int(padding1), int(padding2)
+    if QX8P.numel() != N * (H + 2 * p1) * (W + 2 * p2) * Cp or W8.numel() != KN * KH * KW * Cp:
+        raise RuntimeError("byte operands must be [N,H+2p1,W+2p2,Cp] and [KN,KH,KW,Cp] with Cp = %d" % Cp)
+    OH, OW = conv_out_size(H, W, KH, KW, p1, p2, 1, 1)
+    with torch.cuda.device(QX8P.device):
+        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=QX8P.device)
+        rc = _cabi.lib().tab_conv2d_int8_padded_launch(QX8P.data_ptr(), W8.data_ptr(), Y.data_ptr(), int(type), p1, p2,
+                                                       N, H, W, C, KN, KH, KW, _stream_ptr(QX8P.device))
+    _cabi.check(rc, "tab_conv2d_int8_padded_launch")
+    return Y
+
+
 def Conv2dFused(X, QW, thresholds, btn, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW,
                 residual=None, threshold_scale=None):
-    """``Conv2d`` with the two chaining fusions of ``tab_conv2d_fused_launch``: ``Y = conv(X) + residual`` and,
+    """``Conv2d`` with the chaining fusions of ``tab_conv2d_chain_launch``: ``Y = conv(X) + residual`` and,
     when ``threshold_scale`` is given, the next layer's thresholds ``threshold_scale * mean|Y[n]|``.
     Returns ``(Y, next_thresholds_or_None)``.  Not part of the reference's interface."""
     _check_input(X, "X", torch.float32)
@@ -217,15 +249,13 @@ def Conv2dFused(X, QW, thresholds, btn, type, padding1, padding2, stride1, strid
         Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=X.device)
         ws = torch.empty((max(l.tab_conv2d_workspace_bytes(conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW), 256),), dtype=torch.uint8, device=X.device)
         sums = torch.empty((max(N, 1),), dtype=torch.float64, device=X.device) if threshold_scale is not None else None
+        nxt = torch.empty((N,), dtype=torch.float32, device=X.device) if threshold_scale is not None else None
         st = _stream_ptr(X.device)
-        rc = l.tab_conv2d_fused_launch(X.data_ptr(), QW.data_ptr(), thresholds.data_ptr(), btn.data_ptr(), Y.data_ptr(),
+        rc = l.tab_conv2d_chain_launch(X.data_ptr(), QW.data_ptr(), thresholds.data_ptr(), btn.data_ptr(), Y.data_ptr(),
                                        ws.data_ptr(), ws.numel(), conv_type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
                                        residual.data_ptr() if residual is not None else None,
-                                       sums.data_ptr() if sums is not None else None, st)
-        _cabi.check(rc, "tab_conv2d_fused_launch")
-        nxt = None
-        if sums is not None:
-            nxt = torch.empty((N,), dtype=torch.float32, device=X.device)
-            rc = l.tab_threshold_from_sums_launch(sums.data_ptr(), nxt.data_ptr(), float(threshold_scale), N, KN * OH * OW, st)
-            _cabi.check(rc, "tab_threshold_from_sums_launch")
+                                       sums.data_ptr() if sums is not None else None,
+                                       nxt.data_ptr() if nxt is not None else None,
+                                       float(threshold_scale) if threshold_scale is not None else 0.0, st)
+        _cabi.check(rc, "tab_conv2d_chain_launch")
     return Y, nxt

@@ -61,9 +61,10 @@ def test_workspace_size():
     # the larger of: packed activations (N*H*W*PC*planes words) and byte activations + byte weights
     # (N*H*W*PC*64 + KN*KH*KW*PC*64), each rounded up to 256 bytes
     r = lambda b: (b + 255) // 256 * 256
-    # (the byte activations are sized for their zero-padded form, (H+2*p1) x (W+2*p2) pixels)
-    assert l.tab_conv2d_workspace_bytes(0, 0, 0, 1, 1, 2, 5, 5, 65, 4, 3, 3) == max(r(2 * 25 * 2 * 2 * 8), r(2 * 25 * 128) + r(4 * 9 * 128))
-    assert l.tab_conv2d_workspace_bytes(3, 1, 1, 1, 1, 2, 5, 5, 65, 4, 3, 3) == r(2 * 49 * 128) + r(4 * 9 * 128)
+    # (the byte activations are sized for their zero-padded form, (H+2*p1) x (W+2*p2) pixels; 256 more bytes hold
+    # the completion counter of a chained call)
+    assert l.tab_conv2d_workspace_bytes(0, 0, 0, 1, 1, 2, 5, 5, 65, 4, 3, 3) == max(r(2 * 25 * 2 * 2 * 8), r(2 * 25 * 128) + r(4 * 9 * 128) + 256)
+    assert l.tab_conv2d_workspace_bytes(3, 1, 1, 1, 1, 2, 5, 5, 65, 4, 3, 3) == r(2 * 49 * 128) + r(4 * 9 * 128) + 256
     assert l.tab_conv2d_workspace_bytes(9, 1, 1, 1, 1, 2, 5, 5, 65, 4, 3, 3) == 0
     assert l.tab_conv2d_workspace_bytes(0, 1, 1, 0, 1, 2, 5, 5, 65, 4, 3, 3) == 0
     assert l.tab_conv2d_set_path(7) == -1

@@ -294,6 +294,32 @@ def test_int8_stage_entry_points(cuda):
         assert np.array_equal(y.cpu().numpy(), yo)
 
 
+def test_int8_padded_stage_entry_points(cuda):
+    """quantize_int8_padded writes the convolution's padding (0 ternary, +1 binary, channel tail 0);
+    conv2d_int8_padded on it equals the oracle's Conv2d."""
+    N, H, W, C, KN, K = 3, 9, 8, 130, 70, 3
+    p1, p2 = 1, 2
+    x, ths = make_input(7, N, H, W, C)
+    w, wths = make_input(8, KN, K, K, C)
+    Cp = 192
+    for t in range(4):
+        ab, wb = O.act_bits(t), O.weight_bits(t)
+        qx, _ = O.quantize(x, ths, ab, N, H, W, C)
+        qw, btn = O.quantize(w, wths, wb, KN, K, K, C)
+        q8 = TAB.ops.quantize_int8_padded(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C, p1, p2)
+        w8 = TAB.ops.expand_weights(dev_t(qw, cuda), wb, KN, K, K, C)
+        assert tuple(q8.shape) == (N, H + 2 * p1, W + 2 * p2, Cp)
+        exp_a = np.zeros((N, H + 2 * p1, W + 2 * p2, Cp), np.int8)
+        if ab == 1:
+            exp_a[..., :C] = 1
+        exp_a[:, p1:p1 + H, p2:p2 + W, :C] = O.dequantize(qx, C).astype(np.int8)
+        assert np.array_equal(q8.cpu().numpy(), exp_a)
+        y = TAB.ops.conv2d_int8_padded(q8, w8, t, p1, p2, N, H, W, C, KN, K, K)
+        yo = c_oracle.conv2d(x, qw, ths, btn, t, p1, p2, 1, 1, N, H, W, C, KN, K, K)
+        assert np.array_equal(y.cpu().numpy(), yo)
+        assert _cabi.lib().tab_debug_umma_status() == 0
+
+
 def test_kernels_larger_than_the_tensor_path_limit_fall_back(cuda):
     """9x9 kernels (81 taps) exceed the tensor-core loader's 64-tap mask: the call must still be exact."""
     N, H, W, C, KN, K = 1, 12, 12, 64, 8, 9
