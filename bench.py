@@ -513,24 +513,11 @@ def main():
             yb = torch.empty(n_local * oh * oh * cs.KN, dtype=torch.float32, device=dev)
             geom = (cs.pad, cs.pad, cs.stride, cs.stride, n_local, ih, ih, cs.C, cs.KN, cs.K, cs.K)
             # the GEMM stage alone, through the kernel tab_conv2d_launch picks for this layer
-            if cs.stride == 1:
-                q8 = tab_ops.quantize_int8_padded(xin, ths, 2, n_local, ih, ih, cs.C, cs.pad, cs.pad)
-                gemm_kernel = "persistent tcgen05 (TMA)"
-                ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_padded_launch(
-                    q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, cs.pad, cs.pad, n_local, ih, ih, cs.C, cs.KN, cs.K, cs.K, stream), "int8p"))
-                in_bytes = q8.numel()
-            elif cs.K == 1 and cs.pad == 0:
-                xs = xin[:, ::cs.stride, ::cs.stride, :].contiguous()      # the strided 1x1 reads only these pixels
-                q8 = tab_ops.quantize_int8_padded(xs, ths, 2, n_local, oh, oh, cs.C, 0, 0)
-                gemm_kernel = "persistent tcgen05 (TMA), subsampled input"
-                ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_padded_launch(
-                    q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, 0, 0, n_local, oh, oh, cs.C, cs.KN, 1, 1, stream), "int8p"))
-                in_bytes = q8.numel()
-            else:
-                q8 = tab_ops.quantize_int8(xin, ths, 2, n_local, ih, ih, cs.C)
-                gemm_kernel = "tcgen05 (cp.async im2col)"
-                ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_launch(q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "int8"))
-                in_bytes = q8.numel()
+            q8 = tab_ops.quantize_int8_padded(xin, ths, 2, n_local, ih, ih, cs.C, cs.K, cs.K, cs.pad, cs.pad, cs.stride, cs.stride)
+            gemm_kernel = "conv_umma_persist_kernel"
+            ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_padded_launch(
+                q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "int8p"))
+            in_bytes = q8.numel()
             ms_popc = time_launch(lambda: _cabi.check(lib.tab_conv2d_packed_launch(qx.data_ptr(), qw.data_ptr(), btn.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "popc"))
             ms_call = time_launch(lambda: tab_ops.Conv2d(xin, qw, ths, btn, CONV_TYPE, *geom))
             lops = 2 * n_local * oh * oh * cs.KN * cs.K * cs.K * cs.C
@@ -553,8 +540,8 @@ def main():
     tensor_peak = umma_tops                      # measured in this run; 2 x the measured bf16 figure is reported beside it
     achieved = sums["ops"] / (sums["gemm_ms"] * 1e-3) / 1e12 if sums["gemm_ms"] else None
     roofline = {
-        "kernel": "int8 tensor-core GEMM stage of Conv2d: conv_umma_persist_kernel (persistent TMA-fed tcgen05.mma kind::i8) for the "
-                  "stride-1 and 1x1 layers, conv_umma_kernel (tcgen05, cp.async im2col) for the three stride-2 3x3 layers; %d launches per step" % len(layer_rows),
+        "kernel": "int8 tensor-core GEMM stage of Conv2d: conv_umma_persist_kernel (persistent TMA-fed tcgen05.mma kind::i8), "
+                  "%d launches per step" % len(layer_rows),
         "bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TOP/s",
         "frac": (achieved / tensor_peak) if achieved else None,
         # DRAM bytes of the largest launch of the step (56x56x64->64, batch 256), from the ncu capture summarised under profiles/

@@ -149,18 +149,23 @@ int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int ty
                            int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
 
 /*
- * The same stages in the form tab_conv2d_launch itself uses for stride-1 convolutions: the quantiser writes the
- * padding into the byte tensor, [N][H+2*p1][W+2*p2][Cp] with border pixels 0 (ternary activations) or +1 (binary
- * activations, bitwidth 1) - the reference's padded im2row input (TAB_Utils.cu:23-63) in bytes - and the GEMM
- * stage (the persistent TMA-fed tcgen05 kernel) reads padding taps like any other pixel.
- *   tab_quantize_int8_padded_launch  N <= 65535
- *   tab_conv2d_int8_padded_launch    stride 1 only; weights from tab_expand_weights_launch; returns
- *                                    TAB_E_TOO_LARGE when the shape is not covered (N*(H+2*p1)*(W+2*p2) >= 2^31,
- *                                    KH*KW > 64, N > 65535)
+ * The same stages in the form tab_conv2d_launch itself uses: the quantiser writes the convolution's padding into the
+ * byte tensor - border pixels 0 (ternary activations) or +1 (binary activations, bitwidth 1): the reference's padded
+ * im2row input (TAB_Utils.cu:23-63) in bytes - and, for a strided convolution, splits the padded image into the
+ * s1 x s2 parity planes the taps read:
+ *     qx8p [A*B][N][PH2][PW2][Cp],  A = min(s1, KH), B = min(s2, KW), PH2 = ceil((H+2*p1)/s1), PW2 = ceil((W+2*p2)/s2),
+ *     plane a*B+b, pixel (i, j) = padded pixel (s1*i + a, s2*j + b)        (stride 1: the padded image [N][H+2*p1][W+2*p2][Cp])
+ * so that every tap is a stride-1 window of one plane, which the GEMM stage (the persistent TMA-fed tcgen05 kernel)
+ * addresses as a shifted start into a patch it stages once per tile.
+ *   tab_quantize_int8_padded_launch  N < 65535
+ *   tab_conv2d_int8_padded_launch    weights from tab_expand_weights_launch; returns TAB_E_TOO_LARGE when the shape is
+ *                                    not covered (A*B*N*PH2*PW2 >= 2^31, KH*KW > 64, N >= 65535, or a patch of
+ *                                    128 + (KH-1)/s1*PW2 + (KW-1)/s2 rows that does not fit shared memory)
  */
 int tab_quantize_int8_padded_launch(const float* x, const float* ths, int8_t* qx8p, int bitwidth,
-                                    int N, int H, int W, int C, int p1, int p2, tab_stream_t stream);
-int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y, int type, int p1, int p2,
+                                    int N, int H, int W, int C, int KH, int KW, int p1, int p2, int s1, int s2,
+                                    tab_stream_t stream);
+int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
                                   int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
 
 /*

@@ -29,8 +29,8 @@ SYMBOLS = {
     "tab_quantize_int8_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 5 + [_c.c_void_p]),
     "tab_expand_weights_launch": (_c.c_int, [_c.c_void_p] * 2 + [_c.c_int] * 5 + [_c.c_void_p]),
     "tab_conv2d_int8_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p]),
-    "tab_quantize_int8_padded_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 7 + [_c.c_void_p]),
-    "tab_conv2d_int8_padded_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 10 + [_c.c_void_p]),
+    "tab_quantize_int8_padded_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 11 + [_c.c_void_p]),
+    "tab_conv2d_int8_padded_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p]),
     "tab_conv2d_static_launch": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 12 + [_c.c_void_p]),
     "tab_residual_threshold_launch": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_float, _c.c_int, _c.c_longlong, _c.c_void_p]),
     "tab_pipe_probe_sink_bytes": (_c.c_size_t, []),

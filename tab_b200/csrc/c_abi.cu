@@ -14,7 +14,7 @@ int record_cuda_error(cudaError_t e) {
 void conv_set_csa(bool on);
 void imma_set_variant(int v);
 int umma_status_read_and_clear();
-size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2);
+size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2, int s1, int s2);
 int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
                        int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
                        cudaStream_t stream, const float* residual, double* abs_sums, float* next_ths, float next_scale);
@@ -22,8 +22,8 @@ struct FusedTail;
 int residual_abs_sum_dispatch(float* y, const float* residual, double* sums, int N, long long per_image, cudaStream_t s);
 int quantize_int8_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C, cudaStream_t stream);
 int quantize_int8_padded_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
-                                  int p1, int p2, int Hq, int Wq, int sy, int sx, cudaStream_t stream);
-int conv_int8_padded_dispatch(const int8_t* qx8p, const int8_t* w8, float* y, int p1, int p2, int N, int H, int W, int C,
+                                  int KH, int KW, int p1, int p2, int s1, int s2, cudaStream_t stream);
+int conv_int8_padded_dispatch(const int8_t* qx8p, const int8_t* w8, float* y, int p1, int p2, int s1, int s2, int N, int H, int W, int C,
                               int KN, int KH, int KW, cudaStream_t stream, const float* residual, double* abs_sums);
 int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream);
 int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary_act, int p1, int p2, int s1, int s2,
@@ -83,7 +83,7 @@ static size_t popc_workspace_bytes(int type, int N, int H, int W, int C) {
 
 size_t tab_conv2d_workspace_bytes(int type, int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW) {
     if (type < 0 || type > 3 || !dims_ok(N, H, W, C) || KN < 0 || KH < 1 || KW < 1 || p1 < 0 || p2 < 0 || s1 < 1 || s2 < 1) return 0;
-    const size_t a = popc_workspace_bytes(type, N, H, W, C), b = imma_workspace_bytes(N, H, W, C, KN, KH, KW, p1, p2);
+    const size_t a = popc_workspace_bytes(type, N, H, W, C), b = imma_workspace_bytes(N, H, W, C, KN, KH, KW, p1, p2, s1, s2);
     return a > b ? a : b;
 }
 
@@ -232,26 +232,27 @@ int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int ty
 }
 
 int tab_quantize_int8_padded_launch(const float* x, const float* ths, int8_t* qx8p, int bitwidth,
-                                    int N, int H, int W, int C, int p1, int p2, tab_stream_t stream) {
-    if (!dims_ok(N, H, W, C) || bitwidth < 1 || p1 < 0 || p2 < 0) return TAB_E_BAD_ARGUMENT;
+                                    int N, int H, int W, int C, int KH, int KW, int p1, int p2, int s1, int s2,
+                                    tab_stream_t stream) {
+    if (!dims_ok(N, H, W, C) || bitwidth < 1 || p1 < 0 || p2 < 0 || s1 < 1 || s2 < 1 || KH < 1 || KW < 1) return TAB_E_BAD_ARGUMENT;
     if ((long long)N * (H + 2LL * p1) * (W + 2LL * p2) == 0) return TAB_OK;
     if (!x || !ths || !qx8p) return TAB_E_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) || (reinterpret_cast<uintptr_t>(qx8p) & 15))
         return TAB_E_ALIGNMENT;
-    return quantize_int8_padded_dispatch(x, ths, qx8p, bitwidth == 1 ? 1 : 2, N, H, W, C, p1, p2, H, W, 1, 1,
+    return quantize_int8_padded_dispatch(x, ths, qx8p, bitwidth == 1 ? 1 : 2, N, H, W, C, KH, KW, p1, p2, s1, s2,
                                          reinterpret_cast<cudaStream_t>(stream));
 }
 
-int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y, int type, int p1, int p2,
+int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
                                   int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
-    int rc = conv_args_ok(type, p1, p2, 1, 1, N, H, W, C, KN, KH, KW);
+    int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
     if (rc != TAB_OK) return rc;
-    const long long oh = (long long)H + 2LL * p1 - KH + 1, ow = (long long)W + 2LL * p2 - KW + 1;
+    const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
     if (!qx8p || !w8 || !y) return TAB_E_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(qx8p) & 15) || (reinterpret_cast<uintptr_t>(w8) & 15) || (reinterpret_cast<uintptr_t>(y) & 3))
         return TAB_E_ALIGNMENT;
-    return conv_int8_padded_dispatch(qx8p, w8, y, p1, p2, N, H, W, C, KN, KH, KW, reinterpret_cast<cudaStream_t>(stream),
+    return conv_int8_padded_dispatch(qx8p, w8, y, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, reinterpret_cast<cudaStream_t>(stream),
                                      nullptr, nullptr);
 }
 

@@ -77,11 +77,14 @@ quantize_int8_kernel(const float* __restrict__ x, const float* __restrict__ ths,
     }
 }
 
-// Same quantiser writing a zero-padded (or +1-padded, for binary activations) tensor [N][PH][PW][Cp]: the input
-// of the TMA-fed GEMM, which reads padding taps like any other pixel.  One thread per 16 channels of a PADDED
-// pixel; border pixels get the padding value in the real channels and 0 in the channel padding.
-// The quantised grid may subsample the input: its pixel (i, j) is input pixel (i*sy, j*sx) and it has Hq x Wq
-// pixels before padding (a strided 1x1 convolution only ever reads those pixels).
+// Same quantiser writing the layout of the TMA-fed GEMM: the zero-padded (or +1-padded, for binary activations) image,
+// split into the s1 x s2 "parity planes" a strided convolution reads:  [plane (a, b)][N][PH2][PW2][Cp], where plane
+// pixel (i, j) is padded pixel (s1*i + a, s2*j + b) and only planes that hold a tap exist (a < A = min(s1, KH),
+// b < B = min(s2, KW)).  Tap (kh, kw) of output (oh, ow) is then pixel (oh + kh/s1, ow + kw/s2) of plane
+// (kh % s1, kw % s2): stride 1 inside every plane.  With stride 1 this is the padded image itself.  One thread per
+// 16 channels of a plane pixel; border pixels get the padding value in the real channels, 0 in the channel padding.
+struct QLayout { int p1, p2, s1, s2, A, B, PH2, PW2; };
+
 // One thread per (filter, word k, 16-channel group) of the packed weights: 16 bytes of {-1,0,+1}.
 template <int WB>
 __device__ __forceinline__ void expand_group(const uint64_t* __restrict__ qw, int8_t* __restrict__ w8, long long idx, int PC, int C) {
@@ -129,7 +132,7 @@ struct PrepExtras {
 template <int BITS, bool VEC>
 __global__ void __launch_bounds__(Q8THREADS)
 quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict__ ths, int8_t* __restrict__ q,
-                            int H, int W, int C, int Cp, int p1, int p2, int Hq, int Wq, int sy, int sx, const PrepExtras ex) {
+                            int H, int W, int C, int Cp, const QLayout L, const PrepExtras ex) {
     const int n = blockIdx.y;
     if (ex.qw != nullptr) {                                                // the weights, spread over all CTAs of the launch
         const int PC = Cp >> 6;
@@ -145,18 +148,38 @@ quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict
     }
     const float t = __ldg(ths + n), nt = -t;
     const int gpp = Cp >> 4;
-    const int PH = Hq + 2 * p1, PW = Wq + 2 * p2;
-    const long long groups = (long long)PH * PW * gpp;
+    const long long plane_pix = (long long)L.PH2 * L.PW2;
+    const long long groups = (long long)L.A * L.B * plane_pix * gpp;
     const float* xi = x + (long long)n * H * W * C;
-    int8_t* qi = q + (long long)n * PH * PW * Cp;
+    const long long plane_stride = (long long)gridDim.y * plane_pix;      // pixels of one plane over all images
+    const bool small = groups < (1LL << 31);                               // 32-bit index arithmetic (always, in practice)
+    const bool one_plane = L.A * L.B == 1;
     for (long long g = (long long)blockIdx.x * Q8THREADS + threadIdx.x; g < groups; g += (long long)gridDim.x * Q8THREADS) {
-        const long long pix = g / gpp;
-        const int c0 = (int)(g - pix * gpp) << 4;
-        const int ph = (int)(pix / PW), pw = (int)(pix - (long long)ph * PW);
-        const int ih = ph - p1, iw = pw - p2;
+        int c0, plane, i, j;
+        long long pix;
+        if (small) {
+            const unsigned ug = (unsigned)g, upix = ug / (unsigned)gpp;
+            c0 = (int)(ug - upix * (unsigned)gpp) << 4;
+            const unsigned upl = one_plane ? 0u : upix / (unsigned)plane_pix;
+            const unsigned up = upix - upl * (unsigned)plane_pix;
+            plane = (int)upl;
+            i = (int)(up / (unsigned)L.PW2);
+            j = (int)(up - (unsigned)i * (unsigned)L.PW2);
+            pix = up;
+        } else {
+            const long long pixall = g / gpp;
+            c0 = (int)(g - pixall * gpp) << 4;
+            plane = (int)(pixall / plane_pix);
+            pix = pixall - plane * plane_pix;
+            i = (int)(pix / L.PW2);
+            j = (int)(pix - (long long)i * L.PW2);
+        }
+        const int pa = plane / L.B, pb = plane - pa * L.B;
+        const int ih = L.s1 * i + pa - L.p1, iw = L.s2 * j + pb - L.p2;
+        int8_t* qi = q + (plane * plane_stride + (long long)n * plane_pix) * Cp;
         uint32_t o[4];
-        if ((unsigned)ih < (unsigned)Hq && (unsigned)iw < (unsigned)Wq) {
-            const float* src = xi + ((long long)ih * sy * W + (long long)iw * sx) * C + c0;
+        if ((unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) {
+            const float* src = xi + ((long long)ih * W + iw) * C + c0;
             float v[16];
             if (VEC && c0 + 16 <= C) {
 #pragma unroll
@@ -167,16 +190,16 @@ quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict
                                  : "l"(src + 8 * h));
             } else {
 #pragma unroll
-                for (int i = 0; i < 16; i++) v[i] = (c0 + i < C) ? __ldg(src + i) : 0.f;
+                for (int e = 0; e < 16; e++) v[e] = (c0 + e < C) ? __ldg(src + e) : 0.f;
             }
 #pragma unroll
             for (int w = 0; w < 4; w++) {
                 uint32_t r = 0;
 #pragma unroll
                 for (int b = 0; b < 4; b++) {
-                    const int i = 4 * w + b;
-                    int qv = (BITS == 2) ? q_ternary(v[i], t, nt) : q_binary(v[i], t);
-                    if (c0 + i >= C) qv = 0;
+                    const int e = 4 * w + b;
+                    int qv = (BITS == 2) ? q_ternary(v[e], t, nt) : q_binary(v[e], t);
+                    if (c0 + e >= C) qv = 0;
                     r |= (uint32_t)(qv & 0xFF) << (8 * b);
                 }
                 o[w] = r;
@@ -695,9 +718,17 @@ bool conv_tma_persist_fits(const ImmaParams& p);
 static int g_imma_variant = 0;
 static const bool g_tma_default = true;   // persistent TMA-fed kernel where it applies (measured ahead of the others)
 
-size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2) {
+// Pixels per image of the activation scratch: the padded image, or its parity planes (rounded up per plane).
+static size_t scratch_pixels(int H, int W, int KH, int KW, int p1, int p2, int s1, int s2) {
+    const size_t padded = (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2);
+    const size_t A = s1 < KH ? s1 : KH, B = s2 < KW ? s2 : KW;
+    const size_t planes = A * B * ((H + 2 * (size_t)p1 + s1 - 1) / s1) * ((W + 2 * (size_t)p2 + s2 - 1) / s2);
+    return padded > planes ? padded : planes;
+}
+
+size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2, int s1, int s2) {
     const size_t Cp = (size_t)packed_channels(C) * 64;
-    const size_t a = ((size_t)N * (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2) * Cp + 255) / 256 * 256;   // room for the padded form
+    const size_t a = ((size_t)N * scratch_pixels(H, W, KH, KW, p1, p2, s1, s2) * Cp + 255) / 256 * 256;
     const size_t b = ((size_t)KN * KH * KW * Cp + 255) / 256 * 256;
     return a + b + 256;                          // + completion counter of the fused tail
 }
@@ -787,25 +818,20 @@ int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary
 
 void imma_set_variant(int v) { g_imma_variant = v; }
 
-// x fp32 -> y, all four types, scratch in `workspace` (imma_workspace_bytes).
-static int quantize_prep_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
-                                  int p1, int p2, int Hq, int Wq, int sy, int sx, const PrepExtras& ex, cudaStream_t stream);
-
-// Quantise to the zero-padded byte tensor [N][Hq + 2*p1][Wq + 2*p2][Cp]; quantised pixel (i, j) is input pixel
-// (i*sy, j*sx).  Binary activations (bits 1) get +1 in the border.  N <= 65535.
-int quantize_int8_padded_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
-                                  int p1, int p2, int Hq, int Wq, int sy, int sx, cudaStream_t stream) {
-    PrepExtras none = {};
-    none.images = N;
-    return quantize_prep_dispatch(x, ths, qx8, bits, N, H, W, C, p1, p2, Hq, Wq, sy, sx, none, stream);
+// Plane layout of a convolution geometry (see QLayout).
+static QLayout plane_layout(int H, int W, int KH, int KW, int p1, int p2, int s1, int s2) {
+    QLayout L;
+    L.p1 = p1; L.p2 = p2; L.s1 = s1; L.s2 = s2;
+    L.A = s1 < KH ? s1 : KH; L.B = s2 < KW ? s2 : KW;
+    L.PH2 = (H + 2 * p1 + s1 - 1) / s1; L.PW2 = (W + 2 * p2 + s2 - 1) / s2;
+    return L;
 }
 
 static int quantize_prep_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
-                                  int p1, int p2, int Hq, int Wq, int sy, int sx, const PrepExtras& ex, cudaStream_t stream) {
+                                  const QLayout& L, const PrepExtras& ex, cudaStream_t stream) {
     if (N >= 65535) return TAB_E_TOO_LARGE;
     const int Cp = packed_channels(C) * 64;
-    const long long PH = Hq + 2LL * p1, PW = Wq + 2LL * p2;
-    const long long groups = PH * PW * (Cp / 16);
+    const long long groups = (long long)L.A * L.B * L.PH2 * L.PW2 * (Cp / 16);
     if (N == 0 || groups == 0) return TAB_OK;
     long long per = (groups + Q8THREADS - 1) / Q8THREADS;
     const long long cap = (148LL * 8 * 4 + N - 1) / N;
@@ -814,29 +840,37 @@ static int quantize_prep_dispatch(const float* x, const float* ths, int8_t* qx8,
     dim3 grid((unsigned)per, (unsigned)N);
     const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)H * W * C) % 8 == 0);
     if (bits == 2) {
-        if (vec) quantize_int8_padded_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2, Hq, Wq, sy, sx, ex);
-        else quantize_int8_padded_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2, Hq, Wq, sy, sx, ex);
+        if (vec) quantize_int8_padded_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, L, ex);
+        else quantize_int8_padded_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, L, ex);
     } else {
-        if (vec) quantize_int8_padded_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2, Hq, Wq, sy, sx, ex);
-        else quantize_int8_padded_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, p1, p2, Hq, Wq, sy, sx, ex);
+        if (vec) quantize_int8_padded_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, L, ex);
+        else quantize_int8_padded_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, L, ex);
     }
     return check_launch();
 }
 
-// GEMM stage on activations that already carry their padding (stride 1): the TMA-fed tcgen05 kernels.
+// Quantise to the padded plane layout of a convolution geometry (QLayout).  Binary activations (bits 1) get +1 in
+// the border.  N < 65535.
+int quantize_int8_padded_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
+                                  int KH, int KW, int p1, int p2, int s1, int s2, cudaStream_t stream) {
+    PrepExtras none = {};
+    none.images = N;
+    return quantize_prep_dispatch(x, ths, qx8, bits, N, H, W, C, plane_layout(H, W, KH, KW, p1, p2, s1, s2), none, stream);
+}
+
+// GEMM stage on activations in the padded plane layout: the TMA-fed tcgen05 kernels.
 // TAB_E_TOO_LARGE when the shape is not covered.
-int conv_int8_padded_dispatch(const int8_t* qx8p, const int8_t* w8, float* y, int p1, int p2, int N, int H, int W, int C,
+int conv_int8_padded_dispatch(const int8_t* qx8p, const int8_t* w8, float* y, int p1, int p2, int s1, int s2, int N, int H, int W, int C,
                               int KN, int KH, int KW, cudaStream_t stream, const float* residual, double* abs_sums) {
-    const long long oh = (long long)H + 2LL * p1 - KH + 1, ow = (long long)W + 2LL * p2 - KW + 1;
+    const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (oh <= 0 || ow <= 0 || N == 0 || KN == 0) return TAB_OK;
     int rc = imma_limits(N, H, W, C, KN, KH, KW, oh, ow);
     if (rc != TAB_OK) return rc;
-    const long long PH = H + 2LL * p1, PW = W + 2LL * p2;
-    if (N * PH * PW >= (1LL << 31) - 4096) return TAB_E_TOO_LARGE;
+    if (N >= 65535) return TAB_E_TOO_LARGE;
     ImmaParams p;
     p.qx = qx8p; p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
     p.N = N; p.H = H; p.W = W; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
-    p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = 1; p.s2 = 1;
+    p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
     p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * p.PC;
     return conv_tma_dispatch(p, g_imma_variant == 7 ? 2 : 1, stream);
 }
@@ -854,7 +888,7 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
     if (rc != TAB_OK) return rc;
     if (N >= 65535) return TAB_E_TOO_LARGE;
     int8_t* qx8 = reinterpret_cast<int8_t*>(workspace);
-    int8_t* w8 = qx8 + ((size_t)N * (H + 2 * (size_t)p1) * (W + 2 * (size_t)p2) * Cp + 255) / 256 * 256;
+    int8_t* w8 = qx8 + ((size_t)N * scratch_pixels(H, W, KH, KW, p1, p2, s1, s2) * Cp + 255) / 256 * 256;
     unsigned* counter = reinterpret_cast<unsigned*>(w8 + ((size_t)KN * KH * KW * Cp + 255) / 256 * 256);
     FusedTail tail = {};
     if (next_ths && abs_sums) { tail.ths_out = next_ths; tail.scale = next_scale; tail.counter = counter; }
@@ -865,45 +899,40 @@ int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, floa
     ex.qw = reinterpret_cast<const uint64_t*>(qw); ex.w8 = w8;
     ex.words = (long long)KN * KH * KW * packed_channels(C);
     ex.wbits = weight_bits(type);
-    // A strided 1x1 convolution without padding reads only every s-th pixel: quantise just those, densely, and run
-    // it as a stride-1 convolution on the subsampled grid.
-    int Hq = H, Wq = W, sy = 1, sx = 1, S1 = s1, S2 = s2;
-    if (KH == 1 && KW == 1 && p1 == 0 && p2 == 0 && (s1 > 1 || s2 > 1)) { Hq = (int)oh; Wq = (int)ow; sy = s1; sx = s2; S1 = S2 = 1; }
-    auto quantize_padded = [&](int q1, int q2) -> int {
-        return quantize_prep_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, q1, q2, Hq, Wq, sy, sx, ex, stream);
-    };
-    // Persistent TMA-fed tcgen05 kernel on zero-padded activations: stride 1; at least 4 taps unless there is no
-    // padding at all (with fewer, the padded grid costs more than the patch saves); at least 45 % of the padded
-    // grid useful.
+    // Persistent TMA-fed tcgen05 kernel on the padded plane layout (any stride); at least 4 taps unless there is no
+    // padding at all (with fewer, the padded grid costs more than the patch saves); at least 45 % of the plane grid
+    // useful.  A strided 1x1 convolution has the single plane of the pixels it reads.
     bool quantized = false;
     {
-        const long long PH = Hq + 2LL * p1, PW = Wq + 2LL * p2;
-        const double useful = (double)oh * ow / ((double)PH * PW);
+        const QLayout L = plane_layout(H, W, KH, KW, p1, p2, s1, s2);
+        const long long rows = (long long)L.A * L.B * N * L.PH2 * L.PW2;
+        const double useful = (double)oh * ow / ((double)L.PH2 * L.PW2);
         ImmaParams p;
         p.qx = qx8; p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
-        p.N = N; p.H = Hq; p.W = Wq; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
-        p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = S1; p.s2 = S2;
+        p.N = N; p.H = H; p.W = W; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
+        p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
         p.M = (int)((long long)N * oh * ow); p.Kw = KH * KW * p.PC;
         if (tail.ths_out) {
             p.ths_out = tail.ths_out; p.ths_scale = tail.scale; p.done_counter = tail.counter;
             p.per_image = (double)KN * (double)oh * (double)ow;
         }
-        const bool shape = S1 == 1 && S2 == 1 && (KH * KW >= 4 || (p1 == 0 && p2 == 0)) && N * PH * PW < (1LL << 31) - 4096;
-        const bool want = shape && (g_imma_variant == 6 || g_imma_variant == 7 ||
-                                    (g_imma_variant == 0 && g_tma_default && useful >= 0.45 && conv_tma_persist_fits(p)));
+        const bool unit = s1 == 1 && s2 == 1;
+        const bool shape = (KH * KW >= 4 || (p1 == 0 && p2 == 0)) && rows < (1LL << 31) - 4096;
+        const bool want = shape && (((g_imma_variant == 6 || g_imma_variant == 7) && unit) ||
+                                    ((g_imma_variant == 0 || g_imma_variant == 6) && g_tma_default && useful >= 0.45 && conv_tma_persist_fits(p)));
         if (want) {
-            rc = quantize_padded(p1, p2);
+            rc = quantize_prep_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, L, ex, stream);
             if (rc != TAB_OK) return rc;
-            quantized = p1 == 0 && p2 == 0;           // without padding the layout is the one the other kernels read
+            quantized = unit && p1 == 0 && p2 == 0;   // then the layout is the one the other kernels read
             rc = conv_tma_dispatch(p, g_imma_variant == 7 ? 2 : (g_imma_variant == 6 ? 1 : 0), stream);
             if (rc != TAB_E_TOO_LARGE) return rc;     // shape not covered after all: continue with the unpadded form
         }
     }
     if (!quantized) {
-        rc = quantize_padded(0, 0);
+        rc = quantize_prep_dispatch(x, ths, qx8, act_bits(type), N, H, W, C, plane_layout(H, W, 1, 1, 0, 0, 1, 1), ex, stream);
         if (rc != TAB_OK) return rc;
     }
-    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, S1, S2, N, Hq, Wq, C, KN, KH, KW, stream, residual, abs_sums, &tail);
+    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream, residual, abs_sums, &tail);
 }
 
 }  // namespace tab

@@ -857,7 +857,9 @@ __device__ __forceinline__ bool elect_one() {
 // memory; otherwise it streams through a ring of SB stages, one stage per tap and channel pair.
 constexpr int PTHREADS = 384;                                              // warps 0-2 producers and MMA, 3 idle, 4-11 epilogue
 
-template <int MT, int TNI, int SB, bool BRES, bool FUSED>
+// UNIT: stride 1 in both directions (one plane; the tap loops are then flat, which matters because the MMA warp's
+// instruction stream, not the tensor pipe, limits small tiles).
+template <int MT, int TNI, int SB, bool BRES, bool FUSED, bool UNIT>
 __global__ void __launch_bounds__(PTHREADS, 1)
 conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const ImmaParams p, int* __restrict__ status, const int prow, const int nst,
@@ -880,7 +882,12 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const uint32_t sStage = sbase + tail + 256;                            // [8 epilogue warps][4 KB]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int PH = p.H + 2 * p.p1, PW = p.W + 2 * p.p2, PHW = PH * PW;
+    // Activations come as parity planes (stride 1: the one padded image): plane (a, b), a < PA, b < PB, is a
+    // [N][PH][PW] grid; tap (kh, kw) reads plane (kh % s1, kw % s2) at row offset (kh / s1) * PW + kw / s2.
+    const int s1 = p.s1, s2 = p.s2;
+    const int PA = s1 < p.KH ? s1 : p.KH, PB = s2 < p.KW ? s2 : p.KW;
+    const int PH = (p.H + 2 * p.p1 + s1 - 1) / s1, PW = (p.W + 2 * p.p2 + s2 - 1) / s2, PHW = PH * PW;
+    const int plane_rows = p.N * PHW;
     const int T = p.KH * p.KW, ncp = (p.PC + 1) >> 1;
     const int ntiles = tiles_m * tiles_n;
 
@@ -905,6 +912,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     // In every role the whole warp runs the loops and the waits and one elected lane issues the copies, MMAs and
     // commits: loop counters, addresses and descriptors then stay warp-uniform values (a single-thread role was
     // measured to spend 130-170 cycles per MMA on issue alone; this form 45-90).
+    // All roles walk the same nest: tile, channel pair cp, plane (a, b), taps of that plane.  One patch is staged
+    // per (tile, cp, plane); counters q (patches) and g (ring stages) run across tiles.
     if (warp == 0) {
         // ---- patch producer: runs ahead of the MMAs by up to two patches (across tile boundaries) ----------------
         const int nbox = prow / TMA_BOX_ROWS;
@@ -912,18 +921,21 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         bool dead = false;
         for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x) {
             const int R0 = (t / tiles_n) * (UTM * MT);
-            for (int cp = 0; cp < ncp; cp++, q++) {
-                const unsigned pb = q & 1;
-                if (q >= 2 && !PWAIT(0, mbar_wait_warp(emptyP + 8 * pb, ((q >> 1) - 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 11); break; }
-                if (elect_one()) {
-                    if (PDBG(2)) mbar_arrive(fullP + 8 * pb);
-                    else {
-                        mbar_expect_tx(fullP + 8 * pb, (uint32_t)(nbox * TMA_BOX_ROWS * IROW));
-                        for (int b = 0; b < nbox; b++)
-                            tma_load_2d(sPatch + (pb * prow + b * TMA_BOX_ROWS) * IROW, &tmA, 2 * cp * 64, R0 + b * TMA_BOX_ROWS, fullP + 8 * pb);
+            for (int cp = 0; cp < ncp && !dead; cp++) {
+                for (int pl = 0; pl < PA * PB; pl++, q++) {
+                    const unsigned pb = q & 1;
+                    if (q >= 2 && !PWAIT(0, mbar_wait_warp(emptyP + 8 * pb, ((q >> 1) - 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 11); break; }
+                    if (elect_one()) {
+                        if (PDBG(2)) mbar_arrive(fullP + 8 * pb);
+                        else {
+                            mbar_expect_tx(fullP + 8 * pb, (uint32_t)(nbox * TMA_BOX_ROWS * IROW));
+                            for (int b = 0; b < nbox; b++)
+                                tma_load_2d(sPatch + (pb * prow + b * TMA_BOX_ROWS) * IROW, &tmA, 2 * cp * 64,
+                                            pl * plane_rows + R0 + b * TMA_BOX_ROWS, fullP + 8 * pb);
+                        }
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
         }
     } else if (warp == 2) {
@@ -942,14 +954,32 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x) {
                 const int n0 = (t % tiles_n) * TNI;
                 for (int cp = 0; cp < ncp && !dead; cp++) {
-                    for (int tap = 0; tap < T; tap++, g++) {
+                    if (UNIT) {
+                        for (int tap = 0; tap < T; tap++, g++) {
+                            const unsigned slot = g % SB;
+                            if (g >= (unsigned)SB && !PWAIT(1, mbar_wait_warp(emptyB + 8 * slot, ((g / SB) - 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 12); break; }
+                            if (elect_one()) {
+                                if (PDBG(4)) mbar_arrive(fullB + 8 * slot);
+                                else {
+                                    mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
+                                    tma_load_2d(sRing + slot * BSTAGE, &tmB, (tap * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
+                                }
+                            }
+                            __syncwarp();
+                        }
+                        continue;
+                    }
+                    for (int pa = 0; pa < PA && !dead; pa++)
+                    for (int pbb = 0; pbb < PB && !dead; pbb++)
+                    for (int kh = pa; kh < p.KH && !dead; kh += s1)
+                    for (int kw = pbb; kw < p.KW; kw += s2, g++) {
                         const unsigned slot = g % SB;
                         if (g >= (unsigned)SB && !PWAIT(1, mbar_wait_warp(emptyB + 8 * slot, ((g / SB) - 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 12); break; }
                         if (elect_one()) {
                             if (PDBG(4)) mbar_arrive(fullB + 8 * slot);
                             else {
                                 mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
-                                tma_load_2d(sRing + slot * BSTAGE, &tmB, (tap * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
+                                tma_load_2d(sRing + slot * BSTAGE, &tmB, ((kh * p.KW + kw) * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
                             }
                         }
                         __syncwarp();
@@ -970,63 +1000,91 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             if (a >= 2 && !PWAIT(0, mbar_wait_warp(accEmpty + 8 * buf, ((a >> 1) - 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 13); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem_base + buf * ACOLS;
-            for (int cp = 0; cp < ncp && !dead; cp++, q++) {
-                const unsigned pb = q & 1;
-                if (!PWAIT(1, mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 14); break; }
+            uint32_t accumulate = 0;                                       // 0 for the tile's first MMAs
+            for (int cp = 0; cp < ncp && !dead; cp++) {
                 const bool four = 2 * cp + 1 < p.PC;                       // both 64-channel words of the pair exist
-                uint32_t arow = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;   // descriptor address of the tap's first patch row
-                int kw = 0;
-                if (BRES) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (elect_one()) {
-                        for (int tap = 0; tap < T; tap++) {
-                            const uint64_t da = ((uint64_t)DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4));
-                            const uint64_t db = ((uint64_t)DESC_HI << 32) | ((sRing + (uint32_t)(cp * T + tap) * BSTAGE) >> 4);
-                            const uint32_t first = (cp > 0 || tap > 0) ? 1u : 0u;
+                // the MMAs of one tap: 2 or 4 K steps of 32 bytes, MT row blocks each
+                auto issue_tap = [&](uint64_t da, uint64_t db, uint32_t acc_first) {
 #pragma unroll
-                            for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS, db, IDESC, first);
+                    for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS, db, IDESC, acc_first);
 #pragma unroll
-                            for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 2, db + 2, IDESC, 1u);
-                            if (four) {
+                    for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 2, db + 2, IDESC, 1u);
+                    if (four) {
 #pragma unroll
-                                for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 4, db + 4, IDESC, 1u);
+                        for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 4, db + 4, IDESC, 1u);
 #pragma unroll
-                                for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 6, db + 6, IDESC, 1u);
-                            }
-                            if (++kw == p.KW) { kw = 0; arow += (uint32_t)PW * (IROW >> 4); }
-                        }
-                        umma_commit(emptyP + 8 * pb);
-                        if (cp == ncp - 1) umma_commit(accFull + 8 * buf);
+                        for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 6, db + 6, IDESC, 1u);
                     }
-                    __syncwarp();
-                    continue;
-                }
-                for (int tap = 0; tap < T; tap++, g++) {
-                    const unsigned slot = g % SB;
-                    if (!PWAIT(2, mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 15); break; }
+                };
+                if (UNIT) {
+                    const unsigned pb = q & 1;
+                    if (!PWAIT(1, mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 14); break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (elect_one()) {
-                        const uint64_t da = ((uint64_t)DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4));
-                        const uint64_t db = ((uint64_t)DESC_HI << 32) | ((sRing + slot * BSTAGE) >> 4);
-                        const uint32_t first = (cp > 0 || tap > 0) ? 1u : 0u;
-#pragma unroll
-                        for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS, db, IDESC, first);
-#pragma unroll
-                        for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 2, db + 2, IDESC, 1u);
-                        if (four) {
-#pragma unroll
-                            for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 4, db + 4, IDESC, 1u);
-#pragma unroll
-                            for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 6, db + 6, IDESC, 1u);
-                        }
-                        umma_commit(emptyB + 8 * slot);
-                        if (tap == T - 1) {
+                    uint32_t arow = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;   // descriptor address of the tap's first patch row
+                    int kw = 0;
+                    if (BRES) {
+                        if (elect_one()) {                                 // nothing to wait for between taps: one issue burst
+                            for (int tap = 0; tap < T; tap++) {
+                                issue_tap(((uint64_t)DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4)),
+                                          ((uint64_t)DESC_HI << 32) | ((sRing + (uint32_t)(cp * T + tap) * BSTAGE) >> 4), (cp > 0 || tap > 0) ? 1u : 0u);
+                                if (++kw == p.KW) { kw = 0; arow += (uint32_t)PW * (IROW >> 4); }
+                            }
                             umma_commit(emptyP + 8 * pb);
                             if (cp == ncp - 1) umma_commit(accFull + 8 * buf);
                         }
+                        __syncwarp();
+                    } else {
+                        for (int tap = 0; tap < T; tap++, g++) {
+                            const unsigned slot = g % SB;
+                            if (!PWAIT(2, mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 15); break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            if (elect_one()) {
+                                issue_tap(((uint64_t)DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4)),
+                                          ((uint64_t)DESC_HI << 32) | ((sRing + slot * BSTAGE) >> 4), (cp > 0 || tap > 0) ? 1u : 0u);
+                                umma_commit(emptyB + 8 * slot);
+                                if (tap == T - 1) {
+                                    umma_commit(emptyP + 8 * pb);
+                                    if (cp == ncp - 1) umma_commit(accFull + 8 * buf);
+                                }
+                            }
+                            __syncwarp();
+                            if (++kw == p.KW) { kw = 0; arow += (uint32_t)PW * (IROW >> 4); }
+                        }
                     }
-                    __syncwarp();
-                    if (++kw == p.KW) { kw = 0; arow += (uint32_t)PW * (IROW >> 4); }
+                    q++;
+                    continue;
+                }
+                for (int pa = 0; pa < PA && !dead; pa++)
+                for (int pbb = 0; pbb < PB && !dead; pbb++, q++) {
+                    const unsigned pb = q & 1;
+                    if (!PWAIT(1, mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 14); break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t patch = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;    // descriptor address of the patch
+                    const bool last_group = cp == ncp - 1 && pa == PA - 1 && pbb == PB - 1;
+                    for (int kh = pa, ih = 0; kh < p.KH && !dead; kh += s1, ih++)
+                    for (int kw = pbb, iw = 0; kw < p.KW; kw += s2, iw++) {
+                        const bool last_tap = kh + s1 >= p.KH && kw + s2 >= p.KW;
+                        uint32_t bsm;
+                        if (BRES) bsm = sRing + (uint32_t)(cp * T + kh * p.KW + kw) * BSTAGE;
+                        else {
+                            const unsigned slot = g % SB;
+                            if (!PWAIT(2, mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 15); break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            bsm = sRing + slot * BSTAGE;
+                        }
+                        if (elect_one()) {
+                            issue_tap(((uint64_t)DESC_HI << 32) | (patch + (uint32_t)(ih * PW + iw) * (IROW >> 4)),
+                                      ((uint64_t)DESC_HI << 32) | (bsm >> 4), accumulate);
+                            if (!BRES) umma_commit(emptyB + 8 * (g % SB));
+                            if (last_tap) {
+                                umma_commit(emptyP + 8 * pb);
+                                if (last_group) umma_commit(accFull + 8 * buf);
+                            }
+                        }
+                        __syncwarp();
+                        accumulate = 1u;
+                        if (!BRES) g++;
+                    }
                 }
             }
         }
@@ -1148,11 +1206,23 @@ static int launch_umma_tma(const CUtensorMap& tmA, const CUtensorMap& tmB, const
                                       : launch_umma_tma_f<MT, TNI, SB, false>(tmA, tmB, p, status, prow, npb, stream);
 }
 
+// Plane grid of a geometry (see the persistent kernel): planes, rows and columns of one plane, patch halo rows.
+struct PlaneGrid { long long planes, PH, PW, halo; };
+static PlaneGrid plane_grid(const ImmaParams& p) {
+    PlaneGrid g;
+    const long long A = p.s1 < p.KH ? p.s1 : p.KH, B = p.s2 < p.KW ? p.s2 : p.KW;
+    g.planes = A * B;
+    g.PH = (p.H + 2LL * p.p1 + p.s1 - 1) / p.s1;
+    g.PW = (p.W + 2LL * p.p2 + p.s2 - 1) / p.s2;
+    g.halo = ((p.KH - 1) / p.s1) * g.PW + (p.KW - 1) / p.s2;
+    return g;
+}
+
 static int g_persist_dbg = 0;
 void persist_set_debug(int v) { g_persist_dbg = v; }
 
-template <int MT, int TNI, int SB, bool BRES, bool FUSED>
-static int launch_umma_persist_f(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, int prow, int nst,
+template <int MT, int TNI, int SB, bool BRES, bool FUSED, bool UNIT>
+static int launch_umma_persist_u(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, int prow, int nst,
                                  int smem_bytes, cudaStream_t stream) {
     constexpr int TMI = UTM * MT;
     static int configured[64] = {};
@@ -1161,26 +1231,32 @@ static int launch_umma_persist_f(const CUtensorMap& tmA, const CUtensorMap& tmB,
     if (e != cudaSuccess) return record_cuda_error(e);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (dev < 0 || dev >= 64 || configured[dev] < smem_bytes) {
-        e = cudaFuncSetAttribute(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
+        e = cudaFuncSetAttribute(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, UNIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
         if (e != cudaSuccess) return record_cuda_error(e);
         if (dev >= 0 && dev < 64) configured[dev] = UMMA_SMEM_MAX;
     }
-    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2;
-    const long long Mv = (long long)(p.N - 1) * PH * PW + (long long)(p.OH - 1) * PW + p.OW;
+    const PlaneGrid pg = plane_grid(p);
+    const long long Mv = (long long)(p.N - 1) * pg.PH * pg.PW + (long long)(p.OH - 1) * pg.PW + p.OW;   // last useful virtual row + 1
     const long long tiles_m = (Mv + TMI - 1) / TMI, tiles_n = (p.KN + TNI - 1) / TNI;
     if (tiles_m * tiles_n >= (1LL << 31)) return TAB_E_TOO_LARGE;
     const long long ntiles = tiles_m * tiles_n;
     const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
-    conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED><<<grid, PTHREADS, smem_bytes, stream>>>(tmA, tmB, p, status, prow, nst, (int)tiles_m,
+    conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, UNIT><<<grid, PTHREADS, smem_bytes, stream>>>(tmA, tmB, p, status, prow, nst, (int)tiles_m,
                                                                                              (int)tiles_n, g_persist_dbg);
     return check_launch();
+}
+
+template <int MT, int TNI, int SB, bool BRES, bool FUSED>
+static int launch_umma_persist_f(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, int prow, int nst,
+                                 int smem_bytes, cudaStream_t stream) {
+    return (p.s1 == 1 && p.s2 == 1) ? launch_umma_persist_u<MT, TNI, SB, BRES, FUSED, true>(tmA, tmB, p, status, prow, nst, smem_bytes, stream)
+                                    : launch_umma_persist_u<MT, TNI, SB, BRES, FUSED, false>(tmA, tmB, p, status, prow, nst, smem_bytes, stream);
 }
 
 // Shared-memory need of the persistent kernel for a tile shape; resident (out) says whether the filter block stays
 // in shared memory.  0 = does not fit.
 static long long persist_smem(const ImmaParams& p, int mt, int tn, int sb, bool* resident) {
-    const long long PW = p.W + 2LL * p.p2;
-    const long long prow = (UTM * mt + (p.KH - 1) * PW + p.KW - 1 + TMA_BOX_ROWS - 1) / TMA_BOX_ROWS * TMA_BOX_ROWS;
+    const long long prow = (UTM * mt + plane_grid(p).halo + TMA_BOX_ROWS - 1) / TMA_BOX_ROWS * TMA_BOX_ROWS;
     const long long fixed = 2 * prow * IROW + 256 + 8 * 4096 + 1024;
     const long long nres = (long long)p.KH * p.KW * ((p.PC + 1) / 2);     // stages of a resident filter block
     if (p.KN <= tn && fixed + nres * tn * IROW <= UMMA_SMEM_MAX) { *resident = true; return fixed + nres * tn * IROW; }
@@ -1191,8 +1267,7 @@ static long long persist_smem(const ImmaParams& p, int mt, int tn, int sb, bool*
 
 template <int MT, int TNI, int SB>
 static int launch_umma_persist(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, cudaStream_t stream) {
-    const long long PW = p.W + 2LL * p.p2;
-    const int prow = (int)((UTM * MT + (p.KH - 1) * PW + p.KW - 1 + TMA_BOX_ROWS - 1) / TMA_BOX_ROWS * TMA_BOX_ROWS);
+    const int prow = (int)((UTM * MT + plane_grid(p).halo + TMA_BOX_ROWS - 1) / TMA_BOX_ROWS * TMA_BOX_ROWS);
     bool resident = false;
     const long long smem_bytes = persist_smem(p, MT, TNI, SB, &resident);
     if (!smem_bytes) return TAB_E_TOO_LARGE;
@@ -1219,8 +1294,8 @@ static bool persist_plan(const ImmaParams& p, int* mt, int* tn) {
 }
 
 static bool tma_shape_ok(const ImmaParams& p) {
-    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2, rows = (long long)p.N * PH * PW;
-    return p.s1 == 1 && p.s2 == 1 && rows < (1LL << 31) - 4096;
+    const PlaneGrid pg = plane_grid(p);
+    return pg.planes * p.N * pg.PH * pg.PW < (1LL << 31) - 4096;
 }
 
 // Whether conv_tma_dispatch(p, 0, ..) will take the problem (asked before the activations are laid out padded).
@@ -1236,8 +1311,10 @@ static int* umma_status_ptr();
 // mode 0: persistent kernel or TAB_E_TOO_LARGE; 1: persistent kernel, else the one-tile-per-CTA TMA kernel; 2: the latter only.
 // TAB_E_TOO_LARGE = shape not covered (the caller falls back to the kernels on unpadded activations).
 int conv_tma_dispatch(const ImmaParams& p, int mode, cudaStream_t stream) {
-    const long long PH = p.H + 2LL * p.p1, PW = p.W + 2LL * p.p2, rows = (long long)p.N * PH * PW;
-    if (!tma_shape_ok(p) || !encode_tiled_fn()) return TAB_E_TOO_LARGE;
+    const PlaneGrid pg = plane_grid(p);
+    const long long rows = pg.planes * p.N * pg.PH * pg.PW;
+    const bool unit = p.s1 == 1 && p.s2 == 1;                              // the one-tile-per-CTA kernel knows stride 1 only
+    if (!tma_shape_ok(p) || !encode_tiled_fn() || (mode == 2 && !unit)) return TAB_E_TOO_LARGE;
     if ((reinterpret_cast<uintptr_t>(p.qx) & 15) || (reinterpret_cast<uintptr_t>(p.w8) & 15)) return TAB_E_TOO_LARGE;
     alignas(64) CUtensorMap tmA, tmB;
     const unsigned tn = p.KN <= 64 ? 64 : (p.KN <= 128 ? 128 : 256);
@@ -1251,7 +1328,7 @@ int conv_tma_dispatch(const ImmaParams& p, int mode, cudaStream_t stream) {
             if (ptn == 128) return mt == 2 ? launch_umma_persist<2, 128, 4>(tmA, tmB, p, status, stream) : launch_umma_persist<1, 128, 6>(tmA, tmB, p, status, stream);
             return launch_umma_persist<1, 256, 4>(tmA, tmB, p, status, stream);
         }
-        if (mode == 0) return TAB_E_TOO_LARGE;
+        if (mode == 0 || !unit) return TAB_E_TOO_LARGE;
     }
     if (tn == 64) return launch_umma_tma<2, 64, 4>(tmA, tmB, p, status, stream);
     if (tn == 128) return launch_umma_tma<2, 128, 4>(tmA, tmB, p, status, stream);

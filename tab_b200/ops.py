@@ -192,33 +192,43 @@ def conv2d_int8(QX8, W8, type, padding1, padding2, stride1, stride2, N, H, W, C,
     return Y
 
 
-def quantize_int8_padded(X, thresholds, bitwidth, N, H, W, C, padding1, padding2):
-    """fp32 NHWC -> int8 ``{N,H+2*padding1,W+2*padding2,Cp}``: quantised values with the convolution's padding
-    written in (0 for ternary, +1 for binary activations in the real channels)."""
+def plane_layout(H, W, KH, KW, padding1, padding2, stride1, stride2):
+    """``(A*B, PH2, PW2)`` of the padded plane layout (``include/tab_b200.h``): planes, rows and columns per plane."""
+    A, B = min(int(stride1), int(KH)), min(int(stride2), int(KW))
+    return A * B, -(-(H + 2 * int(padding1)) // int(stride1)), -(-(W + 2 * int(padding2)) // int(stride2))
+
+
+def quantize_int8_padded(X, thresholds, bitwidth, N, H, W, C, KH, KW, padding1, padding2, stride1=1, stride2=1):
+    """fp32 NHWC -> int8 ``{A*B, N, PH2, PW2, Cp}``: quantised values with the convolution's padding written in (0 for
+    ternary, +1 for binary activations in the real channels), split into the parity planes of the stride (one plane,
+    the padded image, for stride 1)."""
     _check_input(X, "X", torch.float32)
     _check_input(thresholds, "thresholds", torch.float32)
     Cp = (int(C) + 63) // 64 * 64
+    planes, PH2, PW2 = plane_layout(H, W, KH, KW, padding1, padding2, stride1, stride2)
     with torch.cuda.device(X.device):
-        q = torch.empty((N, H + 2 * int(padding1), W + 2 * int(padding2), Cp), dtype=torch.int8, device=X.device)
+        q = torch.empty((planes, N, PH2, PW2, Cp), dtype=torch.int8, device=X.device)
         rc = _cabi.lib().tab_quantize_int8_padded_launch(X.data_ptr(), thresholds.data_ptr(), q.data_ptr(), int(bitwidth),
-                                                         N, H, W, C, int(padding1), int(padding2), _stream_ptr(X.device))
+                                                         N, H, W, C, int(KH), int(KW), int(padding1), int(padding2),
+                                                         int(stride1), int(stride2), _stream_ptr(X.device))
     _cabi.check(rc, "tab_quantize_int8_padded_launch")
     return q
 
 
-def conv2d_int8_padded(QX8P, W8, type, padding1, padding2, N, H, W, C, KN, KH, KW):
-    """The stride-1 GEMM stage on padded byte activations (``quantize_int8_padded``); same output as ``Conv2d``.
+def conv2d_int8_padded(QX8P, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW):
+    """The GEMM stage on padded plane-layout byte activations (``quantize_int8_padded``); same output as ``Conv2d``.
     Raises ``TabError`` (TAB_E_TOO_LARGE) for shapes the TMA-fed kernels do not cover."""
     _check_input(QX8P, "QX8P", torch.int8)
     _check_input(W8, "W8", torch.int8)
     Cp = (int(C) + 63) // 64 * 64
-    p1, p2 = int(padding1), int(padding2)
-    if QX8P.numel() != N * (H + 2 * p1) * (W + 2 * p2) * Cp or W8.numel() != KN * KH * KW * Cp:
-        raise RuntimeError("byte operands must be [N,H+2p1,W+2p2,Cp] and [KN,KH,KW,Cp] with Cp = %d" % Cp)
-    OH, OW = conv_out_size(H, W, KH, KW, p1, p2, 1, 1)
+    p1, p2, s1, s2 = int(padding1), int(padding2), int(stride1), int(stride2)
+    planes, PH2, PW2 = plane_layout(H, W, KH, KW, p1, p2, s1, s2)
+    if QX8P.numel() != planes * N * PH2 * PW2 * Cp or W8.numel() != KN * KH * KW * Cp:
+        raise RuntimeError("byte operands must be [A*B,N,PH2,PW2,Cp] and [KN,KH,KW,Cp] with Cp = %d" % Cp)
+    OH, OW = conv_out_size(H, W, KH, KW, p1, p2, s1, s2)
     with torch.cuda.device(QX8P.device):
         Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=QX8P.device)
-        rc = _cabi.lib().tab_conv2d_int8_padded_launch(QX8P.data_ptr(), W8.data_ptr(), Y.data_ptr(), int(type), p1, p2,
+        rc = _cabi.lib().tab_conv2d_int8_padded_launch(QX8P.data_ptr(), W8.data_ptr(), Y.data_ptr(), int(type), p1, p2, s1, s2,
                                                        N, H, W, C, KN, KH, KW, _stream_ptr(QX8P.device))
     _cabi.check(rc, "tab_conv2d_int8_padded_launch")
     return Y

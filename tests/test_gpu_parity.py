@@ -294,28 +294,32 @@ def test_int8_stage_entry_points(cuda):
         assert np.array_equal(y.cpu().numpy(), yo)
 
 
-def test_int8_padded_stage_entry_points(cuda):
-    """quantize_int8_padded writes the convolution's padding (0 ternary, +1 binary, channel tail 0);
-    conv2d_int8_padded on it equals the oracle's Conv2d."""
+@pytest.mark.parametrize("s1,s2", [(1, 1), (2, 2), (3, 2)])
+def test_int8_padded_stage_entry_points(cuda, s1, s2):
+    """quantize_int8_padded writes the convolution's padding (0 ternary, +1 binary, channel tail 0) and splits the padded
+    image into the stride's parity planes; conv2d_int8_padded on it equals the oracle's Conv2d."""
     N, H, W, C, KN, K = 3, 9, 8, 130, 70, 3
     p1, p2 = 1, 2
     x, ths = make_input(7, N, H, W, C)
     w, wths = make_input(8, KN, K, K, C)
     Cp = 192
+    planes, PH2, PW2 = TAB.ops.plane_layout(H, W, K, K, p1, p2, s1, s2)
+    A, B = min(s1, K), min(s2, K)
     for t in range(4):
         ab, wb = O.act_bits(t), O.weight_bits(t)
         qx, _ = O.quantize(x, ths, ab, N, H, W, C)
         qw, btn = O.quantize(w, wths, wb, KN, K, K, C)
-        q8 = TAB.ops.quantize_int8_padded(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C, p1, p2)
+        q8 = TAB.ops.quantize_int8_padded(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C, K, K, p1, p2, s1, s2)
         w8 = TAB.ops.expand_weights(dev_t(qw, cuda), wb, KN, K, K, C)
-        assert tuple(q8.shape) == (N, H + 2 * p1, W + 2 * p2, Cp)
-        exp_a = np.zeros((N, H + 2 * p1, W + 2 * p2, Cp), np.int8)
+        assert tuple(q8.shape) == (A * B, N, PH2, PW2, Cp)
+        padded = np.zeros((N, PH2 * s1, PW2 * s2, Cp), np.int8)           # the padded image, grown to whole planes
         if ab == 1:
-            exp_a[..., :C] = 1
-        exp_a[:, p1:p1 + H, p2:p2 + W, :C] = O.dequantize(qx, C).astype(np.int8)
-        assert np.array_equal(q8.cpu().numpy(), exp_a)
-        y = TAB.ops.conv2d_int8_padded(q8, w8, t, p1, p2, N, H, W, C, KN, K, K)
-        yo = c_oracle.conv2d(x, qw, ths, btn, t, p1, p2, 1, 1, N, H, W, C, KN, K, K)
+            padded[..., :C] = 1
+        padded[:, p1:p1 + H, p2:p2 + W, :C] = O.dequantize(qx, C).astype(np.int8)
+        exp = np.stack([padded[:, a::s1, b::s2, :] for a in range(A) for b in range(B)])
+        assert np.array_equal(q8.cpu().numpy(), exp)
+        y = TAB.ops.conv2d_int8_padded(q8, w8, t, p1, p2, s1, s2, N, H, W, C, KN, K, K)
+        yo = c_oracle.conv2d(x, qw, ths, btn, t, p1, p2, s1, s2, N, H, W, C, KN, K, K)
         assert np.array_equal(y.cpu().numpy(), yo)
         assert _cabi.lib().tab_debug_umma_status() == 0
 
