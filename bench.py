@@ -54,7 +54,7 @@ H0 = W0 = 56
 C0 = 64
 CONV_TYPE = 0
 # dram__bytes_read.sum + dram__bytes_write.sum of conv_umma_persist_kernel on the 56x56x64->64 layer at N=256 (one ncu capture)
-PERSIST_L1_TRAFFIC = None
+PERSIST_L1_TRAFFIC = 199.9e6
 WEIGHT_SEED = 5000
 INPUT_SEED = 5
 
