@@ -19,7 +19,7 @@ step (activation quantise, residual add, thresholds) counts as time but not as o
 ``value``   device-resident input, CUDA-event time of the K steps, L2 flushed between steps, max over ranks.
 ``e2e``     the same step through the TAB_CUDA extension module with the input in pinned host memory: the
             host-to-device copy of the shard and the device-to-host copy of the gathered output are timed.  The shard
-            is processed in four chunks of images so that the copy of one chunk overlaps the forward of the previous.
+            is processed in eight chunks of images so that the copies of one chunk overlap the forward of another.
 ``roofline`` for the dominant kernels (the int8 tensor-core GEMM stage of the convolution: the persistent TMA-fed
             tcgen05 kind::i8 kernel, the cp.async-fed one for stride-2 3x3), timed alone per layer on pre-quantised byte
             operands; denominator = the tcgen05 int8 rate measured in the same run by the library's issue probe
@@ -367,14 +367,15 @@ def main():
     # End-to-end step: the shard is processed in NCH chunks of images (every image is independent), so that the
     # host-to-device copy of chunk i+1 overlaps the forward of chunk i: two input buffers / graphs in ping-pong,
     # copies on their own streams.
-    NCH = 4 if n_local % 4 == 0 and n_local >= 16 else 1
+    NCH = 8 if n_local % 8 == 0 and n_local >= 64 else (4 if n_local % 4 == 0 and n_local >= 16 else 1)
     nb_e2e = n_local // NCH
-    x_chunk = [torch.empty((nb_e2e, H0, W0, C0), dtype=torch.float32, device=dev) for _ in range(2 if NCH > 1 else 1)]
+    x_chunk = [torch.empty((nb_e2e, H0, W0, C0), dtype=torch.float32, device=dev) for _ in range(3 if NCH > 2 else NCH)]
     y_local = torch.empty(n_local * per_img_out, dtype=torch.float32, device=dev)
     graphs["dev"] = make_graph(CountingOps, x_dev)
     graphs["e2e"] = [make_graph(ModuleOps, xb, nb_e2e) for xb in x_chunk]
     use_graph = graphs["dev"][0] is not None and all(g[0] is not None for g in graphs["e2e"])
     h2d_stream = torch.cuda.Stream(dev)
+    d2h_stream = torch.cuda.Stream(dev)
     launches[0] = 0
     if use_graph:
         ths_ = CountingOps.residual_threshold(x_dev, None, chain.THRESHOLD_SCALE)      # count one forward's kernels
@@ -408,8 +409,16 @@ def main():
                 e = torch.cuda.Event(); e.record(h2d_stream); ev_in.append(e)
             main.wait_event(ev_in[i])
             graphs["e2e"][k][0].replay()
-            y_local[i * nb_e2e * per_img_out:(i + 1) * nb_e2e * per_img_out].copy_(graphs["e2e"][k][1].reshape(-1), non_blocking=True)
+            lo, hi = i * nb_e2e * per_img_out, (i + 1) * nb_e2e * per_img_out
+            y_local[lo:hi].copy_(graphs["e2e"][k][1].reshape(-1), non_blocking=True)
             e = torch.cuda.Event(); e.record(main); ev_done.append(e)
+            if world == 1:                               # single GPU: a chunk's result goes back while the next one computes
+                with torch.cuda.stream(d2h_stream):
+                    d2h_stream.wait_event(e)
+                    y_host[lo:hi].copy_(y_local[lo:hi], non_blocking=True)
+        if world == 1:
+            main.wait_stream(d2h_stream)                 # the step ends when the last result is on the host
+            return y_local
         y = finish(y_local)
         if rank == 0:
             y_host.copy_(y, non_blocking=True)

@@ -32,6 +32,25 @@ constexpr int Q8THREADS = 256;
 __device__ __forceinline__ int q_ternary(float v, float t, float nt) { return v > t ? 1 : (v < nt ? -1 : 0); }
 __device__ __forceinline__ int q_binary(float v, float t) { return v < t ? -1 : 1; }
 
+// Four quantised values as the four bytes of a word, built from packed 0/1 flags instead of per-byte selects:
+// ternary = P | N*0xFF with P the "> t" flags and N the "< -t" flags (the "+1" branch is tested first, so N &= ~P);
+// binary = 0x01010101 + N*0xFE (flag set -> 0xFF = -1, clear -> +1).  `valid` = number of real channels among the four
+// (the rest are channel padding and must be 0).
+template <int BITS>
+__device__ __forceinline__ uint32_t q_word(const float* v, float t, float nt, int valid) {
+    uint32_t P = 0, G = 0;
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+        if (BITS == 2) P |= (v[b] > t ? 1u : 0u) << (8 * b);
+        G |= (v[b] < (BITS == 2 ? nt : t) ? 1u : 0u) << (8 * b);
+    }
+    uint32_t r;
+    if (BITS == 2) r = P | ((G & ~P) * 0xFFu);
+    else r = 0x01010101u + G * 0xFEu;
+    if (valid < 4) r &= valid <= 0 ? 0u : (0xFFFFFFFFu >> (8 * (4 - valid)));
+    return r;
+}
+
 // grid = (chunks, N); one thread per 16 consecutive channels of a pixel (one 16-byte store).
 // groups_per_pixel = Cp/16; VEC: C % 16 == 0 and x 32-byte aligned -> two 256-bit loads per thread.
 template <int BITS, bool VEC>
@@ -192,17 +211,12 @@ quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict
 #pragma unroll
                 for (int e = 0; e < 16; e++) v[e] = (c0 + e < C) ? __ldg(src + e) : 0.f;
             }
+            if (VEC && c0 + 16 <= C) {
 #pragma unroll
-            for (int w = 0; w < 4; w++) {
-                uint32_t r = 0;
+                for (int w = 0; w < 4; w++) o[w] = q_word<BITS>(v + 4 * w, t, nt, 4);
+            } else {
 #pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    const int e = 4 * w + b;
-                    int qv = (BITS == 2) ? q_ternary(v[e], t, nt) : q_binary(v[e], t);
-                    if (c0 + e >= C) qv = 0;
-                    r |= (uint32_t)(qv & 0xFF) << (8 * b);
-                }
-                o[w] = r;
+                for (int w = 0; w < 4; w++) o[w] = q_word<BITS>(v + 4 * w, t, nt, C - c0 - 4 * w);
             }
         } else {
 #pragma unroll
