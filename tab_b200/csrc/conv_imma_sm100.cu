@@ -153,6 +153,10 @@ __global__ void __launch_bounds__(Q8THREADS)
 quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict__ ths, int8_t* __restrict__ q,
                             int H, int W, int C, int Cp, const QLayout L, const PrepExtras ex) {
     const int n = blockIdx.y;
+    // Programmatic launch: nothing is read or written before the previous kernel of the stream (the GEMM that produced
+    // x and the thresholds, and that may still be reading the scratch this launch overwrites) has completed; the next
+    // kernel may be scheduled once every CTA of this one is done (a waiting grid polls, so it is not let in earlier).
+    pdl_wait();
     if (ex.qw != nullptr) {                                                // the weights, spread over all CTAs of the launch
         const int PC = Cp >> 6;
         const long long stride = (long long)gridDim.x * gridDim.y * Q8THREADS;
@@ -230,6 +234,7 @@ quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict
         }
         *reinterpret_cast<uint4*>(qi + pix * Cp + c0) = make_uint4(o[0], o[1], o[2], o[3]);
     }
+    pdl_launch_dependents();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -854,13 +859,11 @@ static int quantize_prep_dispatch(const float* x, const float* ths, int8_t* qx8,
     dim3 grid((unsigned)per, (unsigned)N);
     const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)H * W * C) % 8 == 0);
     if (bits == 2) {
-        if (vec) quantize_int8_padded_kernel<2, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, L, ex);
-        else quantize_int8_padded_kernel<2, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, L, ex);
-    } else {
-        if (vec) quantize_int8_padded_kernel<1, true><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, L, ex);
-        else quantize_int8_padded_kernel<1, false><<<grid, Q8THREADS, 0, stream>>>(x, ths, qx8, H, W, C, Cp, L, ex);
+        if (vec) return launch_pdl(quantize_int8_padded_kernel<2, true>, grid, dim3(Q8THREADS), 0, stream, x, ths, qx8, H, W, C, Cp, L, ex);
+        return launch_pdl(quantize_int8_padded_kernel<2, false>, grid, dim3(Q8THREADS), 0, stream, x, ths, qx8, H, W, C, Cp, L, ex);
     }
-    return check_launch();
+    if (vec) return launch_pdl(quantize_int8_padded_kernel<1, true>, grid, dim3(Q8THREADS), 0, stream, x, ths, qx8, H, W, C, Cp, L, ex);
+    return launch_pdl(quantize_int8_padded_kernel<1, false>, grid, dim3(Q8THREADS), 0, stream, x, ths, qx8, H, W, C, Cp, L, ex);
 }
 
 // Quantise to the padded plane layout of a convolution geometry (QLayout).  Binary activations (bits 1) get +1 in

@@ -705,6 +705,13 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     if (FUSED) fused_finish(p);
 }
 
+#ifdef TAB_PERSIST_PROFILE
+__device__ int g_epi_dbg;
+#define EDBG(bit) ((g_epi_dbg & (bit)) != 0)
+#else
+#define EDBG(bit) false
+#endif
+
 // Epilogue with coalesced stores for a warp that owns TMEM lane quarter wq.  tcgen05.ld hands lane r the 32 columns
 // of accumulator row r; written straight out, one store instruction would touch 32 different output rows.  The warp
 // instead passes each 32x32 block through a private 4 KB shared-memory buffer (16-byte chunks XOR-swizzled by row, so
@@ -720,10 +727,29 @@ __device__ __forceinline__ int4 lds_v4(uint32_t a) {
 }
 
 // The warp handles row blocks mb0, mb0 + mbstep, ... and columns [c0, c1) of the tile.
+// |y| sums a warp has computed but not yet added to abs_sums: the global atomic is issued by the caller AFTER it has
+// released the accumulator buffer (an mbarrier arrive has release semantics and would otherwise wait for the atomic's
+// round trip to L2 on every tile).
+struct PendingSums {
+    int img0 = -1;
+    double tot0 = 0.0, tot1 = 0.0;                                         // for images img0 and img0 + 1
+};
+__device__ __forceinline__ void flush_pending(const ImmaParams& p, PendingSums& ps, int lane) {
+    if (ps.img0 >= 0 && lane == 0) {
+        if (ps.tot0 != 0.0 && ps.img0 < p.N) atomicAdd(p.abs_sums + ps.img0, ps.tot0);
+        if (ps.tot1 != 0.0 && ps.img0 + 1 < p.N) atomicAdd(p.abs_sums + ps.img0 + 1, ps.tot1);
+    }
+    ps.img0 = -1;
+}
+
 template <int MT, int TNI, bool FUSED>
 __device__ __forceinline__ void grid_epilogue_coalesced(const ImmaParams& p, uint32_t tmem_base, int R0, int n0, int PW, int PHW,
-                                                        int wq, int lane, uint32_t stage, int mb0, int mbstep, int c0, int c1) {
+                                                        int wq, int lane, uint32_t stage, int mb0, int mbstep, int c0, int c1,
+                                                        PendingSums& ps) {
     const bool vec4 = (p.KN & 3) == 0;
+    const bool small_acc = p.Kw < (1 << 15);                               // |accumulator| <= 64 * Kw < 2^21: the bias conversion is exact
+    const bool has_res = FUSED && p.residual != nullptr;
+    const bool want_sum = FUSED && p.abs_sums != nullptr;
     const int rsub = lane >> 3, chunk = lane & 7;
 #pragma unroll 1
     for (int mb = mb0; mb < MT; mb += mbstep) {
@@ -736,14 +762,19 @@ __device__ __forceinline__ void grid_epilogue_coalesced(const ImmaParams& p, uin
         const bool row_ok = n < p.N && oh < p.OH && ow < p.OW;
         const int wimg0 = Rw / PHW;                                        // image of the warp's first row
         const int m = row_ok ? (n * p.OH + oh) * p.OW + ow : -1;           // output row (M < 2^31 is checked on the host)
-        const int d = n - wimg0;
-        int mi[8], di[8];
+        int mi[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            mi[i] = __shfl_sync(0xFFFFFFFFu, m, 4 * i + rsub);
-            di[i] = __shfl_sync(0xFFFFFFFFu, d, 4 * i + rsub);
-        }
-        double acc0 = 0.0, acc1 = 0.0, acc2 = 0.0;
+        for (int i = 0; i < 8; i++) mi[i] = __shfl_sync(0xFFFFFFFFu, m, 4 * i + rsub);
+        // |y| sums.  Usual case ("fast"): the warp's 32 consecutive grid rows lie in at most two images (rows below
+        // `split` in image wimg0, the others in wimg0 + 1) and the values are small enough for 32 of them to add exactly
+        // in float (|y| < 2^18): a lane adds its values of a block in float per image and keeps running totals as
+        // integers (integer data: exact, one REDUX at the end) or, with a residual, as doubles.  Otherwise ("slow",
+        // rare: images of fewer than 32 grid positions, very long K): one double atomic per row and block.
+        const int split = (wimg0 + 1) * PHW - Rw;                          // first row of the warp that belongs to the next image
+        const bool fast = want_sum && p.Kw < (1 << 12) && (Rw + 31) / PHW - wimg0 <= 1;
+        const bool slow = want_sum && !fast;
+        unsigned isum0 = 0, isum1 = 0;
+        double dsum0 = 0.0, dsum1 = 0.0;
 #pragma unroll 1
         for (int cb = c0; cb < c1; cb += 32) {
             const int nbase = n0 + cb;
@@ -755,65 +786,79 @@ __device__ __forceinline__ void grid_epilogue_coalesced(const ImmaParams& p, uin
                 for (int q = 0; q < 8; q++)
                     sts_v4(stage + lane * 128 + ((q ^ (lane & 7)) << 4), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                 __syncwarp();
-                int4 raw[8];
-                float4 res[8];
+                float4 o[8];
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const int r = 4 * i + rsub;
-                    raw[i] = lds_v4(stage + r * 128 + ((chunk ^ (r & 7)) << 4));
-                    res[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (FUSED && p.residual && mi[i] >= 0)
-                        res[i] = __ldg(reinterpret_cast<const float4*>(p.residual + (long long)mi[i] * p.KN + nbase) + chunk);
+                    const int4 raw = lds_v4(stage + r * 128 + ((chunk ^ (r & 7)) << 4));
+                    if (small_acc) {                                       // int -> float by the 1.5 * 2^23 bias, no I2F
+                        o[i].x = __int_as_float(raw.x + 0x4B400000) - 12582912.f; o[i].y = __int_as_float(raw.y + 0x4B400000) - 12582912.f;
+                        o[i].z = __int_as_float(raw.z + 0x4B400000) - 12582912.f; o[i].w = __int_as_float(raw.w + 0x4B400000) - 12582912.f;
+                    } else {
+                        o[i].x = (float)raw.x; o[i].y = (float)raw.y; o[i].z = (float)raw.z; o[i].w = (float)raw.w;
+                    }
+                }
+                if (has_res) {
+                    float4 res[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        res[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (mi[i] >= 0) res[i] = __ldg(reinterpret_cast<const float4*>(p.residual + (long long)mi[i] * p.KN + nbase) + chunk);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; i++) { o[i].x += res[i].x; o[i].y += res[i].y; o[i].z += res[i].z; o[i].w += res[i].w; }
                 }
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    if (mi[i] < 0) continue;
-                    float4 o;
-                    o.x = (float)raw[i].x + res[i].x; o.y = (float)raw[i].y + res[i].y;
-                    o.z = (float)raw[i].z + res[i].z; o.w = (float)raw[i].w + res[i].w;
-                    reinterpret_cast<float4*>(p.y + (long long)mi[i] * p.KN + nbase)[chunk] = o;
-                    if (FUSED) {
-                        const double sabs = (double)((fabsf(o.x) + fabsf(o.y)) + (fabsf(o.z) + fabsf(o.w)));
-                        if (di[i] == 0) acc0 += sabs;
-                        else if (di[i] == 1) acc1 += sabs;
-                        else if (di[i] == 2) acc2 += sabs;
-                        else if (p.abs_sums) atomicAdd(p.abs_sums + wimg0 + di[i], sabs);
+                for (int i = 0; i < 8; i++)
+                    if (mi[i] >= 0) reinterpret_cast<float4*>(p.y + (long long)mi[i] * p.KN + nbase)[chunk] = o[i];
+                if (fast) {
+                    float fs0 = 0.f, fs1 = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float s4 = mi[i] >= 0 ? (fabsf(o[i].x) + fabsf(o[i].y)) + (fabsf(o[i].z) + fabsf(o[i].w)) : 0.f;
+                        if (4 * i + rsub < split) fs0 += s4; else fs1 += s4;
+                    }
+                    if (has_res) { dsum0 += (double)fs0; dsum1 += (double)fs1; }
+                    else { isum0 += (unsigned)fs0; isum1 += (unsigned)fs1; }   // integer-valued and < 2^24: exact
+                } else if (slow) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int img = (Rw + 4 * i + rsub) / PHW;
+                        if (mi[i] >= 0 && img < p.N)
+                            atomicAdd(p.abs_sums + img, (double)(fabsf(o[i].x) + fabsf(o[i].y)) + (double)(fabsf(o[i].z) + fabsf(o[i].w)));
                     }
                 }
                 __syncwarp();
             } else if (row_ok) {
                 float* yrow = p.y + (long long)m * p.KN;
-                const float* rrow = (FUSED && p.residual) ? p.residual + (long long)m * p.KN : nullptr;
-                float rsum = 0.f;
+                const float* rrow = has_res ? p.residual + (long long)m * p.KN : nullptr;
+                double rsum = 0.0;
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     if (nbase + i < p.KN) {
-                        float o = (float)(int)v[i];
-                        if (FUSED && rrow) o += __ldg(rrow + nbase + i);
-                        yrow[nbase + i] = o;
-                        if (FUSED) rsum += fabsf(o);
+                        float ov = (float)(int)v[i];
+                        if (rrow) ov += __ldg(rrow + nbase + i);
+                        yrow[nbase + i] = ov;
+                        if (FUSED) rsum += (double)fabsf(ov);
                     }
                 }
-                if (FUSED) {
-                    if (d == 0) acc0 += (double)rsum;
-                    else if (d == 1) acc1 += (double)rsum;
-                    else if (d == 2) acc2 += (double)rsum;
-                    else if (p.abs_sums) atomicAdd(p.abs_sums + n, (double)rsum);
-                }
+                if (want_sum) atomicAdd(p.abs_sums + n, rsum);
             }
         }
-        if (FUSED && p.abs_sums) {
+        if (fast) {
+            flush_pending(p, ps, lane);                                    // a previous row block's totals, if the caller has not taken them
+            if (has_res) {
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, o);
-                acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, o);
-                acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, o);
+                for (int sh = 16; sh > 0; sh >>= 1) {
+                    dsum0 += __shfl_xor_sync(0xFFFFFFFFu, dsum0, sh);
+                    dsum1 += __shfl_xor_sync(0xFFFFFFFFu, dsum1, sh);
+                }
+                ps.tot0 = dsum0; ps.tot1 = dsum1;
+            } else {
+                ps.tot0 = (double)__reduce_add_sync(0xFFFFFFFFu, isum0);   // lane totals < 2^26: the warp's fits 32 bits
+                ps.tot1 = (double)__reduce_add_sync(0xFFFFFFFFu, isum1);
             }
-            if (lane == 0) {
-                if (acc0 != 0.0 && wimg0 < p.N) atomicAdd(p.abs_sums + wimg0, acc0);
-                if (acc1 != 0.0 && wimg0 + 1 < p.N) atomicAdd(p.abs_sums + wimg0 + 1, acc1);
-                if (acc2 != 0.0 && wimg0 + 2 < p.N) atomicAdd(p.abs_sums + wimg0 + 2, acc2);
-            }
+            ps.img0 = wimg0;
         }
     }
 }
@@ -904,6 +949,10 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic launch: the set-up above overlapped the tail of the previous kernel (the quantiser); from here on its
+    // output is read.  The next kernel (the next layer's quantiser) may be scheduled when every CTA has finished its tiles
+    // (not earlier: a grid waiting in griddepcontrol.wait was measured to slow the MMA warp of the tiles still running).
+    pdl_wait();
 
 #ifdef TAB_PERSIST_PROFILE
     long long prof[3] = {0, 0, 0};
@@ -1092,6 +1141,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         // ---- epilogue warps (TMEM lane quarter = warp % 4) --------------------------------------------------------
         unsigned a = 0;
         bool dead = false;
+        PendingSums pending;
         for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
             const unsigned buf = a & 1;
             const int R0 = (t / tiles_n) * (UTM * MT), n0 = (t % tiles_n) * TNI;
@@ -1100,12 +1150,13 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             // two warps per TMEM lane quarter: they split the row blocks of a two-block tile, else the columns
             const int wg = (warp - 4) >> 2;
             if (!PDBG(1)) {
-                if (MT == 2) grid_epilogue_coalesced<MT, TNI, FUSED>(p, tmem_base + buf * ACOLS, R0, n0, PW, PHW, warp & 3, lane, sStage + (warp - 4) * 4096, wg, 2, 0, TNI);
-                else grid_epilogue_coalesced<MT, TNI, FUSED>(p, tmem_base + buf * ACOLS, R0, n0, PW, PHW, warp & 3, lane, sStage + (warp - 4) * 4096, 0, 1, wg * (TNI / 2), (wg + 1) * (TNI / 2));
+                if (MT == 2) grid_epilogue_coalesced<MT, TNI, FUSED>(p, tmem_base + buf * ACOLS, R0, n0, PW, PHW, warp & 3, lane, sStage + (warp - 4) * 4096, wg, 2, 0, TNI, pending);
+                else grid_epilogue_coalesced<MT, TNI, FUSED>(p, tmem_base + buf * ACOLS, R0, n0, PW, PHW, warp & 3, lane, sStage + (warp - 4) * 4096, 0, 1, wg * (TNI / 2), (wg + 1) * (TNI / 2), pending);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(accEmpty + 8 * buf);
+            if (FUSED) flush_pending(p, pending, lane);                    // the |y| atomics, off the buffer's critical path
         }
     }
 #ifdef TAB_PERSIST_PROFILE
@@ -1117,10 +1168,11 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #endif
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    pdl_launch_dependents();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)(2 * ACOLS)) : "memory");
     }
-    if (FUSED) fused_finish(p);
+    if (FUSED && !EDBG(32)) fused_finish(p);
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
@@ -1219,7 +1271,12 @@ static PlaneGrid plane_grid(const ImmaParams& p) {
 }
 
 static int g_persist_dbg = 0;
-void persist_set_debug(int v) { g_persist_dbg = v; }
+void persist_set_debug(int v) {
+    g_persist_dbg = v & 7;
+#ifdef TAB_PERSIST_PROFILE
+    cudaMemcpyToSymbol(g_epi_dbg, &v, sizeof(int));
+#endif
+}
 
 template <int MT, int TNI, int SB, bool BRES, bool FUSED, bool UNIT>
 static int launch_umma_persist_u(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, int prow, int nst,
@@ -1241,9 +1298,8 @@ static int launch_umma_persist_u(const CUtensorMap& tmA, const CUtensorMap& tmB,
     if (tiles_m * tiles_n >= (1LL << 31)) return TAB_E_TOO_LARGE;
     const long long ntiles = tiles_m * tiles_n;
     const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
-    conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, UNIT><<<grid, PTHREADS, smem_bytes, stream>>>(tmA, tmB, p, status, prow, nst, (int)tiles_m,
-                                                                                             (int)tiles_n, g_persist_dbg);
-    return check_launch();
+    return launch_pdl(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, UNIT>, dim3(grid), dim3(PTHREADS), (size_t)smem_bytes, stream,
+                      tmA, tmB, p, status, prow, nst, (int)tiles_m, (int)tiles_n, g_persist_dbg);
 }
 
 template <int MT, int TNI, int SB, bool BRES, bool FUSED>

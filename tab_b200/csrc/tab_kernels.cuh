@@ -15,6 +15,28 @@ inline int check_launch() {
     return e == cudaSuccess ? TAB_OK : record_cuda_error(e);
 }
 
+// Launch with programmatic stream serialisation: the kernel may be scheduled while its predecessor in the stream is
+// still draining (the predecessor executed griddepcontrol.launch_dependents in every CTA); it must execute
+// griddepcontrol.wait before it touches anything a predecessor wrote or may still read.  Works under stream capture
+// (the dependency becomes a programmatic edge of the graph).
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    return e == cudaSuccess ? TAB_OK : record_cuda_error(e);
+}
+
+#ifdef __CUDACC__
+// Device side of the above.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 inline int packed_channels(int C) { return (C + 63) / 64; }
 inline int act_bits(int type) { return (type == 2 || type == 3) ? 1 : 2; }      // TAB_GEMM.cu:367-372
 inline int weight_bits(int type) { return (type == 1 || type == 3) ? 1 : 2; }   // TAB_GEMM.cu:374-379
