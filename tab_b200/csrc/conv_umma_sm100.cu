@@ -742,96 +742,122 @@ __device__ __forceinline__ void flush_pending(const ImmaParams& p, PendingSums& 
     ps.img0 = -1;
 }
 
-template <int MT, int TNI, bool FUSED>
-__device__ __forceinline__ void grid_epilogue_coalesced(const ImmaParams& p, uint32_t tmem_base, int R0, int n0, int PW, int PHW,
-                                                        int wq, int lane, uint32_t stage, int mb0, int mbstep, int c0, int c1,
-                                                        PendingSums& ps) {
+// Row data of a warp's 32-row slab (grid rows Rw .. Rw + 31) in the transposed domain: lane (rsub = lane / 8,
+// chunk = lane % 8) handles rows 4i + rsub, i = 0..7, and four columns per row.  Computed before the accumulator
+// is waited for.
+struct SlabRows {
+    int mi[8];               // output row (index into [M][KN]) of row 4i + rsub, -1 = not an output position
+    int m_own;               // the same for row `lane` (the ragged path works row per lane)
+    int n_own;               // image of row `lane`
+    int Rw, wimg0, split;    // first grid row, its image, first slab row that belongs to the next image
+    bool fast, slow;         // how |y| is summed, see slab_rows
+};
+
+// |y| sums.  Usual case ("fast"): the slab's 32 consecutive grid rows lie in at most two images (rows below `split`
+// in image wimg0, the others in wimg0 + 1) and the values are small enough for 32 of them to add exactly in float
+// (|y| < 2^18): a lane adds its values of a block in float per image and keeps running totals as integers (integer
+// data: exact, one REDUX at the end) or, with a residual, as doubles.  Otherwise ("slow", rare: images of fewer than
+// 32 grid positions, very long K): one double atomic per row and block.
+template <bool FUSED>
+__device__ __forceinline__ void slab_rows(const ImmaParams& p, int Rw, int PW, int PHW, int lane, SlabRows& sr) {
+    const int R = Rw + lane;
+    const int n = R / PHW;
+    const int rr = R - n * PHW;
+    const int oh = rr / PW;
+    const int ow = rr - oh * PW;
+    const bool row_ok = n < p.N && oh < p.OH && ow < p.OW;
+    sr.m_own = row_ok ? (n * p.OH + oh) * p.OW + ow : -1;                  // M < 2^31 is checked on the host
+    sr.n_own = n;
+#pragma unroll
+    for (int i = 0; i < 8; i++) sr.mi[i] = __shfl_sync(0xFFFFFFFFu, sr.m_own, 4 * i + (lane >> 3));
+    sr.Rw = Rw;
+    sr.wimg0 = Rw / PHW;
+    sr.split = (sr.wimg0 + 1) * PHW - Rw;
+    const bool want_sum = FUSED && p.abs_sums != nullptr;
+    sr.fast = want_sum && p.Kw < (1 << 12) && (Rw + 31) / PHW - sr.wimg0 <= 1;
+    sr.slow = want_sum && !sr.fast;
+}
+
+// Residual values of the 32-column block at filter nbase, in the transposed layout (res[i] = row 4i + rsub, 4 columns).
+__device__ __forceinline__ void slab_load_residual(const ImmaParams& p, const SlabRows& sr, int nbase, int lane, float4 (&res)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        res[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (sr.mi[i] >= 0) res[i] = __ldg(reinterpret_cast<const float4*>(p.residual + (long long)sr.mi[i] * p.KN + nbase) + (lane & 7));
+    }
+}
+
+// Columns [c0, c1) (multiples of 32, relative to the tile's first filter n0) of one 128-row accumulator block whose
+// TMEM address (column 0, this warp's lane quarter) is taddr.  The residual of a block is fetched one block ahead -
+// for the first block by the caller, before it waits for the accumulator (res / res_loaded) - because a load issued
+// when the block is processed costs the warp its whole DRAM latency (measured 1 700 cycles per block).
+template <bool FUSED>
+__device__ __forceinline__ void slab_columns(const ImmaParams& p, uint32_t taddr, const SlabRows& sr, int n0, int c0, int c1, int PHW,
+                                             int lane, uint32_t stage, float4 (&res)[8], bool res_loaded, PendingSums& ps) {
     const bool vec4 = (p.KN & 3) == 0;
     const bool small_acc = p.Kw < (1 << 15);                               // |accumulator| <= 64 * Kw < 2^21: the bias conversion is exact
     const bool has_res = FUSED && p.residual != nullptr;
     const bool want_sum = FUSED && p.abs_sums != nullptr;
     const int rsub = lane >> 3, chunk = lane & 7;
+    unsigned isum0 = 0, isum1 = 0;
+    double dsum0 = 0.0, dsum1 = 0.0;
 #pragma unroll 1
-    for (int mb = mb0; mb < MT; mb += mbstep) {
-        const int Rw = R0 + mb * UTM + wq * 32;
-        const int R = Rw + lane;
-        const int n = R / PHW;
-        const int rr = R - n * PHW;
-        const int oh = rr / PW;
-        const int ow = rr - oh * PW;
-        const bool row_ok = n < p.N && oh < p.OH && ow < p.OW;
-        const int wimg0 = Rw / PHW;                                        // image of the warp's first row
-        const int m = row_ok ? (n * p.OH + oh) * p.OW + ow : -1;           // output row (M < 2^31 is checked on the host)
-        int mi[8];
+    for (int cb = c0; cb < c1; cb += 32) {
+        const int nbase = n0 + cb;
+        if (nbase >= p.KN) break;                                          // uniform over the warp
+        uint32_t v[32];
+        tmem_ld32(taddr + (uint32_t)cb, v);
+        if (vec4 && nbase + 32 <= p.KN) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) mi[i] = __shfl_sync(0xFFFFFFFFu, m, 4 * i + rsub);
-        // |y| sums.  Usual case ("fast"): the warp's 32 consecutive grid rows lie in at most two images (rows below
-        // `split` in image wimg0, the others in wimg0 + 1) and the values are small enough for 32 of them to add exactly
-        // in float (|y| < 2^18): a lane adds its values of a block in float per image and keeps running totals as
-        // integers (integer data: exact, one REDUX at the end) or, with a residual, as doubles.  Otherwise ("slow",
-        // rare: images of fewer than 32 grid positions, very long K): one double atomic per row and block.
-        const int split = (wimg0 + 1) * PHW - Rw;                          // first row of the warp that belongs to the next image
-        const bool fast = want_sum && p.Kw < (1 << 12) && (Rw + 31) / PHW - wimg0 <= 1;
-        const bool slow = want_sum && !fast;
-        unsigned isum0 = 0, isum1 = 0;
-        double dsum0 = 0.0, dsum1 = 0.0;
-#pragma unroll 1
-        for (int cb = c0; cb < c1; cb += 32) {
-            const int nbase = n0 + cb;
-            if (nbase >= p.KN) break;                                      // uniform over the warp
-            uint32_t v[32];
-            tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(mb * TNI + cb), v);
-            if (vec4 && nbase + 32 <= p.KN) {
+            for (int q = 0; q < 8; q++)
+                sts_v4(stage + lane * 128 + ((q ^ (lane & 7)) << 4), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            if (has_res && !res_loaded) slab_load_residual(p, sr, nbase, lane, res);
+            __syncwarp();
+            float4 o[8];
 #pragma unroll
-                for (int q = 0; q < 8; q++)
-                    sts_v4(stage + lane * 128 + ((q ^ (lane & 7)) << 4), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                __syncwarp();
-                float4 o[8];
+            for (int i = 0; i < 8; i++) {
+                const int r = 4 * i + rsub;
+                const int4 raw = lds_v4(stage + r * 128 + ((chunk ^ (r & 7)) << 4));
+                if (small_acc) {                                           // int -> float by the 1.5 * 2^23 bias, no I2F
+                    o[i].x = __int_as_float(raw.x + 0x4B400000) - 12582912.f; o[i].y = __int_as_float(raw.y + 0x4B400000) - 12582912.f;
+                    o[i].z = __int_as_float(raw.z + 0x4B400000) - 12582912.f; o[i].w = __int_as_float(raw.w + 0x4B400000) - 12582912.f;
+                } else {
+                    o[i].x = (float)raw.x; o[i].y = (float)raw.y; o[i].z = (float)raw.z; o[i].w = (float)raw.w;
+                }
+            }
+            if (has_res) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) { o[i].x += res[i].x; o[i].y += res[i].y; o[i].z += res[i].z; o[i].w += res[i].w; }
+                // the next block's residual, in flight while this block is stored and summed
+                res_loaded = vec4 && cb + 32 < c1 && nbase + 64 <= p.KN;
+                if (res_loaded) slab_load_residual(p, sr, nbase + 32, lane, res);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if (sr.mi[i] >= 0) reinterpret_cast<float4*>(p.y + (long long)sr.mi[i] * p.KN + nbase)[chunk] = o[i];
+            if (sr.fast) {
+                float fs0 = 0.f, fs1 = 0.f;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const int r = 4 * i + rsub;
-                    const int4 raw = lds_v4(stage + r * 128 + ((chunk ^ (r & 7)) << 4));
-                    if (small_acc) {                                       // int -> float by the 1.5 * 2^23 bias, no I2F
-                        o[i].x = __int_as_float(raw.x + 0x4B400000) - 12582912.f; o[i].y = __int_as_float(raw.y + 0x4B400000) - 12582912.f;
-                        o[i].z = __int_as_float(raw.z + 0x4B400000) - 12582912.f; o[i].w = __int_as_float(raw.w + 0x4B400000) - 12582912.f;
-                    } else {
-                        o[i].x = (float)raw.x; o[i].y = (float)raw.y; o[i].z = (float)raw.z; o[i].w = (float)raw.w;
-                    }
+                    const float s4 = sr.mi[i] >= 0 ? (fabsf(o[i].x) + fabsf(o[i].y)) + (fabsf(o[i].z) + fabsf(o[i].w)) : 0.f;
+                    if (4 * i + rsub < sr.split) fs0 += s4; else fs1 += s4;
                 }
-                if (has_res) {
-                    float4 res[8];
+                if (has_res) { dsum0 += (double)fs0; dsum1 += (double)fs1; }
+                else { isum0 += (unsigned)fs0; isum1 += (unsigned)fs1; }   // integer-valued and < 2^24: exact
+            } else if (sr.slow) {
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        res[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (mi[i] >= 0) res[i] = __ldg(reinterpret_cast<const float4*>(p.residual + (long long)mi[i] * p.KN + nbase) + chunk);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; i++) { o[i].x += res[i].x; o[i].y += res[i].y; o[i].z += res[i].z; o[i].w += res[i].w; }
+                for (int i = 0; i < 8; i++) {
+                    const int img = (sr.Rw + 4 * i + rsub) / PHW;
+                    if (sr.mi[i] >= 0 && img < p.N)
+                        atomicAdd(p.abs_sums + img, (double)(fabsf(o[i].x) + fabsf(o[i].y)) + (double)(fabsf(o[i].z) + fabsf(o[i].w)));
                 }
-#pragma unroll
-                for (int i = 0; i < 8; i++)
-                    if (mi[i] >= 0) reinterpret_cast<float4*>(p.y + (long long)mi[i] * p.KN + nbase)[chunk] = o[i];
-                if (fast) {
-                    float fs0 = 0.f, fs1 = 0.f;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float s4 = mi[i] >= 0 ? (fabsf(o[i].x) + fabsf(o[i].y)) + (fabsf(o[i].z) + fabsf(o[i].w)) : 0.f;
-                        if (4 * i + rsub < split) fs0 += s4; else fs1 += s4;
-                    }
-                    if (has_res) { dsum0 += (double)fs0; dsum1 += (double)fs1; }
-                    else { isum0 += (unsigned)fs0; isum1 += (unsigned)fs1; }   // integer-valued and < 2^24: exact
-                } else if (slow) {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int img = (Rw + 4 * i + rsub) / PHW;
-                        if (mi[i] >= 0 && img < p.N)
-                            atomicAdd(p.abs_sums + img, (double)(fabsf(o[i].x) + fabsf(o[i].y)) + (double)(fabsf(o[i].z) + fabsf(o[i].w)));
-                    }
-                }
-                __syncwarp();
-            } else if (row_ok) {
-                float* yrow = p.y + (long long)m * p.KN;
-                const float* rrow = has_res ? p.residual + (long long)m * p.KN : nullptr;
+            }
+            __syncwarp();
+        } else {
+            res_loaded = false;
+            if (sr.m_own >= 0) {                                           // ragged right edge / odd filter counts: a row per lane
+                float* yrow = p.y + (long long)sr.m_own * p.KN;
+                const float* rrow = has_res ? p.residual + (long long)sr.m_own * p.KN : nullptr;
                 double rsum = 0.0;
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
@@ -842,24 +868,24 @@ __device__ __forceinline__ void grid_epilogue_coalesced(const ImmaParams& p, uin
                         if (FUSED) rsum += (double)fabsf(ov);
                     }
                 }
-                if (want_sum) atomicAdd(p.abs_sums + n, rsum);
+                if (want_sum && sr.n_own < p.N) atomicAdd(p.abs_sums + sr.n_own, rsum);
             }
         }
-        if (fast) {
-            flush_pending(p, ps, lane);                                    // a previous row block's totals, if the caller has not taken them
-            if (has_res) {
+    }
+    if (sr.fast) {
+        flush_pending(p, ps, lane);                                        // totals the caller has not taken yet
+        if (has_res) {
 #pragma unroll
-                for (int sh = 16; sh > 0; sh >>= 1) {
-                    dsum0 += __shfl_xor_sync(0xFFFFFFFFu, dsum0, sh);
-                    dsum1 += __shfl_xor_sync(0xFFFFFFFFu, dsum1, sh);
-                }
-                ps.tot0 = dsum0; ps.tot1 = dsum1;
-            } else {
-                ps.tot0 = (double)__reduce_add_sync(0xFFFFFFFFu, isum0);   // lane totals < 2^26: the warp's fits 32 bits
-                ps.tot1 = (double)__reduce_add_sync(0xFFFFFFFFu, isum1);
+            for (int sh = 16; sh > 0; sh >>= 1) {
+                dsum0 += __shfl_xor_sync(0xFFFFFFFFu, dsum0, sh);
+                dsum1 += __shfl_xor_sync(0xFFFFFFFFu, dsum1, sh);
             }
-            ps.img0 = wimg0;
+            ps.tot0 = dsum0; ps.tot1 = dsum1;
+        } else {
+            ps.tot0 = (double)__reduce_add_sync(0xFFFFFFFFu, isum0);       // lane totals < 2^26: the warp's fits 32 bits
+            ps.tot1 = (double)__reduce_add_sync(0xFFFFFFFFu, isum1);
         }
+        ps.img0 = sr.wimg0;
     }
 }
 
@@ -1145,14 +1171,22 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
             const unsigned buf = a & 1;
             const int R0 = (t / tiles_n) * (UTM * MT), n0 = (t % tiles_n) * TNI;
+            // two warps per TMEM lane quarter: they split the row blocks of a two-block tile, else the columns.  Row data
+            // and the first block's residual are fetched before the accumulator is waited for.
+            const int wg = (warp - 4) >> 2;
+            const int emb = MT == 2 ? wg : 0, ec0 = MT == 2 ? 0 : wg * (TNI / 2), ec1 = MT == 2 ? TNI : (wg + 1) * (TNI / 2);
+            SlabRows sr;
+            slab_rows<FUSED>(p, R0 + emb * UTM + (warp & 3) * 32, PW, PHW, lane, sr);
+            float4 res[8];
+            bool res_loaded = false;
+            if (FUSED && p.residual != nullptr && (p.KN & 3) == 0 && n0 + ec0 + 32 <= p.KN) {
+                slab_load_residual(p, sr, n0 + ec0, lane, res);
+                res_loaded = true;
+            }
             if (!PWAIT(0, mbar_wait_warp(accFull + 8 * buf, (a >> 1) & 1u))) { dead = true; if (status && lane == 0) atomicExch(status, 16); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // two warps per TMEM lane quarter: they split the row blocks of a two-block tile, else the columns
-            const int wg = (warp - 4) >> 2;
-            if (!PDBG(1)) {
-                if (MT == 2) grid_epilogue_coalesced<MT, TNI, FUSED>(p, tmem_base + buf * ACOLS, R0, n0, PW, PHW, warp & 3, lane, sStage + (warp - 4) * 4096, wg, 2, 0, TNI, pending);
-                else grid_epilogue_coalesced<MT, TNI, FUSED>(p, tmem_base + buf * ACOLS, R0, n0, PW, PHW, warp & 3, lane, sStage + (warp - 4) * 4096, 0, 1, wg * (TNI / 2), (wg + 1) * (TNI / 2), pending);
-            }
+            if (!PDBG(1)) slab_columns<FUSED>(p, tmem_base + buf * ACOLS + (uint32_t)(emb * TNI) + ((uint32_t)((warp & 3) * 32) << 16), sr, n0, ec0, ec1, PHW,
+                                              lane, sStage + (warp - 4) * 4096, res, res_loaded, pending);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(accEmpty + 8 * buf);
