@@ -799,8 +799,8 @@ __device__ __forceinline__ void slab_columns(const ImmaParams& p, uint32_t taddr
     const bool has_res = FUSED && p.residual != nullptr;
     const bool want_sum = FUSED && p.abs_sums != nullptr;
     const int rsub = lane >> 3, chunk = lane & 7;
-    unsigned isum0 = 0, isum1 = 0;
-    double dsum0 = 0.0, dsum1 = 0.0;
+    unsigned isum_own = 0;                                                 // integer data: |y| total of the lane's own row
+    double dsum0 = 0.0, dsum1 = 0.0;                                       // float data: totals per image in the transposed domain
 #pragma unroll 1
     for (int cb = c0; cb < c1; cb += 32) {
         const int nbase = n0 + cb;
@@ -811,6 +811,12 @@ __device__ __forceinline__ void slab_columns(const ImmaParams& p, uint32_t taddr
 #pragma unroll
             for (int q = 0; q < 8; q++)
                 sts_v4(stage + lane * 128 + ((q ^ (lane & 7)) << 4), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            if (sr.fast && !has_res) {                                     // y is the accumulator itself: sum |acc| of the lane's own row
+                unsigned rs = 0;                                           // (row `lane` of the slab), in integers, before the transposition
+#pragma unroll
+                for (int j = 0; j < 32; j++) rs += (unsigned)abs((int)v[j]);
+                isum_own += sr.m_own >= 0 ? rs : 0u;
+            }
             if (has_res && !res_loaded) slab_load_residual(p, sr, nbase, lane, res);
             __syncwarp();
             float4 o[8];
@@ -835,15 +841,14 @@ __device__ __forceinline__ void slab_columns(const ImmaParams& p, uint32_t taddr
 #pragma unroll
             for (int i = 0; i < 8; i++)
                 if (sr.mi[i] >= 0) reinterpret_cast<float4*>(p.y + (long long)sr.mi[i] * p.KN + nbase)[chunk] = o[i];
-            if (sr.fast) {
+            if (sr.fast && has_res) {
                 float fs0 = 0.f, fs1 = 0.f;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const float s4 = sr.mi[i] >= 0 ? (fabsf(o[i].x) + fabsf(o[i].y)) + (fabsf(o[i].z) + fabsf(o[i].w)) : 0.f;
                     if (4 * i + rsub < sr.split) fs0 += s4; else fs1 += s4;
                 }
-                if (has_res) { dsum0 += (double)fs0; dsum1 += (double)fs1; }
-                else { isum0 += (unsigned)fs0; isum1 += (unsigned)fs1; }   // integer-valued and < 2^24: exact
+                dsum0 += (double)fs0; dsum1 += (double)fs1;
             } else if (sr.slow) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
@@ -881,9 +886,9 @@ __device__ __forceinline__ void slab_columns(const ImmaParams& p, uint32_t taddr
                 dsum1 += __shfl_xor_sync(0xFFFFFFFFu, dsum1, sh);
             }
             ps.tot0 = dsum0; ps.tot1 = dsum1;
-        } else {
-            ps.tot0 = (double)__reduce_add_sync(0xFFFFFFFFu, isum0);       // lane totals < 2^26: the warp's fits 32 bits
-            ps.tot1 = (double)__reduce_add_sync(0xFFFFFFFFu, isum1);
+        } else {                                                           // row totals < 2^26 (|y| < 2^18, at most 256 columns): the warp's fit 32 bits
+            ps.tot0 = (double)__reduce_add_sync(0xFFFFFFFFu, lane < sr.split ? isum_own : 0u);
+            ps.tot1 = (double)__reduce_add_sync(0xFFFFFFFFu, lane < sr.split ? 0u : isum_own);
         }
         ps.img0 = sr.wimg0;
     }
