@@ -324,6 +324,35 @@ def test_int8_padded_stage_entry_points(cuda, s1, s2):
         assert _cabi.lib().tab_debug_umma_status() == 0
 
 
+@pytest.mark.parametrize("t", [0, 3])
+@pytest.mark.parametrize("geom", [
+    # p1 p2 s1 s2  N   H    W    C   KN KH KW
+    (3, 3, 2, 2, 2, 224, 224, 3, 64, 7, 7),      # ResNet stem: 49 taps over four parity planes
+    (1, 1, 1, 1, 1, 224, 224, 64, 64, 3, 3),     # wide image: the patch only fits with one row block per tile
+    (1, 1, 1, 1, 1, 300, 500, 64, 40, 3, 3),     # patch does not fit shared memory: the other kernels take over
+    (2, 1, 3, 2, 2, 33, 17, 192, 200, 5, 3),     # stride 3 x 2, six parity planes, ragged filter count
+    (1, 1, 1, 1, 70, 3, 3, 64, 64, 3, 3),        # 25 grid positions per image: a 32-row slab spans three images
+    (0, 0, 1, 1, 2, 28, 28, 128, 1000, 1, 1),    # 1x1, filter count not a multiple of 32
+])
+def test_large_and_odd_shapes_plain_and_chained(cuda, t, geom):
+    """Shapes that steer the dispatch to every branch, as plain Conv2d and as the chained call (residual, |y| sums, next
+    thresholds from the GEMM's last CTA)."""
+    p1, p2, s1, s2, N, H, W, C, KN, KH, KW = geom
+    x, ths = make_input(41, N, H, W, C)
+    w, wths = make_input(42, KN, KH, KW, C)
+    qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, KH, KW, C)
+    yo = c_oracle.conv2d(x, qw, ths, btn, t, *geom)
+    xd, qd, td, bd = dev_t(x, cuda), dev_t(qw, cuda), dev_t(ths, cuda), dev_t(btn, cuda)
+    y = TAB.Conv2d(xd, qd, td, bd, t, *geom)
+    assert np.array_equal(y.cpu().numpy(), yo)
+    r = torch.round(torch.randn(*yo.shape, device=cuda) * 5)
+    y2, nxt = TAB.ops.Conv2dFused(xd, qd, td, bd, t, *geom, r, 0.7)
+    y2o = yo + r.cpu().numpy()
+    assert np.array_equal(y2.cpu().numpy(), y2o)
+    exp = (np.float64(np.float32(0.7)) * (np.abs(y2o).astype(np.float64).reshape(N, -1).sum(1) / y2o[0].size)).astype(np.float32)
+    assert np.array_equal(nxt.cpu().numpy(), exp)
+
+
 def test_kernels_larger_than_the_tensor_path_limit_fall_back(cuda):
     """9x9 kernels (81 taps) exceed the tensor-core loader's 64-tap mask: the call must still be exact."""
     N, H, W, C, KN, K = 1, 12, 12, 64, 8, 9
