@@ -705,12 +705,6 @@ conv_umma_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     if (FUSED) fused_finish(p);
 }
 
-#ifdef TAB_PERSIST_PROFILE
-__device__ int g_epi_dbg;
-#define EDBG(bit) ((g_epi_dbg & (bit)) != 0)
-#else
-#define EDBG(bit) false
-#endif
 
 // Epilogue with coalesced stores for a warp that owns TMEM lane quarter wq.  tcgen05.ld hands lane r the 32 columns
 // of accumulator row r; written straight out, one store instruction would touch 32 different output rows.  The warp
@@ -1047,8 +1041,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                             }
                             __syncwarp();
                         }
-                        continue;
-                    }
+                    } else
                     for (int pa = 0; pa < PA && !dead; pa++)
                     for (int pbb = 0; pbb < PB && !dead; pbb++)
                     for (int kh = pa; kh < p.KH && !dead; kh += s1)
@@ -1132,8 +1125,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                         }
                     }
                     q++;
-                    continue;
-                }
+                } else
                 for (int pa = 0; pa < PA && !dead; pa++)
                 for (int pbb = 0; pbb < PB && !dead; pbb++, q++) {
                     const unsigned pb = q & 1;
@@ -1211,7 +1203,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)(2 * ACOLS)) : "memory");
     }
-    if (FUSED && !EDBG(32)) fused_finish(p);
+    if (FUSED) fused_finish(p);
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).
@@ -1310,12 +1302,7 @@ static PlaneGrid plane_grid(const ImmaParams& p) {
 }
 
 static int g_persist_dbg = 0;
-void persist_set_debug(int v) {
-    g_persist_dbg = v & 7;
-#ifdef TAB_PERSIST_PROFILE
-    cudaMemcpyToSymbol(g_epi_dbg, &v, sizeof(int));
-#endif
-}
+void persist_set_debug(int v) { g_persist_dbg = v & 7; }
 
 template <int MT, int TNI, int SB, bool BRES, bool FUSED, bool UNIT>
 static int launch_umma_persist_u(const CUtensorMap& tmA, const CUtensorMap& tmB, const ImmaParams& p, int* status, int prow, int nst,
