@@ -149,7 +149,7 @@ struct PrepExtras {
 };
 
 template <int BITS, bool VEC>
-__global__ void __launch_bounds__(Q8THREADS)
+__global__ void __launch_bounds__(Q8THREADS, 8)
 quantize_int8_padded_kernel(const float* __restrict__ x, const float* __restrict__ ths, int8_t* __restrict__ q,
                             int H, int W, int C, int Cp, const QLayout L, const PrepExtras ex) {
     const int n = blockIdx.y;
