@@ -32,21 +32,34 @@ constexpr int Q8THREADS = 256;
 __device__ __forceinline__ int q_ternary(float v, float t, float nt) { return v > t ? 1 : (v < nt ? -1 : 0); }
 __device__ __forceinline__ int q_binary(float v, float t) { return v < t ? -1 : 1; }
 
-// Four quantised values as the four bytes of a word, built from packed 0/1 flags instead of per-byte selects:
-// ternary = P | N*0xFF with P the "> t" flags and N the "< -t" flags (the "+1" branch is tested first, so N &= ~P);
-// binary = 0x01010101 + N*0xFE (flag set -> 0xFF = -1, clear -> +1).  `valid` = number of real channels among the four
-// (the rest are channel padding and must be 0).
+// Four quantised values as the four bytes of a word.  `set` gives a compare as an all-ones/zero word in one instruction
+// (false for NaN, like the reference's `>` and `<`), two byte permutes per pair of words gather the low bytes, so a word
+// costs 8 compares + 6 permutes + 2 logic operations instead of a select, shift and OR per value.
+// ternary = (pos & 0x01) | (neg & ~pos)  (the "+1" branch is tested first); binary = neg | 0x01 (flag -> 0xFF = -1, else +1).
+// `valid` = number of real channels among the four (the rest are channel padding and must be 0).
+__device__ __forceinline__ uint32_t cmp_mask_gt(float a, float b) {
+    uint32_t d;
+    asm("set.gt.u32.f32 %0, %1, %2;" : "=r"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t cmp_mask_lt(float a, float b) {
+    uint32_t d;
+    asm("set.lt.u32.f32 %0, %1, %2;" : "=r"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t low_bytes4(uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3) {
+    return __byte_perm(__byte_perm(m0, m1, 0x0040), __byte_perm(m2, m3, 0x0040), 0x5410);
+}
 template <int BITS>
 __device__ __forceinline__ uint32_t q_word(const float* v, float t, float nt, int valid) {
-    uint32_t P = 0, G = 0;
-#pragma unroll
-    for (int b = 0; b < 4; b++) {
-        if (BITS == 2) P |= (v[b] > t ? 1u : 0u) << (8 * b);
-        G |= (v[b] < (BITS == 2 ? nt : t) ? 1u : 0u) << (8 * b);
-    }
     uint32_t r;
-    if (BITS == 2) r = P | ((G & ~P) * 0xFFu);
-    else r = 0x01010101u + G * 0xFEu;
+    if (BITS == 2) {
+        const uint32_t pos = low_bytes4(cmp_mask_gt(v[0], t), cmp_mask_gt(v[1], t), cmp_mask_gt(v[2], t), cmp_mask_gt(v[3], t));
+        const uint32_t neg = low_bytes4(cmp_mask_lt(v[0], nt), cmp_mask_lt(v[1], nt), cmp_mask_lt(v[2], nt), cmp_mask_lt(v[3], nt));
+        r = (pos & 0x01010101u) | (neg & ~pos);
+    } else {
+        r = low_bytes4(cmp_mask_lt(v[0], t), cmp_mask_lt(v[1], t), cmp_mask_lt(v[2], t), cmp_mask_lt(v[3], t)) | 0x01010101u;
+    }
     if (valid < 4) r &= valid <= 0 ? 0u : (0xFFFFFFFFu >> (8 * (4 - valid)));
     return r;
 }
