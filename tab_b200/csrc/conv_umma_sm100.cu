@@ -806,10 +806,13 @@ __device__ __forceinline__ void slab_columns(const ImmaParams& p, uint32_t taddr
             for (int q = 0; q < 8; q++)
                 sts_v4(stage + lane * 128 + ((q ^ (lane & 7)) << 4), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             if (sr.fast && !has_res) {                                     // y is the accumulator itself: sum |acc| of the lane's own row
-                unsigned rs = 0;                                           // (row `lane` of the slab), in integers, before the transposition
-#pragma unroll
-                for (int j = 0; j < 32; j++) rs += (unsigned)abs((int)v[j]);
-                isum_own += sr.m_own >= 0 ? rs : 0u;
+                unsigned r0 = 0, r1 = 0, r2 = 0, r3 = 0;                   // (row `lane` of the slab), in integers, before the transposition;
+#pragma unroll                                                             // four independent |x| + acc chains (one SAD instruction each)
+                for (int j = 0; j < 32; j += 4) {
+                    r0 = __sad((int)v[j], 0, r0); r1 = __sad((int)v[j + 1], 0, r1);
+                    r2 = __sad((int)v[j + 2], 0, r2); r3 = __sad((int)v[j + 3], 0, r3);
+                }
+                isum_own += sr.m_own >= 0 ? (r0 + r1) + (r2 + r3) : 0u;
             }
             if (has_res && !res_loaded) slab_load_residual(p, sr, nbase, lane, res);
             __syncwarp();
