@@ -865,10 +865,16 @@ static int quantize_prep_dispatch(const float* x, const float* ths, int8_t* qx8,
     const int Cp = packed_channels(C) * 64;
     const long long groups = (long long)L.A * L.B * L.PH2 * L.PW2 * (Cp / 16);
     if (N == 0 || groups == 0) return TAB_OK;
-    long long per = (groups + Q8THREADS - 1) / Q8THREADS;
-    const long long cap = (148LL * 8 * 4 + N - 1) / N;
-    if (per > cap) per = cap;
-    if (per < 1) per = 1;
+    // CTAs per image: at most four full waves of 8 CTAs per SM over all images, and every CTA the same number of
+    // grid-stride iterations (a ragged last iteration or a fifth, nearly empty wave costs a whole wave's time).
+    const long long steps = (groups + Q8THREADS - 1) / Q8THREADS;
+    long long cap = (148LL * 8 * 4) / N;
+    if (cap < 1) cap = 1;
+    long long per = steps;
+    if (per > cap) {
+        const long long iters = (steps + cap - 1) / cap;
+        per = (steps + iters - 1) / iters;
+    }
     dim3 grid((unsigned)per, (unsigned)N);
     const bool vec = (C % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0) && (((long long)H * W * C) % 8 == 0);
     if (bits == 2) {
