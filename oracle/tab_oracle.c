@@ -15,9 +15,10 @@
  *   GEMMs      TAB_CPU.cpp:242-328 (== TAB_GEMM.cu:25-147)
  *   pipeline   TAB_GEMM.cu:325-527; output float32 [N][OH][OW][KN] (:349,:509,:526)
  *
- * Parity status: pinned against the reference's own compiled GEMMs (oracle/_ref, built by
- * build_ref.py from TAB_CPU.cpp where it lies) and against the committed golden vectors; the
- * reference itself ships no golden vectors for this path.
+ * Parity status: pinned, stage by stage, against the reference's own code run on the host - its CUDA
+ * kernel bodies (TAB_GEMM.cu:25-247, TAB_GEMM.cuh:73-115) and its CPU GEMMs (TAB_CPU.cpp:242-328),
+ * both compiled by build.py from the files where they lie into oracle/_ref - and against the
+ * committed golden vectors that code produced; the reference itself ships no golden vectors.
  */
 #include <stdint.h>
 #include <stdlib.h>

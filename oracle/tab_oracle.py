@@ -5,11 +5,16 @@ benchmark's CPU-baseline leg may import it.  It restates, in numpy, the algorith
 CUDA backend (the behavioural authority for the API) with the integer arithmetic of the reference's
 CPU GEMMs.  Every function cites the reference lines it follows.
 
-Parity status: the reference ships no tests, golden vectors or seeded outputs for this path, so the
-oracle is pinned (a) against the reference's own ``*GEMM_baseline`` functions compiled from
-``TAB_CPU.cpp:242-328`` into ``oracle/_ref`` (see ``build_ref.py``), (b) against the facts recorded
-in the reference's demo notebook (shapes, dtypes, "binary word == complement of ternary magnitude
-word"), and (c) against an independent float64 dense convolution of the de-quantised values.
+Parity status: pinned.  The reference ships no tests, golden vectors or seeded outputs for this path,
+so the oracle is pinned against outputs of the reference's own code run in the container that built
+it: (a) every stage - quantise, BTN_Weight, pad, im2row, the four GEMMs and the whole
+``ConvWithCuda_TAB`` sequence - against the reference's CUDA kernel bodies (``TAB_GEMM.cu:25-247``,
+``TAB_GEMM.cuh:73-115``) compiled for the host and looped over their own launch shapes
+(``oracle/_ref/libtab_ref_cuda.so``, built by ``build.py`` through ``ref_cuda_shim.cpp``), (b) the GEMMs
+also against the reference's ``*GEMM_baseline`` functions compiled from ``TAB_CPU.cpp:242-328``, (c) the
+committed golden vectors under ``tests/golden``, which that same reference code produced, (d) the
+facts recorded in the reference's demo notebook (shapes, dtypes, "binary word == complement of ternary
+magnitude word"), and (e) an independent float64 dense convolution of the de-quantised values.
 
 Decisions where the reference's two backends disagree or are defective (each is followed here):
   * input layout is NHWC                                  (TAB_GEMM.cu:184,231; TAB_GPU.cpp:48)

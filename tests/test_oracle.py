@@ -1,6 +1,7 @@
 """The oracle is pinned before anything is compared with it: against golden vectors produced by the
-reference's own compiled GEMMs, against those GEMMs directly when ``oracle/_ref`` is present, against
-the facts the reference's demo notebook records, and against an independent dense formulation."""
+reference's own code (its CUDA kernel bodies run on the host for every stage, its CPU GEMMs), against
+that code directly when ``oracle/_ref`` is present, against the facts the reference's demo notebook
+records, and against an independent dense formulation."""
 import glob
 import os
 
@@ -92,6 +93,87 @@ def test_im2row_against_reference_build():
         n = c_oracle.ref_lib().ref_im2row_3x3(q.ctypes.data, out.ctypes.data, N, Cp, H, W, KH, KW, s, s)
         assert n == rows.size
         assert np.array_equal(out, rows)
+
+
+need_ref_cuda = pytest.mark.skipif(not c_oracle.ref_cuda_available(),
+                                   reason="oracle/_ref/libtab_ref_cuda.so not built (reference tree absent)")
+CHANNELS = [3, 64, 65, 200]
+
+
+def _edge_input(N, H, W, C, seed):
+    """N(0,1) data with the compare edge cases planted in every image: +-threshold, the floats next to it,
+    +-0, NaN, +-inf, denormals."""
+    x, ths = make_input(seed, N, H, W, C)
+    for n in range(N):
+        t = ths[n]
+        edge = np.array([t, -t, np.nextafter(t, np.float32(9)), np.nextafter(-t, np.float32(-9)), np.nextafter(t, np.float32(0)),
+                         np.nextafter(-t, np.float32(0)), 0.0, -0.0, np.nan, np.inf, -np.inf, 1e-45, -1e-45], dtype=np.float32)
+        flat = x[n].reshape(-1)
+        k = min(edge.size, flat.size)
+        flat[(np.arange(k) * 7 + n) % flat.size] = edge[:k]
+    return x, ths
+
+
+@need_ref_cuda
+@pytest.mark.parametrize("C", CHANNELS)
+@pytest.mark.parametrize("bw", [2, 1])
+def test_quantize_against_reference_cuda_kernels(C, bw):
+    """TerOnlyKernel / BinOnlyKernel / BTN_Weight themselves (TAB_GEMM.cu:150-247), on random data with edge values."""
+    for N, H, W in [(16, 3, 5), (32, 1, 1), (5, 4, 3)]:
+        x, ths = _edge_input(N, H, W, C, 40 + C + bw)
+        ths[0] = 0.0                                               # +-0 against a zero threshold
+        qr, br = c_oracle.ref_cuda_quantize(x, ths, bw, N, H, W, C)
+        for q, b in (O.quantize(x, ths, bw, N, H, W, C), c_oracle.quantize(x, ths, bw, N, H, W, C)):
+            assert np.array_equal(q, qr)
+            done = 16 * (N // 16)                                  # the reference's <<<16, N/16>>> launch covers these
+            assert np.array_equal(b[:done], br[:done])
+            if bw == 1:
+                assert not b.any() and not br.any()
+
+
+@need_ref_cuda
+@pytest.mark.parametrize("Cw", [1, 2, 3, 8])
+def test_pad_and_im2row_against_reference_cuda_kernels(Cw):
+    rng = np.random.default_rng(Cw)
+    for N, H, W, p1, p2, KH, KW, s1, s2 in [(2, 5, 6, 1, 1, 3, 3, 1, 1), (1, 7, 4, 2, 0, 3, 1, 2, 1), (3, 6, 6, 0, 3, 1, 5, 1, 2),
+                                            (2, 9, 8, 1, 1, 3, 3, 3, 2), (1, 4, 4, 0, 0, 1, 1, 2, 2)]:
+        q = rng.integers(-2**63, 2**63 - 1, size=(N, H, W, Cw), dtype=np.int64)
+        padded = O.pad_packed(q, p1, p2)
+        assert np.array_equal(padded, c_oracle.ref_cuda_pad(q, p1, p2))
+        assert np.array_equal(O.im2row(padded, KH, KW, s1, s2), c_oracle.ref_cuda_im2row(padded, KH, KW, s1, s2))
+
+
+@need_ref_cuda
+@pytest.mark.parametrize("t", range(4))
+def test_gemm_against_reference_cuda_kernels(t):
+    """TNN/TBN/BTN/BNNGEMM (TAB_GEMM.cu:25-147) under GEMMWithCuda's launch shape, incl. KN >= 1008 where that
+    shape is not launchable on a device (a block of 16 x 64 threads) but is still well defined."""
+    rng = np.random.default_rng(50 + t)
+    for M, KN, K in [(1, 1, 1), (17, 5, 3), (40, 33, 9), (3, 1030, 2)]:
+        ab, wb = O.act_bits(t), O.weight_bits(t)
+        a = rng.integers(-2**63, 2**63 - 1, size=(M, K * ab), dtype=np.int64)
+        b = rng.integers(-2**63, 2**63 - 1, size=(KN, K * wb), dtype=np.int64)
+        btn = rng.integers(0, 64 * K, size=KN).astype(np.int32)
+        ref = c_oracle.ref_cuda_gemm(a, b, btn, t, M, KN, K, 64 * K)
+        assert ref.dtype == np.float32
+        assert np.array_equal(O.gemm(a, b, btn, t, K, 64 * K).astype(np.float32), ref)
+        assert np.array_equal(c_oracle.gemm(a, b, btn, t, M, KN, K, 64 * K).astype(np.float32), ref)
+
+
+@need_ref_cuda
+@pytest.mark.parametrize("t", range(4))
+@pytest.mark.parametrize("C", CHANNELS)
+def test_conv2d_against_reference_cuda_pipeline(t, C):
+    """The whole ConvWithCuda_TAB sequence on the reference's kernels == both oracles."""
+    geoms = [(1, 1, 1, 1, 2, 6, 7, 5, 3, 3), (0, 0, 1, 1, 2, 3, 4, 6, 1, 1), (1, 0, 2, 1, 1, 7, 5, 4, 3, 3),
+             (0, 0, 2, 2, 3, 6, 6, 17, 1, 1), (2, 2, 1, 1, 1, 5, 5, 3, 5, 5), (1, 1, 3, 2, 2, 10, 7, 6, 3, 3)]
+    for gi, (p1, p2, s1, s2, N, H, W, KN, KH, KW) in enumerate(geoms):
+        x, ths = _edge_input(N, H, W, C, 60 + gi)
+        w, wths = make_input(70 + gi, KN, KH, KW, C)
+        qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, KH, KW, C)
+        ref = c_oracle.ref_cuda_conv2d(x, qw, ths, btn, t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
+        assert np.array_equal(O.conv2d(x, qw, ths, btn, t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW), ref)
+        assert np.array_equal(c_oracle.conv2d(x, qw, ths, btn, t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW), ref)
 
 
 def test_notebook_facts():
