@@ -16,18 +16,21 @@ total work is fixed, i.e. strong scaling.
 binary-ops = 2*M*KN*KH*KW*C summed over the convolutions (0.868e12 per step); every other kernel in the
 step (activation quantise, residual add, thresholds) counts as time but not as ops.
 
-``value``   device-resident input, CUDA-event time of the K steps, L2 flushed between steps, max over ranks.
-``e2e``     the same step through the TAB_CUDA extension module with the input in pinned host memory: the
-            host-to-device copy of the shard and the device-to-host copy of the gathered output are timed.  The shard
-            is processed in eight chunks of images so that the copies of one chunk overlap the forward of another.
-``roofline`` for the dominant kernels (the int8 tensor-core GEMM stage of the convolution: the persistent TMA-fed
-            tcgen05 kind::i8 kernel, the cp.async-fed one for stride-2 3x3), timed alone per layer on pre-quantised byte
-            operands; denominator = the tcgen05 int8 rate measured in the same run by the library's issue probe
-            (MMAs from shared memory, no copies), which is above 2 x the measured bf16 peak.
-``roofline_hbm_layers`` the launches of that stage that are bound by their bytes rather than their MMAs, in GB/s
-            against the measured copy bandwidth.
-``roofline_popcount`` the bit-packed LOP3/POPC kernel on the same layers against the integer-pipe bound derived
-            from POPC and LOP3 issue rates measured in the same run by the library's register-only probe.
+``value``   device-resident input, CUDA-event time of the K steps, L2 flushed between steps, max over ranks.  The chain runs
+            on prepared convolutions (``tab_b200.nn.TABConv2d``: weights quantised and byte-expanded once, as an inference
+            caller holds them): per convolution input one ``tab_quantize_launch`` (fp32 -> bit-planes, shared by a block's
+            first convolution and its shortcut) and per convolution one ``tab_conv2d_bits_launch`` (persistent tcgen05
+            kernel; residual, |y| sums and the next thresholds in its epilogue).
+``e2e``     the same step through the TAB_CUDA extension module with the input in pinned host memory: the host-to-device
+            copy of the shard and the device-to-host copy of the output are inside the timed region.  The shard is processed
+            in chunks of images so that the copies of one chunk overlap the forward of another.
+``roofline`` the whole step against HBM (the fp32-in / fp32-out operator interface makes the step byte-bound: algorithmic bytes
+            of every launch, summed, over ``ms_per_step``), with the GEMM stage alone against the tensor pipe
+            (``gemm_stage``, denominator measured in the same run by the library's tcgen05 issue probe), ``TAB_Quantize``
+            alone against HBM (``quantize``) and the bit-packed popcount kernel against the integer pipes (``popcount``).
+``parity_check`` (inside ``config``) after the timed loops the outputs of sampled images (at N > 1: one image of every
+            rank's shard, taken from the gathered tensor) are compared bit for bit with the CPU oracle chain run on the
+            input thresholds the GPU computed; a mismatch makes the run exit non-zero.
 ``cpu_baseline`` / ``--impl reference``: the reference's CPU algorithm (quantise, pad, im2row, its own
             compiled *GEMM_baseline functions when oracle/_ref exists, else the C port) on the host cores,
             on a bounded sample of images of the same workload.
@@ -53,10 +56,11 @@ GLOBAL_BATCH = 256
 H0 = W0 = 56
 C0 = 64
 CONV_TYPE = 0
-# dram__bytes_read.sum + dram__bytes_write.sum of conv_umma_persist_kernel on the 56x56x64->64 layer at N=256 (one ncu capture)
-PERSIST_L1_TRAFFIC = 199.9e6
 WEIGHT_SEED = 5000
 INPUT_SEED = 5
+# dram__bytes_read.sum + dram__bytes_write.sum per image of conv_umma_persist_kernel on the 56x56x64->64 layer, from the
+# ncu capture summarised under profiles/ (taken at 64 images; the kernel's traffic is proportional to the images it processes)
+L1_TRAFFIC_PER_IMAGE = None
 
 
 def parse_args():
@@ -68,22 +72,41 @@ def parse_args():
     ap.add_argument("--cpu-sample-images", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-layer-table", action="store_true")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0)
     return ap.parse_args()
+
+
+def workload_config(n_gpus):
+    from tab_b200 import chain
+    return {"workload": "resnet18-shaped TNN chain: 16x conv3x3 + 3x conv1x1 (s2,p0), 56x56x64 -> 7x7x512, type 0",
+            "global_batch": GLOBAL_BATCH, "per_gpu_batch": GLOBAL_BATCH // max(n_gpus, 1), "input": "fp32 NHWC N(0,1)",
+            "thresholds": "0.7*mean|.| per image / per filter", "parallelism": "dp%d (batch sharded, weights replicated, NCCL all-gather of outputs)" % n_gpus,
+            "l2": "flushed between timed steps (256 MiB write)", "binary_ops_per_step": chain.chain_binary_ops(GLOBAL_BATCH)}
 
 
 # ------------------------------------------------------------------------------------------------
 # CPU arm (the only place this file touches oracle/)
 # ------------------------------------------------------------------------------------------------
 
-def cpu_chain_once(sample_images, variant, use_ref, x=None, qweights=None):
+def host_threads():
+    """Threads the CPU arm uses: every core this process may run on, set explicitly in the OpenMP runtime, so that a
+    launcher's OMP_NUM_THREADS=1 (torch.distributed.run exports it for more than one process per node) does not apply."""
+    from oracle import c_oracle
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    c_oracle.omp_threads(n, "v3")
+    c_oracle.omp_threads(n, "shipped")
+    return n
+
+
+def cpu_chain_once(sample_images, variant, use_ref, x=None, qweights=None, ths=None):
     from oracle.oracle_ops import OracleOps
     from oracle import c_oracle
     from tab_b200 import chain
 
     class Ops(OracleOps):
         @staticmethod
-        def Conv2d(x_, qw, ths, btn, t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW):
-            return c_oracle.conv2d(np.asarray(x_).reshape(-1), qw, ths, btn, t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+        def Conv2d(x_, qw, ths_, btn, t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW):
+            return c_oracle.conv2d(np.asarray(x_).reshape(-1), qw, ths_, btn, t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
                                    use_ref_gemm=use_ref, variant=variant)
 
     if x is None:
@@ -92,7 +115,8 @@ def cpu_chain_once(sample_images, variant, use_ref, x=None, qweights=None):
     if qweights is None:
         qweights = chain.quantize_weights(chain.make_weights(WEIGHT_SEED, CONV_TYPE), CONV_TYPE, OracleOps.Quantize)
     t0 = time.perf_counter()
-    ths = OracleOps.residual_threshold(x.copy(), None, chain.THRESHOLD_SCALE)
+    if ths is None:
+        ths = OracleOps.residual_threshold(x.copy(), None, chain.THRESHOLD_SCALE)
     y, _, _, _ = chain.forward(Ops, x, ths, qweights, CONV_TYPE, sample_images)
     dt = time.perf_counter() - t0
     return dt, x, qweights, y
@@ -100,13 +124,13 @@ def cpu_chain_once(sample_images, variant, use_ref, x=None, qweights=None):
 
 def cpu_baseline(sample_images, repeats=2):
     """Time the CPU pipeline on `sample_images` images of the workload.  Returns the JSON object."""
+    threads = host_threads()
     from oracle import build, c_oracle
     from tab_b200 import chain
     build.build_oracle()
     build.build_ref()       # no-op without the reference tree; prebuilt libraries are used if present
     use_ref = c_oracle.ref_available("v3")
     ops = chain.chain_binary_ops(sample_images)
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     out = {}
     x = qw = None
     for variant in ("v3", "shipped"):
@@ -115,14 +139,15 @@ def cpu_baseline(sample_images, repeats=2):
             dt, x, qw, _ = cpu_chain_once(sample_images, variant, use_ref and c_oracle.ref_available(variant), x, qw)
             best = dt if best is None else min(best, dt)
         out[variant] = ops / best / 1e12
+    used = c_oracle.omp_threads()
     return {
-        "value": out["v3"], "unit": "TOPS", "cores": cores,
+        "value": out["v3"], "unit": "TOPS", "cores": used,
         "kind": "reference" if use_ref else "port",
         "sample": "%d of %d images of the same chain (all 19 convolutions, thresholds and residuals included); "
-                  "OpenMP over all cores; GEMM stage = %s; flags of the reference's Setup_GCC.py plus -march=x86-64-v3 "
-                  "(as-shipped flags: %.4f TOPS)" % (sample_images, GLOBAL_BATCH,
-                                                     "the reference's compiled *GEMM_baseline" if use_ref else "C port of it",
-                                                     out["shipped"]),
+                  "OpenMP, %d threads (omp_get_max_threads; %d cores available); GEMM stage = %s; flags of the reference's Setup_GCC.py "
+                  "plus -march=x86-64-v3 (as-shipped flags: %.4f TOPS)" % (sample_images, GLOBAL_BATCH, used, threads,
+                                                                          "the reference's compiled *GEMM_baseline" if use_ref else "C port of it",
+                                                                          out["shipped"]),
         "as_shipped_flags_value": out["shipped"],
     }
 
@@ -131,6 +156,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    threads = host_threads()
     from oracle import build, c_oracle
     from tab_b200 import chain
     build.build_oracle()
@@ -145,28 +171,30 @@ def run_reference_arm(args):
     for _ in range(args.steps):
         dt, x, qw, _ = cpu_chain_once(S, "v3", use_ref, x, qw)
         t += dt
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    used = c_oracle.omp_threads()
     val = ops * args.steps / t / 1e12
-    sample = ("each step = %d of %d images of the chain on the host cores (OpenMP, %d threads); GEMM stage = %s; "
-              "Setup_GCC.py flags + -march=x86-64-v3" % (S, GLOBAL_BATCH, cores,
-                                                         "reference *GEMM_baseline (oracle/_ref)" if use_ref else "C port"))
+    sample = ("each step = %d of %d images of the chain on the host cores (OpenMP, %d threads by omp_get_max_threads, %d cores available); "
+              "GEMM stage = %s; Setup_GCC.py flags + -march=x86-64-v3" % (S, GLOBAL_BATCH, used, threads,
+                                                                         "reference *GEMM_baseline (oracle/_ref)" if use_ref else "C port"))
     line = {
         "impl": "reference", "metric": "TAB_Conv2d binary-op TOPS", "value": val, "unit": "TOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u64 popcount", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": val, "unit": "TOPS", "cores": cores, "kind": "reference" if use_ref else "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TOPS", "cores": used, "kind": "reference" if use_ref else "port", "sample": sample},
         "e2e": {"value": val, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus):
-    return {"workload": "resnet18-shaped TNN chain: 16x conv3x3 + 3x conv1x1 (s2,p0), 56x56x64 -> 7x7x512, type 0",
-            "global_batch": GLOBAL_BATCH, "per_gpu_batch": GLOBAL_BATCH // max(n_gpus, 1), "input": "fp32 NHWC N(0,1)",
-            "thresholds": "0.7*mean|.| per image / per filter", "parallelism": "dp%d (batch sharded, weights replicated, NCCL all-gather of outputs)" % n_gpus,
-            "l2": "flushed between timed steps (256 MiB write)", "binary_ops_per_step": None}
+def oracle_chain_images(x_images, ths_images):
+    """The CPU oracle chain on a few images with given input thresholds (every later threshold follows from the data)."""
+    from oracle.oracle_ops import OracleOps
+    from tab_b200 import chain
+    qweights = chain.quantize_weights(chain.make_weights(WEIGHT_SEED, CONV_TYPE), CONV_TYPE, OracleOps.Quantize)
+    y, _, _, _ = chain.forward(OracleOps, np.ascontiguousarray(x_images), np.ascontiguousarray(ths_images), qweights, CONV_TYPE, x_images.shape[0])
+    return np.asarray(y).reshape(x_images.shape[0], -1)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -202,14 +230,14 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         try:
             for ln in open(self.path):
                 f = [v.strip() for v in ln.split(",")]
                 if len(f) < 7:
                     continue
                 try:
-                    sm.append(float(f[0])); mx.append(float(f[1]))
+                    sm.append(float(f[0])); mx.append(float(f[1])); pw.append(float(f[2]))
                 except ValueError:
                     continue
                 for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
@@ -219,10 +247,33 @@ class ClockSampler:
         except Exception:
             pass
         if sm:
-            # under load = upper half of the samples (the sampler also sees the gaps between steps)
-            hi = sorted(sm)[len(sm) // 2:]
-            out.update(sm_mhz=statistics.median(hi), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            # under load = the samples drawing the most power (the sampler also sees the gaps between steps)
+            order = sorted(range(len(sm)), key=lambda i: pw[i])[len(sm) // 2:]
+            out.update(sm_mhz=statistics.median([sm[i] for i in order]), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=max(pw))
         return out
+
+
+def step_algorithmic_bytes(n_images):
+    """Bytes every launch of one step must move, summed: per convolution input 4 B/element read and 2 bits/element written by
+    the quantiser; per convolution those bit-planes read, the byte weights read, 4 B/element of output written and, where a
+    shortcut is added, 4 B/element of residual read; the input statistics pass reads x once."""
+    from tab_b200 import chain
+    total = 4 * n_images * H0 * W0 * C0
+    h = H0
+    for b in chain.resnet18_blocks():
+        a, bb, sc = b.conv_a, b.conv_b, b.shortcut
+        oh = (h + 2 * a.pad - a.K + 1) // a.stride
+        x_el, y_el = n_images * h * h * a.C, n_images * oh * oh * a.KN
+        bits_in, bits_mid = x_el // 4, y_el // 4
+        total += 4 * x_el + bits_in                                        # quantise x
+        total += bits_in + a.KN * 9 * a.C + 4 * y_el                       # conv_a
+        if sc is not None:
+            total += bits_in + sc.KN * sc.C + 4 * y_el                     # shortcut on the same bit-planes
+        total += 4 * y_el + bits_mid                                       # quantise y1
+        total += bits_mid + bb.KN * 9 * bb.C + 4 * y_el + 4 * y_el         # conv_b + residual
+        h = oh
+    return total
 
 
 def main():
@@ -231,18 +282,18 @@ def main():
         run_reference_arm(args)
         return
 
+    import ctypes
     import torch
     import torch.distributed as dist
-    from tab_b200 import _cabi, chain, dp, ops as tab_ops
+    from tab_b200 import _cabi, chain, dp, nn as tab_nn, ops as tab_ops
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch with torch.distributed.run --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -259,72 +310,77 @@ def main():
     gen.manual_seed(INPUT_SEED)
     x_host_full = torch.randn(N, H0, W0, C0, generator=gen)
     x_host = x_host_full[lo:hi].contiguous().pin_memory()
-    del x_host_full
     x_dev = x_host.to(dev)
     weights = chain.make_weights(WEIGHT_SEED, CONV_TYPE)
-    qweights = chain.quantize_weights(weights, CONV_TYPE, tab_ops.Quantize, lambda a: torch.from_numpy(a).to(dev))
+    specs = {cs.name: cs for cs in chain.conv_specs()}
+    launches = [0]
+
+    class CountingConv(tab_nn.TABConv2d):
+        """tab_b200.nn.TABConv2d with a kernel-launch counter (quantize = one kernel, conv_bits = one kernel)."""
+        def quantize(self, x, thresholds=None):
+            launches[0] += 1
+            return super().quantize(x, thresholds)
+
+        def conv_bits(self, *a, **k):
+            launches[0] += 1
+            return super().conv_bits(*a, **k)
+
+    class ModuleConv:
+        """The same prepared convolution through the TAB_CUDA extension module."""
+        def __init__(self, conv):
+            self.c = conv
+            wb = tab_nn.weight_bitwidth(conv.conv_type)
+            self.W8 = TAB_CUDA.ExpandWeights(conv.QW, wb, conv.KN, conv.KH, conv.KW, conv.C)
+            self.state = None
+
+        def quantize(self, x, thresholds):
+            n, h, w = (int(v) for v in x.shape[:3])
+            return TAB_CUDA.Quantize(x, thresholds, tab_nn.act_bitwidth(self.c.conv_type), n, h, w, self.c.C)[0]
+
+        def conv_bits(self, QX, n, h, w, residual, scale):
+            if scale is not None and (self.state is None or self.state.numel() < lib.tab_conv2d_state_bytes(n)):
+                self.state = TAB_CUDA.NewState(QX, n)
+            y, nxt = TAB_CUDA.Conv2dBits(QX, self.W8, self.c.conv_type, *self.c.geometry(n, h, w), residual,
+                                         self.state if scale is not None else None, scale if scale is not None else 0.0)
+            return y.view(n, y.shape[2], y.shape[3], y.shape[1]), (nxt if scale is not None else None)
+
+    def nhwc(y):                                             # Conv2d's {N,KN,OH,OW} label over the [N][OH][OW][KN] buffer
+        return y.view(y.shape[0], y.shape[2], y.shape[3], y.shape[1])
+
+    class NhwcConv(CountingConv):
+        def conv_bits(self, *a, **k):
+            y, nxt = super().conv_bits(*a, **k)
+            return nhwc(y), nxt
+
+    convs = {}
+    for name, (w, t) in weights.items():
+        cs = specs[name]
+        convs[name] = NhwcConv.from_float(torch.from_numpy(w).to(dev), CONV_TYPE, cs.pad, cs.stride, torch.from_numpy(t).to(dev), chain.THRESHOLD_SCALE)
+    mconvs = {k: ModuleConv(v) for k, v in convs.items()}
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     ops_per_step = chain.chain_binary_ops(N)
     per_img_out = 7 * 7 * 512
 
-    launches = [0]
-
-    class CountingOps:
-        """tab_b200.ops with a kernel-launch counter (each Conv2d or Conv2dFused = two kernels: quantise, with the weight
-        expansion and the clears folded in, and the GEMM, whose last CTA also finishes the next thresholds; each
-        residual_threshold = reduce + finalise kernels)."""
-        @staticmethod
-        def Conv2d(*a):
-            launches[0] += 2
-            return tab_ops.Conv2d(*a)
-
-        @staticmethod
-        def Conv2dFused(*a):
-            launches[0] += 2
-            return tab_ops.Conv2dFused(*a)
-
-        @staticmethod
-        def residual_threshold(*a):
-            launches[0] += 2
-            return tab_ops.residual_threshold(*a)
-
-    class ModuleOps:
-        """The same chain through the TAB_CUDA extension module."""
-        Conv2d = staticmethod(TAB_CUDA.Conv2d)
-        residual_threshold = staticmethod(tab_ops.residual_threshold)
-
-        @staticmethod
-        def Conv2dFused(*a):
-            y, nxt = TAB_CUDA.Conv2dFused(*a[:16], a[16], a[17] if a[17] is not None else 0.0)
-            return y, nxt
-
     y_full = torch.empty(N * per_img_out, dtype=torch.float32, device=dev)
     y_host = torch.empty(N * per_img_out, dtype=torch.float32).pin_memory() if rank == 0 else None
 
-    def step_device(op_set, x_in):
-        ths = op_set.residual_threshold(x_in, None, chain.THRESHOLD_SCALE)
-        y, _, _, _ = chain.forward(op_set, x_in, ths, qweights, CONV_TYPE, n_local)
-        if world > 1:
-            dist.all_gather_into_tensor(y_full, y.reshape(-1))
-            return y_full
-        return y.reshape(-1)
-
-    def step_e2e():
-        xin = x_host.to(dev, non_blocking=True)
-        y = step_device(ModuleOps, xin)
-        if rank == 0:
-            y_host.copy_(y, non_blocking=True)
-        return y
+    def forward(cset, x_in, nb, count=True):
+        if count:
+            launches[0] += 2
+        ths = tab_ops.residual_threshold(x_in.reshape(nb, -1), None, chain.THRESHOLD_SCALE)      # reduce + finalise kernels
+        y, _, _, _ = chain.forward_prepared(cset, x_in, ths, nb)
+        return y, ths
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, flush=True):
         evs = []
         for _ in range(steps):
-            flush_buf.fill_(1)                      # L2 flush: 256 MiB write, outside the timed events
+            if flush:
+                flush_buf.fill_(1)                  # L2 flush: 256 MiB write, outside the timed events
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()
@@ -340,65 +396,57 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- CUDA graph of one forward (the step is ~40 short launches: replaying a graph removes the launch
+    # ---- CUDA graph of one forward (the step is ~37 short launches: replaying a graph removes the launch
     #      gaps; the library's launches take a stream and never allocate or synchronise, so they capture) ----
-    graphs = {}
-
-    def make_graph(op_set, x_static, nb=None):
-        nb = n_local if nb is None else nb
+    def make_graph(cset, x_static, nb):
         try:
             side = torch.cuda.Stream(dev)
             side.wait_stream(torch.cuda.current_stream(dev))
             with torch.cuda.stream(side):
-                for _ in range(2):                       # first calls set kernel attributes: outside capture
-                    ths = op_set.residual_threshold(x_static, None, chain.THRESHOLD_SCALE)
-                    chain.forward(op_set, x_static, ths, qweights, CONV_TYPE, nb)
+                for _ in range(2):                       # first calls set kernel attributes and look up symbols: outside capture
+                    forward(cset, x_static, nb, count=False)
             torch.cuda.current_stream(dev).wait_stream(side)
             torch.cuda.synchronize()
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr):
-                ths = op_set.residual_threshold(x_static, None, chain.THRESHOLD_SCALE)
-                y, _, _, _ = chain.forward(op_set, x_static, ths, qweights, CONV_TYPE, nb)
-            return gr, y
+                y, ths = forward(cset, x_static, nb, count=False)
+            return gr, y, ths
         except Exception as exc:                          # report and fall back to eager launches
             sys.stderr.write("cuda graph capture failed (%s): timing eager launches\n" % exc)
-            return None, None
+            return None, None, None
 
     # End-to-end step: the shard is processed in NCH chunks of images (every image is independent), so that the
-    # host-to-device copy of chunk i+1 overlaps the forward of chunk i: two input buffers / graphs in ping-pong,
+    # host-to-device copy of chunk i+1 overlaps the forward of chunk i: input buffers / graphs in rotation,
     # copies on their own streams.
     NCH = 8 if n_local % 8 == 0 and n_local >= 64 else (4 if n_local % 4 == 0 and n_local >= 16 else 1)
     nb_e2e = n_local // NCH
     x_chunk = [torch.empty((nb_e2e, H0, W0, C0), dtype=torch.float32, device=dev) for _ in range(3 if NCH > 2 else NCH)]
     y_local = torch.empty(n_local * per_img_out, dtype=torch.float32, device=dev)
-    graphs["dev"] = make_graph(CountingOps, x_dev)
-    graphs["e2e"] = [make_graph(ModuleOps, xb, nb_e2e) for xb in x_chunk]
-    use_graph = graphs["dev"][0] is not None and all(g[0] is not None for g in graphs["e2e"])
+    g_dev = make_graph(convs, x_dev, n_local)
+    g_e2e = [make_graph(mconvs, xb, nb_e2e) for xb in x_chunk]
+    use_graph = g_dev[0] is not None and all(g[0] is not None for g in g_e2e)
     h2d_stream = torch.cuda.Stream(dev)
     d2h_stream = torch.cuda.Stream(dev)
     launches[0] = 0
-    if use_graph:
-        ths_ = CountingOps.residual_threshold(x_dev, None, chain.THRESHOLD_SCALE)      # count one forward's kernels
-        chain.forward(CountingOps, x_dev, ths_, qweights, CONV_TYPE, n_local)
+    forward(convs, x_dev, n_local)                        # count one forward's kernels
     launches_per_step = launches[0]
+    torch.cuda.synchronize()
 
-    def finish(y):
-        if world > 1:
+    def finish(y, gather=True):
+        if world > 1 and gather:
             dist.all_gather_into_tensor(y_full, y.reshape(-1))
             return y_full
         return y.reshape(-1)
 
-    def step_value():
+    def step_value(gather=True):
         if use_graph:
-            graphs["dev"][0].replay()
-            return finish(graphs["dev"][1])
-        return step_device(CountingOps, x_dev)
+            g_dev[0].replay()
+            return finish(g_dev[1], gather)
+        return finish(forward(convs, x_dev, n_local)[0], gather)
 
-    def step_e2e_any():
-        if not use_graph:
-            return step_e2e()
-        main = torch.cuda.current_stream(dev)
-        h2d_stream.wait_stream(main)                 # the step starts where the caller's stream is
+    def step_e2e():
+        main_s = torch.cuda.current_stream(dev)
+        h2d_stream.wait_stream(main_s)               # the step starts where the caller's stream is
         ev_in, ev_done = [], []
         for i in range(NCH):
             k = i % len(x_chunk)
@@ -407,43 +455,90 @@ def main():
                     h2d_stream.wait_event(ev_done[i - len(x_chunk)])     # the buffer's previous chunk has been consumed
                 x_chunk[k].copy_(x_host[i * nb_e2e:(i + 1) * nb_e2e], non_blocking=True)
                 e = torch.cuda.Event(); e.record(h2d_stream); ev_in.append(e)
-            main.wait_event(ev_in[i])
-            graphs["e2e"][k][0].replay()
-            lo, hi = i * nb_e2e * per_img_out, (i + 1) * nb_e2e * per_img_out
-            y_local[lo:hi].copy_(graphs["e2e"][k][1].reshape(-1), non_blocking=True)
-            e = torch.cuda.Event(); e.record(main); ev_done.append(e)
+            main_s.wait_event(ev_in[i])
+            if use_graph:
+                g_e2e[k][0].replay()
+                yk = g_e2e[k][1]
+            else:
+                yk = forward(mconvs, x_chunk[k], nb_e2e, count=False)[0]
+            lo_, hi_ = i * nb_e2e * per_img_out, (i + 1) * nb_e2e * per_img_out
+            y_local[lo_:hi_].copy_(yk.reshape(-1), non_blocking=True)
+            e = torch.cuda.Event(); e.record(main_s); ev_done.append(e)
             if world == 1:                               # single GPU: a chunk's result goes back while the next one computes
                 with torch.cuda.stream(d2h_stream):
                     d2h_stream.wait_event(e)
-                    y_host[lo:hi].copy_(y_local[lo:hi], non_blocking=True)
+                    y_host[lo_:hi_].copy_(y_local[lo_:hi_], non_blocking=True)
         if world == 1:
-            main.wait_stream(d2h_stream)                 # the step ends when the last result is on the host
+            main_s.wait_stream(d2h_stream)               # the step ends when the last result is on the host
             return y_local
         y = finish(y_local)
         if rank == 0:
             y_host.copy_(y, non_blocking=True)
         return y
 
-    # ---- warm-up, then the timed region ---------------------------------------------------------------
+    # ---- warm-up, then the timed regions ---------------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
         step_value()
-        step_e2e_any()
+        step_e2e()
     barrier()
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
-    sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+    uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+    sampler = ClockSampler(uuid)
     sampler.start()
     time.sleep(0.15)
-    launches[0] = 0
     barrier()
     ms_total = timed(step_value, args.steps)
     barrier()
     ms_total = max_over_ranks(ms_total)
-    gpu_launches = launches_per_step * args.steps if use_graph else launches[0]
+    ms_nogather = None
+    if world > 1:
+        barrier()
+        ms_nogather = max_over_ranks(timed(lambda: step_value(False), args.steps))
     barrier()
-    ms_e2e = timed(step_e2e_any, args.steps)
+    ms_e2e = timed(step_e2e, args.steps)
     barrier()
     ms_e2e = max_over_ranks(ms_e2e)
     clocks = sampler.stop()
+    gpu_launches = launches_per_step * args.steps
+
+    # ---- sustained: back-to-back steps for >= sustained-seconds, no flush (each step moves > 4 GB at N = 1) ----------
+    sustained = None
+    if args.sustained_seconds > 0:
+        per = ms_total / args.steps
+        reps = max(int(args.sustained_seconds * 1e3 / max(per, 1e-3)), args.steps)
+        s2 = ClockSampler(uuid)
+        s2.start()
+        barrier()
+        ms_sus = max_over_ranks(timed(step_value, reps, flush=False))
+        c2 = s2.stop()
+        sustained = {"value": ops_per_step * reps / (ms_sus * 1e-3) / 1e12, "unit": "TOPS", "steps": reps, "seconds": ms_sus * 1e-3,
+                     "ms_per_step": ms_sus / reps, "sm_mhz_median": c2["sm_mhz"], "power_w_max": c2.get("power_w_max"), "reasons": c2["reasons"],
+                     "note": "steps back to back, no L2 flush between them (a step streams more than the L2 holds)"}
+
+    # ---- parity: sampled images against the CPU oracle chain, outside every timed region ------------------------
+    y_chk = step_value().clone()
+    ths_in = tab_ops.residual_threshold(x_dev.reshape(n_local, -1), None, chain.THRESHOLD_SCALE)
+    if world > 1:
+        ths_all = torch.empty(N, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(ths_all, ths_in)
+    else:
+        ths_all = ths_in
+    y_e2e_chk = step_e2e().clone() if world == 1 else None
+    torch.cuda.synchronize()
+    parity = None
+    if rank == 0:
+        per_rank = N // world
+        picks = sorted(set([0, N // 2, N - 1] + [r * per_rank + (r * 7) % max(per_rank, 1) for r in range(world)]))
+        host_threads()
+        yo = oracle_chain_images(x_host_full[picks].numpy(), ths_all[picks].cpu().numpy())
+        got = y_chk.reshape(N, -1)[picks].cpu().numpy()
+        ok = bool(np.array_equal(got, yo))
+        if y_e2e_chk is not None:
+            ok = ok and bool(np.array_equal(y_e2e_chk.reshape(N, -1)[picks].cpu().numpy(), yo))
+        parity = {"images": len(picks), "image_indices": picks, "ok": ok,
+                  "what": "final 7x7x512 outputs of the sampled images%s == CPU oracle chain on the GPU's input thresholds, bit for bit"
+                          % (" (value and e2e paths)" if y_e2e_chk is not None else " (from the all-gathered tensor)")}
+    del x_host_full
 
     if rank != 0:
         if world > 1:
@@ -453,13 +548,10 @@ def main():
 
     value = ops_per_step * args.steps / (ms_total * 1e-3) / 1e12
     e2e_value = ops_per_step * args.steps / (ms_e2e * 1e-3) / 1e12
-
-    # ---- roofline of the dominant kernel (popcount conv), timed alone per layer ----------------------
     stream = torch.cuda.current_stream(dev).cuda_stream
 
     def probe(kind):
         sink = torch.empty(lib.tab_pipe_probe_sink_bytes(), dtype=torch.uint8, device=dev)
-        import ctypes
         n_ops = ctypes.c_double(0)
         best = None
         for i in range(4):
@@ -476,27 +568,34 @@ def main():
     popc_rate = probe(0)          # lane-level POPC per second, whole device
     lop3_rate = probe(1)
     imma_sync_tops = probe(2) / 1e12   # s8 mma.sync from registers: the ceiling of the legacy MMA instruction
+    umma_tops = probe(7) / 1e12        # tcgen05.mma kind::i8 128x256x32 from shared memory, no copies: the tensor ceiling
     # TNN per 32-bit word pair: 2 LOP3 to form t,u; f full adders (2 LOP3 each) per word and stream remove f POPC.
     # time(f) = max((2+4f)/lop3, 2(1-f)/popc); balanced f* gives the integer-pipe bound.
-    f_star = (2 * lop3_rate - 2 * popc_rate) / (4 * popc_rate + 2 * lop3_rate)
-    f_star = min(max(f_star, 0.0), 1.0)
+    f_star = min(max((2 * lop3_rate - 2 * popc_rate) / (4 * popc_rate + 2 * lop3_rate), 0.0), 1.0)
     pair_rate = 1.0 / max((2 + 4 * f_star) / lop3_rate, 2 * (1 - f_star) / popc_rate)
-    peak_tops = pair_rate * 64 / 1e12
+    peak_popc_tops = pair_rate * 64 / 1e12
     naive_popc_tops = popc_rate * 64 / 2 / 1e12
 
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        bf16_peak, peak_src = float(peaks["bf16_tflops"]), "of measured"
+        hbm_peak, hbm_src = float(peaks["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs (of measured)"
+    except Exception:
+        bf16_peak, peak_src = 1590.0, "of fallback"
+        hbm_peak, hbm_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
+
+    # ---- per-layer table: every launch of the step timed alone (CUDA events, L2 flushed) ---------------------------
     layer_rows = []
-    sums = {"gemm_ms": 0.0, "popc_ms": 0.0, "call_ms": 0.0, "ops": 0, "hbm_ms": 0.0, "hbm_bytes": 0}
-    umma_tops = probe(7) / 1e12        # tcgen05.mma kind::i8 128x256x32 from shared memory, no copies: the tensor ceiling
-    hbm_peak_guess, tensor_peak_guess = 6.5e12, umma_tops * 1e12           # only to label a layer memory- or tensor-bound
+    sums = {"gemm_ms": 0.0, "popc_ms": 0.0, "quant_ms": 0.0, "ops": 0, "gemm_bytes": 0, "quant_bytes": 0}
     if not args.no_layer_table:
         h = H0
         jobs = []
         for b in chain.resnet18_blocks():
             oh_a = (h + 2 * b.conv_a.pad - b.conv_a.K + 1) // b.conv_a.stride
-            jobs.append((b.conv_a, h))
-            jobs.append((b.conv_b, oh_a))
+            jobs.append((b.conv_a, h, False))
+            jobs.append((b.conv_b, oh_a, True))
             if b.shortcut is not None:
-                jobs.append((b.shortcut, h))
+                jobs.append((b.shortcut, h, False))
             h = oh_a
 
         def time_launch(fn):
@@ -512,75 +611,39 @@ def main():
                     times.append(e0.elapsed_time(e1))
             return statistics.mean(times)
 
-        for cs, ih in jobs:
+        state = tab_ops.new_state(n_local, dev)
+        for cs, ih, has_res in jobs:
             oh = (ih + 2 * cs.pad - cs.K + 1) // cs.stride
+            conv = convs[cs.name]
             xin = torch.randn(n_local, ih, ih, cs.C, device=dev)
-            ths = tab_ops.residual_threshold(xin, None, 0.7)
-            qw, btn = qweights[cs.name]
+            ths = tab_ops.residual_threshold(xin.reshape(n_local, -1), None, 0.7)
             qx = tab_ops.Quantize(xin, ths, 2, n_local, ih, ih, cs.C)[0]
-            w8 = tab_ops.expand_weights(qw, 2, cs.KN, cs.K, cs.K, cs.C)
             yb = torch.empty(n_local * oh * oh * cs.KN, dtype=torch.float32, device=dev)
-            geom = (cs.pad, cs.pad, cs.stride, cs.stride, n_local, ih, ih, cs.C, cs.KN, cs.K, cs.K)
-            # the GEMM stage alone, through the kernel tab_conv2d_launch picks for this layer
-            q8 = tab_ops.quantize_int8_padded(xin, ths, 2, n_local, ih, ih, cs.C, cs.K, cs.K, cs.pad, cs.pad, cs.stride, cs.stride)
-            gemm_kernel = "conv_umma_persist_kernel"
-            ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_int8_padded_launch(
-                q8.data_ptr(), w8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "int8p"))
-            in_bytes = q8.numel()
-            ms_popc = time_launch(lambda: _cabi.check(lib.tab_conv2d_packed_launch(qx.data_ptr(), qw.data_ptr(), btn.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, stream), "popc"))
-            ms_call = time_launch(lambda: tab_ops.Conv2d(xin, qw, ths, btn, CONV_TYPE, *geom))
+            res = torch.round(torch.randn(n_local * oh * oh * cs.KN, device=dev) * 8) if has_res else None
+            nxt = torch.empty(n_local, dtype=torch.float32, device=dev)
+            btn = torch.empty(n_local, dtype=torch.int32, device=dev)
+            geom = conv.geometry(n_local, ih, ih)
+            chained = cs.K == 3                                             # the 3x3 convolutions feed thresholds, the shortcuts do not
+            ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_bits_launch(
+                qx.data_ptr(), conv.W8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, res.data_ptr() if has_res else None,
+                state.data_ptr() if chained else None, nxt.data_ptr() if chained else None, 0.7, stream), "bits"))
+            kernel = lib.tab_last_conv_kernel().decode()
+            ms_quant = time_launch(lambda: _cabi.check(lib.tab_quantize_launch(xin.data_ptr(), ths.data_ptr(), qx.data_ptr(), None, 2,
+                                                                                n_local, ih, ih, cs.C, stream), "quantize"))
+            ms_popc = time_launch(lambda: _cabi.check(lib.tab_conv2d_packed_launch(qx.data_ptr(), conv.QW.data_ptr(), conv.BTN_W.data_ptr(), yb.data_ptr(),
+                                                                                    CONV_TYPE, *geom, stream), "popc"))
             lops = 2 * n_local * oh * oh * cs.KN * cs.K * cs.K * cs.C
-            gemm_bytes = in_bytes + w8.numel() + 4 * yb.numel()             # byte activations + byte weights read, fp32 output written
-            sums["gemm_ms"] += ms_gemm; sums["popc_ms"] += ms_popc; sums["call_ms"] += ms_call; sums["ops"] += lops
-            if gemm_bytes / hbm_peak_guess > lops / tensor_peak_guess:
-                sums["hbm_ms"] += ms_gemm; sums["hbm_bytes"] += gemm_bytes
-            layer_rows.append({"layer": cs.name, "in": [ih, ih, cs.C], "KN": cs.KN, "K": cs.K, "s": cs.stride,
-                               "gemm_kernel": gemm_kernel,
-                               "gemm_ms": round(ms_gemm, 4), "gemm_tops": round(lops / ms_gemm / 1e9, 1),
+            gemm_bytes = qx.numel() * 8 + conv.W8.numel() + 4 * yb.numel() * (2 if has_res else 1)
+            quant_bytes = 4 * xin.numel() + qx.numel() * 8
+            sums["gemm_ms"] += ms_gemm; sums["popc_ms"] += ms_popc; sums["ops"] += lops; sums["gemm_bytes"] += gemm_bytes
+            if cs.K == 3:                                                   # the shortcut reuses conv_a's bit-planes: no quantiser launch of its own
+                sums["quant_ms"] += ms_quant; sums["quant_bytes"] += quant_bytes
+            layer_rows.append({"layer": cs.name, "in": [ih, ih, cs.C], "KN": cs.KN, "K": cs.K, "s": cs.stride, "residual": has_res,
+                               "gemm_kernel": kernel, "gemm_ms": round(ms_gemm, 4), "gemm_tops": round(lops / ms_gemm / 1e9, 1),
                                "gemm_GBps": round(gemm_bytes / ms_gemm / 1e6, 1),
-                               "popcount_kernel_tops": round(lops / ms_popc / 1e9, 1),
-                               "conv2d_call_ms": round(ms_call, 4), "conv2d_call_tops": round(lops / ms_call / 1e9, 1)})
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        bf16_peak, peak_src = float(peaks["bf16_tflops"]), "of measured"
-    except Exception:
-        peaks = None
-        bf16_peak, peak_src = 1590.0, "of fallback"
-    tensor_peak = umma_tops                      # measured in this run; 2 x the measured bf16 figure is reported beside it
-    achieved = sums["ops"] / (sums["gemm_ms"] * 1e-3) / 1e12 if sums["gemm_ms"] else None
-    roofline = {
-        "kernel": "int8 tensor-core GEMM stage of Conv2d: conv_umma_persist_kernel (persistent TMA-fed tcgen05.mma kind::i8), "
-                  "%d launches per step" % len(layer_rows),
-        "bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TOP/s",
-        "frac": (achieved / tensor_peak) if achieved else None,
-        # DRAM bytes of the largest launch of the step (56x56x64->64, batch 256), from the ncu capture summarised under profiles/
-        "traffic": PERSIST_L1_TRAFFIC, "traffic_note": "largest launch (56x56x64->64 conv, N=256), ncu dram bytes read+written; algorithmic %.1fe6 "
-                   "(padded byte activations + byte weights + fp32 output)" % ((256 * 58 * 58 * 64 + 64 * 9 * 64 + 4 * 256 * 56 * 56 * 64) / 1e6),
-        "peak_source": "measured in this run: tcgen05.mma kind::i8 128x256x32 issued back to back from shared memory on every SM (no copies, "
-                       "no epilogue); 2 x MEASURED_PEAKS.json bf16_tflops would be %.0f TOP/s (%s); s8 mma.sync ceiling measured in this run: %.0f TOP/s"
-                       % (2.0 * bf16_peak, peak_src, imma_sync_tops),
-        "frac_of_2x_bf16_measured": (achieved / (2.0 * bf16_peak)) if achieved else None,
-        "avg_launch_ms": sums["gemm_ms"] / max(len(layer_rows), 1),
-    }
-    if peaks is not None and "hbm_gbs" in peaks:
-        hbm_peak, hbm_src = float(peaks["hbm_gbs"]), "MEASURED_PEAKS.json hbm_gbs (of measured)"
-    else:
-        hbm_peak, hbm_src = 6650.0, "fallback 6.65 TB/s (of fallback)"
-    hbm_achieved = sums["hbm_bytes"] / (sums["hbm_ms"] * 1e-3) / 1e9 if sums["hbm_ms"] else None
-    roofline_hbm_layers = {
-        "kernel": "the GEMM-stage launches whose byte traffic, not their MMAs, sets the floor (few filters per byte of output: the 56x56x64 layers and the 1x1 shortcuts)",
-        "bound": "hbm", "achieved": hbm_achieved, "peak": hbm_peak, "unit": "GB/s",
-        "frac": (hbm_achieved / hbm_peak) if hbm_achieved else None, "peak_source": hbm_src,
-        "bytes": "algorithmic: byte activations + byte weights read, fp32 output written",
-    }
-    popc_achieved = sums["ops"] / (sums["popc_ms"] * 1e-3) / 1e12 if sums["popc_ms"] else None
-    roofline_popcount = {
-        "kernel": "conv_popc_kernel<TNN> (bit-packed LOP3/POPC path, TAB_PATH_POPCOUNT), same layers",
-        "bound": "alu", "achieved": popc_achieved, "peak": peak_tops, "unit": "TOP/s",
-        "frac": (popc_achieved / peak_tops) if popc_achieved else None,
-        "peak_source": "measured in this run: POPC %.3e/s, LOP3 %.3e/s (register-only probe); balanced carry-save bound "
-                       "(f*=%.2f full adders per word); one-POPC-per-word bound would be %.1f TOP/s" % (popc_rate, lop3_rate, f_star, naive_popc_tops),
-    }
+                               "quantize_ms": round(ms_quant, 4), "quantize_GBps": round(quant_bytes / ms_quant / 1e6, 1),
+                               "popcount_kernel_tops": round(lops / ms_popc / 1e9, 1)})
+        assert lib.tab_device_status() == 0, "a bounded wait expired in the tensor-core kernel"
 
     # ---- TAB_Quantize alone at N=256, 56x56x256 (HBM-bound), against the measured copy bandwidth ---------
     quant = {}
@@ -612,28 +675,71 @@ def main():
                       "peak_GBps": hbm_peak, "peak_source": hbm_src, "bound": "hbm"})
         del xq
 
+    ms_step = ms_total / args.steps
+    step_bytes = step_algorithmic_bytes(n_local)
+    step_gbs = step_bytes / ms_step / 1e6
+    gemm_achieved = sums["ops"] / (sums["gemm_ms"] * 1e-3) / 1e12 if sums["gemm_ms"] else None
+    popc_achieved = sums["ops"] / (sums["popc_ms"] * 1e-3) / 1e12 if sums["popc_ms"] else None
+    l1_images = n_local
+    roofline = {
+        "kernel": "whole step: %d launches (quantize_c64_kernel x16, conv_umma_persist_kernel x19, threshold kernels x2)" % launches_per_step,
+        "bound": "hbm", "achieved": step_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": step_gbs / hbm_peak, "peak_source": hbm_src,
+        "algorithmic_bytes_per_step": step_bytes, "images_per_gpu": n_local,
+        "traffic": (L1_TRAFFIC_PER_IMAGE * l1_images) if L1_TRAFFIC_PER_IMAGE else None,
+        "traffic_note": "ncu dram bytes read + written of the step's largest launch (conv_umma_persist_kernel, 56x56x64 -> 64), captured at 64 images and "
+                        "scaled to this rank's %d images; its algorithmic bytes are %.1fe6 (bit-planes + byte weights + fp32 output)"
+                        % (l1_images, (l1_images * 56 * 56 * 16 + 64 * 9 * 64 + 4 * l1_images * 56 * 56 * 64) / 1e6),
+        "gemm_stage": {
+            "kernel": "conv_umma_persist_kernel (persistent tcgen05.mma kind::i8 on bit-plane activations), %d launches per step, each timed alone" % len(layer_rows),
+            "bound": "tensor", "achieved": gemm_achieved, "peak": umma_tops, "unit": "TOP/s",
+            "frac": (gemm_achieved / umma_tops) if gemm_achieved else None,
+            "frac_of_2x_bf16_measured": (gemm_achieved / (2.0 * bf16_peak)) if gemm_achieved else None,
+            "hbm_GBps": (sums["gemm_bytes"] / (sums["gemm_ms"] * 1e-3) / 1e9) if sums["gemm_ms"] else None,
+            "avg_launch_ms": sums["gemm_ms"] / max(len(layer_rows), 1),
+            "peak_source": "measured in this run: tcgen05.mma kind::i8 128x256x32 issued back to back from shared memory on every SM (no copies, "
+                           "no epilogue); 2 x MEASURED_PEAKS.json bf16_tflops would be %.0f TOP/s (%s); s8 mma.sync ceiling measured in this run: %.0f TOP/s"
+                           % (2.0 * bf16_peak, peak_src, imma_sync_tops)},
+        "quantize_in_step": {
+            "kernel": "quantize_c64_kernel, the 16 launches of the step, each timed alone", "bound": "hbm",
+            "achieved": (sums["quant_bytes"] / (sums["quant_ms"] * 1e-3) / 1e9) if sums["quant_ms"] else None, "peak": hbm_peak, "unit": "GB/s"},
+        "quantize": quant,
+        "popcount": {
+            "kernel": "conv_popc_kernel<TNN> (bit-packed LOP3/POPC path, TAB_PATH_POPCOUNT), same layers", "bound": "alu",
+            "achieved": popc_achieved, "peak": peak_popc_tops, "unit": "TOP/s", "frac": (popc_achieved / peak_popc_tops) if popc_achieved else None,
+            "peak_source": "measured in this run: POPC %.3e/s, LOP3 %.3e/s (register-only probe); balanced carry-save bound "
+                           "(f*=%.2f full adders per word); one-POPC-per-word bound would be %.1f TOP/s" % (popc_rate, lop3_rate, f_star, naive_popc_tops)},
+    }
+    if roofline["quantize_in_step"]["achieved"]:
+        roofline["quantize_in_step"]["frac"] = roofline["quantize_in_step"]["achieved"] / hbm_peak
+
+    config = workload_config(world)
+    config["parity_check"] = parity
     line = {
         "metric": "TAB_Conv2d binary-op TOPS", "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong",
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "s8 (ternary values on the integer tensor cores, s32 accumulate; exact)", "data": "synthetic",
-        "config": dict(workload_config(world), binary_ops_per_step=ops_per_step),
+        "config": config,
         "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(N * per_img_out * 4),
-                "api": "TAB_CUDA.Conv2d / Conv2dFused (extension module) + pinned-host copies, %d chunks of images pipelined; bytes are rank 0's" % NCH},
-        "gpu_launches": gpu_launches, "cuda_graph": bool(use_graph),
+                "api": "TAB_CUDA.Quantize / Conv2dBits (extension module, prepared weights) + pinned-host copies, %d chunks of images pipelined; bytes are rank 0's" % NCH},
+        "gpu_launches": gpu_launches, "launches_per_step": launches_per_step, "cuda_graph": bool(use_graph),
         "clocks": clocks,
         "roofline": roofline,
-        "roofline_hbm_layers": roofline_hbm_layers,
-        "roofline_popcount": roofline_popcount,
-        "quantize": quant,
+        "value_sustained": sustained,
         "layers": layer_rows,
     }
+    if world > 1:
+        line["value_no_gather"] = ops_per_step * args.steps / (ms_nogather * 1e-3) / 1e12
+        line["ms_per_step_no_gather"] = ms_nogather / args.steps
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.cpu_sample_images)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.stderr.write("parity check FAILED: sampled outputs differ from the CPU oracle\n")
+        sys.exit(3)
 
 
 if __name__ == "__main__":

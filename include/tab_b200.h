@@ -4,7 +4,8 @@
  * Every entry point takes plain device pointers and sizes, enqueues work on the given CUDA stream and
  * returns immediately (no host synchronisation).  Return value: 0 on success, a negative TAB_E_* code
  * otherwise; nothing is thrown across this boundary.  None of the *_launch functions allocates or
- * frees device memory: scratch is a caller-provided workspace.
+ * frees device memory: scratch is a caller-provided workspace.  The library keeps no mutable global state
+ * besides per-thread settings, a per-device error record and caches of immutable driver objects.
  *
  * Data formats (identical to the reference CUDA backend):
  *   x    float32, N·H·W·C elements in N,H,W,C order                       (TAB_GEMM.cu:184,231)
@@ -58,23 +59,33 @@ int tab_quantize_launch(const float* x, const float* ths, int64_t* qx, int32_t* 
                         int bitwidth, int N, int H, int W, int C, tab_stream_t stream);
 
 /*
- * Bytes of scratch tab_conv2d_launch needs for these sizes, whichever compute path is selected (the
- * quantised activations - in zero-padded form where the kernel wants them so - and, for the tensor-core path, the
- * byte-expanded weights).  Same geometry arguments, in the same order, as tab_conv2d_launch.
- * Returns 0 for invalid arguments.
+ * Bytes of scratch tab_conv2d_launch needs for these sizes, whichever compute path is selected: the activations'
+ * bit-planes (N*H*W*ceil(C/64) words per plane), the byte-expanded weights of the tensor-core path and a 256-byte
+ * completion counter.  Same geometry arguments, in the same order, as tab_conv2d_launch.  Returns 0 for invalid arguments.
  */
 size_t tab_conv2d_workspace_bytes(int type, int p1, int p2, int s1, int s2,
                                   int N, int H, int W, int C, int KN, int KH, int KW);
 
 /*
- * Compute path of tab_conv2d_launch (process-wide; results are identical bit for bit):
- *   TAB_PATH_AUTO (default)  int8 tensor-core implicit GEMM (quantised values as bytes, s8 MMA)
- *   TAB_PATH_POPCOUNT        bit-packed LOP3/POPC kernel - the reference's formulation (TAB_GEMM.cu:25-147);
- *                            this is also what tab_conv2d_packed_launch always runs
+ * Compute path of the convolution entry points, per calling thread (results are identical bit for bit):
+ *   TAB_PATH_AUTO (default)   the bit-planes are expanded to int8 inside a persistent tcgen05 kernel (s8 MMA, exact);
+ *                             shapes that kernel does not cover fall back to TAB_PATH_POPCOUNT
+ *   TAB_PATH_POPCOUNT         bit-packed LOP3/POPC kernel with a carry-save popcount tree - the reference's formulation
+ *                             (TAB_GEMM.cu:25-147); this is also what tab_conv2d_packed_launch runs
+ *   TAB_PATH_POPCOUNT_PLAIN   the same kernel with one POPC per word
  * Returns the previous setting, or TAB_E_BAD_ARGUMENT.
  */
-enum { TAB_PATH_AUTO = 0, TAB_PATH_POPCOUNT = 1 };
+enum { TAB_PATH_AUTO = 0, TAB_PATH_POPCOUNT = 1, TAB_PATH_POPCOUNT_PLAIN = 2 };
 int tab_conv2d_set_path(int path);
+/* Name and tile of the kernel the calling thread's most recent tensor-core convolution launched ("none" before the first, or
+   when the last convolution ran the popcount kernel).  Static storage per thread. */
+const char* tab_last_conv_kernel(void);
+/*
+ * Every wait inside the tensor-core kernel is bounded; a wait that ran out makes the kernel record a code and return
+ * early, leaving y incomplete.  This call synchronises the current device, returns that code (0 = none) and clears it.
+ * A non-zero code invalidates the outputs of every convolution launched on the device since the previous call.
+ */
+int tab_device_status(void);
 
 /*
  * Quantise activations, then convolve with pre-quantised weights as an implicit-im2col GEMM
@@ -82,8 +93,10 @@ int tab_conv2d_set_path(int path);
  * Img2RowKernel :92-115, GEMMWithCuda :22-66 and TNN/TBN/BTN/BNNGEMM TAB_GEMM.cu:25-147).
  * type: 0 TNN, 1 TBN, 2 BTN, 3 BNN.  qw is the tab_quantize_launch output of the weights
  * [KN][KH][KW][C] at bitwidth 2 for types 0,2 and bitwidth 1 for types 1,3.  btn (int32[KN]) is read
- * for type 2 only and may be NULL otherwise.  OH = (H + 2·p1 − KH + 1) / s1, OW likewise (integer
- * division, TAB_GEMM.cu:354-357).  y receives N·OH·OW·KN floats.  workspace must be 256-byte aligned.
+ * for type 2 only and may be NULL otherwise.  OH = (H + 2*p1 - KH + 1) / s1, OW likewise (integer
+ * division, TAB_GEMM.cu:354-357).  y receives N*OH*OW*KN floats.  workspace must be 256-byte aligned.
+ * Two launches: the quantiser (which also expands the weights to bytes) and the GEMM.  The first tensor-core call on a
+ * device looks up a driver entry point and a device symbol: make it outside any stream capture.
  */
 int tab_conv2d_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
                       float* y, void* workspace, size_t workspace_bytes, int type,
@@ -108,8 +121,7 @@ int tab_conv2d_fused_launch(const float* x, const int64_t* qw, const float* ths,
  * tab_conv2d_fused_launch that also finishes the next layer's thresholds (no counterpart in the reference):
  *   next_ths   float [N] or NULL: receives next_scale * abs_sums[n] / (KN*OH*OW), i.e. next_scale * mean|y[n]|;
  *              needs abs_sums.  On the tensor-core path the GEMM kernel's last CTA writes it, so a chained layer
- *              costs two launches (quantise with the weight expansion and the clears folded in, GEMM); on the
- *              other paths it is tab_threshold_from_sums_launch after the sums.
+ *              costs two launches; on the other paths it is tab_threshold_from_sums_launch after the sums.
  */
 int tab_conv2d_chain_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
                             float* y, void* workspace, size_t workspace_bytes, int type,
@@ -123,50 +135,37 @@ int tab_threshold_from_sums_launch(const double* sums, float* ths, float scale, 
 
 /*
  * Same convolution on activations that are already bit-packed (the qx layout above with bits = 2 for
- * types 0,1 and bits = 1 for types 2,3).  This is the GEMM stage of tab_conv2d_launch on its own
- * (GEMMWithCuda, TAB_GEMM.cuh:22-66, with padding and im2row folded in); it needs no workspace.
+ * types 0,1 and bits = 1 for types 2,3), by the bit-packed LOP3/POPC kernel.  This is the GEMM stage of the
+ * reference on its own (GEMMWithCuda, TAB_GEMM.cuh:22-66, with padding and im2row folded in); it needs no workspace.
  */
 int tab_conv2d_packed_launch(const int64_t* qx, const int64_t* qw, const int32_t* btn, float* y,
                              int type, int p1, int p2, int s1, int s2,
                              int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
 
 /*
- * The three stages of the tensor-core path of tab_conv2d_launch on their own, for callers that keep the
- * byte-expanded weights between calls (weights are constant during inference) or already hold
- * quantised activations.  Byte tensors hold the quantised values {-1,0,+1} as int8 with the channel
- * dimension padded to Cp = 64*ceil(C/64) (padding bytes 0): activations [N][H][W][Cp], weights
- * [KN][KH][KW][Cp].  All byte pointers must be 16-byte aligned.
- *   tab_quantize_int8_launch   same compares as tab_quantize_launch (TAB_GEMM.cu:184-192, :231), byte output
- *   tab_expand_weights_launch  tab_quantize_launch's packed weights (bitwidth 1 or 2) -> bytes
- *   tab_conv2d_int8_launch     the GEMM stage (GEMMWithCuda, TAB_GEMM.cuh:22-66, with padding and im2row
- *                              folded in); returns TAB_E_TOO_LARGE for KH*KW > 64 or N > 65535
+ * The stages of the tensor-core path on their own, for callers that keep prepared weights between calls (weights
+ * are constant during inference) or feed several convolutions from one quantised tensor.  No counterpart in the
+ * reference, which re-reads packed weights and re-quantises fp32 activations in every call (TAB_GEMM.cu:419-426).
+ *
+ *   tab_expand_weights_launch   tab_quantize_launch's packed weights (bitwidth 1 or 2) -> int8 {-1,0,+1},
+ *                               [KN][KH][KW][Cp] with Cp = 64*ceil(C/64), channel padding 0; w8 16-byte aligned.
+ *   tab_conv2d_bits_launch      the GEMM stage: activations as tab_quantize_launch wrote them (qx, bitwidth 2 for types
+ *                               0,1 and 1 for types 2,3; 16-byte aligned), weights from tab_expand_weights_launch.
+ *                               y and residual 16-byte aligned.  Optional chaining as in tab_conv2d_chain_launch:
+ *                               y = conv + residual; next_ths[n] = next_scale * mean|y[n]|, which needs `state`:
+ *                               tab_conv2d_state_bytes(N) bytes, 8-byte aligned, that the caller zeroes once
+ *                               (cudaMemsetAsync) before its first use; every call leaves it zeroed again, so one state
+ *                               block serves any number of calls that are ordered on a stream.  One launch.
+ *                               Returns TAB_E_TOO_LARGE for shapes the tensor-core kernel does not cover (a patch of
+ *                               128 + (KH-1)/s1*VW + (KW-1)/s2 rows of 128 bytes that does not fit shared memory beside
+ *                               the filters, or index ranges beyond 2^31): use tab_conv2d_packed_launch for those.
  */
-int tab_quantize_int8_launch(const float* x, const float* ths, int8_t* qx8, int bitwidth,
-                             int N, int H, int W, int C, tab_stream_t stream);
 int tab_expand_weights_launch(const int64_t* qw, int8_t* w8, int bitwidth, int KN, int KH, int KW, int C,
                               tab_stream_t stream);
-int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
-                           int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
-
-/*
- * The same stages in the form tab_conv2d_launch itself uses: the quantiser writes the convolution's padding into the
- * byte tensor - border pixels 0 (ternary activations) or +1 (binary activations, bitwidth 1): the reference's padded
- * im2row input (TAB_Utils.cu:23-63) in bytes - and, for a strided convolution, splits the padded image into the
- * s1 x s2 parity planes the taps read:
- *     qx8p [A*B][N][PH2][PW2][Cp],  A = min(s1, KH), B = min(s2, KW), PH2 = ceil((H+2*p1)/s1), PW2 = ceil((W+2*p2)/s2),
- *     plane a*B+b, pixel (i, j) = padded pixel (s1*i + a, s2*j + b)        (stride 1: the padded image [N][H+2*p1][W+2*p2][Cp])
- * so that every tap is a stride-1 window of one plane, which the GEMM stage (the persistent TMA-fed tcgen05 kernel)
- * addresses as a shifted start into a patch it stages once per tile.
- *   tab_quantize_int8_padded_launch  N < 65535
- *   tab_conv2d_int8_padded_launch    weights from tab_expand_weights_launch; returns TAB_E_TOO_LARGE when the shape is
- *                                    not covered (A*B*N*PH2*PW2 >= 2^31, KH*KW > 64, N >= 65535, or a patch of
- *                                    128 + (KH-1)/s1*PW2 + (KW-1)/s2 rows that does not fit shared memory)
- */
-int tab_quantize_int8_padded_launch(const float* x, const float* ths, int8_t* qx8p, int bitwidth,
-                                    int N, int H, int W, int C, int KH, int KW, int p1, int p2, int s1, int s2,
-                                    tab_stream_t stream);
-int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
-                                  int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream);
+size_t tab_conv2d_state_bytes(int N);
+int tab_conv2d_bits_launch(const int64_t* qx, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
+                           int N, int H, int W, int C, int KN, int KH, int KW,
+                           const float* residual, void* state, float* next_ths, float next_scale, tab_stream_t stream);
 
 /*
  * tab_conv2d_launch without a workspace argument.  No counterpart in the reference (its host code calls
@@ -189,7 +188,10 @@ int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y
  *     give wrong results; serialise them on one stream or with events.
  *   - The array keeps whatever the last call left; this function overwrites every word it later reads,
  *     so no clearing is needed between calls.
- * Arguments and results are otherwise exactly those of tab_conv2d_launch.
+ *   - This entry point always runs the bit-packed LOP3/POPC kernel (TAB_PATH_POPCOUNT, about 150 binary TOP/s on a
+ *     B200 against several hundred for the tensor-core path of tab_conv2d_launch): the tensor-core path also needs
+ *     byte-expanded weights, which would not fit a modest fixed array.
+ * Arguments, checks, error codes and results are otherwise exactly those of tab_conv2d_launch.
  */
 #define TAB_STATIC_SCRATCH_BYTES (16u << 20)
 int tab_conv2d_static_launch(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
@@ -207,11 +209,12 @@ int tab_residual_threshold_launch(float* y, const float* residual, float* ths, d
                                   float scale, int N, long long per_image, tab_stream_t stream);
 
 /*
- * Register-only micro-benchmark of the integer pipes used by the convolution, for roofline
+ * Register-only micro-benchmark of the pipes used by the convolution, for roofline
  * denominators: runs `iters` rounds on a grid that fills the device and writes elapsed-independent
  * checksums to `sink` (at least tab_pipe_probe_sink_bytes() bytes).  kind: 0 = 32-bit POPC,
- * 1 = LOP3, 2 = s8 mma.sync m16n8k32, 3 / 4 = 1-bit mma.sync m16n8k256 and.popc / xor.popc.  *ops_out receives
- * the number of lane-level instructions of that kind issued (kinds 2-4: multiply-adds * 2); the caller times the call with CUDA events.  Has no
+ * 1 = LOP3, 2 = s8 mma.sync m16n8k32, 3 / 4 = 1-bit mma.sync m16n8k256 and.popc / xor.popc, 5 / 6 / 7 = tcgen05.mma kind::i8
+ * 128 x 64 / 128 / 256 x 32 issued back to back from shared memory.  *ops_out receives the number of lane-level
+ * instructions of that kind issued (kinds 2-7: multiply-adds * 2); the caller times the call with CUDA events.  Has no
  * counterpart in the reference.
  */
 size_t tab_pipe_probe_sink_bytes(void);

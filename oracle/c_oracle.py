@@ -35,8 +35,15 @@ def oracle_lib(variant="v3"):
         l.oracle_im2row.restype = None
         l.oracle_conv2d_with.argtypes = [C.c_void_p] * 6 + [C.c_int] * 12
         l.oracle_conv2d_with.restype = C.c_int
+        l.oracle_omp_threads.argtypes = [C.c_int]
+        l.oracle_omp_threads.restype = C.c_int
         _libs[key] = l
     return _libs[key]
+
+
+def omp_threads(n=0, variant="v3"):
+    """OpenMP threads the CPU pipeline uses (``omp_get_max_threads``); ``n > 0`` sets the count first."""
+    return int(oracle_lib(variant).oracle_omp_threads(int(n)))
 
 
 def ref_available(variant="v3"):

@@ -43,3 +43,25 @@ def torch_cpu_conv(x, qw, ths, btn, conv_type, p1, p2, s1, s2, N, H, W, C, KN, K
     y = c_oracle.conv2d(x.numpy().reshape(-1), qw.numpy(), ths.numpy(), btn.numpy(), conv_type,
                         p1, p2, s1, s2, N, H, W, C, KN, KH, KW)
     return torch.from_numpy(y)
+
+
+class OraclePreparedConv:
+    """Stand-in for ``tab_b200.nn.TABConv2d`` on the CPU oracle: ``quantize`` / ``conv_bits`` with the same meaning."""
+
+    def __init__(self, qw, btn, conv_type, cs):
+        self.qw, self.btn, self.t, self.cs = qw, btn, conv_type, cs
+
+    def quantize(self, x, ths):
+        N, H, W = x.shape[:3]
+        return (np.ascontiguousarray(x, dtype=np.float32), np.asarray(ths, dtype=np.float32), N, H, W)     # the oracle quantises inside conv2d
+
+    def conv_bits(self, qx, N, H, W, residual=None, next_threshold_scale=None):
+        x, ths, _, _, _ = qx
+        cs = self.cs
+        y = c_oracle.conv2d(x.reshape(-1), self.qw, ths, self.btn, self.t, cs.pad, cs.pad, cs.stride, cs.stride, N, H, W, cs.C, cs.KN, cs.K, cs.K)
+        y = y.reshape(N, y.shape[2], y.shape[3], y.shape[1])                    # the buffer is [N][OH][OW][KN]
+        if next_threshold_scale is None:
+            if residual is not None:
+                y += np.asarray(residual, dtype=np.float32).reshape(y.shape)
+            return y, None
+        return y, OracleOps.residual_threshold(y, residual, next_threshold_scale)

@@ -23,6 +23,9 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #define CNTBITS 64
 #define popcnt64(a) __builtin_popcountll(a)
@@ -186,4 +189,17 @@ int oracle_conv2d(const float* x, const int64_t* qw, const float* ths, const int
                   int type, int p1, int p2, int s1, int s2,
                   int N, int H, int W, int C, int KN, int KH, int KW) {
     return oracle_conv2d_with(NULL, x, qw, ths, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
+}
+
+
+/* Threads the OpenMP loops above (and the reference's GEMMs, which share the runtime) will use; n > 0 sets it first.
+ * A launcher may export OMP_NUM_THREADS=1 for its children: the CPU baseline sets the count it reports explicitly. */
+int oracle_omp_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
 }

@@ -26,11 +26,11 @@ SYMBOLS = {
     "tab_conv2d_chain_launch": (_c.c_int, [_c.c_void_p] * 6 + [_c.c_size_t] + [_c.c_int] * 12 + [_c.c_void_p] * 3 + [_c.c_float, _c.c_void_p]),
     "tab_threshold_from_sums_launch": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_float, _c.c_int, _c.c_longlong, _c.c_void_p]),
     "tab_conv2d_packed_launch": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int] * 12 + [_c.c_void_p]),
-    "tab_quantize_int8_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 5 + [_c.c_void_p]),
     "tab_expand_weights_launch": (_c.c_int, [_c.c_void_p] * 2 + [_c.c_int] * 5 + [_c.c_void_p]),
-    "tab_conv2d_int8_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p]),
-    "tab_quantize_int8_padded_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 11 + [_c.c_void_p]),
-    "tab_conv2d_int8_padded_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p]),
+    "tab_conv2d_state_bytes": (_c.c_size_t, [_c.c_int]),
+    "tab_conv2d_bits_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p] * 3 + [_c.c_float, _c.c_void_p]),
+    "tab_last_conv_kernel": (_c.c_char_p, []),
+    "tab_device_status": (_c.c_int, []),
     "tab_conv2d_static_launch": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 12 + [_c.c_void_p]),
     "tab_residual_threshold_launch": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_float, _c.c_int, _c.c_longlong, _c.c_void_p]),
     "tab_pipe_probe_sink_bytes": (_c.c_size_t, []),

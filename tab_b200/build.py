@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtab_b200.so")
-SOURCES = ["c_abi.cu", "quantize_sm100.cu", "conv_sm100.cu", "conv_imma_sm100.cu", "conv_umma_sm100.cu", "conv_static_sm100.cu", "chain_sm100.cu", "pipe_probe.cu"]
+SOURCES = ["c_abi.cu", "quantize_sm100.cu", "conv_sm100.cu", "conv_umma_sm100.cu", "umma_probe.cu", "conv_static_sm100.cu", "chain_sm100.cu", "pipe_probe.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
@@ -29,24 +29,46 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _compile_one(args):
+    nvcc, src, obj = args
+    r = subprocess.run([nvcc] + NVCC_FLAGS + ["-c", "-o", obj, src], capture_output=True, text=True)
+    return src, r.returncode, r.stdout, r.stderr
+
+
 def build_library(force=False, verbose=False):
-    """nvcc -> tab_b200/libtab_b200.so.  Returns the ptxas resource report."""
+    """nvcc -> tab_b200/libtab_b200.so (one object per source, compiled in parallel under ``build/``).  Returns the
+    ptxas resource report, which is also kept as ``build/libtab_b200.ptxas.txt``."""
+    from concurrent.futures import ThreadPoolExecutor
     srcs = [os.path.join(CSRC, s) for s in SOURCES]
-    deps = srcs + [os.path.join(CSRC, "tab_kernels.cuh"), os.path.join(CSRC, "conv_int8.cuh"),
-                   os.path.join(ROOT, "include", "tab_b200.h"), __file__]
-    log = os.path.join(HERE, "libtab_b200.ptxas.txt")
-    if not force and not _stale(LIB, deps):
-        return open(log).read() if os.path.exists(log) else ""
+    hdrs = [os.path.join(CSRC, "tab_kernels.cuh"), os.path.join(CSRC, "umma_common.cuh"),
+            os.path.join(ROOT, "include", "tab_b200.h"), __file__]
+    objdir = os.path.join(ROOT, "build", "libtab_b200")
+    os.makedirs(objdir, exist_ok=True)
+    log = os.path.join(ROOT, "build", "libtab_b200.ptxas.txt")
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + ["-shared", "-o", LIB] + srcs
-    r = subprocess.run(cmd, capture_output=True, text=True)
+    jobs, objs = [], []
+    for s in srcs:
+        obj = os.path.join(objdir, os.path.basename(s) + ".o")
+        objs.append(obj)
+        if force or _stale(obj, [s] + hdrs):
+            jobs.append((nvcc, s, obj))
+    if not jobs and not _stale(LIB, objs):
+        return open(log).read() if os.path.exists(log) else ""
+    report = []
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as ex:
+        for src, rc, out, err in ex.map(_compile_one, jobs):
+            if rc != 0:
+                raise RuntimeError("nvcc failed on %s:\n%s\n%s" % (src, out, err))
+            report.append("==== %s\n%s" % (os.path.basename(src), err))
+    r = subprocess.run([nvcc, "-shared", "-o", LIB] + objs, capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError("nvcc failed:\n%s\n%s" % (r.stdout, r.stderr))
-    with open(log, "w") as f:
-        f.write(r.stderr)
+        raise RuntimeError("nvcc link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    text = "\n".join(report)
+    with open(log, "a" if len(jobs) < len(srcs) and os.path.exists(log) else "w") as f:
+        f.write(text)
     if verbose:
-        print(r.stderr)
-    return r.stderr
+        print(text)
+    return text
 
 
 def module_path():

@@ -1,37 +1,54 @@
 // extern "C" entry points declared in include/tab_b200.h: argument validation, then kernel dispatch.
-// No entry point in this file allocates or frees device memory, and none synchronises the host.
+// No entry point in this file allocates or frees device memory, and none synchronises the host (tab_device_status
+// excepted, which exists to synchronise).
 #include "tab_kernels.cuh"
+#include "umma_common.cuh"
 
 namespace tab {
 
 static thread_local int g_last_cuda_error = 0;
+static thread_local int g_conv_path = TAB_PATH_AUTO;
 
 int record_cuda_error(cudaError_t e) {
     g_last_cuda_error = (int)e;
     return TAB_E_CUDA;
 }
 
-void conv_set_csa(bool on);
-void imma_set_variant(int v);
 int umma_status_read_and_clear();
-size_t imma_workspace_bytes(int N, int H, int W, int C, int KN, int KH, int KW, int p1, int p2, int s1, int s2);
-int conv_imma_dispatch(const float* x, const int64_t* qw, const float* ths, float* y, void* workspace, int type,
-                       int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
-                       cudaStream_t stream, const float* residual, double* abs_sums, float* next_ths, float next_scale);
-struct FusedTail;
+const char* tc_last_kernel();
+void tc_forget_last_kernel();
+int tc_conv_dispatch(TcConvParams p, cudaStream_t stream);
+bool tc_conv_covers(TcConvParams p);
 int residual_abs_sum_dispatch(float* y, const float* residual, double* sums, int N, long long per_image, cudaStream_t s);
-int quantize_int8_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C, cudaStream_t stream);
-int quantize_int8_padded_dispatch(const float* x, const float* ths, int8_t* qx8, int bits, int N, int H, int W, int C,
-                                  int KH, int KW, int p1, int p2, int s1, int s2, cudaStream_t stream);
-int conv_int8_padded_dispatch(const int8_t* qx8p, const int8_t* w8, float* y, int p1, int p2, int s1, int s2, int N, int H, int W, int C,
-                              int KN, int KH, int KW, cudaStream_t stream, const float* residual, double* abs_sums);
-int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream);
-int conv_int8_dispatch(const int8_t* qx8, const int8_t* w8, float* y, int binary_act, int p1, int p2, int s1, int s2,
-                       int N, int H, int W, int C, int KN, int KH, int KW, cudaStream_t stream,
-                       const float* residual, double* abs_sums, const FusedTail* tail);
-static int g_conv_path = TAB_PATH_AUTO;
 
 static bool dims_ok(int N, int H, int W, int C) { return N >= 0 && H >= 0 && W >= 0 && C >= 1; }
+static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+static bool misaligned(const void* p, uintptr_t mask) { return (reinterpret_cast<uintptr_t>(p) & mask) != 0; }
+
+static size_t bits_bytes(int type, int N, int H, int W, int C) {
+    return round256((size_t)N * H * W * packed_channels(C) * act_bits(type) * 8);
+}
+static size_t w8_bytes(int C, int KN, int KH, int KW) { return round256((size_t)KN * KH * KW * packed_channels(C) * 64); }
+
+static int conv_args_ok(int type, int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW) {
+    if (type < 0 || type > 3) return TAB_E_BAD_ARGUMENT;
+    if (!dims_ok(N, H, W, C) || KN < 0 || KH < 1 || KW < 1 || p1 < 0 || p2 < 0 || s1 < 1 || s2 < 1) return TAB_E_BAD_ARGUMENT;
+    return TAB_OK;
+}
+
+// Geometry part of the tensor-core parameter block (pointers and the tail are the caller's).
+static TcConvParams tc_geometry(int type, int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW,
+                                long long oh, long long ow) {
+    TcConvParams p = {};
+    p.N = N; p.H = H; p.W = W; p.C = C; p.PC = packed_channels(C); p.KN = KN; p.KH = KH; p.KW = KW;
+    p.OH = (int)oh; p.OW = (int)ow; p.p1 = p1; p.p2 = p2; p.s1 = s1; p.s2 = s2;
+    const long long M = (long long)N * oh * ow, Kw = (long long)KH * KW * p.PC;
+    p.M = M < (1LL << 31) ? (int)M : 0x7FFFFFFF;
+    p.Kw = Kw < (1LL << 31) ? (int)Kw : 0x7FFFFFFF;
+    p.abits = act_bits(type);
+    p.per_image = (double)KN * (double)oh * (double)ow;
+    return p;
+}
 
 }  // namespace tab
 
@@ -47,20 +64,24 @@ const char* tab_error_string(int code) {
         case TAB_E_WORKSPACE: return "workspace too small or not 256-byte aligned";
         case TAB_E_CUDA: return "CUDA runtime error (see tab_last_cuda_error)";
         case TAB_E_TOO_LARGE: return "problem size exceeds the supported range";
-        case TAB_E_ALIGNMENT: return "pointer not aligned to its element type";
+        case TAB_E_ALIGNMENT: return "pointer not aligned as the entry point requires";
         default: return "unknown error code";
     }
 }
 
 int tab_last_cuda_error(void) { return g_last_cuda_error; }
 
-int tab_version(void) { return 100; }
+int tab_version(void) { return 200; }
+
+int tab_device_status(void) { return umma_status_read_and_clear(); }
+
+const char* tab_last_conv_kernel(void) { return tc_last_kernel(); }
 
 int tab_quantize_launch(const float* x, const float* ths, int64_t* qx, int32_t* btn,
                         int bitwidth, int N, int H, int W, int C, tab_stream_t stream) {
     if (!dims_ok(N, H, W, C) || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
     if (N == 0) return TAB_OK;
-    if (reinterpret_cast<uintptr_t>(btn) & 3) return TAB_E_ALIGNMENT;
+    if (misaligned(btn, 3)) return TAB_E_ALIGNMENT;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (btn) {
         cudaError_t e = cudaMemsetAsync(btn, 0, sizeof(int32_t) * (size_t)N, s);
@@ -68,37 +89,29 @@ int tab_quantize_launch(const float* x, const float* ths, int64_t* qx, int32_t* 
     }
     if ((long long)H * W == 0) return TAB_OK;
     if (!x || !ths || !qx) return TAB_E_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) ||
-        (reinterpret_cast<uintptr_t>(qx) & 7))
-        return TAB_E_ALIGNMENT;
+    if (misaligned(x, 3) || misaligned(ths, 3) || misaligned(qx, 7)) return TAB_E_ALIGNMENT;
     if ((long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
     const int bits = (bitwidth == 1) ? 1 : 2;                      // TAB_GEMM.cu:267,309
     return quantize_dispatch(x, ths, qx, bits == 2 ? btn : nullptr, bits, N, H, W, C, s);
 }
 
-static size_t popc_workspace_bytes(int type, int N, int H, int W, int C) {
-    const size_t words = (size_t)N * H * W * packed_channels(C) * act_bits(type);
-    return (words * 8 + 255) / 256 * 256;
-}
-
 size_t tab_conv2d_workspace_bytes(int type, int p1, int p2, int s1, int s2, int N, int H, int W, int C, int KN, int KH, int KW) {
-    if (type < 0 || type > 3 || !dims_ok(N, H, W, C) || KN < 0 || KH < 1 || KW < 1 || p1 < 0 || p2 < 0 || s1 < 1 || s2 < 1) return 0;
-    const size_t a = popc_workspace_bytes(type, N, H, W, C), b = imma_workspace_bytes(N, H, W, C, KN, KH, KW, p1, p2, s1, s2);
-    return a > b ? a : b;
+    if (conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW) != TAB_OK) return 0;
+    return bits_bytes(type, N, H, W, C) + w8_bytes(C, KN, KH, KW) + 256;
 }
 
 int tab_conv2d_set_path(int path) {
-    if (path != TAB_PATH_AUTO && path != TAB_PATH_POPCOUNT) return TAB_E_BAD_ARGUMENT;
+    if (path != TAB_PATH_AUTO && path != TAB_PATH_POPCOUNT && path != TAB_PATH_POPCOUNT_PLAIN) return TAB_E_BAD_ARGUMENT;
     const int prev = g_conv_path;
     g_conv_path = path;
     return prev;
 }
 
-static int conv_args_ok(int type, int p1, int p2, int s1, int s2, int N, int H, int W, int C,
-                        int KN, int KH, int KW) {
-    if (type < 0 || type > 3) return TAB_E_BAD_ARGUMENT;
-    if (!dims_ok(N, H, W, C) || KN < 0 || KH < 1 || KW < 1 || p1 < 0 || p2 < 0 || s1 < 1 || s2 < 1)
-        return TAB_E_BAD_ARGUMENT;
+// Validation shared by the two entry points that run the popcount kernel on packed activations.
+static int packed_checks(const int64_t* qx, const int64_t* qw, const int32_t* btn, float* y, int type) {
+    if (!qx || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
+    const uintptr_t qx_mask = act_bits(type) == 2 ? 15 : 7;        // 16-byte (sign, magnitude) pairs
+    if (misaligned(qx, qx_mask) || misaligned(qw, 7) || misaligned(y, 3) || misaligned(btn, 3)) return TAB_E_ALIGNMENT;
     return TAB_OK;
 }
 
@@ -109,13 +122,10 @@ int tab_conv2d_packed_launch(const int64_t* qx, const int64_t* qw, const int32_t
     if (rc != TAB_OK) return rc;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
-    if (!qx || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
-    const uintptr_t qx_mask = act_bits(type) == 2 ? 15 : 7;        // 16-byte (sign, magnitude) pairs
-    if ((reinterpret_cast<uintptr_t>(qx) & qx_mask) || (reinterpret_cast<uintptr_t>(qw) & 7) ||
-        (reinterpret_cast<uintptr_t>(y) & 3) || (reinterpret_cast<uintptr_t>(btn) & 3))
-        return TAB_E_ALIGNMENT;
+    rc = packed_checks(qx, qw, btn, y, type);
+    if (rc != TAB_OK) return rc;
     return conv_packed_dispatch(qx, qw, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
-                                reinterpret_cast<cudaStream_t>(stream));
+                                reinterpret_cast<cudaStream_t>(stream), g_conv_path != TAB_PATH_POPCOUNT_PLAIN);
 }
 
 static int conv2d_impl(const float* x, const int64_t* qw, const float* ths, const int32_t* btn,
@@ -127,10 +137,10 @@ static int conv2d_impl(const float* x, const int64_t* qw, const float* ths, cons
     if (rc != TAB_OK) return rc;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (next_ths && !abs_sums) return TAB_E_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(abs_sums) & 7) || (reinterpret_cast<uintptr_t>(next_ths) & 3)) return TAB_E_ALIGNMENT;
+    if (misaligned(abs_sums, 7) || misaligned(next_ths, 3)) return TAB_E_ALIGNMENT;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
-    // empty output, or any path but the tensor-core one: the sums are cleared and the thresholds finished by
-    // separate small launches (the tensor-core path folds both into its two kernels)
+    // empty output, or the popcount path: the sums are cleared and the thresholds finished by separate small launches
+    // (the tensor-core path folds both into its two kernels)
     auto clear_sums = [&]() -> int {
         if (!abs_sums || N <= 0) return TAB_OK;
         cudaError_t e = cudaMemsetAsync(abs_sums, 0, sizeof(double) * (size_t)N, s);
@@ -146,24 +156,32 @@ static int conv2d_impl(const float* x, const int64_t* qw, const float* ths, cons
     }
     if (!x || !ths || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
     const size_t need = tab_conv2d_workspace_bytes(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
-    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
-        return TAB_E_WORKSPACE;
-    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) ||
-        (reinterpret_cast<uintptr_t>(residual) & 3))
+    if (!workspace || workspace_bytes < need || misaligned(workspace, 255)) return TAB_E_WORKSPACE;
+    if (misaligned(x, 3) || misaligned(ths, 3) || misaligned(residual, 3) || misaligned(qw, 7) || misaligned(y, 3) || misaligned(btn, 3))
         return TAB_E_ALIGNMENT;
     if ((long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
-    if (g_conv_path == TAB_PATH_AUTO) {
-        if ((reinterpret_cast<uintptr_t>(qw) & 7) || (reinterpret_cast<uintptr_t>(y) & 3)) return TAB_E_ALIGNMENT;
-        const bool r8 = residual && ((reinterpret_cast<uintptr_t>(residual) & 7) == 0) && ((reinterpret_cast<uintptr_t>(y) & 7) == 0);
-        if (!residual || r8) {
-            rc = conv_imma_dispatch(x, qw, ths, y, workspace, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, s, residual, abs_sums,
-                                    next_ths, next_scale);
-            if (rc != TAB_E_TOO_LARGE) return rc;       // sizes beyond the tensor-core path: fall through
+    int64_t* qx = reinterpret_cast<int64_t*>(workspace);
+    int8_t* w8 = reinterpret_cast<int8_t*>(workspace) + bits_bytes(type, N, H, W, C);
+    unsigned* counter = reinterpret_cast<unsigned*>(w8 + w8_bytes(C, KN, KH, KW));
+    tc_forget_last_kernel();
+    if (g_conv_path == TAB_PATH_AUTO && !misaligned(y, 15) && !misaligned(residual, 15)) {
+        TcConvParams p = tc_geometry(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, oh, ow);
+        p.qx = reinterpret_cast<const uint64_t*>(qx); p.w8 = w8; p.y = y; p.residual = residual; p.abs_sums = abs_sums;
+        if (next_ths) { p.ths_out = next_ths; p.ths_scale = next_scale; p.done_counter = counter; }
+        if (tc_conv_covers(p)) {
+            // launch 1: quantise (TAB_GEMM.cu:419-426) + weight expansion + clears; launch 2: the GEMM
+            QuantExtras ex;
+            ex.zero_sums = abs_sums;
+            ex.zero_counter = next_ths ? counter : nullptr;
+            ex.qw = reinterpret_cast<const uint64_t*>(qw); ex.w8 = w8;
+            ex.words = (long long)KN * KH * KW * p.PC; ex.wbits = weight_bits(type); ex.PC = p.PC; ex.C = C;
+            rc = quantize_dispatch(x, ths, qx, nullptr, act_bits(type), N, H, W, C, s, &ex);
+            if (rc != TAB_OK) return rc;
+            return tc_conv_dispatch(p, s);
         }
     }
     rc = clear_sums();
     if (rc != TAB_OK) return rc;
-    int64_t* qx = reinterpret_cast<int64_t*>(workspace);
     rc = quantize_dispatch(x, ths, qx, nullptr, act_bits(type), N, H, W, C, s);   // TAB_GEMM.cu:419-426
     if (rc != TAB_OK) return rc;
     rc = tab_conv2d_packed_launch(qx, qw, btn, y, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream);
@@ -200,75 +218,43 @@ int tab_conv2d_chain_launch(const float* x, const int64_t* qw, const float* ths,
                        residual, abs_sums, next_ths, next_scale, stream);
 }
 
-int tab_quantize_int8_launch(const float* x, const float* ths, int8_t* qx8, int bitwidth,
-                             int N, int H, int W, int C, tab_stream_t stream) {
-    if (!dims_ok(N, H, W, C) || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
-    if ((long long)N * H * W == 0) return TAB_OK;
-    if (!x || !ths || !qx8) return TAB_E_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) || (reinterpret_cast<uintptr_t>(qx8) & 15))
-        return TAB_E_ALIGNMENT;
-    return quantize_int8_dispatch(x, ths, qx8, bitwidth == 1 ? 1 : 2, N, H, W, C, reinterpret_cast<cudaStream_t>(stream));
-}
-
 int tab_expand_weights_launch(const int64_t* qw, int8_t* w8, int bitwidth, int KN, int KH, int KW, int C, tab_stream_t stream) {
     if (KN < 0 || KH < 1 || KW < 1 || C < 1 || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
     if (KN == 0) return TAB_OK;
     if (!qw || !w8) return TAB_E_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(qw) & 7) || (reinterpret_cast<uintptr_t>(w8) & 15)) return TAB_E_ALIGNMENT;
+    if (misaligned(qw, 7) || misaligned(w8, 15)) return TAB_E_ALIGNMENT;
     return expand_weights_dispatch(qw, w8, bitwidth == 1 ? 1 : 2, KN, KH, KW, C, reinterpret_cast<cudaStream_t>(stream));
 }
 
-int tab_conv2d_int8_launch(const int8_t* qx8, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
-                           int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
+size_t tab_conv2d_state_bytes(int N) { return N < 0 ? 0 : round256((size_t)N * 8 + 8); }
+
+int tab_conv2d_bits_launch(const int64_t* qx, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
+                           int N, int H, int W, int C, int KN, int KH, int KW,
+                           const float* residual, void* state, float* next_ths, float next_scale, tab_stream_t stream) {
     int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
     if (rc != TAB_OK) return rc;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
-    if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
-    if (!qx8 || !w8 || !y) return TAB_E_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(qx8) & 15) || (reinterpret_cast<uintptr_t>(w8) & 15) || (reinterpret_cast<uintptr_t>(y) & 3))
+    if (next_ths && !state) return TAB_E_NULL_POINTER;
+    if (N == 0) return TAB_OK;
+    if (KN == 0 || oh <= 0 || ow <= 0) {                            // empty output: mean |y| of nothing is 0
+        if (next_ths) {
+            cudaError_t e = cudaMemsetAsync(next_ths, 0, sizeof(float) * (size_t)N, reinterpret_cast<cudaStream_t>(stream));
+            if (e != cudaSuccess) return record_cuda_error(e);
+        }
+        return TAB_OK;
+    }
+    if (!qx || !w8 || !y) return TAB_E_NULL_POINTER;
+    if (misaligned(qx, 15) || misaligned(w8, 15) || misaligned(y, 15) || misaligned(residual, 15) || misaligned(state, 7) || misaligned(next_ths, 3))
         return TAB_E_ALIGNMENT;
-    return conv_int8_dispatch(qx8, w8, y, act_bits(type) == 1, p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
-                              reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr);
+    TcConvParams p = tc_geometry(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, oh, ow);
+    p.qx = reinterpret_cast<const uint64_t*>(qx); p.w8 = w8; p.y = y; p.residual = residual;
+    if (next_ths) {
+        p.abs_sums = reinterpret_cast<double*>(state);
+        p.done_counter = reinterpret_cast<unsigned*>(reinterpret_cast<double*>(state) + N);
+        p.ths_out = next_ths; p.ths_scale = next_scale; p.self_clean = 1;
+    }
+    tc_forget_last_kernel();
+    return tc_conv_dispatch(p, reinterpret_cast<cudaStream_t>(stream));
 }
-
-int tab_quantize_int8_padded_launch(const float* x, const float* ths, int8_t* qx8p, int bitwidth,
-                                    int N, int H, int W, int C, int KH, int KW, int p1, int p2, int s1, int s2,
-                                    tab_stream_t stream) {
-    if (!dims_ok(N, H, W, C) || bitwidth < 1 || p1 < 0 || p2 < 0 || s1 < 1 || s2 < 1 || KH < 1 || KW < 1) return TAB_E_BAD_ARGUMENT;
-    if ((long long)N * (H + 2LL * p1) * (W + 2LL * p2) == 0) return TAB_OK;
-    if (!x || !ths || !qx8p) return TAB_E_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) || (reinterpret_cast<uintptr_t>(qx8p) & 15))
-        return TAB_E_ALIGNMENT;
-    return quantize_int8_padded_dispatch(x, ths, qx8p, bitwidth == 1 ? 1 : 2, N, H, W, C, KH, KW, p1, p2, s1, s2,
-                                         reinterpret_cast<cudaStream_t>(stream));
-}
-
-int tab_conv2d_int8_padded_launch(const int8_t* qx8p, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
-                                  int N, int H, int W, int C, int KN, int KH, int KW, tab_stream_t stream) {
-    int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
-    if (rc != TAB_OK) return rc;
-    const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
-    if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
-    if (!qx8p || !w8 || !y) return TAB_E_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(qx8p) & 15) || (reinterpret_cast<uintptr_t>(w8) & 15) || (reinterpret_cast<uintptr_t>(y) & 3))
-        return TAB_E_ALIGNMENT;
-    return conv_int8_padded_dispatch(qx8p, w8, y, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, reinterpret_cast<cudaStream_t>(stream),
-                                     nullptr, nullptr);
-}
-
-/* Test/benchmark hook: GEMM variant of the tensor-core path: 0 = default, 1 = mma.sync + im2col staging,
-   2 = mma.sync (patch or im2col staging), 3 = tcgen05. */
-void tab_debug_set_imma_variant(int v) { imma_set_variant(v); }
-/* Test hook: code of the last expired wait in the tcgen05 kernel on this device (0 = none); clears it. */
-int tab_debug_umma_status(void) { return umma_status_read_and_clear(); }
-
-/* Test/benchmark hook: 1 = carry-save popcount tree (default), 0 = one POPC per word. */
-void tab_debug_set_csa(int on) { conv_set_csa(on != 0); }
 
 }  // extern "C"
-
-#ifdef TAB_PERSIST_PROFILE
-namespace tab { int persist_profile_read(unsigned long long* out16); void persist_set_debug(int v); }
-extern "C" void tab_debug_persist_set(int v) { tab::persist_set_debug(v); }
-extern "C" int tab_debug_persist_profile(unsigned long long* out16) { return tab::persist_profile_read(out16); }
-#endif

@@ -30,7 +30,7 @@ residual_abs_sum_kernel(float* __restrict__ y, const float* __restrict__ r, doub
                 v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
                 y4[i] = v;
             }
-            acc += (double)(fabsf(v.x) + fabsf(v.y)) + (double)(fabsf(v.z) + fabsf(v.w));
+            acc += ((double)fabsf(v.x) + (double)fabsf(v.y)) + ((double)fabsf(v.z) + (double)fabsf(v.w));
         }
     } else {
         for (long long i = (long long)blockIdx.x * RTHREADS + threadIdx.x; i < per_image; i += stride) {

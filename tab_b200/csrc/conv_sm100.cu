@@ -365,12 +365,9 @@ static int launch_conv(const ConvParams& p, cudaStream_t stream) {
     return check_launch();
 }
 
-static bool g_use_csa = true;
-void conv_set_csa(bool on) { g_use_csa = on; }
-
 int conv_packed_dispatch(const int64_t* qx, const int64_t* qw, const int32_t* btn, float* y, int type,
                          int p1, int p2, int s1, int s2, int N, int H, int W, int C,
-                         int KN, int KH, int KW, cudaStream_t stream) {
+                         int KN, int KH, int KW, cudaStream_t stream, bool use_csa) {
     ConvParams p;
     p.qx = reinterpret_cast<const uint64_t*>(qx);
     p.qw = reinterpret_cast<const uint64_t*>(qw);
@@ -390,12 +387,11 @@ int conv_packed_dispatch(const int64_t* qx, const int64_t* qw, const int32_t* bt
     p.OH = (int)oh; p.OW = (int)ow; p.M = (int)M; p.Kw = (int)Kw; p.NUM = KH * KW * C;
     p.qw16 = (reinterpret_cast<uintptr_t>(qw) & 15) == 0;
     for (int i = 0; i < 5; i++) { p.wpos[i] = 1 << i; p.wneg[i] = -(2 << i); }
-    const bool csa = g_use_csa;
     switch (type) {
-        case 0: return csa ? launch_conv<0, true>(p, stream) : launch_conv<0, false>(p, stream);
-        case 1: return csa ? launch_conv<1, true>(p, stream) : launch_conv<1, false>(p, stream);
-        case 2: return csa ? launch_conv<2, true>(p, stream) : launch_conv<2, false>(p, stream);
-        case 3: return csa ? launch_conv<3, true>(p, stream) : launch_conv<3, false>(p, stream);
+        case 0: return use_csa ? launch_conv<0, true>(p, stream) : launch_conv<0, false>(p, stream);
+        case 1: return use_csa ? launch_conv<1, true>(p, stream) : launch_conv<1, false>(p, stream);
+        case 2: return use_csa ? launch_conv<2, true>(p, stream) : launch_conv<2, false>(p, stream);
+        case 3: return use_csa ? launch_conv<3, true>(p, stream) : launch_conv<3, false>(p, stream);
         default: return TAB_E_BAD_ARGUMENT;
     }
 }

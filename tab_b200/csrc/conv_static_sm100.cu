@@ -8,7 +8,9 @@
 // forbidden because they synchronise the device.  tab_conv2d_launch needs scratch for the bit-packed
 // activations; this entry point keeps that scratch inside the library image instead, as a fixed
 // array in device global memory that exists from the moment the library is loaded on a GPU until the
-// process exits.  The price is a hard size limit and no concurrency (see below).
+// process exits.  The price is a hard size limit, no concurrency (see below) and the slower of the two compute
+// paths: this entry point always runs the bit-packed LOP3/POPC kernel, because the tensor-core path also needs the
+// weights expanded to bytes, which a modest fixed array cannot hold.
 #include <mutex>
 #include "tab_kernels.cuh"
 
@@ -53,11 +55,18 @@ extern "C" int tab_conv2d_static_launch(const float* x, const int64_t* qw, const
         return TAB_E_BAD_ARGUMENT;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (N == 0 || KN == 0 || oh <= 0 || ow <= 0) return TAB_OK;
-    // packed activations: N*H*W*ceil(C/64) words per plane, 2 planes for types 0,1 and 1 for types 2,3
-    const unsigned long long need = (unsigned long long)N * H * W * packed_channels(C) * act_bits(type) * 8ULL;
-    if (need > (unsigned long long)TAB_STATIC_SCRATCH_BYTES || (long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
+    // packed activations: N*H*W*ceil(C/64) words per plane, 2 planes for types 0,1 and 1 for types 2,3.  The size is
+    // bounded factor by factor, so that no product of unchecked ints can wrap around before it is compared.
+    const unsigned long long cap_words = (unsigned long long)TAB_STATIC_SCRATCH_BYTES / 8ULL;
+    const unsigned long long pixels = (unsigned long long)H * (unsigned long long)W;      // both < 2^31: no overflow
+    if (pixels >= (1ULL << 31) || pixels > cap_words) return TAB_E_TOO_LARGE;
+    const unsigned long long per_image = pixels * (unsigned long long)packed_channels(C) * (unsigned long long)act_bits(type);   // < 2^59
+    if (per_image > cap_words || (unsigned long long)N > cap_words / per_image) return TAB_E_TOO_LARGE;
     if (!x || !ths || !qw || !y || (type == 2 && !btn)) return TAB_E_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3)) return TAB_E_ALIGNMENT;
+    // same alignment rules as tab_conv2d_launch: nothing misaligned may reach a kernel
+    if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(ths) & 3) || (reinterpret_cast<uintptr_t>(qw) & 7) ||
+        (reinterpret_cast<uintptr_t>(y) & 3) || (reinterpret_cast<uintptr_t>(btn) & 3))
+        return TAB_E_ALIGNMENT;
     void* scratch = nullptr;
     int rc = static_scratch_for_current_device(&scratch);
     if (rc != TAB_OK) return rc;

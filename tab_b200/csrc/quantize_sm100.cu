@@ -13,6 +13,10 @@
 // by that instruction's pipe at 37 % of DRAM bandwidth).
 // General path (any C, any alignment): one warp per word, two coalesced 32-bit loads per lane, the
 // two 32-bit halves come straight out of __ballot_sync.
+//
+// Inside a convolution call the same launch also does the call's small set-up jobs (QuantExtras), so that they cost no
+// launch of their own: all CTAs share the expansion of the packed weights to the bytes the tensor-core kernel
+// multiplies, and the first CTA of every image clears that image's |y| sum (the first of all the completion counter).
 #include "tab_kernels.cuh"
 
 namespace tab {
@@ -22,6 +26,63 @@ constexpr int QUNROLL = 4;                                   // independent 256-
 constexpr int QWORDS_PER_ITER = (QTHREADS / 8) * QUNROLL;    // 128 words = 32 KB of fp32 per CTA step
 
 struct f8 { float v[8]; };
+
+// One thread per (filter, word k, 16-channel group) of packed weights [KN][KH*KW*PC][WB]: 16 bytes of {-1,0,+1}
+// into [KN][KH*KW*PC][64]; channels beyond C become 0.
+template <int WB>
+__device__ __forceinline__ void expand_group(const uint64_t* __restrict__ qw, int8_t* __restrict__ w8, long long idx, int PC, int C) {
+    const long long word = idx >> 2;
+    const int grp = (int)(idx & 3);
+    const int pc = (int)(word % PC);
+    const int cbase = pc * 64 + grp * 16;
+    uint32_t s16, m16;
+    if (WB == 2) {
+        m16 = (uint32_t)(qw[word * 2 + 1] >> (grp * 16)) & 0xFFFFu;
+        s16 = (uint32_t)(qw[word * 2] >> (grp * 16)) & m16;
+    } else {
+        s16 = (uint32_t)(qw[word] >> (grp * 16)) & 0xFFFFu;     // bit = 1 means -1
+        m16 = 0xFFFFu;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        uint32_t r = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int i = 4 * w + b;
+            int v = ((m16 >> i) & 1u) ? (((s16 >> i) & 1u) ? -1 : 1) : 0;
+            if (cbase + i >= C) v = 0;
+            r |= (uint32_t)(v & 0xFF) << (8 * b);
+        }
+        o[w] = r;
+    }
+    *reinterpret_cast<uint4*>(w8 + word * 64 + grp * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <int WB>
+__global__ void expand_weights_kernel(const uint64_t* __restrict__ qw, int8_t* __restrict__ w8, long long words, int PC, int C) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= words * 4) return;
+    expand_group<WB>(qw, w8, idx, PC, C);
+}
+
+// Runs at the top of both quantiser kernels.  Programmatic launch: nothing is read or written before the previous
+// kernel of the stream (which produced x and the thresholds, and may still be reading the scratch this launch
+// overwrites) has completed.
+__device__ __forceinline__ void quant_prologue(const QuantExtras& ex, int n) {
+    pdl_wait();
+    if (ex.qw != nullptr) {                                                // the weights, spread over all CTAs of the launch
+        const long long stride = (long long)gridDim.x * gridDim.y * blockDim.x;
+        for (long long idx = ((long long)blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x; idx < ex.words * 4; idx += stride) {
+            if (ex.wbits == 2) expand_group<2>(ex.qw, ex.w8, idx, ex.PC, ex.C);
+            else expand_group<1>(ex.qw, ex.w8, idx, ex.PC, ex.C);
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        if (ex.zero_sums) ex.zero_sums[n] = 0.0;
+        if (n == 0 && ex.zero_counter) *ex.zero_counter = 0u;
+    }
+}
 
 // 256-bit streaming load (sm_100): a lane reads 8 consecutive channels, a warp 1 KB contiguous.
 __device__ __forceinline__ f8 ld_stream_f8(const float* p) {
@@ -38,8 +99,9 @@ __device__ __forceinline__ f8 ld_stream_f8(const float* p) {
 template <int BITS>
 __global__ void __launch_bounds__(QTHREADS)
 quantize_c64_kernel(const float* __restrict__ x, const float* __restrict__ ths,
-                    uint64_t* __restrict__ qx, int* __restrict__ btn, long long words_per_image) {
+                    uint64_t* __restrict__ qx, int* __restrict__ btn, long long words_per_image, const QuantExtras ex) {
     const int n = blockIdx.y;
+    quant_prologue(ex, n);
     const float t = __ldg(ths + n);
     const float nt = -t;
     const int byte = threadIdx.x & 7;
@@ -94,6 +156,7 @@ quantize_c64_kernel(const float* __restrict__ x, const float* __restrict__ ths,
             if (tot) atomicAdd(btn + n, tot);                 // integer: order-independent, exact
         }
     }
+    pdl_launch_dependents();                                  // the next kernel may be scheduled once every CTA got here
 }
 
 // One warp per output word; works for every C and alignment.  grid = (ctas_per_image, N).
@@ -101,8 +164,9 @@ template <int BITS>
 __global__ void __launch_bounds__(QTHREADS)
 quantize_generic_kernel(const float* __restrict__ x, const float* __restrict__ ths,
                         uint64_t* __restrict__ qx, int* __restrict__ btn,
-                        long long pixels_per_image, int C, int PC) {
+                        long long pixels_per_image, int C, int PC, const QuantExtras ex) {
     const int n = blockIdx.y;
+    quant_prologue(ex, n);
     const float t = __ldg(ths + n);
     const float nt = -t;
     const int lane = threadIdx.x & 31;
@@ -139,10 +203,12 @@ quantize_generic_kernel(const float* __restrict__ x, const float* __restrict__ t
         }
     }
     if (BITS == 2 && btn != nullptr && lane == 0 && cnt) atomicAdd(btn + n, cnt);
+    pdl_launch_dependents();
 }
 
 int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* btn, int bits,
-                      int N, int H, int W, int C, cudaStream_t stream) {
+                      int N, int H, int W, int C, cudaStream_t stream, const QuantExtras* extras) {
+    const QuantExtras ex = extras ? *extras : QuantExtras{};
     const long long pixels = (long long)H * W;
     const int PC = (C + 63) / 64;
     const long long wpi = pixels * PC;
@@ -153,7 +219,7 @@ int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* bt
             const int nn = (N - n0 < 65535) ? (N - n0) : 65535;
             int rc = quantize_dispatch(x + (long long)n0 * pixels * C, ths + n0,
                                        qx + (long long)n0 * wpi * bits, btn ? btn + n0 : nullptr,
-                                       bits, nn, H, W, C, stream);
+                                       bits, nn, H, W, C, stream, n0 == 0 ? extras : nullptr);
             if (rc != TAB_OK) return rc;
         }
         return TAB_OK;
@@ -171,8 +237,8 @@ int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* bt
             if (per_image > steps) per_image = steps;
         }
         dim3 grid((unsigned)per_image, (unsigned)N);
-        if (bits == 2) quantize_c64_kernel<2><<<grid, QTHREADS, 0, stream>>>(x, ths, q, btn, wpi);
-        else quantize_c64_kernel<1><<<grid, QTHREADS, 0, stream>>>(x, ths, q, btn, wpi);
+        if (bits == 2) return launch_pdl(quantize_c64_kernel<2>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
+        return launch_pdl(quantize_c64_kernel<1>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
     } else {
         long long steps = (wpi + (QTHREADS / 32) - 1) / (QTHREADS / 32);
         long long per_image = steps;
@@ -183,9 +249,20 @@ int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* bt
             if (per_image > steps) per_image = steps;
         }
         dim3 grid((unsigned)per_image, (unsigned)N);
-        if (bits == 2) quantize_generic_kernel<2><<<grid, QTHREADS, 0, stream>>>(x, ths, q, btn, pixels, C, PC);
-        else quantize_generic_kernel<1><<<grid, QTHREADS, 0, stream>>>(x, ths, q, btn, pixels, C, PC);
+        if (bits == 2) return launch_pdl(quantize_generic_kernel<2>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
+        return launch_pdl(quantize_generic_kernel<1>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
     }
+}
+
+int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream) {
+    const int PC = packed_channels(C);
+    const long long words = (long long)KN * KH * KW * PC;
+    if (words == 0) return TAB_OK;
+    if (words * 4 >= (1LL << 31) * 256) return TAB_E_TOO_LARGE;
+    const unsigned blocks = (unsigned)((words * 4 + 255) / 256);
+    const uint64_t* q = reinterpret_cast<const uint64_t*>(qw);
+    if (wbits == 2) expand_weights_kernel<2><<<blocks, 256, 0, stream>>>(q, w8, words, PC, C);
+    else expand_weights_kernel<1><<<blocks, 256, 0, stream>>>(q, w8, words, PC, C);
     return check_launch();
 }
 

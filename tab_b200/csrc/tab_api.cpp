@@ -125,8 +125,75 @@ std::vector<torch::Tensor> TAB_Conv2dFused(torch::Tensor X, torch::Tensor QW, to
     return {Y, next};
 }
 
+// Extensions for callers that keep prepared weights (tab_b200.nn.TABConv2d and the like): the stages of Conv2d on their own.
+// ExpandWeights: packed weights -> int8 {KN,KH,KW,Cp}.
+torch::Tensor TAB_ExpandWeights(torch::Tensor QW, int bitwidth, int KN, int KH, int KW, int C) {
+    CHECK_INPUT(QW);
+    TORCH_CHECK(QW.scalar_type() == torch::kInt64, "QW must have dtype torch.int64");
+    TORCH_CHECK(KN >= 0 && KH >= 1 && KW >= 1 && C >= 1 && bitwidth >= 1, "ExpandWeights: invalid size or bitwidth");
+    const int PC = (C + 63) / 64, bits = bitwidth == 1 ? 1 : 2;
+    TORCH_CHECK(QW.numel() == (int64_t)KN * KH * KW * PC * bits, "QW has ", QW.numel(), " words, expected ", (int64_t)KN * KH * KW * PC * bits);
+    const c10::cuda::CUDAGuard guard(QW.device());
+    auto W8 = torch::empty({KN, KH, KW, PC * 64}, torch::device(QW.device()).dtype(torch::kInt8));
+    check_rc(tab_expand_weights_launch(QW.data_ptr<int64_t>(), W8.data_ptr<int8_t>(), bits, KN, KH, KW, C, current_stream()),
+             "tab_expand_weights_launch");
+    return W8;
+}
+
+// NewState: the zeroed block Conv2dBits needs when it is asked for thresholds.
+torch::Tensor TAB_NewState(torch::Tensor like, int N) {
+    CHECK_CUDA(like);
+    return torch::zeros({(int64_t)std::max<size_t>(tab_conv2d_state_bytes(N), 8)}, torch::device(like.device()).dtype(torch::kUInt8));
+}
+
+// Conv2dBits: the GEMM stage of Conv2d on activations Quantize wrote (bitwidth 2 for types 0,1; 1 for types 2,3) and
+// weights from ExpandWeights; residual / state may be None; threshold_scale <= 0 skips the thresholds.
+// Returns {Y, next_thresholds (empty when skipped)}.
+std::vector<torch::Tensor> TAB_Conv2dBits(torch::Tensor QX, torch::Tensor W8, int type,
+                                          int padding1, int padding2, int stride1, int stride2,
+                                          int N, int H, int W, int C, int KN, int KH, int KW,
+                                          c10::optional<torch::Tensor> residual, c10::optional<torch::Tensor> state, double threshold_scale) {
+    CHECK_INPUT(QX);
+    CHECK_INPUT(W8);
+    TORCH_CHECK(QX.scalar_type() == torch::kInt64, "QX must have dtype torch.int64");
+    TORCH_CHECK(W8.scalar_type() == torch::kInt8, "W8 must have dtype torch.int8");
+    TORCH_CHECK(type >= 0 && type <= 3, "type must be 0 (TNN), 1 (TBN), 2 (BTN) or 3 (BNN)");
+    TORCH_CHECK(N >= 0 && H >= 0 && W >= 0 && KN >= 0 && C >= 1 && KH >= 1 && KW >= 1 && padding1 >= 0 && padding2 >= 0 &&
+                stride1 >= 1 && stride2 >= 1, "Conv2d: invalid size, padding or stride");
+    const int PC = (C + 63) / 64, ab = (type == 2 || type == 3) ? 1 : 2;
+    TORCH_CHECK(QX.numel() == (int64_t)N * H * W * PC * ab, "QX has ", QX.numel(), " words, type ", type, " needs ", (int64_t)N * H * W * PC * ab);
+    TORCH_CHECK(W8.numel() == (int64_t)KN * KH * KW * PC * 64, "W8 has ", W8.numel(), " bytes, expected KN*KH*KW*Cp = ", (int64_t)KN * KH * KW * PC * 64);
+    const c10::cuda::CUDAGuard guard(QX.device());
+    const int64_t OH = std::max<int64_t>(((int64_t)H + 2 * padding1 - KH + 1) / stride1, 0);
+    const int64_t OW = std::max<int64_t>(((int64_t)W + 2 * padding2 - KW + 1) / stride2, 0);
+    const float* rptr = nullptr;
+    if (residual.has_value() && residual->defined()) {
+        CHECK_INPUT((*residual));
+        TORCH_CHECK(residual->scalar_type() == torch::kFloat32 && residual->numel() == (int64_t)N * KN * OH * OW, "residual must be float32 with N*KN*OH*OW elements");
+        rptr = residual->data_ptr<float>();
+    }
+    const bool want = threshold_scale > 0;
+    void* sptr = nullptr;
+    if (want) {
+        TORCH_CHECK(state.has_value() && state->defined(), "threshold_scale needs a state block (NewState)");
+        CHECK_INPUT((*state));
+        TORCH_CHECK((size_t)state->numel() * state->element_size() >= tab_conv2d_state_bytes(N), "state block too small");
+        sptr = state->data_ptr();
+    }
+    auto Y = torch::empty({N, KN, OH, OW}, torch::device(QX.device()).dtype(torch::kFloat32));
+    auto next = torch::empty({want ? N : 0}, torch::device(QX.device()).dtype(torch::kFloat32));
+    check_rc(tab_conv2d_bits_launch(QX.data_ptr<int64_t>(), W8.data_ptr<int8_t>(), Y.data_ptr<float>(), type, padding1, padding2, stride1, stride2,
+                                    N, H, W, C, KN, KH, KW, rptr, sptr, (want && N > 0) ? next.data_ptr<float>() : nullptr, (float)threshold_scale,
+                                    current_stream()),
+             "tab_conv2d_bits_launch");
+    return {Y, next};
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("Conv2dFused", &TAB_Conv2dFused, "Conv2d + residual + next-layer thresholds (extension)");
+    m.def("ExpandWeights", &TAB_ExpandWeights, "Packed weights -> int8 for the tensor-core GEMM stage (extension)");
+    m.def("NewState", &TAB_NewState, "Zeroed state block for Conv2dBits thresholds (extension)");
+    m.def("Conv2dBits", &TAB_Conv2dBits, "GEMM stage of Conv2d on Quantize's bit-planes and ExpandWeights' bytes (extension)");
     m.def("Quantize", &TAB_Quantize, "Ternarization or binarization of fp32 data in NHWC format");
     m.def("Conv2d", &TAB_Conv2d, "Conv2d of all TAB series CNNs (0 TNN, 1 TBN, 2 BTN, 3 BNN)");
     m.def("TAB_Quantize", &TAB_Quantize, "Alias of Quantize");

@@ -41,13 +41,24 @@ inline int packed_channels(int C) { return (C + 63) / 64; }
 inline int act_bits(int type) { return (type == 2 || type == 3) ? 1 : 2; }      // TAB_GEMM.cu:367-372
 inline int weight_bits(int type) { return (type == 1 || type == 3) ? 1 : 2; }   // TAB_GEMM.cu:374-379
 
+// Small jobs a quantiser launch does on the side for the convolution that follows it (all optional).
+struct QuantExtras {
+    double* zero_sums = nullptr;         // [N]: cleared
+    unsigned* zero_counter = nullptr;    // cleared
+    const uint64_t* qw = nullptr;        // packed weights [KN][KH*KW*PC][wbits] to expand into w8 [KN][KH*KW*PC][64]
+    int8_t* w8 = nullptr;
+    long long words = 0;                 // KN*KH*KW*PC
+    int wbits = 2, PC = 1, C = 64;       // of the weights
+};
+
 // quantize_sm100.cu: bits is 1 or 2; btn may be null; btn must already be zero.
 int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* btn, int bits,
-                      int N, int H, int W, int C, cudaStream_t stream);
+                      int N, int H, int W, int C, cudaStream_t stream, const QuantExtras* extras = nullptr);
+int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream);
 
-// conv_sm100.cu: implicit-im2col popcount GEMM on packed activations.
+// conv_sm100.cu: implicit-im2col popcount GEMM on packed activations.  csa: carry-save popcount tree (else one POPC per word).
 int conv_packed_dispatch(const int64_t* qx, const int64_t* qw, const int32_t* btn, float* y, int type,
                          int p1, int p2, int s1, int s2, int N, int H, int W, int C,
-                         int KN, int KH, int KW, cudaStream_t stream);
+                         int KN, int KH, int KW, cudaStream_t stream, bool csa = true);
 
 }  // namespace tab

@@ -147,23 +147,10 @@ def residual_threshold(Y, residual=None, scale=0.7):
     return ths
 
 
-# ---- stages of the tensor-core path (byte operands), for callers that cache expanded weights -------------
-
-def quantize_int8(X, thresholds, bitwidth, N, H, W, C):
-    """fp32 NHWC -> int8 ``{N,H,W,Cp}`` holding the quantised values, ``Cp = 64*ceil(C/64)`` (padding 0)."""
-    _check_input(X, "X", torch.float32)
-    _check_input(thresholds, "thresholds", torch.float32)
-    Cp = (int(C) + 63) // 64 * 64
-    with torch.cuda.device(X.device):
-        q = torch.empty((N, H, W, Cp), dtype=torch.int8, device=X.device)
-        rc = _cabi.lib().tab_quantize_int8_launch(X.data_ptr(), thresholds.data_ptr(), q.data_ptr(), int(bitwidth),
-                                                  N, H, W, C, _stream_ptr(X.device))
-    _cabi.check(rc, "tab_quantize_int8_launch")
-    return q
-
+# ---- stages of the tensor-core path, for callers that keep prepared weights -----------------------------------
 
 def expand_weights(QW, bitwidth, KN, KH, KW, C):
-    """Packed weights (``Quantize`` output) -> int8 ``{KN,KH,KW,Cp}``."""
+    """Packed weights (``Quantize`` output) -> int8 ``{KN,KH,KW,Cp}`` holding {-1,0,+1}, ``Cp = 64*ceil(C/64)``."""
     _check_input(QW, "QW", torch.int64)
     Cp = (int(C) + 63) // 64 * 64
     bits = 1 if int(bitwidth) == 1 else 2
@@ -176,62 +163,48 @@ def expand_weights(QW, bitwidth, KN, KH, KW, C):
     return w8
 
 
-def conv2d_int8(QX8, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW):
-    """The GEMM stage on byte operands; same output as ``Conv2d``."""
-    _check_input(QX8, "QX8", torch.int8)
+def new_state(N, device):
+    """Zeroed state block for ``conv2d_bits(..., threshold_scale=...)``; one block serves any number of calls that are
+    ordered on a stream (every call leaves it zeroed)."""
+    return torch.zeros((max(_cabi.lib().tab_conv2d_state_bytes(int(N)), 8),), dtype=torch.uint8, device=device)
+
+
+def conv2d_bits(QX, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW,
+                residual=None, threshold_scale=None, state=None):
+    """The GEMM stage on the tensor cores: activations as ``Quantize`` wrote them (bitwidth 2 for types 0,1; 1 for
+    types 2,3), weights from ``expand_weights``.  Returns ``(Y, next_thresholds_or_None)``; ``Y = conv + residual``.
+    ``threshold_scale`` needs ``state`` (``new_state``).  Raises ``TabError`` (TAB_E_TOO_LARGE) for shapes the
+    tensor-core kernel does not cover."""
+    _check_input(QX, "QX", torch.int64)
     _check_input(W8, "W8", torch.int8)
-    Cp = (int(C) + 63) // 64 * 64
-    if QX8.numel() != N * H * W * Cp or W8.numel() != KN * KH * KW * Cp:
-        raise RuntimeError("byte operands must be [N,H,W,Cp] and [KN,KH,KW,Cp] with Cp = %d" % Cp)
-    OH, OW = conv_out_size(H, W, KH, KW, int(padding1), int(padding2), int(stride1), int(stride2))
-    with torch.cuda.device(QX8.device):
-        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=QX8.device)
-        rc = _cabi.lib().tab_conv2d_int8_launch(QX8.data_ptr(), W8.data_ptr(), Y.data_ptr(), int(type), int(padding1), int(padding2),
-                                                int(stride1), int(stride2), N, H, W, C, KN, KH, KW, _stream_ptr(QX8.device))
-    _cabi.check(rc, "tab_conv2d_int8_launch")
-    return Y
-
-
-def plane_layout(H, W, KH, KW, padding1, padding2, stride1, stride2):
-    """``(A*B, PH2, PW2)`` of the padded plane layout (``include/tab_b200.h``): planes, rows and columns per plane."""
-    A, B = min(int(stride1), int(KH)), min(int(stride2), int(KW))
-    return A * B, -(-(H + 2 * int(padding1)) // int(stride1)), -(-(W + 2 * int(padding2)) // int(stride2))
-
-
-def quantize_int8_padded(X, thresholds, bitwidth, N, H, W, C, KH, KW, padding1, padding2, stride1=1, stride2=1):
-    """fp32 NHWC -> int8 ``{A*B, N, PH2, PW2, Cp}``: quantised values with the convolution's padding written in (0 for
-    ternary, +1 for binary activations in the real channels), split into the parity planes of the stride (one plane,
-    the padded image, for stride 1)."""
-    _check_input(X, "X", torch.float32)
-    _check_input(thresholds, "thresholds", torch.float32)
-    Cp = (int(C) + 63) // 64 * 64
-    planes, PH2, PW2 = plane_layout(H, W, KH, KW, padding1, padding2, stride1, stride2)
-    with torch.cuda.device(X.device):
-        q = torch.empty((planes, N, PH2, PW2, Cp), dtype=torch.int8, device=X.device)
-        rc = _cabi.lib().tab_quantize_int8_padded_launch(X.data_ptr(), thresholds.data_ptr(), q.data_ptr(), int(bitwidth),
-                                                         N, H, W, C, int(KH), int(KW), int(padding1), int(padding2),
-                                                         int(stride1), int(stride2), _stream_ptr(X.device))
-    _cabi.check(rc, "tab_quantize_int8_padded_launch")
-    return q
-
-
-def conv2d_int8_padded(QX8P, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW):
-    """The GEMM stage on padded plane-layout byte activations (``quantize_int8_padded``); same output as ``Conv2d``.
-    Raises ``TabError`` (TAB_E_TOO_LARGE) for shapes the TMA-fed kernels do not cover."""
-    _check_input(QX8P, "QX8P", torch.int8)
-    _check_input(W8, "W8", torch.int8)
-    Cp = (int(C) + 63) // 64 * 64
+    conv_type = int(type)
     p1, p2, s1, s2 = int(padding1), int(padding2), int(stride1), int(stride2)
-    planes, PH2, PW2 = plane_layout(H, W, KH, KW, p1, p2, s1, s2)
-    if QX8P.numel() != planes * N * PH2 * PW2 * Cp or W8.numel() != KN * KH * KW * Cp:
-        raise RuntimeError("byte operands must be [A*B,N,PH2,PW2,Cp] and [KN,KH,KW,Cp] with Cp = %d" % Cp)
+    N, H, W, C, KN, KH, KW = (int(v) for v in (N, H, W, C, KN, KH, KW))
+    PC = (C + 63) // 64
+    ab = 1 if conv_type in (2, 3) else 2
+    if QX.numel() != N * H * W * PC * ab:
+        raise RuntimeError("QX has %d words, type %d needs %d" % (QX.numel(), conv_type, N * H * W * PC * ab))
+    if W8.numel() != KN * KH * KW * PC * 64:
+        raise RuntimeError("W8 has %d bytes, expected KN*KH*KW*Cp = %d" % (W8.numel(), KN * KH * KW * PC * 64))
     OH, OW = conv_out_size(H, W, KH, KW, p1, p2, s1, s2)
-    with torch.cuda.device(QX8P.device):
-        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=QX8P.device)
-        rc = _cabi.lib().tab_conv2d_int8_padded_launch(QX8P.data_ptr(), W8.data_ptr(), Y.data_ptr(), int(type), p1, p2, s1, s2,
-                                                       N, H, W, C, KN, KH, KW, _stream_ptr(QX8P.device))
-    _cabi.check(rc, "tab_conv2d_int8_padded_launch")
-    return Y
+    if residual is not None:
+        _check_input(residual, "residual", torch.float32)
+        if residual.numel() != N * KN * OH * OW:
+            raise RuntimeError("residual has %d elements, expected %d" % (residual.numel(), N * KN * OH * OW))
+    if threshold_scale is not None and state is None:
+        raise RuntimeError("threshold_scale needs a state block (new_state)")
+    with torch.cuda.device(QX.device):
+        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=QX.device)
+        nxt = torch.empty((N,), dtype=torch.float32, device=QX.device) if threshold_scale is not None else None
+        rc = _cabi.lib().tab_conv2d_bits_launch(QX.data_ptr(), W8.data_ptr(), Y.data_ptr(), conv_type, p1, p2, s1, s2,
+                                                N, H, W, C, KN, KH, KW,
+                                                residual.data_ptr() if residual is not None else None,
+                                                state.data_ptr() if nxt is not None else None,
+                                                nxt.data_ptr() if nxt is not None else None,
+                                                float(threshold_scale) if threshold_scale is not None else 0.0,
+                                                _stream_ptr(QX.device))
+    _cabi.check(rc, "tab_conv2d_bits_launch")
+    return Y, nxt
 
 
 def Conv2dFused(X, QW, thresholds, btn, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW,

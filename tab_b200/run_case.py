@@ -3,6 +3,7 @@ profilers and quick measurements).
 
     python -m tab_b200.run_case conv     --type 0 --N 64 --H 56 --C 64 --KN 64 --K 3 --stride 1 --pad 1
     python -m tab_b200.run_case packed   ...        # the popcount convolution alone on pre-packed activations
+    python -m tab_b200.run_case bits     ...        # the tensor-core GEMM stage alone (bit-planes + prepared byte weights)
     python -m tab_b200.run_case quantize --bitwidth 2 --N 256 --H 56 --C 256
 
 Prints one JSON line: milliseconds per call (CUDA events, after warm-up) and the derived TOPS or GB/s.
@@ -19,7 +20,7 @@ from . import ops
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["conv", "packed", "quantize", "probe"])
+    ap.add_argument("op", choices=["conv", "packed", "bits", "quantize", "probe"])
     ap.add_argument("--kind", type=int, default=0, help="probe: 0 POPC, 1 LOP3, 2 s8 mma.sync, 3 b1 mma and.popc, 4 b1 mma xor.popc")
     ap.add_argument("--type", type=int, default=0)
     ap.add_argument("--bitwidth", type=int, default=2)
@@ -32,12 +33,11 @@ def main():
     ap.add_argument("--pad", type=int, default=1)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
-    ap.add_argument("--gemm-variant", type=int, default=0,
-                    help="tensor-core GEMM kernel: 0 library choice, 1 mma.sync+im2col, 2 mma.sync, 3/4 tcgen05 im2col shapes, 5 tcgen05 patch")
+    ap.add_argument("--path", type=int, default=0, help="conv: 0 tensor cores, 1 popcount kernel, 2 popcount kernel, one POPC per word")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     from . import _cabi
-    _cabi.lib().tab_debug_set_imma_variant(a.gemm_variant)
+    _cabi.lib().tab_conv2d_set_path(a.path)
     torch.manual_seed(0)
     if a.op == "probe":
         import ctypes
@@ -75,7 +75,11 @@ def main():
             fn = lambda: ops.Conv2d(x, qw, ths, btn, t, p, p, s, s, N, H, W, C, KN, K, K)
         else:
             qx, _ = ops.Quantize(x, ths, 1 if t in (2, 3) else 2, N, H, W, C)
-            fn = lambda: ops.conv2d_packed(qx, qw, btn, t, p, p, s, s, N, H, W, C, KN, K, K)
+            if a.op == "bits":
+                w8 = ops.expand_weights(qw, 1 if t in (1, 3) else 2, KN, K, K, C)
+                fn = lambda: ops.conv2d_bits(qx, w8, t, p, p, s, s, N, H, W, C, KN, K, K)
+            else:
+                fn = lambda: ops.conv2d_packed(qx, qw, btn, t, p, p, s, s, N, H, W, C, KN, K, K)
     for _ in range(a.warmup):
         fn()
     torch.cuda.synchronize()
@@ -86,7 +90,8 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / a.iters
-    print(json.dumps({"op": a.op, "args": vars(a), "ms": ms, "value": work / ms / scale, "unit": unit}))
+    print(json.dumps({"op": a.op, "args": vars(a), "ms": ms, "value": work / ms / scale, "unit": unit,
+                      "kernel": _cabi.lib().tab_last_conv_kernel().decode(), "device_status": _cabi.lib().tab_device_status()}))
 
 
 if __name__ == "__main__":

@@ -58,16 +58,33 @@ def test_argument_validation_without_a_device():
 
 def test_workspace_size():
     l = _cabi.lib()
-    # the larger of: packed activations (N*H*W*PC*planes words) and byte activations + byte weights
-    # (N*H*W*PC*64 + KN*KH*KW*PC*64), each rounded up to 256 bytes
+    # bit-planes of the activations (N*H*W*PC words per plane) + byte weights (KN*KH*KW*PC*64), each rounded up to
+    # 256 bytes, + 256 bytes for the completion counter of a chained call
     r = lambda b: (b + 255) // 256 * 256
-    # (the byte activations are sized for their zero-padded form, (H+2*p1) x (W+2*p2) pixels; 256 more bytes hold
-    # the completion counter of a chained call)
-    assert l.tab_conv2d_workspace_bytes(0, 0, 0, 1, 1, 2, 5, 5, 65, 4, 3, 3) == max(r(2 * 25 * 2 * 2 * 8), r(2 * 25 * 128) + r(4 * 9 * 128) + 256)
-    assert l.tab_conv2d_workspace_bytes(3, 1, 1, 1, 1, 2, 5, 5, 65, 4, 3, 3) == r(2 * 49 * 128) + r(4 * 9 * 128) + 256
+    assert l.tab_conv2d_workspace_bytes(0, 0, 0, 1, 1, 2, 5, 5, 65, 4, 3, 3) == r(2 * 25 * 2 * 2 * 8) + r(4 * 9 * 128) + 256
+    assert l.tab_conv2d_workspace_bytes(3, 1, 1, 1, 1, 2, 5, 5, 65, 4, 3, 3) == r(2 * 25 * 2 * 1 * 8) + r(4 * 9 * 128) + 256
     assert l.tab_conv2d_workspace_bytes(9, 1, 1, 1, 1, 2, 5, 5, 65, 4, 3, 3) == 0
     assert l.tab_conv2d_workspace_bytes(0, 1, 1, 0, 1, 2, 5, 5, 65, 4, 3, 3) == 0
+    assert l.tab_conv2d_state_bytes(256) >= 256 * 8 + 4 and l.tab_conv2d_state_bytes(-1) == 0
     assert l.tab_conv2d_set_path(7) == -1
+    assert l.tab_conv2d_set_path(2) == 0 and l.tab_conv2d_set_path(0) == 2
+
+
+def test_static_entry_point_checks_before_any_launch():
+    """Return codes of tab_conv2d_static_launch that need no device: a misaligned qw, y or btn is refused like
+    tab_conv2d_launch refuses it, and sizes whose product would wrap around are refused, not wrapped."""
+    l = _cabi.lib()
+    base = 1 << 20                                                  # fake, aligned addresses: nothing dereferences them
+    geom = (0, 1, 1, 1, 1, 1, 8, 8, 64, 4, 3, 3)
+    for bad in range(5):
+        ptrs = [base, base, base, base, base]
+        ptrs[bad] += 1
+        assert l.tab_conv2d_static_launch(*ptrs, *geom, None) == -6, bad
+    big = 2 ** 31 - 1
+    assert l.tab_conv2d_static_launch(base, base, base, base, base, 0, 1, 1, 1, 1, big, big, big, big, 4, 3, 3, None) == -5
+    assert l.tab_conv2d_static_launch(base, base, base, base, base, 0, 1, 1, 1, 1, 65536, 65536, 4, 64, 4, 3, 3, None) == -5
+    assert l.tab_conv2d_bits_launch(base + 1, base, base, *geom, None, None, None, 0.0, None) == -6
+    assert l.tab_conv2d_bits_launch(base, base, base, *geom, None, None, base, 0.7, None) == -2     # thresholds need a state block
 
 
 def test_missing_library_fails_loudly(monkeypatch):

@@ -18,22 +18,18 @@ GOLD = os.path.join(os.path.dirname(__file__), "golden")
 NAMES = ["tnn", "tbn", "btn", "bnn"]
 
 
-@pytest.fixture(autouse=True, params=["tensor", "tensor-tcgen05", "tensor-tma", "tensor-mma-sync", "tensor-im2col", "popcount"])
+@pytest.fixture(autouse=True, params=["tensor", "popcount", "popcount-plain"])
 def conv_path(request):
-    """Every test of this module runs once per compute path of tab_conv2d_launch: the tensor-core GEMM with the
-    library's own choice of kernel, the same forced to the tcgen05 kernels (cp.async-fed; TMA-fed where the shape
-    allows), to the mma.sync kernels (patch or
-    im2col staging), to mma.sync with im2col staging only, and the popcount kernel.  After each test the
-    tcgen05 kernel's record of expired waits must be clean."""
+    """Every test of this module runs once per compute path of the convolution entry points: the persistent tcgen05
+    kernel (shapes it does not cover fall back to the popcount kernel inside the call), the bit-packed popcount
+    kernel with its carry-save tree, and the same with one POPC per word.  After each test the tensor-core kernel's
+    record of expired waits must be clean."""
     l = _cabi.lib()
-    l.tab_debug_umma_status.restype = int
-    prev = l.tab_conv2d_set_path(1 if request.param == "popcount" else 0)
-    l.tab_debug_set_imma_variant({"tensor-tcgen05": 3, "tensor-tma": 6, "tensor-mma-sync": 2, "tensor-im2col": 1}.get(request.param, 0))
+    prev = l.tab_conv2d_set_path({"tensor": 0, "popcount": 1, "popcount-plain": 2}[request.param])
     yield request.param
-    l.tab_debug_set_imma_variant(0)
     l.tab_conv2d_set_path(prev)
     torch.cuda.synchronize()
-    assert l.tab_debug_umma_status() == 0
+    assert l.tab_device_status() == 0
 
 
 def dev_t(a, cuda):
@@ -190,23 +186,16 @@ def test_conv_shapes(cuda, t, geom):
 
 
 @pytest.mark.parametrize("t", range(4))
-def test_popcount_tree_equals_plain_popcount(cuda, t, conv_path):
-    """The carry-save reduction and the one-POPC-per-word variant are separate code paths."""
-    if conv_path != "popcount":
-        pytest.skip("only meaningful on the popcount path")
+def test_selected_path_is_the_one_that_runs(cuda, t, conv_path):
+    """The path setting is honoured: the tensor-core kernel reports its tile, the popcount paths report none."""
     N, H, W, C, KN = 4, 14, 14, 256, 96
     x, ths = make_input(5, N, H, W, C)
     w, wths = make_input(6, KN, 3, 3, C)
     qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, 3, 3, C)
-    l = _cabi.lib()
-    try:
-        l.tab_debug_set_csa(0)
-        y0 = gpu_conv(cuda, x, qw, ths, btn, t, 1, 1, 1, 1, N, H, W, C, KN, 3, 3)
-    finally:
-        l.tab_debug_set_csa(1)
-    y1 = gpu_conv(cuda, x, qw, ths, btn, t, 1, 1, 1, 1, N, H, W, C, KN, 3, 3)
-    yo = c_oracle.conv2d(x, qw, ths, btn, t, 1, 1, 1, 1, N, H, W, C, KN, 3, 3)
-    assert np.array_equal(y0, yo) and np.array_equal(y1, yo)
+    y = gpu_conv(cuda, x, qw, ths, btn, t, 1, 1, 1, 1, N, H, W, C, KN, 3, 3)
+    name = _cabi.lib().tab_last_conv_kernel().decode()
+    assert name.startswith("conv_umma_persist_kernel<") if conv_path == "tensor" else name == "none"
+    assert np.array_equal(y, c_oracle.conv2d(x, qw, ths, btn, t, 1, 1, 1, 1, N, H, W, C, KN, 3, 3))
 
 
 RESNET_LAYERS = [
@@ -271,57 +260,51 @@ def test_packed_entry_point_equals_fused_call(cuda):
         assert np.array_equal(y.cpu().numpy(), yo)
 
 
-def test_int8_stage_entry_points(cuda):
-    """quantize_int8 / expand_weights / conv2d_int8 against the de-quantised oracle planes and the fused call."""
-    N, H, W, C, KN, K = 3, 9, 8, 130, 70, 3
-    x, ths = make_input(1, N, H, W, C)
+def test_expand_weights(cuda):
+    """expand_weights against the de-quantised oracle planes (channel padding 0)."""
+    KN, K, C, Cp = 70, 3, 130, 192
     w, wths = make_input(2, KN, K, K, C)
-    Cp = 192
-    for t in range(4):
-        ab, wb = O.act_bits(t), O.weight_bits(t)
-        qx, _ = O.quantize(x, ths, ab, N, H, W, C)
-        qw, btn = O.quantize(w, wths, wb, KN, K, K, C)
-        q8 = TAB.ops.quantize_int8(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C)
+    for wb in (2, 1):
+        qw, _ = O.quantize(w, wths, wb, KN, K, K, C)
         w8 = TAB.ops.expand_weights(dev_t(qw, cuda), wb, KN, K, K, C)
-        assert tuple(q8.shape) == (N, H, W, Cp) and tuple(w8.shape) == (KN, K, K, Cp)
-        exp_a = np.zeros((N, H, W, Cp), np.int8)
-        exp_a[..., :C] = O.dequantize(qx, C).astype(np.int8)
+        assert tuple(w8.shape) == (KN, K, K, Cp)
         exp_w = np.zeros((KN, K, K, Cp), np.int8)
         exp_w[..., :C] = O.dequantize(qw, C).astype(np.int8)
-        assert np.array_equal(q8.cpu().numpy(), exp_a) and np.array_equal(w8.cpu().numpy(), exp_w)
-        y = TAB.ops.conv2d_int8(q8, w8, t, 1, 1, 2, 1, N, H, W, C, KN, K, K)
-        yo = c_oracle.conv2d(x, qw, ths, btn, t, 1, 1, 2, 1, N, H, W, C, KN, K, K)
-        assert np.array_equal(y.cpu().numpy(), yo)
+        assert np.array_equal(w8.cpu().numpy(), exp_w)
 
 
-@pytest.mark.parametrize("s1,s2", [(1, 1), (2, 2), (3, 2)])
-def test_int8_padded_stage_entry_points(cuda, s1, s2):
-    """quantize_int8_padded writes the convolution's padding (0 ternary, +1 binary, channel tail 0) and splits the padded
-    image into the stride's parity planes; conv2d_int8_padded on it equals the oracle's Conv2d."""
-    N, H, W, C, KN, K = 3, 9, 8, 130, 70, 3
-    p1, p2 = 1, 2
+@pytest.mark.parametrize("geom", [
+    # p1 p2 s1 s2  N  H  W   C   KN KH KW
+    (1, 1, 2, 1, 3, 9, 8, 130, 70, 3, 3),
+    (1, 2, 1, 1, 3, 9, 8, 130, 70, 3, 3),
+    (1, 2, 2, 2, 3, 9, 8, 130, 70, 3, 3),
+    (1, 2, 3, 2, 3, 9, 8, 130, 70, 3, 3),
+    (0, 0, 2, 2, 5, 14, 14, 64, 128, 1, 1),
+    (3, 3, 1, 1, 2, 6, 5, 64, 16, 3, 3),         # padding wider than the kernel reaches: the grid does not share padding
+    (0, 0, 1, 1, 2, 9, 9, 200, 300, 3, 3),
+])
+def test_bits_stage_entry_point(cuda, geom):
+    """Quantize -> expand_weights -> conv2d_bits (the tensor-core GEMM stage on its own, prepared weights) equals the
+    oracle's Conv2d, plain and chained through one state block that every call leaves zeroed."""
+    p1, p2, s1, s2, N, H, W, C, KN, KH, KW = geom
     x, ths = make_input(7, N, H, W, C)
-    w, wths = make_input(8, KN, K, K, C)
-    Cp = 192
-    planes, PH2, PW2 = TAB.ops.plane_layout(H, W, K, K, p1, p2, s1, s2)
-    A, B = min(s1, K), min(s2, K)
+    w, wths = make_input(8, KN, KH, KW, C)
+    state = TAB.ops.new_state(N, cuda)
     for t in range(4):
         ab, wb = O.act_bits(t), O.weight_bits(t)
-        qx, _ = O.quantize(x, ths, ab, N, H, W, C)
-        qw, btn = O.quantize(w, wths, wb, KN, K, K, C)
-        q8 = TAB.ops.quantize_int8_padded(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C, K, K, p1, p2, s1, s2)
-        w8 = TAB.ops.expand_weights(dev_t(qw, cuda), wb, KN, K, K, C)
-        assert tuple(q8.shape) == (A * B, N, PH2, PW2, Cp)
-        padded = np.zeros((N, PH2 * s1, PW2 * s2, Cp), np.int8)           # the padded image, grown to whole planes
-        if ab == 1:
-            padded[..., :C] = 1
-        padded[:, p1:p1 + H, p2:p2 + W, :C] = O.dequantize(qx, C).astype(np.int8)
-        exp = np.stack([padded[:, a::s1, b::s2, :] for a in range(A) for b in range(B)])
-        assert np.array_equal(q8.cpu().numpy(), exp)
-        y = TAB.ops.conv2d_int8_padded(q8, w8, t, p1, p2, s1, s2, N, H, W, C, KN, K, K)
-        yo = c_oracle.conv2d(x, qw, ths, btn, t, p1, p2, s1, s2, N, H, W, C, KN, K, K)
-        assert np.array_equal(y.cpu().numpy(), yo)
-        assert _cabi.lib().tab_debug_umma_status() == 0
+        qw, btn = O.quantize(w, wths, wb, KN, KH, KW, C)
+        qx, _ = TAB.Quantize(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C)
+        w8 = TAB.ops.expand_weights(dev_t(qw, cuda), wb, KN, KH, KW, C)
+        yo = c_oracle.conv2d(x, qw, ths, btn, t, *geom)
+        y, nxt = TAB.ops.conv2d_bits(qx, w8, t, *geom)
+        assert nxt is None and np.array_equal(y.cpu().numpy(), yo)
+        r = torch.round(torch.randn(*yo.shape, device=cuda) * 5)
+        y2, nxt = TAB.ops.conv2d_bits(qx, w8, t, *geom, residual=r, threshold_scale=0.7, state=state)
+        y2o = yo + r.cpu().numpy()
+        assert np.array_equal(y2.cpu().numpy(), y2o)
+        assert np.array_equal(nxt.cpu().numpy(), OracleOps.residual_threshold(y2o.copy(), None, 0.7))
+        assert not state.any().item()
+        assert _cabi.lib().tab_device_status() == 0
 
 
 @pytest.mark.parametrize("t", [0, 3])
@@ -329,7 +312,7 @@ def test_int8_padded_stage_entry_points(cuda, s1, s2):
     # p1 p2 s1 s2  N   H    W    C   KN KH KW
     (3, 3, 2, 2, 2, 224, 224, 3, 64, 7, 7),      # ResNet stem: 49 taps over four parity planes
     (1, 1, 1, 1, 1, 224, 224, 64, 64, 3, 3),     # wide image: the patch only fits with one row block per tile
-    (1, 1, 1, 1, 1, 300, 500, 64, 40, 3, 3),     # patch does not fit shared memory: the other kernels take over
+    (1, 1, 1, 1, 1, 300, 500, 64, 40, 3, 3),     # wide image: a 1 130-row patch
     (2, 1, 3, 2, 2, 33, 17, 192, 200, 5, 3),     # stride 3 x 2, six parity planes, ragged filter count
     (1, 1, 1, 1, 70, 3, 3, 64, 64, 3, 3),        # 25 grid positions per image: a 32-row slab spans three images
     (0, 0, 1, 1, 2, 28, 28, 128, 1000, 1, 1),    # 1x1, filter count not a multiple of 32
@@ -353,15 +336,16 @@ def test_large_and_odd_shapes_plain_and_chained(cuda, t, geom):
     assert np.array_equal(nxt.cpu().numpy(), exp)
 
 
-def test_kernels_larger_than_the_tensor_path_limit_fall_back(cuda):
-    """9x9 kernels (81 taps) exceed the tensor-core loader's 64-tap mask: the call must still be exact."""
-    N, H, W, C, KN, K = 1, 12, 12, 64, 8, 9
-    x, ths = make_input(3, N, H, W, C)
-    w, wths = make_input(4, KN, K, K, C)
-    for t in (0, 3):
-        qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, K, K, C)
-        y = gpu_conv(cuda, x, qw, ths, btn, t, 4, 4, 1, 1, N, H, W, C, KN, K, K)
-        assert np.array_equal(y, c_oracle.conv2d(x, qw, ths, btn, t, 4, 4, 1, 1, N, H, W, C, KN, K, K))
+def test_shapes_beyond_the_tensor_kernel_fall_back(cuda):
+    """A 9x9 kernel on a 300-pixel-wide image needs a patch that does not fit shared memory: the call falls back to the
+    popcount kernel and must still be exact; the same kernel on a narrow image stays on the tensor cores."""
+    for N, H, W, C, KN, K in ((1, 12, 12, 64, 8, 9), (1, 20, 300, 64, 8, 9)):
+        x, ths = make_input(3, N, H, W, C)
+        w, wths = make_input(4, KN, K, K, C)
+        for t in (0, 3):
+            qw, btn = O.quantize(w, wths, O.weight_bits(t), KN, K, K, C)
+            y = gpu_conv(cuda, x, qw, ths, btn, t, 4, 4, 1, 1, N, H, W, C, KN, K, K)
+            assert np.array_equal(y, c_oracle.conv2d(x, qw, ths, btn, t, 4, 4, 1, 1, N, H, W, C, KN, K, K))
 
 
 # ------------------------------------------------------------------------------------------ chain

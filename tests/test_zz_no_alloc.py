@@ -2,13 +2,14 @@
 memory is owned by another component's pool, or their binding can only forward buffers it was given, or
 an allocation's device synchronisation is not allowed where they call from).  Its scratch is a fixed
 array inside the library, so the test checks three things through the C ABI: the result equals
-``tab_conv2d_launch`` exactly (integer-valued outputs: tolerance 0), a second call right after the first
-is not disturbed by what the first left in the shared array, and a problem larger than the array is
-refused with TAB_E_TOO_LARGE instead of being launched.  The file name sorts last on purpose."""
+``tab_conv2d_launch`` and the CPU oracle exactly (integer-valued outputs: tolerance 0), a second call right
+after the first is not disturbed by what the first left in the shared array, and a problem larger than the
+array is refused with TAB_E_TOO_LARGE instead of being launched.  The file name sorts last on purpose."""
 import numpy as np
 import pytest
 import torch
 
+from oracle import c_oracle
 from tab_b200 import _cabi
 from util import make_input
 
@@ -45,7 +46,8 @@ def _both(l, cuda, t, geom, seed):
                                     t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, stream)
     assert rc == 0, l.tab_error_string(rc)
     torch.cuda.synchronize()
-    return y_ws.cpu().numpy(), y_st.cpu().numpy()
+    y_cpu = c_oracle.conv2d(x, qw.cpu().numpy(), ths, btn.cpu().numpy(), t, p1, p2, s1, s2, N, H, W, C, KN, KH, KW).reshape(-1)
+    return y_ws.cpu().numpy(), y_st.cpu().numpy(), y_cpu
 
 
 def test_static_scratch_entry_point_matches_workspace_entry_point(cuda):
@@ -55,10 +57,10 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(cuda):
     first = (1, 1, 1, 1, 8, 28, 28, 128, 96, 3, 3)
     second = (0, 1, 2, 1, 3, 9, 7, 65, 10, 3, 3)
     for t in range(4):
-        a_ws, a_st = _both(l, cuda, t, first, 10 + t)
-        b_ws, b_st = _both(l, cuda, (t + 2) % 4, second, 20 + t)
-        assert np.array_equal(a_ws, a_st), "type %d, first call" % t
-        assert np.array_equal(b_ws, b_st), "type %d, second call" % ((t + 2) % 4)
+        a_ws, a_st, a_cpu = _both(l, cuda, t, first, 10 + t)
+        b_ws, b_st, b_cpu = _both(l, cuda, (t + 2) % 4, second, 20 + t)
+        assert np.array_equal(a_st, a_cpu) and np.array_equal(a_ws, a_st), "type %d, first call" % t
+        assert np.array_equal(b_st, b_cpu) and np.array_equal(b_ws, b_st), "type %d, second call" % ((t + 2) % 4)
         assert a_st.min() > -4609 and not np.all(a_st == -9.0)
 
 
