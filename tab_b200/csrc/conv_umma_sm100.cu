@@ -64,11 +64,14 @@ __device__ __forceinline__ uint32_t expand4(uint32_t mnib, uint32_t snib) {
 }
 
 // The (sign, magnitude) words of XUNROLL items of a patch, held in registers between the loads and the expansion.
+// Nothing is computed on them before store_items: an instruction that consumes a loaded register would make the thread
+// wait for that load, and the point of loading a patch ahead is not to wait.
 struct RawItems { uint64_t sg[XUNROLL], mg[XUNROLL]; };
 
 // Loads items base + u*NXT + xt (u < XUNROLL) of the patch at virtual row Rbase of plane (pa, pb), channel words 2*cp and
 // 2*cp + 1.  Item = (row, word); the two words of a pixel go to neighbouring threads (32 contiguous bytes).  Padding
-// positions are not loaded: they are zero words (ternary: 0; binary: +1 in the real channels).
+// positions are not loaded: they are zero words (ternary: 0; binary: +1 in the real channels).  Binary activations
+// have one plane: its word is the sign, the magnitude is all ones.
 template <bool UNIT>
 __device__ __forceinline__ void load_items(const TcConvParams& p, RawItems& raw, int Rbase, int nrows, int cp, int pa, int pb, int base, int xt) {
     const int nw = (2 * cp + 1 < p.PC) ? 2 : 1;
@@ -77,7 +80,8 @@ __device__ __forceinline__ void load_items(const TcConvParams& p, RawItems& raw,
 #pragma unroll
     for (int u = 0; u < XUNROLL; u++) {
         const int it = base + u * NXT + xt;
-        raw.sg[u] = 0; raw.mg[u] = 0;
+        raw.sg[u] = 0;
+        raw.mg[u] = p.abits == 1 ? ~0ull : 0ull;
         if (it < items) {
             const int r = nw == 2 ? it >> 1 : it, w = nw == 2 ? it & 1 : 0;
             const uint32_t R = (uint32_t)(Rbase + r);
@@ -87,28 +91,22 @@ __device__ __forceinline__ void load_items(const TcConvParams& p, RawItems& raw,
             const uint32_t j = rem - i * (uint32_t)p.VW;
             const int ih = (UNIT ? (int)i : (int)i * p.s1 + pa) - p.p1;
             const int iw = (UNIT ? (int)j : (int)j * p.s2 + pb) - p.p2;
-            const int word = 2 * cp + w;
-            const int cvalid = p.C - 64 * word;                            // real channels in this word (>= 1)
-            const uint64_t vmask = cvalid >= 64 ? ~0ull : ((1ull << cvalid) - 1ull);
             if ((int)n < p.N && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W) {
-                const long long widx = (((long long)n * p.H + ih) * p.W + iw) * p.PC + word;
+                const long long widx = (((long long)n * p.H + ih) * p.W + iw) * p.PC + 2 * cp + w;
                 if (p.abits == 2) {
                     const ulonglong2 v = __ldg(reinterpret_cast<const ulonglong2*>(p.qx + 2 * widx));
-                    raw.mg[u] = v.y & vmask;
                     raw.sg[u] = v.x;
+                    raw.mg[u] = v.y;
                 } else {
-                    raw.mg[u] = vmask;
                     raw.sg[u] = __ldg(p.qx + widx);
                 }
-            } else if (p.abits == 1) {
-                raw.mg[u] = vmask;                                         // binary activations pad with +1 (a zero word)
             }
         }
     }
 }
 
 // Expands the items load_items fetched into rows of patch buffer `buf` (K-major, 128-byte swizzle: 16-byte unit u of
-// row r lives at r*128 + ((u ^ (r & 7)) << 4); buf is 1024-byte aligned).
+// row r lives at r*128 + ((u ^ (r & 7)) << 4); buf is 1024-byte aligned).  Channels beyond C become 0.
 __device__ __forceinline__ void store_items(const TcConvParams& p, const RawItems& raw, uint32_t buf, int nrows, int cp, int base, int xt) {
     const int nw = (2 * cp + 1 < p.PC) ? 2 : 1;
     const int items = nrows * nw;
@@ -118,7 +116,9 @@ __device__ __forceinline__ void store_items(const TcConvParams& p, const RawItem
         if (it < items) {
             const int r = nw == 2 ? it >> 1 : it, w = nw == 2 ? it & 1 : 0;
             const uint32_t rowaddr = buf + (uint32_t)r * IROW;
-            const uint64_t mg = raw.mg[u], sg = raw.sg[u] & mg;
+            const int cvalid = p.C - 64 * (2 * cp + w);                    // real channels in this word (>= 1)
+            const uint64_t vmask = cvalid >= 64 ? ~0ull : ((1ull << cvalid) - 1ull);
+            const uint64_t mg = raw.mg[u] & vmask, sg = raw.sg[u] & mg;
 #pragma unroll
             for (int q = 0; q < 4; q++) {                                  // 16 channels = one 16-byte unit
                 const uint32_t m16 = (uint32_t)(mg >> (16 * q)) & 0xFFFFu, s16 = (uint32_t)(sg >> (16 * q)) & 0xFFFFu;
