@@ -7,14 +7,14 @@
 // decode to +1 (the reference's padding rule), channel tails decode to 0.
 //
 // One CTA per SM walks over output tiles of 128*MT virtual rows x TN filters (see TcConvParams for the virtual grid):
-//   * expander warps (0, 3, 12-15): stage the *patch* of a tile - the 128*MT + halo consecutive virtual rows all its
+//   * expander warps (0, 12-15): stage the *patch* of a tile - the 128*MT + halo consecutive virtual rows all its
 //     taps read - for one pair of 64-channel words and one stride plane: 16 bytes of (sign, magnitude) per pixel and
 //     word are loaded from global memory (padding positions are not loaded at all) and expanded to 64 bytes of int8
 //     in the K-major, 128-byte-swizzled layout the MMA descriptors expect.  Two patch buffers; the expanders run up to
 //     two patches ahead of the MMAs, across tile boundaries.
 //   * warp 2: TMA copies of the filter slice (TN x 128 B per tap and channel pair) into a ring of SB stages, or - when
 //     the filters of all taps fit beside the patches (BRES) - once per CTA.
-//   * warp 1: tcgen05.mma.cta_group::1.kind::i8, 128 x TN x 32 per instruction.  Tap (kh, kw) of the 128 rows of an MMA
+//   * warps 1 and 3 (even and odd tiles): tcgen05.mma.cta_group::1.kind::i8, 128 x TN x 32 per instruction.  Tap (kh, kw) of the 128 rows of an MMA
 //     is 128 consecutive patch rows starting (kh/s1)*VW + kw/s2 rows into the patch: the A descriptor simply starts
 //     there (the 128-byte swizzle is a function of absolute shared-memory address bits).  Two TMEM accumulator buffers.
 //   * warps 4-11: epilogue of the other accumulator buffer: tcgen05.ld, transposition through a private shared-memory
@@ -33,7 +33,7 @@
 namespace tab {
 
 constexpr int PTHREADS = 512;                                              // 16 warps
-constexpr int NXT = 192;                                                   // expander threads (6 warps)
+constexpr int NXT = 160;                                                   // expander threads (5 warps)
 constexpr int XUNROLL = 4;                                                 // (pixel, word) items a thread has in flight
 
 // Called by every thread of every CTA at the end of the kernel, after the CTA's last atomic on abs_sums.
@@ -72,8 +72,8 @@ struct RawItems { uint64_t sg[XUNROLL], mg[XUNROLL]; };
 // 2*cp + 1.  Item = (row, word); the two words of a pixel go to neighbouring threads (32 contiguous bytes).  Padding
 // positions are not loaded: they are zero words (ternary: 0; binary: +1 in the real channels).  Binary activations
 // have one plane: its word is the sign, the magnitude is all ones.
-template <bool UNIT>
 __device__ __forceinline__ void load_items(const TcConvParams& p, RawItems& raw, int Rbase, int nrows, int cp, int pa, int pb, int base, int xt) {
+    const bool UNIT = p.s1 == 1 && p.s2 == 1;
     const int nw = (2 * cp + 1 < p.PC) ? 2 : 1;
     const int items = nrows * nw;
     const int VHW = p.VH * p.VW;
@@ -175,7 +175,7 @@ struct SlabRows {
 // (|y| < 2^18): a lane keeps running totals per image as integers straight from the accumulators (exact, one REDUX at
 // the end) or, with a residual - which need not be integer-valued - as doubles, every term converted before it is added.  Otherwise ("slow", rare: images of fewer than
 // 32 virtual positions, very long K): one double atomic per row and block.
-template <bool FUSED>
+template <int FUSED>
 __device__ __forceinline__ void slab_rows(const TcConvParams& p, int Rw, int lane, SlabRows& sr) {
     const int VHW = p.VH * p.VW;
     const uint32_t R = (uint32_t)(Rw + lane);
@@ -209,12 +209,12 @@ __device__ __forceinline__ void slab_load_residual(const TcConvParams& p, const 
 // TMEM address (column 0, this warp's lane quarter) is taddr.  The residual of a block is fetched one block ahead -
 // for the first block by the caller, before it waits for the accumulator (res / res_loaded) - because a load issued
 // when the block is processed costs the warp its whole DRAM latency.
-template <bool FUSED>
+template <int FUSED>
 __device__ __forceinline__ void slab_columns(const TcConvParams& p, uint32_t taddr, const SlabRows& sr, int n0, int c0, int c1,
                                              int lane, uint32_t stage, float4 (&res)[8], bool res_loaded, PendingSums& ps) {
     const bool vec4 = (p.KN & 3) == 0;
     const bool small_acc = p.Kw < (1 << 15);                               // |accumulator| <= 64 * Kw < 2^21: the bias conversion is exact
-    const bool has_res = FUSED && p.residual != nullptr;
+    constexpr bool has_res = FUSED == 2;
     const bool want_sum = FUSED && p.abs_sums != nullptr;
     const int rsub = lane >> 3, chunk = lane & 7;
     const int VHW = p.VH * p.VW;
@@ -263,12 +263,22 @@ __device__ __forceinline__ void slab_columns(const TcConvParams& p, uint32_t tad
 #pragma unroll
             for (int i = 0; i < 8; i++)
                 if (sr.mi[i] >= 0) reinterpret_cast<float4*>(p.y + (long long)sr.mi[i] * p.KN + nbase)[chunk] = o[i];
-            if (sr.fast && has_res) {                                     // the residual need not be integer-valued: every term in double
+            if (sr.fast && has_res) {
+                // the residual need not be integer-valued: compensated (Kahan) float sums, two chains per image, whose value
+                // and compensation go to the double totals (good to about 1e-14 of the total)
+                float sa0 = 0.f, sa1 = 0.f, ca0 = 0.f, ca1 = 0.f, sb0 = 0.f, sb1 = 0.f, cb0 = 0.f, cb1 = 0.f;
+                auto kahan = [](float x, float& sv, float& cv) { const float yv = x - cv, tv = sv + yv; cv = (tv - sv) - yv; sv = tv; };
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const double s4 = sr.mi[i] >= 0 ? ((double)fabsf(o[i].x) + (double)fabsf(o[i].y)) + ((double)fabsf(o[i].z) + (double)fabsf(o[i].w)) : 0.0;
-                    if (4 * i + rsub < sr.split) dsum0 += s4; else dsum1 += s4;
+                    if (sr.mi[i] < 0) continue;
+                    if (4 * i + rsub < sr.split) {
+                        kahan(fabsf(o[i].x), sa0, ca0); kahan(fabsf(o[i].y), sa1, ca1); kahan(fabsf(o[i].z), sa0, ca0); kahan(fabsf(o[i].w), sa1, ca1);
+                    } else {
+                        kahan(fabsf(o[i].x), sb0, cb0); kahan(fabsf(o[i].y), sb1, cb1); kahan(fabsf(o[i].z), sb0, cb0); kahan(fabsf(o[i].w), sb1, cb1);
+                    }
                 }
+                dsum0 += ((double)sa0 + (double)sa1) - ((double)ca0 + (double)ca1);
+                dsum1 += ((double)sb0 + (double)sb1) - ((double)cb0 + (double)cb1);
             } else if (sr.slow) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
@@ -315,15 +325,64 @@ __device__ __forceinline__ void slab_columns(const TcConvParams& p, uint32_t tad
     (void)VHW;
 }
 
+// ---- epilogue through TMA (TEPI) ---------------------------------------------------------------------------------------
+// With a virtual grid whose row length divides 32 or is a multiple of 32 (TcConvParams::tepi), the 32 virtual rows of a
+// warp's slab are one box of the output tensor [N][OH][OW][KN]: 32 positions of one grid row, or 32/VW whole grid rows of
+// one image.  The box's positions outside the real output (ow >= OW, oh >= OH, n >= N) are exactly the rows the other
+// epilogue drops, and the TMA engine drops them by itself.  So a 32 x 32 block needs no transposition: lane r keeps
+// accumulator row r, reads its residual row from the warp's shared-memory buffer (a TMA load that was issued a whole
+// block earlier put it there), converts, adds, writes the row back into the same buffer (128-byte swizzle: conflict
+// free both ways) and one lane issues the TMA store.  Two buffers per warp: while block b is processed, the store of
+// block b-1 drains and the residual of block b+1 arrives.  No address arithmetic per row, no global load or store
+// instruction in the warp, and the bytes in flight are bounded by shared memory instead of registers.
+struct TepiBox { int c0, c1, c2, c3; bool live; };
+
+// Box of the slab at virtual row Rw, filters from nbase.
+__device__ __forceinline__ TepiBox tepi_box(const TcConvParams& p, int Rw, int nbase) {
+    const int VHW = p.VH * p.VW;
+    const int n = (int)p.dVHW.div((uint32_t)Rw);
+    const int rem = Rw - n * VHW;
+    const int i = (int)p.dVW.div((uint32_t)rem);
+    const int j = rem - i * p.VW;
+    TepiBox b;
+    b.c0 = nbase; b.c1 = j; b.c2 = i; b.c3 = n;
+    b.live = n < p.N && i < p.OH && j < p.OW && nbase < p.KN;              // else nothing of the box is a real output
+    return b;
+}
+
+// The warp's blocks in order: columns [ec0, ec1) of its slab of tile t (those below KN), then the same of tile t + step, ...
+struct TepiIter {
+    int t, cb;
+    __device__ __forceinline__ void settle(int ec0, int step, int ntiles, int tiles_n, int tni, int KN) {
+        while (t < ntiles && (t % tiles_n) * tni + cb >= KN) { t += step; cb = ec0; }
+    }
+    __device__ __forceinline__ void next(int ec0, int ec1, int step, int ntiles, int tiles_n, int tni, int KN) {
+        cb += 32;
+        if (cb >= ec1) { cb = ec0; t += step; }
+        settle(ec0, step, ntiles, tiles_n, tni, KN);
+    }
+};
+
+// Requests the residual of a block into buffer `buf` (arrives on mbar), or just arrives when the box is dead.
+__device__ __forceinline__ void tepi_request_residual(const void* tmR, const TepiBox& b, uint32_t buf, uint32_t mbar) {
+    if (b.live) {
+        mbar_expect_tx(mbar, 4096u);
+        tma_load_4d(buf, tmR, b.c0, b.c1, b.c2, b.c3, mbar);
+    } else {
+        mbar_arrive(mbar);
+    }
+}
+
 // ---- the kernel ------------------------------------------------------------------------------------------------------------
+// FUSED: 0 plain; 1 per-image |y| sums and the threshold tail; 2 residual added (sums and tail when asked for).
 // BRES: the filter block of the CTA (all taps, all channel pairs; needs KN <= TNI) is copied once and stays in shared
 // memory; otherwise it streams through a ring of SB stages, one stage per tap and channel pair.
-// UNIT: stride 1 in both directions (one plane; the tap loops are then flat, which matters because the MMA warp's
-// instruction stream, not the tensor pipe, limits small tiles).
+// TEPI: the epilogue moves the output (and the residual) with TMA boxes; needs the aligned virtual grid (p.tepi).
 // Counters g (ring stages), q (patches) and a (accumulator buffers) run across tiles; barrier parities follow from them.
-template <int MT, int TNI, int SB, bool BRES, bool FUSED, bool UNIT>
+template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI>
 __global__ void __launch_bounds__(PTHREADS, 1)
-conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvParams p, int* __restrict__ status,
+conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmR,
+                         const TcConvParams p, int* __restrict__ status,
                          const int prow, const int nrows, const int nst, const int tiles_m, const int tiles_n) {
     constexpr int BSTAGE = TNI * IROW;
     constexpr int ACOLS = MT * TNI;                                        // columns of one accumulator buffer
@@ -340,20 +399,26 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
     const uint32_t fullP = emptyB + 64, emptyP = fullP + 16, accFull = emptyP + 16, accEmpty = accFull + 16;
     const uint32_t tslot = accEmpty + 16;                                  // = fullB + 192
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + tail + 192);
-    const uint32_t sStage = sbase + tail + 256;                            // [8 epilogue warps][4 KB]
+    volatile int* deadp = reinterpret_cast<volatile int*>(smem + tail + 200);     // set by a role whose bounded wait ran out
+    const uint32_t resB = sbase + tail + 256;                              // [8 epilogue warps][2]: residual arrived (TEPI)
+    const uint32_t sStage = sbase + tail + 1024;                           // [8 epilogue warps][4 KB, or 2 x 4 KB with TEPI]; 1024-byte aligned
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int s1 = p.s1, s2 = p.s2;
+    const bool UNIT = s1 == 1 && s2 == 1;                                  // one plane: flat tap loops
     const int PA = p.PA, PB = p.PB, VW = p.VW;
     const int T = p.KH * p.KW, ncp = (p.PC + 1) >> 1;
     const int ntiles = tiles_m * tiles_n;
 
     if (tid == 0) {
-        for (int s = 0; s < 16; s++) mbar_init(fullB + 8 * s, 1);          // fullB[8], emptyB[8]
+        *deadp = 0;
+        for (int s = 0; s < 8; s++) mbar_init(fullB + 8 * s, 1);
         mbar_init(fullP, NXT); mbar_init(fullP + 8, NXT);                  // one arrival per expander thread
-        mbar_init(emptyP, 1); mbar_init(emptyP + 8, 1);
-        mbar_init(accFull, 1); mbar_init(accFull + 8, 1);
+        for (int s = 0; s < 8; s++) mbar_init(emptyB + 8 * s, MT);          // one commit per MMA warp (MT = 2: two warps)
+        mbar_init(emptyP, MT); mbar_init(emptyP + 8, MT);
+        mbar_init(accFull, MT); mbar_init(accFull + 8, MT);
         mbar_init(accEmpty, 8); mbar_init(accEmpty + 8, 8);                // one arrival per epilogue warp
+        if (TEPI) for (int i = 0; i < 16; i++) mbar_init(resB + 8 * i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(tslot, (uint32_t)(2 * ACOLS));
@@ -368,42 +433,51 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
 
     // In every role the whole warp runs the loops and the waits and one elected lane issues the copies, MMAs and
     // commits.  All roles walk the same nest: tile, channel pair cp, plane (a, b), taps of that plane.
-    if (warp == 0 || warp == 3 || warp >= 12) {
+    if (warp == 0 || warp >= 12) {
         // ---- expanders: up to two patches ahead of the MMAs (across tile boundaries).  The global loads of a patch are
         //      issued a whole patch earlier than they are used (they need registers, not the patch buffer), so that their
         //      latency - long when the epilogue's stores fill the memory system - is off the critical path. -----------------
-        const int xt = (warp == 0 ? 0 : (warp == 3 ? 1 : warp - 10)) * 32 + lane;
+        const int xt = (warp == 0 ? 0 : warp - 11) * 32 + lane;
         const int planes = PA * PB, step = (int)gridDim.x;
         PatchIter cur = {(int)blockIdx.x, 0, 0};
-        RawItems raw;
-        if (cur.t < ntiles) load_items<UNIT>(p, raw, (cur.t / tiles_n) * (UTM * MT), nrows, 0, 0, 0, 0, xt);
         unsigned q = 0;
         bool dead = false;
-        while (cur.t < ntiles && !dead) {
-            PatchIter nxt = cur;
-            nxt.next(ncp, planes, step);
-            RawItems ahead;
-            const int npa = UNIT ? 0 : nxt.pl / PB;
-            if (nxt.t < ntiles) load_items<UNIT>(p, ahead, (nxt.t / tiles_n) * (UTM * MT), nrows, nxt.cp, npa, UNIT ? 0 : nxt.pl - npa * PB, 0, xt);
+        // One patch: wait for its buffer, expand the words loaded earlier (mine), hand the patch to the MMA warp.
+        auto stage_patch = [&](const RawItems& mine) {
             const unsigned pb = q & 1;
-            if (q >= 2 && !mbar_wait_warp(emptyP + 8 * pb, ((q >> 1) - 1) & 1u)) { dead = true; if (status && lane == 0) atomicExch(status, 11); break; }
+            if (q >= 2 && !mbar_wait_warp(emptyP + 8 * pb, ((q >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 11); *deadp = 1; } return; }
             const uint32_t buf = sPatch + (uint32_t)(pb * prow) * IROW;
-            store_items(p, raw, buf, nrows, cur.cp, 0, xt);
+            store_items(p, mine, buf, nrows, cur.cp, 0, xt);
             const int items = nrows * ((2 * cur.cp + 1 < p.PC) ? 2 : 1);
             if (items > NXT * XUNROLL) {                                   // long patches (large halo): the rest, chunk by chunk
                 const int R0 = (cur.t / tiles_n) * (UTM * MT);
                 const int pa = UNIT ? 0 : cur.pl / PB;
                 for (int base = NXT * XUNROLL; base < items; base += NXT * XUNROLL) {
                     RawItems more;
-                    load_items<UNIT>(p, more, R0, nrows, cur.cp, pa, UNIT ? 0 : cur.pl - pa * PB, base, xt);
+                    load_items(p, more, R0, nrows, cur.cp, pa, UNIT ? 0 : cur.pl - pa * PB, base, xt);
                     store_items(p, more, buf, nrows, cur.cp, base, xt);
                 }
             }
             fence_async_smem();
             mbar_arrive(fullP + 8 * pb);
+            q++;
+        };
+        auto load_patch = [&](RawItems& into, const PatchIter& at) {
+            const int pa = UNIT ? 0 : at.pl / PB;
+            if (at.t < ntiles) load_items(p, into, (at.t / tiles_n) * (UTM * MT), nrows, at.cp, pa, UNIT ? 0 : at.pl - pa * PB, 0, xt);
+        };
+        // The words of the next patch are loaded before this one is expanded.  (The hand-over raw = ahead comes after the
+        // expansion, when those loads have long arrived: a move of a register whose load is in flight would wait for it.)
+        RawItems raw;
+        load_patch(raw, cur);
+        while (cur.t < ntiles && !dead) {
+            PatchIter nxt = cur;
+            nxt.next(ncp, planes, step);
+            RawItems ahead;
+            load_patch(ahead, nxt);
+            stage_patch(raw);
             raw = ahead;
             cur = nxt;
-            q++;
         }
     } else if (warp == 2) {
         // ---- filter producer ---------------------------------------------------------------------------------------------
@@ -427,7 +501,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
                     for (int kh = pa; kh < p.KH && !dead; kh += s1)
                     for (int kw = pbb; kw < p.KW; kw += s2, g++) {
                         const unsigned slot = g % SB;
-                        if (g >= (unsigned)SB && !mbar_wait_warp(emptyB + 8 * slot, ((g / SB) - 1) & 1u)) { dead = true; if (status && lane == 0) atomicExch(status, 12); break; }
+                        if (g >= (unsigned)SB && !mbar_wait_warp(emptyB + 8 * slot, ((g / SB) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 12); *deadp = 1; } break; }
                         if (elect_one()) {
                             mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
                             tma_load_2d(sRing + slot * BSTAGE, &tmB, ((kh * p.KW + kw) * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
@@ -437,16 +511,23 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---- MMA warp --------------------------------------------------------------------------------------------------
+    } else if (warp == 1 || warp == 3) {
+        // ---- MMA warps.  One thread cannot issue the MMAs of a stage, its commits and the waits between stages as fast
+        //      as the tensor pipe executes them (about 300 cycles per handshake and 80 per MMA against 48-128 cycles of
+        //      execution).  With two row blocks per tile (MT = 2) warp 1 issues row block 0 and warp 3 row block 1: separate
+        //      accumulators, the same operands and the same barrier phases (both warps follow every stage, so a parity
+        //      wait never sees a phase other than the current or the previous one); the "empty" and "accumulator full"
+        //      barriers then count one commit from each.  With one row block warp 3 idles. -----------------------------------
         constexpr uint32_t IDESC = umma_idesc(TNI);
         constexpr uint32_t MB_UNITS = (UTM * IROW) >> 4;                   // next 128-row block of the patch, in 16-byte units
+        const int mw = warp == 1 ? 0 : 1;
+        const int mb_lo = MT == 2 ? mw : 0, mb_hi = MT == 2 ? mw + 1 : 1;  // this warp's row blocks
         unsigned g = 0, q = 0, a = 0;
-        bool dead = false;
-        if (BRES && !mbar_wait_warp(fullB, 0)) { dead = true; if (status && lane == 0) atomicExch(status, 15); }
+        bool dead = MT == 1 && mw == 1;                                    // nothing to do for the second warp
+        if (BRES && !dead && !mbar_wait_warp(fullB, 0)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } }
         for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
             const unsigned buf = a & 1;
-            if (a >= 2 && !mbar_wait_warp(accEmpty + 8 * buf, ((a >> 1) - 1) & 1u)) { dead = true; if (status && lane == 0) atomicExch(status, 13); break; }
+            if (a >= 2 && !mbar_wait_warp(accEmpty + 8 * buf, ((a >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 13); *deadp = 1; } break; }
             tc_fence_after();
             const uint32_t acc = tmem_base + buf * ACOLS;
             uint32_t accumulate = 0;                                       // 0 for the tile's first MMAs
@@ -454,20 +535,20 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
                 const bool four = 2 * cp + 1 < p.PC;                       // both 64-channel words of the pair exist
                 // the MMAs of one tap: 2 or 4 K steps of 32 bytes, MT row blocks each
                 auto issue_tap = [&](uint64_t da, uint64_t db, uint32_t acc_first) {
-#pragma unroll
-                    for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS, db, IDESC, acc_first);
-#pragma unroll
-                    for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 2, db + 2, IDESC, 1u);
-                    if (four) {
-#pragma unroll
-                        for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 4, db + 4, IDESC, 1u);
-#pragma unroll
-                        for (int mb = 0; mb < MT; mb++) umma_i8(acc + mb * TNI, da + mb * MB_UNITS + 6, db + 6, IDESC, 1u);
+                    for (int mb = mb_lo; mb < mb_hi; mb++) {
+                        const uint32_t d = acc + mb * TNI;
+                        const uint64_t dam = da + mb * MB_UNITS;
+                        umma_i8(d, dam, db, IDESC, acc_first);
+                        umma_i8(d, dam + 2, db + 2, IDESC, 1u);
+                        if (four) {
+                            umma_i8(d, dam + 4, db + 4, IDESC, 1u);
+                            umma_i8(d, dam + 6, db + 6, IDESC, 1u);
+                        }
                     }
                 };
                 if (UNIT) {
                     const unsigned pb = q & 1;
-                    if (!mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (status && lane == 0) atomicExch(status, 14); break; }
+                    if (!mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
                     tc_fence_after();
                     uint32_t arow = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;   // descriptor address of the tap's first patch row
                     int kw = 0;
@@ -485,7 +566,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
                     } else {
                         for (int tap = 0; tap < T; tap++, g++) {
                             const unsigned slot = g % SB;
-                            if (!mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (status && lane == 0) atomicExch(status, 15); break; }
+                            if (!mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
                             tc_fence_after();
                             if (elect_one()) {
                                 issue_tap(((uint64_t)UMMA_DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4)),
@@ -505,7 +586,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
                 for (int pa = 0; pa < PA && !dead; pa++)
                 for (int pbb = 0; pbb < PB && !dead; pbb++, q++) {
                     const unsigned pb = q & 1;
-                    if (!mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (status && lane == 0) atomicExch(status, 14); break; }
+                    if (!mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
                     tc_fence_after();
                     const uint32_t patch = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;    // descriptor address of the patch
                     const bool last_group = cp == ncp - 1 && pa == PA - 1 && pbb == PB - 1;
@@ -516,7 +597,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
                         if (BRES) bsm = sRing + (uint32_t)(cp * T + kh * p.KW + kw) * BSTAGE;
                         else {
                             const unsigned slot = g % SB;
-                            if (!mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (status && lane == 0) atomicExch(status, 15); break; }
+                            if (!mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
                             tc_fence_after();
                             bsm = sRing + slot * BSTAGE;
                         }
@@ -536,6 +617,145 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
                 }
             }
         }
+    } else if (TEPI) {
+        // ---- epilogue warps 4-11 through TMA (TMEM lane quarter = warp % 4) -------------------------------------------
+        const int ew = warp - 4, wg = ew >> 2, step = (int)gridDim.x;
+        const uint32_t sbuf = sStage + (uint32_t)ew * 8192u;               // two 4 KB block buffers
+        const uint32_t mres = resB + 16u * (uint32_t)ew;                   // their "residual arrived" barriers
+        const int emb = MT == 2 ? wg : 0, ec0 = MT == 2 ? 0 : wg * (TNI / 2), ec1 = MT == 2 ? TNI : (wg + 1) * (TNI / 2);
+        constexpr bool has_res = FUSED == 2;
+        const bool want_sum = FUSED && p.abs_sums != nullptr;
+        const bool small_acc = p.Kw < (1 << 15);                           // |accumulator| <= 64 * Kw < 2^21: the bias conversion is exact
+        const int VHW = p.VH * p.VW;
+        auto slab_row = [&](int t) { return (t / tiles_n) * (UTM * MT) + emb * UTM + (warp & 3) * 32; };
+        unsigned a = 0, blk = 0;
+        bool dead = false;
+        PendingSums pending;
+        if (has_res && lane == 0) {                                        // the residual of the warp's first block
+            TepiIter first = {(int)blockIdx.x, ec0};
+            first.settle(ec0, step, ntiles, tiles_n, TNI, p.KN);
+            if (first.t < ntiles) tepi_request_residual(&tmR, tepi_box(p, slab_row(first.t), (first.t % tiles_n) * TNI + first.cb), sbuf, mres);
+        }
+        for (int t = blockIdx.x; t < ntiles && !dead; t += step, a++) {
+            const unsigned buf = a & 1;
+            const int n0 = (t % tiles_n) * TNI, Rw = slab_row(t);
+            // the lane's own row, for the |y| sums: lanes of image wimg0 and of wimg0 + 1 are totalled separately ("fast":
+            // the slab touches at most two images and row totals stay below 2^26), else every lane adds its own total
+            const uint32_t R = (uint32_t)(Rw + lane);
+            const int n_own = (int)p.dVHW.div(R);
+            const int rr = (int)R - n_own * VHW, oh = (int)p.dVW.div((uint32_t)rr), ow = rr - oh * p.VW;
+            const bool row_ok = n_own < p.N && oh < p.OH && ow < p.OW;
+            const int wimg0 = (int)p.dVHW.div((uint32_t)Rw);
+            const bool fast = want_sum && p.Kw < (1 << 12) && (int)p.dVHW.div((uint32_t)(Rw + 31)) - wimg0 <= 1;
+            unsigned isum = 0;
+            double dsum = 0.0;
+            if (has_res && lane == 0 && t + step < ntiles) {               // the next tile's residual boxes on their way into L2
+                const int tn_ = t + step, n0n = (tn_ % tiles_n) * TNI;
+                for (int cb = ec0; cb < ec1 && n0n + cb < p.KN; cb += 32) {
+                    const TepiBox bx = tepi_box(p, slab_row(tn_), n0n + cb);
+                    if (bx.live) tma_prefetch_4d(&tmR, bx.c0, bx.c1, bx.c2, bx.c3);
+                }
+            }
+            if (!mbar_wait_warp(accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + buf * ACOLS + (uint32_t)(emb * TNI) + ((uint32_t)((warp & 3) * 32) << 16);
+#pragma unroll 1
+            for (int cb = ec0; cb < ec1 && n0 + cb < p.KN; cb += 32, blk++) {
+                const unsigned k = blk & 1;
+                const uint32_t sb = sbuf + k * 4096u;
+                const int nbase = n0 + cb, ncols = min(32, p.KN - nbase);
+                uint32_t v[32];
+                tmem_ld32(taddr + (uint32_t)cb, v);
+                float o[32];
+                if (has_res) {
+                    if (lane == 0) {
+                        // the other buffer's last store must have finished reading it before the next residual lands there
+                        bulk_wait_read<0>();
+                        TepiIter nx = {t, cb};
+                        nx.next(ec0, ec1, step, ntiles, tiles_n, TNI, p.KN);
+                        if (nx.t < ntiles)
+                            tepi_request_residual(&tmR, tepi_box(p, slab_row(nx.t), (nx.t % tiles_n) * TNI + nx.cb), sbuf + (k ^ 1u) * 4096u, mres + 8u * (k ^ 1u));
+                    }
+                    if (!mbar_wait_warp(mres + 8u * k, (blk >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 17); *deadp = 1; } break; }
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        const int4 rv = lds_v4(sb + (uint32_t)lane * 128u + ((uint32_t)(q ^ (lane & 7)) << 4));
+                        o[4 * q] = __int_as_float(rv.x); o[4 * q + 1] = __int_as_float(rv.y); o[4 * q + 2] = __int_as_float(rv.z); o[4 * q + 3] = __int_as_float(rv.w);
+                    }
+                } else {
+                    if (lane == 0) bulk_wait_read<1>();                    // this buffer's previous store (two blocks ago) has read it
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) o[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const float f = small_acc ? __int_as_float((int)v[j] + 0x4B400000) - 12582912.f : (float)(int)v[j];
+                    o[j] = has_res ? o[j] + f : f;
+                }
+                if (want_sum && row_ok) {
+                    if (!has_res && fast) {
+                        // y is the accumulator itself: integers below 2^18, so 32 of them add exactly in float (|.| is free)
+                        float f0 = 0.f, f1 = 0.f, f2 = 0.f, f3 = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (j < ncols) f0 += fabsf(o[j]);
+                            if (j + 1 < ncols) f1 += fabsf(o[j + 1]);
+                            if (j + 2 < ncols) f2 += fabsf(o[j + 2]);
+                            if (j + 3 < ncols) f3 += fabsf(o[j + 3]);
+                        }
+                        isum += __float2uint_rn((f0 + f1) + (f2 + f3));
+                    } else {
+                        // the residual need not be integer-valued: compensated (Kahan) float sums, four chains, whose value and
+                        // compensation go to the double total - the total is then good to about 1e-14 of itself
+                        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (j < ncols) { const float yv = fabsf(o[j]) - c0, tv = s0 + yv; c0 = (tv - s0) - yv; s0 = tv; }
+                            if (j + 1 < ncols) { const float yv = fabsf(o[j + 1]) - c1, tv = s1 + yv; c1 = (tv - s1) - yv; s1 = tv; }
+                            if (j + 2 < ncols) { const float yv = fabsf(o[j + 2]) - c2, tv = s2 + yv; c2 = (tv - s2) - yv; s2 = tv; }
+                            if (j + 3 < ncols) { const float yv = fabsf(o[j + 3]) - c3, tv = s3 + yv; c3 = (tv - s3) - yv; s3 = tv; }
+                        }
+                        dsum += (((double)s0 + (double)s1) + ((double)s2 + (double)s3)) - (((double)c0 + (double)c1) + ((double)c2 + (double)c3));
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    sts_v4(sb + (uint32_t)lane * 128u + ((uint32_t)(q ^ (lane & 7)) << 4), __float_as_uint(o[4 * q]), __float_as_uint(o[4 * q + 1]),
+                           __float_as_uint(o[4 * q + 2]), __float_as_uint(o[4 * q + 3]));
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    const TepiBox bx = tepi_box(p, Rw, nbase);
+                    if (bx.live) tma_store_4d(&tmY, bx.c0, bx.c1, bx.c2, bx.c3, sb);
+                    bulk_commit();
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accEmpty + 8 * buf);
+            if (want_sum) {                                                // the |y| atomics, off the buffer's critical path
+                flush_pending(p, pending, lane);
+                if (fast) {
+                    const bool first_img = n_own == wimg0;
+                    if (has_res) {
+                        double t0 = first_img ? dsum : 0.0, t1 = first_img ? 0.0 : dsum;
+#pragma unroll
+                        for (int sh = 16; sh > 0; sh >>= 1) { t0 += __shfl_xor_sync(0xFFFFFFFFu, t0, sh); t1 += __shfl_xor_sync(0xFFFFFFFFu, t1, sh); }
+                        pending.tot0 = t0; pending.tot1 = t1;
+                    } else {
+                        pending.tot0 = (double)__reduce_add_sync(0xFFFFFFFFu, first_img ? isum : 0u);
+                        pending.tot1 = (double)__reduce_add_sync(0xFFFFFFFFu, first_img ? 0u : isum);
+                    }
+                    pending.img0 = wimg0;
+                    flush_pending(p, pending, lane);
+                } else if (row_ok && dsum != 0.0) {
+                    atomicAdd(p.abs_sums + n_own, dsum);
+                }
+            }
+        }
+        if (lane == 0) bulk_wait_all();                                    // every store of this warp has left shared memory and landed
+        __syncwarp();
     } else {
         // ---- epilogue warps 4-11 (TMEM lane quarter = warp % 4) -------------------------------------------------------
         unsigned a = 0;
@@ -552,11 +772,11 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
             slab_rows<FUSED>(p, R0 + emb * UTM + (warp & 3) * 32, lane, sr);
             float4 res[8];
             bool res_loaded = false;
-            if (FUSED && p.residual != nullptr && (p.KN & 3) == 0 && n0 + ec0 + 32 <= p.KN) {
+            if (FUSED == 2 && (p.KN & 3) == 0 && n0 + ec0 + 32 <= p.KN) {
                 slab_load_residual(p, sr, n0 + ec0, lane, res);
                 res_loaded = true;
             }
-            if (!mbar_wait_warp(accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (status && lane == 0) atomicExch(status, 16); break; }
+            if (!mbar_wait_warp(accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
             tc_fence_after();
             slab_columns<FUSED>(p, tmem_base + buf * ACOLS + (uint32_t)(emb * TNI) + ((uint32_t)((warp & 3) * 32) << 16), sr, n0, ec0, ec1,
                                 lane, sStage + (warp - 4) * 4096, res, res_loaded, pending);
@@ -567,6 +787,12 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const TcConvPa
         }
     }
     tc_fence_before();
+    __syncthreads();
+    if (*deadp != 0) {
+        // a wait ran out in this CTA: give copies and MMAs that may still be in flight time to land before this
+        // CTA frees its tensor memory and its shared memory goes to another CTA (never taken when the protocol is intact)
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+    }
     __syncthreads();
     pdl_launch_dependents();
     if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(2 * ACOLS));
@@ -595,6 +821,11 @@ static EncodeTiledFn encode_tiled_fn() {
 // Encoding a map costs tens of microseconds on the host, more than a small convolution takes on the device, and
 // callers reuse their buffers: the last few maps are kept, keyed by everything that goes into them.
 struct MapKey { const void* base; unsigned long long row_bytes, rows; unsigned box_rows; };
+struct MapKey4 { const void* base; int d[4]; int bw, bh; };
+
+// 4-D float tensor [N][OH][OW][KN] (innermost first: KN, OW, OH, N), box = 32 filters x bw positions x bh rows x 1 image,
+// 128-byte swizzle, out-of-range elements read as zero.  Needs KN % 4 == 0 and a 16-byte aligned base.
+static bool make_map_4d(CUtensorMap* m, const void* base, int KN, int OW, int OH, int N, int bw, int bh);
 static bool make_map_2d(CUtensorMap* m, const void* base, unsigned long long row_bytes, unsigned long long rows, unsigned box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
@@ -618,6 +849,33 @@ static bool make_map_2d(CUtensorMap* m, const void* base, unsigned long long row
            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     keys[next] = MapKey{base, row_bytes, rows, box_rows};
+    maps[next] = *m;
+    next = (next + 1) % NCACHE;
+    if (used < NCACHE) used++;
+    return true;
+}
+
+static bool make_map_4d(CUtensorMap* m, const void* base, int KN, int OW, int OH, int N, int bw, int bh) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    constexpr int NCACHE = 128;
+    static std::mutex mu;
+    static MapKey4 keys[NCACHE] = {};
+    static CUtensorMap maps[NCACHE];
+    static int used = 0, next = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; i++) {
+        const MapKey4& k = keys[i];
+        if (k.base == base && k.d[0] == KN && k.d[1] == OW && k.d[2] == OH && k.d[3] == N && k.bw == bw && k.bh == bh) { *m = maps[i]; return true; }
+    }
+    const cuuint64_t dims[4] = {(cuuint64_t)KN, (cuuint64_t)OW, (cuuint64_t)OH, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)KN * 4, (cuuint64_t)KN * 4 * OW, (cuuint64_t)KN * 4 * OW * OH};
+    const cuuint32_t box[4] = {32, (cuuint32_t)bw, (cuuint32_t)bh, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    keys[next] = MapKey4{base, {KN, OW, OH, N}, bw, bh};
     maps[next] = *m;
     next = (next + 1) % NCACHE;
     if (used < NCACHE) used++;
@@ -649,8 +907,11 @@ int umma_status_read_and_clear() {
     return v;
 }
 
-// Virtual grid of a geometry (see TcConvParams).
-static void set_virtual_grid(TcConvParams& p) {
+// Virtual grid of a geometry (see TcConvParams).  aligned: rows of the grid are stretched so that a 32-row slab is one
+// box of the output tensor - VW a divisor or a multiple of 32, and, where a slab spans several grid rows, VH a multiple
+// of that number (the stretch is more padding, which the expanders and the drop rules already handle).  Returns false
+// when that cannot be had (images of fewer than 32 positions).
+static bool set_virtual_grid(TcConvParams& p, bool aligned) {
     const bool unit = p.s1 == 1 && p.s2 == 1;
     p.PA = p.s1 < p.KH ? p.s1 : p.KH;
     p.PB = p.s2 < p.KW ? p.s2 : p.KW;
@@ -661,59 +922,94 @@ static void set_virtual_grid(TcConvParams& p) {
         p.VH = (p.H + 2 * p.p1 + p.s1 - 1) / p.s1;
         p.VW = (p.W + 2 * p.p2 + p.s2 - 1) / p.s2;
     }
+    p.tepi = 0;
+    if (!aligned) return true;
+    if (p.VW >= 32) {
+        p.VW = (p.VW + 31) / 32 * 32;
+    } else {
+        int w = 1;
+        while (w < p.VW) w *= 2;
+        p.VW = w;
+        const int rows = 32 / w;                                           // grid rows per slab
+        p.VH = (p.VH + rows - 1) / rows * rows;
+    }
+    p.tepi = 1;
+    return true;
 }
 
-// A tile shape with what it needs and what it is expected to cost.
-struct TcPlan { int mt, tn, sb; bool resident; int prow, nrows, nst, smem; long long tiles_m, tiles_n; double cost; };
+// A tile shape and what it needs.
+struct TcPlan { int mt, tn, sb; bool resident; int prow, nrows, nst, smem; long long tiles_m, tiles_n; };
 
-static bool plan_shape(const TcConvParams& p, int mt, int tn, int sb, int sms, bool has_res, TcPlan* out) {
+static bool plan_shape(const TcConvParams& p, int mt, int tn, int sb, TcPlan* out) {
     const long long halo = (long long)((p.KH - 1) / p.s1) * p.VW + (p.KW - 1) / p.s2;
     const long long nrows = 128LL * mt + halo, prow = (nrows + 7) / 8 * 8;
-    const long long fixed = 2 * prow * IROW + 256 + 8 * 4096 + 1024;
-    const long long T = (long long)p.KH * p.KW, ncp = (p.PC + 1) / 2;
-    const long long nres = T * ncp;
+    const long long fixed = 2 * prow * IROW + 1024 + 8 * (p.tepi ? 8192 : 4096) + 1024;   // patches, barriers, epilogue buffers, alignment
+    const long long nres = (long long)p.KH * p.KW * ((p.PC + 1) / 2);
     TcPlan pl;
     pl.mt = mt; pl.tn = tn; pl.sb = sb;
     pl.resident = p.KN <= tn && fixed + nres * tn * IROW <= UMMA_SMEM_MAX;
     const long long smem = pl.resident ? fixed + nres * tn * IROW : fixed + (long long)sb * tn * IROW;
-    if (smem > UMMA_SMEM_MAX || (!pl.resident && T * ncp * p.PA * p.PB < 1)) return false;
+    if (smem > UMMA_SMEM_MAX) return false;
     pl.prow = (int)prow; pl.nrows = (int)nrows; pl.nst = pl.resident ? (int)nres : sb; pl.smem = (int)smem;
     const long long Mv = (long long)(p.N - 1) * p.VH * p.VW + (long long)(p.OH - 1) * p.VW + p.OW;   // last useful virtual row + 1
     pl.tiles_m = (Mv + 128LL * mt - 1) / (128LL * mt);
     pl.tiles_n = (p.KN + tn - 1) / tn;
     if (pl.tiles_m * pl.tiles_n >= (1LL << 31)) return false;
-    // Cost in SM cycles: rounds of tiles x the slowest of a tile's three pipelines (they overlap across tiles):
-    // MMAs (128 x tn x 32 takes 48 / 64 / 128 cycles for tn = 64 / 128 / 256; a ring stage also costs the MMA warp a
-    // handshake and moves tn*128 bytes of filters at about 64 B/clk), the epilogue (output and residual bytes at
-    // about 24 B/clk per SM) and the expanders (about 1.5 cycles per byte of patch with four warps).
-    const double mma_clk = tn == 64 ? 48.0 : (tn == 128 ? 64.0 : 128.0);
-    const double words = (double)p.PC;                                      // K steps of 32 bytes per tap: 2 per word
-    const double mma_tile = (double)T * words * 2.0 * mt * mma_clk;
-    const double stage_over = pl.resident ? 0.0 : (double)T * (double)ncp * std::max(0.0, std::max(300.0 + 45.0 * 4 * mt, tn * 2.0) - 4.0 * mt * mma_clk);
-    const double epi_tile = 128.0 * mt * std::min(tn, p.KN) * 4.0 * (has_res ? 2.0 : 1.0) / 24.0;
-    const double exp_tile = (double)nrows * 64.0 * words * p.PA * p.PB * 1.5 / 64.0 * 1.0;
-    const double tile = std::max(std::max(mma_tile + stage_over, epi_tile), exp_tile) + 600.0;
-    const double rounds = (double)((pl.tiles_m * pl.tiles_n + sms - 1) / sms);
-    pl.cost = rounds * tile + 4000.0;
     *out = pl;
     return true;
 }
 
-// Best tile for a problem; false = no shape fits (very wide images with many taps).
-static bool tc_plan(const TcConvParams& p, int sms, bool has_res, TcPlan* best) {
-    static const int cands[5][3] = {{2, 64, 6}, {1, 64, 6}, {2, 128, 4}, {1, 128, 6}, {1, 256, 4}};
+// Tile for a problem on the grid p holds; false = no shape fits (very wide images with many taps).
+// Measured on the ResNet-18-shaped layers at batch 256 (every shape forced in turn): the widest tile the filter count
+// fills is fastest - the MMA warps pay about 300 cycles per ring stage whatever the stage holds, so wide MMAs amortise
+// it - and two row blocks per tile beat one where they fit (the two MMA warps then issue in parallel).  A problem that
+// gives the SMs less than half a wave of such tiles takes the next narrower tile instead.
+static bool tc_plan(const TcConvParams& p, int sms, TcPlan* best) {
+    static const int cands[5][3] = {{1, 256, 4}, {2, 128, 4}, {1, 128, 6}, {2, 64, 6}, {1, 64, 6}};
+    const int tn0 = p.KN <= 64 ? 64 : (p.KN <= 128 ? 128 : 256);
     bool found = false;
     for (const auto& c : cands) {
-        if (c[1] > 64 && c[1] / 2 >= p.KN) continue;                       // a tile twice as wide as the filter count only wastes
+        if (c[1] > tn0) continue;
         TcPlan pl;
-        if (!plan_shape(p, c[0], c[1], c[2], sms, has_res, &pl)) continue;
-        if (!found || pl.cost < best->cost) { *best = pl; found = true; }
+        if (!plan_shape(p, c[0], c[1], c[2], &pl)) continue;
+        if (!found) { *best = pl; found = true; }
+        if (pl.tiles_m * pl.tiles_n * 2 > sms) { *best = pl; break; }      // enough tiles: take it; else keep looking for more tiles
+        if (pl.tiles_m * pl.tiles_n > best->tiles_m * best->tiles_n) *best = pl;
     }
     return found;
 }
 
-template <int MT, int TNI, int SB, bool BRES, bool FUSED, bool UNIT>
-static int launch_persist_u(const CUtensorMap& tmB, const TcConvParams& p, const TcPlan& pl, int sms, int* status, cudaStream_t stream) {
+static bool grid_in_range(const TcConvParams& p) {
+    const long long rows = (long long)p.N * p.VH * p.VW;
+    return rows < (1LL << 31) - 65536;
+}
+
+// Chooses the virtual grid and the tile.  The TMA epilogue (aligned grid) is taken where it measured faster: layers with
+// a residual whose arithmetic is light against their bytes (at most 64 filters and 1024 terms per output), where the
+// transposing epilogue's residual loads and stores leave the memory system idle half of the time.
+static bool tc_prepare(TcConvParams& p, int sms, TcPlan* pl) {
+    if ((long long)p.N * p.H * p.W >= (1LL << 31) || (long long)p.M >= (1LL << 31) - 512) return false;
+    if ((long long)p.KH * p.KW * p.PC >= (1LL << 20)) return false;
+    const bool tepi_ok = (p.KN & 3) == 0 && !(reinterpret_cast<uintptr_t>(p.y) & 15) && !(reinterpret_cast<uintptr_t>(p.residual) & 15) &&
+                         (long long)p.KN * p.OW * p.OH * 4 < (1LL << 40);
+    const bool tepi_pays = p.residual != nullptr && p.KN <= 64 && (long long)p.KH * p.KW * p.C <= 1024;
+    bool have = false;
+    if (tepi_ok && tepi_pays) {
+        TcConvParams q = p;
+        if (set_virtual_grid(q, true) && grid_in_range(q) && tc_plan(q, sms, pl)) { p = q; have = true; }
+    }
+    if (!have) {
+        set_virtual_grid(p, false);
+        if (!grid_in_range(p) || !tc_plan(p, sms, pl)) return false;
+    }
+    p.dVHW = make_fastdiv((uint32_t)(p.VH * p.VW));
+    p.dVW = make_fastdiv((uint32_t)p.VW);
+    return true;
+}
+
+template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI>
+static int launch_persist_u(const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcConvParams& p, const TcPlan& pl,
+                            int sms, int* status, cudaStream_t stream) {
     static std::mutex mu;
     static bool configured[64] = {};
     int dev = 0;
@@ -722,55 +1018,45 @@ static int launch_persist_u(const CUtensorMap& tmB, const TcConvParams& p, const
     {
         std::lock_guard<std::mutex> lock(mu);
         if (dev < 0 || dev >= 64 || !configured[dev]) {
-            e = cudaFuncSetAttribute(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, UNIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
+            e = cudaFuncSetAttribute(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
             if (e != cudaSuccess) return record_cuda_error(e);
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
     }
     const long long ntiles = pl.tiles_m * pl.tiles_n;
     const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
-    return launch_pdl(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, UNIT>, dim3(grid), dim3(PTHREADS), (size_t)pl.smem, stream,
-                      tmB, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
+    return launch_pdl(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI>, dim3(grid), dim3(PTHREADS), (size_t)pl.smem, stream,
+                      tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
 }
 
 template <int MT, int TNI, int SB>
-static int launch_persist(const CUtensorMap& tmB, const TcConvParams& p, const TcPlan& pl, int sms, int* status, cudaStream_t stream) {
-    const bool fused = p.residual || p.abs_sums;
-    const bool unit = p.s1 == 1 && p.s2 == 1;
-#define TAB_LAUNCH(BR, FU, UN) return launch_persist_u<MT, TNI, SB, BR, FU, UN>(tmB, p, pl, sms, status, stream)
-    if (pl.resident) {
-        if (fused) { if (unit) TAB_LAUNCH(true, true, true); TAB_LAUNCH(true, true, false); }
-        if (unit) TAB_LAUNCH(true, false, true);
-        TAB_LAUNCH(true, false, false);
-    }
-    if (fused) { if (unit) TAB_LAUNCH(false, true, true); TAB_LAUNCH(false, true, false); }
-    if (unit) TAB_LAUNCH(false, false, true);
-    TAB_LAUNCH(false, false, false);
+static int launch_persist(const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcConvParams& p, const TcPlan& pl,
+                          int sms, int* status, cudaStream_t stream) {
+    const int fused = p.residual ? 2 : (p.abs_sums ? 1 : 0);
+    const bool tepi = p.tepi != 0;
+#define TAB_LAUNCH(BR, FU, TE) return launch_persist_u<MT, TNI, SB, BR, FU, TE>(tmB, tmY, tmR, p, pl, sms, status, stream)
+#define TAB_LAUNCH_F(BR, TE) do { if (fused == 2) TAB_LAUNCH(BR, 2, TE); if (fused == 1) TAB_LAUNCH(BR, 1, TE); TAB_LAUNCH(BR, 0, TE); } while (0)
+    if (pl.resident) { if (tepi) TAB_LAUNCH_F(true, true); TAB_LAUNCH_F(true, false); }
+    if (tepi) TAB_LAUNCH_F(false, true);
+    TAB_LAUNCH_F(false, false);
+#undef TAB_LAUNCH_F
 #undef TAB_LAUNCH
 }
 
-// Whether tc_conv_dispatch will take the problem, and - through kernel_name - which tile it would run.
-static bool tc_prepare(TcConvParams& p, int sms, TcPlan* pl) {
-    set_virtual_grid(p);
-    const long long rows = (long long)p.N * p.VH * p.VW;
-    if (rows >= (1LL << 31) - 65536 || (long long)p.N * p.H * p.W >= (1LL << 31) || (long long)p.M >= (1LL << 31) - 512) return false;
-    if ((long long)p.KH * p.KW * p.PC >= (1LL << 20)) return false;
-    p.dVHW = make_fastdiv((uint32_t)(p.VH * p.VW));
-    p.dVW = make_fastdiv((uint32_t)p.VW);
-    return tc_plan(p, sms, p.residual != nullptr, pl);
-}
-
-static thread_local char g_last_kernel[96] = "none";
+static thread_local char g_last_kernel[112] = "none";
 const char* tc_last_kernel() { return g_last_kernel; }
 void tc_forget_last_kernel() { snprintf(g_last_kernel, sizeof(g_last_kernel), "none"); }
+
+static bool operands_aligned(const TcConvParams& p) {
+    return !((reinterpret_cast<uintptr_t>(p.w8) & 15) || (reinterpret_cast<uintptr_t>(p.qx) & (p.abits == 2 ? 15 : 7)));
+}
 
 // Whether tc_conv_dispatch will take the problem (asked before the quantiser is given the weight expansion to do).
 bool tc_conv_covers(TcConvParams p) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     TcPlan pl;
-    if (!encode_tiled_fn() || !tc_prepare(p, sms, &pl)) return false;
-    return !((reinterpret_cast<uintptr_t>(p.w8) & 15) || (reinterpret_cast<uintptr_t>(p.qx) & (p.abits == 2 ? 15 : 7)));
+    return encode_tiled_fn() && operands_aligned(p) && tc_prepare(p, sms, &pl);
 }
 
 // GEMM stage on the tensor cores.  TAB_E_TOO_LARGE when the shape is not covered (the caller falls back to the
@@ -779,16 +1065,21 @@ int tc_conv_dispatch(TcConvParams p, cudaStream_t stream) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     TcPlan pl;
-    if (!encode_tiled_fn() || !tc_prepare(p, sms, &pl)) return TAB_E_TOO_LARGE;
-    if ((reinterpret_cast<uintptr_t>(p.w8) & 15) || (reinterpret_cast<uintptr_t>(p.qx) & (p.abits == 2 ? 15 : 7))) return TAB_E_TOO_LARGE;
-    alignas(64) CUtensorMap tmB;
+    if (!encode_tiled_fn() || !operands_aligned(p) || !tc_prepare(p, sms, &pl)) return TAB_E_TOO_LARGE;
+    alignas(64) CUtensorMap tmB, tmY, tmR;
     if (!make_map_2d(&tmB, p.w8, (unsigned long long)p.Kw * 64, (unsigned long long)p.KN, (unsigned)pl.tn)) return TAB_E_TOO_LARGE;
+    tmY = tmB; tmR = tmB;                                                   // placeholders when the epilogue does not use them
+    if (p.tepi) {
+        const int bw = p.VW >= 32 ? 32 : p.VW, bh = 32 / bw;
+        if (!make_map_4d(&tmY, p.y, p.KN, p.OW, p.OH, p.N, bw, bh)) return TAB_E_TOO_LARGE;
+        if (p.residual && !make_map_4d(&tmR, p.residual, p.KN, p.OW, p.OH, p.N, bw, bh)) return TAB_E_TOO_LARGE;
+    }
     int* status = umma_status_ptr();
-    snprintf(g_last_kernel, sizeof(g_last_kernel), "conv_umma_persist_kernel<%d,%d,%d,%d,%d,%d>", pl.mt, pl.tn, pl.sb, (int)pl.resident,
-             (int)(p.residual || p.abs_sums), (int)(p.s1 == 1 && p.s2 == 1));
-    if (pl.tn == 64) return pl.mt == 2 ? launch_persist<2, 64, 6>(tmB, p, pl, sms, status, stream) : launch_persist<1, 64, 6>(tmB, p, pl, sms, status, stream);
-    if (pl.tn == 128) return pl.mt == 2 ? launch_persist<2, 128, 4>(tmB, p, pl, sms, status, stream) : launch_persist<1, 128, 6>(tmB, p, pl, sms, status, stream);
-    return launch_persist<1, 256, 4>(tmB, p, pl, sms, status, stream);
+    snprintf(g_last_kernel, sizeof(g_last_kernel), "conv_umma_persist_kernel<%d,%d,%d,%d,%d,%d> grid %dx%d", pl.mt, pl.tn, pl.sb, (int)pl.resident,
+             p.residual ? 2 : (p.abs_sums ? 1 : 0), p.tepi, p.VH, p.VW);
+    if (pl.tn == 64) return pl.mt == 2 ? launch_persist<2, 64, 6>(tmB, tmY, tmR, p, pl, sms, status, stream) : launch_persist<1, 64, 6>(tmB, tmY, tmR, p, pl, sms, status, stream);
+    if (pl.tn == 128) return pl.mt == 2 ? launch_persist<2, 128, 4>(tmB, tmY, tmR, p, pl, sms, status, stream) : launch_persist<1, 128, 6>(tmB, tmY, tmR, p, pl, sms, status, stream);
+    return launch_persist<1, 256, 4>(tmB, tmY, tmR, p, pl, sms, status, stream);
 }
 
 }  // namespace tab

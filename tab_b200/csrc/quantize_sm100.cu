@@ -227,15 +227,13 @@ int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* bt
     const bool fast = (C % 64 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0);
     uint64_t* q = reinterpret_cast<uint64_t*>(qx);
     if (fast) {
-        // enough CTAs to fill the device several times over, each looping a few steps
-        long long steps = (wpi + QWORDS_PER_ITER - 1) / QWORDS_PER_ITER;
-        long long per_image = steps;
-        const long long target_total = 148LL * 8 * 4;
-        if ((long long)N * per_image > target_total) {
-            per_image = (target_total + N - 1) / N;
-            if (per_image < 1) per_image = 1;
-            if (per_image > steps) per_image = steps;
-        }
+        // CTAs per image: every CTA the same whole number of 128-word steps (a ragged last step, or a nearly empty extra
+        // wave, costs a whole step's time), at most about six waves of eight CTAs per SM over all images
+        const long long steps = (wpi + QWORDS_PER_ITER - 1) / QWORDS_PER_ITER;
+        const long long cap = 148LL * 8 * 6;
+        const long long iters = ((long long)N * steps + cap - 1) / cap;    // steps per CTA
+        long long per_image = (steps + iters - 1) / iters;
+        if (per_image < 1) per_image = 1;
         dim3 grid((unsigned)per_image, (unsigned)N);
         if (bits == 2) return launch_pdl(quantize_c64_kernel<2>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
         return launch_pdl(quantize_c64_kernel<1>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);

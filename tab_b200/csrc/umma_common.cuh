@@ -8,7 +8,7 @@ namespace tab {
 
 constexpr int UTM = 128;                     // rows of one MMA (= TMEM lanes)
 constexpr int IROW = 128;                    // bytes of K per shared-memory operand row (two 64-channel words)
-constexpr uint32_t UMMA_WAIT_LIMIT = 1u << 20;
+constexpr uint32_t UMMA_WAIT_LIMIT = 1u << 16;       // about a quarter of a second per wait
 constexpr int UMMA_SMEM_MAX = 227 * 1024;    // dynamic shared memory a kernel may ask for (one CTA per SM)
 
 // Exact n / d for 0 <= n < 2^31 by one multiply-high and a shift (d >= 1), set up on the host.
@@ -53,6 +53,7 @@ struct TcConvParams {
     int M, Kw;
     int abits;               // planes of the activations: 2 ternary, 1 binary
     int VH, VW, PA, PB;      // virtual grid of one plane; planes
+    int tepi;                // the grid is aligned for the TMA epilogue: a 32-row slab is one box of the output tensor
     FastDiv dVHW, dVW;
     // Optional tail: the CTA that finishes last turns the sums into the next layer's thresholds,
     // ths_out[n] = ths_scale * abs_sums[n] / per_image, and (self_clean) leaves abs_sums and the counter zero again.
@@ -105,6 +106,28 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  :: "r"(dst), "l"(tmap), "r"(mbar), "r"(x), "r"(y) : "memory");
 }
+// 4-D tiled copies (float tensors [N][OH][OW][KN], innermost coordinate first).  A load fills out-of-range elements of
+// its box with zeros and always delivers the whole box; a store writes only the in-range part of its box.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 :: "r"(dst), "l"(tmap), "r"(mbar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const void* tmap, int c0, int c1, int c2, int c3, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 :: "l"(tmap), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+// Brings a box into L2 ahead of the load that will want it.
+__device__ __forceinline__ void tma_prefetch_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global [%0, {%1, %2, %3, %4}];"
+                 :: "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk-store groups have not finished READING their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+// Waits until all of this thread's bulk-store groups have completed.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Generic-proxy writes to shared memory made visible to the async proxy (the tensor core reads operands through it).
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

@@ -33,21 +33,28 @@ def shard_batch(x: torch.Tensor, ths: torch.Tensor, N: int, world: int, rank: in
     return x.reshape(-1)[lo * per:hi * per], ths.reshape(-1)[lo:hi], hi - lo
 
 
-def gather_output(y_local: torch.Tensor, N: int, world: int, rank: int, group=None) -> torch.Tensor:
+def gather_output(y_local: torch.Tensor, N: int, world: int, rank: int, group=None, per_image: int = None) -> torch.Tensor:
     """All-gather the per-rank output slices (N outermost, so each slice is one contiguous block) into the
     full ``[N, ...]`` buffer on every rank.  Equal shards use one ``all_gather_into_tensor``; ragged
-    shards are padded to the largest shard for the collective and trimmed afterwards."""
-    n_local = shard_bounds(N, world, rank)[1] - shard_bounds(N, world, rank)[0]
-    per = y_local.numel() // n_local if n_local else 0
+    shards are padded to the largest shard for the collective and trimmed afterwards.
+
+    ``per_image`` is the number of elements of one image's output.  Pass it whenever some rank may hold no image
+    (N < world): such a rank cannot derive it from its empty slice.  When it is not passed, every rank takes part in
+    one MAX all-reduce that agrees on it - every rank, so that the sequence of collectives is the same everywhere."""
     counts = [shard_bounds(N, world, r)[1] - shard_bounds(N, world, r)[0] for r in range(world)]
-    if per == 0:
-        # a rank without images cannot know the per-image size: agree on it first
-        t = torch.tensor([per], dtype=torch.int64, device=y_local.device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-        per = int(t.item())
+    n_local = counts[rank]
     flat = y_local.reshape(-1)
     if world == 1:
         return flat.clone()
+    if per_image is None:
+        per = flat.numel() // n_local if n_local else 0
+        t = torch.tensor([per], dtype=torch.int64, device=y_local.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        per = int(t.item())
+    else:
+        per = int(per_image)
+    if flat.numel() != n_local * per:
+        raise ValueError("rank %d holds %d elements, expected %d images x %d" % (rank, flat.numel(), n_local, per))
     if len(set(counts)) == 1:
         out = torch.empty(N * per, dtype=y_local.dtype, device=y_local.device)
         dist.all_gather_into_tensor(out, flat.contiguous(), group=group)
@@ -69,4 +76,6 @@ def conv2d_data_parallel(conv_fn, X, QW, thresholds, btn, conv_type, p1, p2, s1,
     y_local = conv_fn(xs, QW, ts, btn, conv_type, p1, p2, s1, s2, n_local, H, W, C, KN, KH, KW)
     if not gather:
         return y_local
-    return gather_output(y_local, N, world, rank, group)
+    oh = max((H + 2 * p1 - KH + 1) // s1, 0)
+    ow = max((W + 2 * p2 - KW + 1) // s2, 0)
+    return gather_output(y_local, N, world, rank, group, per_image=oh * ow * KN)

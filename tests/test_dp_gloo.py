@@ -33,6 +33,12 @@ def _worker(rank, world, port, N, result_dir):
             full = dp.conv2d_data_parallel(torch_cpu_conv, torch.from_numpy(x), torch.from_numpy(qw), torch.from_numpy(ths),
                                            torch.from_numpy(btn), t, 1, 1, 1, 2, N, H, W, C, KN, K, K, world, rank)
             np.save(os.path.join(result_dir, "y_t%d_r%d.npy" % (t, rank)), full.numpy())
+            if t == 0:
+                # the gather alone, without the per-image size: every rank must take part in the agreeing all-reduce
+                lo, hi = dp.shard_bounds(N, world, rank)
+                per = full.numel() // N
+                again = dp.gather_output(full.reshape(N, per)[lo:hi].contiguous(), N, world, rank)
+                assert torch.equal(again, full)
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -58,3 +64,8 @@ def test_equal_shards(tmp_path):
 
 def test_ragged_shards(tmp_path):
     _run(5, tmp_path)
+
+
+def test_fewer_images_than_ranks(tmp_path):
+    """N = 1 on two ranks: rank 1 holds nothing and still issues the same collectives as rank 0."""
+    _run(1, tmp_path)
