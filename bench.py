@@ -255,9 +255,10 @@ class ClockSampler:
 
 
 def step_algorithmic_bytes(n_images):
-    """Bytes every launch of one step must move, summed: per convolution input 4 B/element read and 2 bits/element written by
-    the quantiser; per convolution those bit-planes read, the byte weights read, 4 B/element of output written and, where a
-    shortcut is added, 4 B/element of residual read; the input statistics pass reads x once."""
+    """Bytes every launch of one step must move, summed: per convolution input its elements read (4 B each; 2 B where the
+    producer handed it over as int16) and 2 bits/element written by the quantiser; per convolution those bit-planes read, the
+    byte weights read, the output written (4 B/element; 2 B for a block's first convolution, whose only reader is the next
+    quantiser) and, where a shortcut is added, 4 B/element of residual read; the input statistics pass reads x once."""
     from tab_b200 import chain
     total = 4 * n_images * H0 * W0 * C0
     h = H0
@@ -267,10 +268,10 @@ def step_algorithmic_bytes(n_images):
         x_el, y_el = n_images * h * h * a.C, n_images * oh * oh * a.KN
         bits_in, bits_mid = x_el // 4, y_el // 4
         total += 4 * x_el + bits_in                                        # quantise x
-        total += bits_in + a.KN * 9 * a.C + 4 * y_el                       # conv_a
+        total += bits_in + a.KN * 9 * a.C + 2 * y_el                       # conv_a, int16 out
         if sc is not None:
             total += bits_in + sc.KN * sc.C + 4 * y_el                     # shortcut on the same bit-planes
-        total += 4 * y_el + bits_mid                                       # quantise y1
+        total += 2 * y_el + bits_mid                                       # quantise y1 (int16)
         total += bits_mid + bb.KN * 9 * bb.C + 4 * y_el + 4 * y_el         # conv_b + residual
         h = oh
     return total
@@ -335,13 +336,16 @@ def main():
 
         def quantize(self, x, thresholds):
             n, h, w = (int(v) for v in x.shape[:3])
-            return TAB_CUDA.Quantize(x, thresholds, tab_nn.act_bitwidth(self.c.conv_type), n, h, w, self.c.C)[0]
+            ab = tab_nn.act_bitwidth(self.c.conv_type)
+            if x.dtype == torch.int16:
+                return TAB_CUDA.QuantizeI16(x, thresholds, ab, n, h, w, self.c.C)
+            return TAB_CUDA.Quantize(x, thresholds, ab, n, h, w, self.c.C)[0]
 
-        def conv_bits(self, QX, n, h, w, residual, scale):
+        def conv_bits(self, QX, n, h, w, residual, scale, out_int16=False):
             if scale is not None and (self.state is None or self.state.numel() < lib.tab_conv2d_state_bytes(n)):
                 self.state = TAB_CUDA.NewState(QX, n)
             y, nxt = TAB_CUDA.Conv2dBits(QX, self.W8, self.c.conv_type, *self.c.geometry(n, h, w), residual,
-                                         self.state if scale is not None else None, scale if scale is not None else 0.0)
+                                         self.state if scale is not None else None, scale if scale is not None else 0.0, bool(out_int16))
             return y.view(n, y.shape[2], y.shape[3], y.shape[1]), (nxt if scale is not None else None)
 
     def nhwc(y):                                             # Conv2d's {N,KN,OH,OW} label over the [N][OH][OW][KN] buffer
@@ -368,7 +372,7 @@ def main():
         if count:
             launches[0] += 2
         ths = tab_ops.residual_threshold(x_in.reshape(nb, -1), None, chain.THRESHOLD_SCALE)      # reduce + finalise kernels
-        y, _, _, _ = chain.forward_prepared(cset, x_in, ths, nb)
+        y, _, _, _ = chain.forward_prepared(cset, x_in, ths, nb, compact_mid=True)
         return y, ths
 
     def barrier():
@@ -624,17 +628,28 @@ def main():
             btn = torch.empty(n_local, dtype=torch.int32, device=dev)
             geom = conv.geometry(n_local, ih, ih)
             chained = cs.K == 3                                             # the 3x3 convolutions feed thresholds, the shortcuts do not
-            ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_bits_launch(
-                qx.data_ptr(), conv.W8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, res.data_ptr() if has_res else None,
-                state.data_ptr() if chained else None, nxt.data_ptr() if chained else None, 0.7, stream), "bits"))
+            compact = chained and not has_res                               # a block's first convolution hands int16 to the next quantiser
+            if compact:
+                y16 = torch.empty(n_local * oh * oh * cs.KN, dtype=torch.int16, device=dev)
+                ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_bits_i16_launch(
+                    qx.data_ptr(), conv.W8.data_ptr(), y16.data_ptr(), CONV_TYPE, *geom, state.data_ptr(), nxt.data_ptr(), 0.7, stream), "bits16"))
+            else:
+                ms_gemm = time_launch(lambda: _cabi.check(lib.tab_conv2d_bits_launch(
+                    qx.data_ptr(), conv.W8.data_ptr(), yb.data_ptr(), CONV_TYPE, *geom, res.data_ptr() if has_res else None,
+                    state.data_ptr() if chained else None, nxt.data_ptr() if chained else None, 0.7, stream), "bits"))
             kernel = lib.tab_last_conv_kernel().decode()
-            ms_quant = time_launch(lambda: _cabi.check(lib.tab_quantize_launch(xin.data_ptr(), ths.data_ptr(), qx.data_ptr(), None, 2,
-                                                                                n_local, ih, ih, cs.C, stream), "quantize"))
+            if has_res:                                                     # a block's second convolution quantises the first one's int16 output
+                x16 = torch.round(xin * 8).to(torch.int16)
+                ms_quant = time_launch(lambda: _cabi.check(lib.tab_quantize_i16_launch(x16.data_ptr(), ths.data_ptr(), qx.data_ptr(), 2,
+                                                                                        n_local, ih, ih, cs.C, stream), "quantize16"))
+            else:
+                ms_quant = time_launch(lambda: _cabi.check(lib.tab_quantize_launch(xin.data_ptr(), ths.data_ptr(), qx.data_ptr(), None, 2,
+                                                                                    n_local, ih, ih, cs.C, stream), "quantize"))
             ms_popc = time_launch(lambda: _cabi.check(lib.tab_conv2d_packed_launch(qx.data_ptr(), conv.QW.data_ptr(), conv.BTN_W.data_ptr(), yb.data_ptr(),
                                                                                     CONV_TYPE, *geom, stream), "popc"))
             lops = 2 * n_local * oh * oh * cs.KN * cs.K * cs.K * cs.C
-            gemm_bytes = qx.numel() * 8 + conv.W8.numel() + 4 * yb.numel() * (2 if has_res else 1)
-            quant_bytes = 4 * xin.numel() + qx.numel() * 8
+            gemm_bytes = qx.numel() * 8 + conv.W8.numel() + (2 * yb.numel() if compact else 4 * yb.numel() * (2 if has_res else 1))
+            quant_bytes = (2 if has_res else 4) * xin.numel() + qx.numel() * 8
             sums["gemm_ms"] += ms_gemm; sums["popc_ms"] += ms_popc; sums["ops"] += lops; sums["gemm_bytes"] += gemm_bytes
             if cs.K == 3:                                                   # the shortcut reuses conv_a's bit-planes: no quantiser launch of its own
                 sums["quant_ms"] += ms_quant; sums["quant_bytes"] += quant_bytes

@@ -166,6 +166,20 @@ size_t tab_conv2d_state_bytes(int N);
 int tab_conv2d_bits_launch(const int64_t* qx, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
                            int N, int H, int W, int C, int KN, int KH, int KW,
                            const float* residual, void* state, float* next_ths, float next_scale, tab_stream_t stream);
+/*
+ * Compact intermediate for chained layers (no counterpart in the reference, whose every tensor between layers is fp32):
+ * a convolution's result is integer-valued with |y| <= KH*KW*C, so where its only reader is the next layer's quantiser it
+ * can travel as int16 - half the bytes written and read back.  The results are the same numbers.
+ *   tab_conv2d_bits_i16_launch   tab_conv2d_bits_launch without a residual, writing int16 [N][OH][OW][KN] (16-byte aligned);
+ *                                TAB_E_TOO_LARGE when KH*KW*C > 32767
+ *   tab_quantize_i16_launch      tab_quantize_launch on such a tensor (same compares, on the integers converted to float);
+ *                                no btn output
+ */
+int tab_conv2d_bits_i16_launch(const int64_t* qx, const int8_t* w8, int16_t* y16, int type, int p1, int p2, int s1, int s2,
+                               int N, int H, int W, int C, int KN, int KH, int KW,
+                               void* state, float* next_ths, float next_scale, tab_stream_t stream);
+int tab_quantize_i16_launch(const int16_t* x, const float* ths, int64_t* qx, int bitwidth, int N, int H, int W, int C,
+                            tab_stream_t stream);
 
 /*
  * tab_conv2d_launch without a workspace argument.  No counterpart in the reference (its host code calls

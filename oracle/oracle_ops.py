@@ -55,7 +55,7 @@ class OraclePreparedConv:
         N, H, W = x.shape[:3]
         return (np.ascontiguousarray(x, dtype=np.float32), np.asarray(ths, dtype=np.float32), N, H, W)     # the oracle quantises inside conv2d
 
-    def conv_bits(self, qx, N, H, W, residual=None, next_threshold_scale=None):
+    def conv_bits(self, qx, N, H, W, residual=None, next_threshold_scale=None, out_int16=False):
         x, ths, _, _, _ = qx
         cs = self.cs
         y = c_oracle.conv2d(x.reshape(-1), self.qw, ths, self.btn, self.t, cs.pad, cs.pad, cs.stride, cs.stride, N, H, W, cs.C, cs.KN, cs.K, cs.K)
@@ -64,4 +64,5 @@ class OraclePreparedConv:
             if residual is not None:
                 y += np.asarray(residual, dtype=np.float32).reshape(y.shape)
             return y, None
-        return y, OracleOps.residual_threshold(y, residual, next_threshold_scale)
+        nxt = OracleOps.residual_threshold(y, residual, next_threshold_scale)
+        return (y.astype(np.int16) if out_int16 and residual is None else y), nxt

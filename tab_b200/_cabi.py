@@ -29,6 +29,8 @@ SYMBOLS = {
     "tab_expand_weights_launch": (_c.c_int, [_c.c_void_p] * 2 + [_c.c_int] * 5 + [_c.c_void_p]),
     "tab_conv2d_state_bytes": (_c.c_size_t, [_c.c_int]),
     "tab_conv2d_bits_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p] * 3 + [_c.c_float, _c.c_void_p]),
+    "tab_conv2d_bits_i16_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p] * 2 + [_c.c_float, _c.c_void_p]),
+    "tab_quantize_i16_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 5 + [_c.c_void_p]),
     "tab_last_conv_kernel": (_c.c_char_p, []),
     "tab_device_status": (_c.c_int, []),
     "tab_conv2d_static_launch": (_c.c_int, [_c.c_void_p] * 5 + [_c.c_int] * 12 + [_c.c_void_p]),

@@ -142,11 +142,14 @@ def forward(ops, x, ths, qweights, conv_type: int, N: int, H: int = 56, W: int =
     return x, h, w, resnet18_blocks()[-1].conv_b.KN
 
 
-def forward_prepared(convs, x, ths, N: int, H: int = 56, W: int = 56):
+def forward_prepared(convs, x, ths, N: int, H: int = 56, W: int = 56, compact_mid: bool = False):
     """The same chain on prepared convolutions: ``convs`` maps a layer name to an object with
     ``quantize(x, thresholds) -> QX`` and ``conv_bits(QX, N, H, W, residual, next_threshold_scale) -> (Y, next_ths)``
     (``tab_b200.nn.TABConv2d``: weights quantised and expanded once).  Every convolution input is quantised once:
     a block's first convolution and its strided shortcut read the same bit-planes (same input, same thresholds).
+    ``compact_mid``: a block's first convolution hands its result to the second one's quantiser as int16 (it is
+    integer-valued and nothing else reads it), half the bytes of fp32; the convolution objects must accept
+    ``conv_bits(..., out_int16=True)`` and int16 input to ``quantize``.
     Returns ``(y, OH, OW, KN)`` like ``forward``; the results are identical."""
     h, w = H, W
     for b in resnet18_blocks():
@@ -154,7 +157,7 @@ def forward_prepared(convs, x, ths, N: int, H: int = 56, W: int = 56):
         oh, ow = (h + 2 * b.conv_a.pad - b.conv_a.K + 1) // b.conv_a.stride, (w + 2 * b.conv_a.pad - b.conv_a.K + 1) // b.conv_a.stride
         qx = a.quantize(x, ths)
         short = x if sc is None else sc.conv_bits(qx, N, h, w, None, None)[0]
-        y1, t1 = a.conv_bits(qx, N, h, w, None, THRESHOLD_SCALE)
+        y1, t1 = a.conv_bits(qx, N, h, w, None, THRESHOLD_SCALE, out_int16=True) if compact_mid else a.conv_bits(qx, N, h, w, None, THRESHOLD_SCALE)
         y2, ths = bb.conv_bits(bb.quantize(y1, t1), N, oh, ow, short, THRESHOLD_SCALE)     # y2 = conv + shortcut
         x, h, w = y2, oh, ow
     return x, h, w, resnet18_blocks()[-1].conv_b.KN

@@ -228,9 +228,10 @@ int tab_expand_weights_launch(const int64_t* qw, int8_t* w8, int bitwidth, int K
 
 size_t tab_conv2d_state_bytes(int N) { return N < 0 ? 0 : round256((size_t)N * 8 + 8); }
 
-int tab_conv2d_bits_launch(const int64_t* qx, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
-                           int N, int H, int W, int C, int KN, int KH, int KW,
-                           const float* residual, void* state, float* next_ths, float next_scale, tab_stream_t stream) {
+// Shared by the two GEMM-stage entry points: y (float) or y16 (int16) receives the result.
+static int bits_impl(const int64_t* qx, const int8_t* w8, float* y, int16_t* y16, int type, int p1, int p2, int s1, int s2,
+                     int N, int H, int W, int C, int KN, int KH, int KW,
+                     const float* residual, void* state, float* next_ths, float next_scale, tab_stream_t stream) {
     int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
     if (rc != TAB_OK) return rc;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
@@ -243,11 +244,13 @@ int tab_conv2d_bits_launch(const int64_t* qx, const int8_t* w8, float* y, int ty
         }
         return TAB_OK;
     }
-    if (!qx || !w8 || !y) return TAB_E_NULL_POINTER;
-    if (misaligned(qx, 15) || misaligned(w8, 15) || misaligned(y, 15) || misaligned(residual, 15) || misaligned(state, 7) || misaligned(next_ths, 3))
+    if (!qx || !w8 || (!y && !y16)) return TAB_E_NULL_POINTER;
+    if (misaligned(qx, 15) || misaligned(w8, 15) || misaligned(y, 15) || misaligned(y16, 15) || misaligned(residual, 15) || misaligned(state, 7) ||
+        misaligned(next_ths, 3))
         return TAB_E_ALIGNMENT;
+    if (y16 && (long long)KH * KW * C > 32767) return TAB_E_TOO_LARGE;   // |y| <= KH*KW*C must fit 16 bits
     TcConvParams p = tc_geometry(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, oh, ow);
-    p.qx = reinterpret_cast<const uint64_t*>(qx); p.w8 = w8; p.y = y; p.residual = residual;
+    p.qx = reinterpret_cast<const uint64_t*>(qx); p.w8 = w8; p.y = y; p.y16 = y16; p.residual = residual;
     if (next_ths) {
         p.abs_sums = reinterpret_cast<double*>(state);
         p.done_counter = reinterpret_cast<unsigned*>(reinterpret_cast<double*>(state) + N);
@@ -255,6 +258,27 @@ int tab_conv2d_bits_launch(const int64_t* qx, const int8_t* w8, float* y, int ty
     }
     tc_forget_last_kernel();
     return tc_conv_dispatch(p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int tab_conv2d_bits_launch(const int64_t* qx, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
+                           int N, int H, int W, int C, int KN, int KH, int KW,
+                           const float* residual, void* state, float* next_ths, float next_scale, tab_stream_t stream) {
+    return bits_impl(qx, w8, y, nullptr, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, residual, state, next_ths, next_scale, stream);
+}
+
+int tab_conv2d_bits_i16_launch(const int64_t* qx, const int8_t* w8, int16_t* y16, int type, int p1, int p2, int s1, int s2,
+                               int N, int H, int W, int C, int KN, int KH, int KW,
+                               void* state, float* next_ths, float next_scale, tab_stream_t stream) {
+    return bits_impl(qx, w8, nullptr, y16, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, nullptr, state, next_ths, next_scale, stream);
+}
+
+int tab_quantize_i16_launch(const int16_t* x, const float* ths, int64_t* qx, int bitwidth, int N, int H, int W, int C, tab_stream_t stream) {
+    if (!dims_ok(N, H, W, C) || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
+    if ((long long)N * H * W == 0) return TAB_OK;
+    if (!x || !ths || !qx) return TAB_E_NULL_POINTER;
+    if (misaligned(x, 1) || misaligned(ths, 3) || misaligned(qx, 7)) return TAB_E_ALIGNMENT;
+    if ((long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
+    return quantize_dispatch(x, ths, qx, nullptr, bitwidth == 1 ? 1 : 2, N, H, W, C, reinterpret_cast<cudaStream_t>(stream), nullptr, true);
 }
 
 }  // extern "C"

@@ -241,6 +241,23 @@ __device__ __forceinline__ void slab_columns(const TcConvParams& p, uint32_t tad
             }
             if (has_res && !res_loaded) slab_load_residual(p, sr, nbase, lane, res);
             __syncwarp();
+            if (!has_res && p.y16 != nullptr) {                            // compact output: the integers themselves, 16 bits each
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int r = 4 * i + rsub;
+                    const int4 raw = lds_v4(stage + r * 128 + ((chunk ^ (r & 7)) << 4));
+                    if (sr.mi[i] >= 0) {
+                        reinterpret_cast<uint2*>(p.y16 + (long long)sr.mi[i] * p.KN + nbase)[chunk] =
+                            make_uint2(__byte_perm((uint32_t)raw.x, (uint32_t)raw.y, 0x5410), __byte_perm((uint32_t)raw.z, (uint32_t)raw.w, 0x5410));
+                        if (sr.slow) {
+                            const int img = (int)p.dVHW.div((uint32_t)(sr.Rw + r));
+                            if (img < p.N) atomicAdd(p.abs_sums + img, (double)abs(raw.x) + (double)abs(raw.y) + (double)abs(raw.z) + (double)abs(raw.w));
+                        }
+                    }
+                }
+                __syncwarp();
+                continue;
+            }
             float4 o[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -299,7 +316,8 @@ __device__ __forceinline__ void slab_columns(const TcConvParams& p, uint32_t tad
                     if (nbase + i < p.KN) {
                         float ov = (float)(int)v[i];
                         if (rrow) ov += __ldg(rrow + nbase + i);
-                        yrow[nbase + i] = ov;
+                        if (!has_res && p.y16 != nullptr) p.y16[(long long)sr.m_own * p.KN + nbase + i] = (int16_t)(int)v[i];
+                        else yrow[nbase + i] = ov;
                         if (FUSED) rsum += (double)fabsf(ov);
                     }
                 }
@@ -992,7 +1010,7 @@ static bool tc_prepare(TcConvParams& p, int sms, TcPlan* pl) {
     if ((long long)p.KH * p.KW * p.PC >= (1LL << 20)) return false;
     const bool tepi_ok = (p.KN & 3) == 0 && !(reinterpret_cast<uintptr_t>(p.y) & 15) && !(reinterpret_cast<uintptr_t>(p.residual) & 15) &&
                          (long long)p.KN * p.OW * p.OH * 4 < (1LL << 40);
-    const bool tepi_pays = p.residual != nullptr && p.KN <= 64 && (long long)p.KH * p.KW * p.C <= 1024;
+    const bool tepi_pays = p.residual != nullptr && p.y16 == nullptr && p.KN <= 64 && (long long)p.KH * p.KW * p.C <= 1024;
     bool have = false;
     if (tepi_ok && tepi_pays) {
         TcConvParams q = p;

@@ -84,6 +84,23 @@ __device__ __forceinline__ void quant_prologue(const QuantExtras& ex, int n) {
     }
 }
 
+// Eight consecutive channels held as 16-bit integers (the compact output of a convolution): one 128-bit load.
+struct u4 { uint32_t a, b, c, d; };
+__device__ __forceinline__ u4 ld_stream_u4(const int16_t* p) {
+    u4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.a), "=r"(r.b), "=r"(r.c), "=r"(r.d) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ f8 i16x8_to_f8(const u4& q) {
+    const uint32_t a = q.a, b = q.b, c = q.c, d = q.d;
+    f8 r;
+    r.v[0] = (float)(int16_t)(a & 0xFFFFu); r.v[1] = (float)(int16_t)(a >> 16);
+    r.v[2] = (float)(int16_t)(b & 0xFFFFu); r.v[3] = (float)(int16_t)(b >> 16);
+    r.v[4] = (float)(int16_t)(c & 0xFFFFu); r.v[5] = (float)(int16_t)(c >> 16);
+    r.v[6] = (float)(int16_t)(d & 0xFFFFu); r.v[7] = (float)(int16_t)(d >> 16);
+    return r;
+}
+
 // 256-bit streaming load (sm_100): a lane reads 8 consecutive channels, a warp 1 KB contiguous.
 __device__ __forceinline__ f8 ld_stream_f8(const float* p) {
     f8 r;
@@ -96,9 +113,10 @@ __device__ __forceinline__ f8 ld_stream_f8(const float* p) {
 // grid = (ctas_per_image, N).  words_per_image = H*W*PC with PC = C/64.
 // Eight lanes own one 64-channel word: lane b of the group quantises channels 8b..8b+7 and stores byte b
 // of the sign and of the magnitude word itself, so no cross-lane traffic is needed at all.
-template <int BITS>
+// IN16: x holds 16-bit integers instead of floats (same element order).
+template <int BITS, bool IN16>
 __global__ void __launch_bounds__(QTHREADS)
-quantize_c64_kernel(const float* __restrict__ x, const float* __restrict__ ths,
+quantize_c64_kernel(const void* __restrict__ x, const float* __restrict__ ths,
                     uint64_t* __restrict__ qx, int* __restrict__ btn, long long words_per_image, const QuantExtras ex) {
     const int n = blockIdx.y;
     quant_prologue(ex, n);
@@ -106,28 +124,36 @@ quantize_c64_kernel(const float* __restrict__ x, const float* __restrict__ ths,
     const float nt = -t;
     const int byte = threadIdx.x & 7;
     const int grp = threadIdx.x >> 3;                         // word slot within the CTA: 0..31
-    const float* xi = x + (long long)n * words_per_image * 64;
+    const float* xi = reinterpret_cast<const float*>(x) + (IN16 ? 0 : (long long)n * words_per_image * 64);
+    const int16_t* xs = reinterpret_cast<const int16_t*>(x) + (IN16 ? (long long)n * words_per_image * 64 : 0);
     unsigned char* qi = reinterpret_cast<unsigned char*>(qx + (long long)n * words_per_image * BITS);
     int cnt = 0;
 
-    for (long long w0 = (long long)blockIdx.x * QWORDS_PER_ITER; w0 < words_per_image;
-         w0 += (long long)gridDim.x * QWORDS_PER_ITER) {
-        f8 v[QUNROLL];
-        long long w[QUNROLL];
+    // 16-bit input halves the bytes of a load: twice as many loads in flight keep the same bytes in flight
+    constexpr int UN = IN16 ? 2 * QUNROLL : QUNROLL;
+    constexpr int WORDS = (QTHREADS / 8) * UN;
+    for (long long w0 = (long long)blockIdx.x * WORDS; w0 < words_per_image; w0 += (long long)gridDim.x * WORDS) {
+        f8 v[IN16 ? 1 : UN];
+        u4 raw[IN16 ? UN : 1];                                 // 16-bit input: converted only when used, after every load is issued
+        long long w[UN];
 #pragma unroll
-        for (int u = 0; u < QUNROLL; u++) {
+        for (int u = 0; u < UN; u++) {
             w[u] = w0 + u * (QTHREADS / 8) + grp;
-            if (w[u] < words_per_image) v[u] = ld_stream_f8(xi + w[u] * 64 + byte * 8);
+            if (w[u] < words_per_image) {
+                if (IN16) raw[u] = ld_stream_u4(xs + w[u] * 64 + byte * 8);
+                else v[u] = ld_stream_f8(xi + w[u] * 64 + byte * 8);
+            }
         }
 #pragma unroll
-        for (int u = 0; u < QUNROLL; u++) {
+        for (int u = 0; u < UN; u++) {
             if (w[u] >= words_per_image) continue;
+            const f8 val = IN16 ? i16x8_to_f8(raw[IN16 ? u : 0]) : v[IN16 ? 0 : u];
             if (BITS == 2) {
                 unsigned pos = 0, neg = 0;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    pos |= (v[u].v[i] > t) ? (1u << i) : 0u;
-                    neg |= (v[u].v[i] < nt) ? (1u << i) : 0u;
+                    pos |= (val.v[i] > t) ? (1u << i) : 0u;
+                    neg |= (val.v[i] < nt) ? (1u << i) : 0u;
                 }
                 neg &= ~pos;                                   // the "+1" branch is tested first
                 const unsigned mag = pos | neg;
@@ -138,7 +164,7 @@ quantize_c64_kernel(const float* __restrict__ x, const float* __restrict__ ths,
             } else {
                 unsigned b = 0;
 #pragma unroll
-                for (int i = 0; i < 8; i++) b |= (v[u].v[i] < t) ? (1u << i) : 0u;
+                for (int i = 0; i < 8; i++) b |= (val.v[i] < t) ? (1u << i) : 0u;
                 qi[w[u] * 8 + byte] = (unsigned char)b;
             }
         }
@@ -160,9 +186,9 @@ quantize_c64_kernel(const float* __restrict__ x, const float* __restrict__ ths,
 }
 
 // One warp per output word; works for every C and alignment.  grid = (ctas_per_image, N).
-template <int BITS>
+template <int BITS, bool IN16>
 __global__ void __launch_bounds__(QTHREADS)
-quantize_generic_kernel(const float* __restrict__ x, const float* __restrict__ ths,
+quantize_generic_kernel(const void* __restrict__ x, const float* __restrict__ ths,
                         uint64_t* __restrict__ qx, int* __restrict__ btn,
                         long long pixels_per_image, int C, int PC, const QuantExtras ex) {
     const int n = blockIdx.y;
@@ -172,7 +198,8 @@ quantize_generic_kernel(const float* __restrict__ x, const float* __restrict__ t
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const long long words_per_image = pixels_per_image * PC;
-    const float* xi = x + (long long)n * pixels_per_image * C;
+    const float* xi = reinterpret_cast<const float*>(x) + (IN16 ? 0 : (long long)n * pixels_per_image * C);
+    const int16_t* xs = reinterpret_cast<const int16_t*>(x) + (IN16 ? (long long)n * pixels_per_image * C : 0);
     uint64_t* qi = qx + (long long)n * words_per_image * BITS;
     int cnt = 0;
 
@@ -182,9 +209,10 @@ quantize_generic_kernel(const float* __restrict__ x, const float* __restrict__ t
         const int pc = (int)(w - pix * PC);
         const int c0 = pc * 64 + lane, c1 = c0 + 32;
         const float* row = xi + pix * C;
+        const int16_t* rows = xs + pix * C;
         const bool in0 = c0 < C, in1 = c1 < C;
-        const float a = in0 ? __ldg(row + c0) : 0.f;
-        const float b = in1 ? __ldg(row + c1) : 0.f;
+        const float a = in0 ? (IN16 ? (float)__ldg(rows + c0) : __ldg(row + c0)) : 0.f;
+        const float b = in1 ? (IN16 ? (float)__ldg(rows + c1) : __ldg(row + c1)) : 0.f;
         if (BITS == 2) {
             const bool pa = in0 && a > t, pb = in1 && b > t;
             const bool na = in0 && !pa && a < nt, nb = in1 && !pb && b < nt;
@@ -206,8 +234,8 @@ quantize_generic_kernel(const float* __restrict__ x, const float* __restrict__ t
     pdl_launch_dependents();
 }
 
-int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* btn, int bits,
-                      int N, int H, int W, int C, cudaStream_t stream, const QuantExtras* extras) {
+int quantize_dispatch(const void* x, const float* ths, int64_t* qx, int32_t* btn, int bits,
+                      int N, int H, int W, int C, cudaStream_t stream, const QuantExtras* extras, bool in16) {
     const QuantExtras ex = extras ? *extras : QuantExtras{};
     const long long pixels = (long long)H * W;
     const int PC = (C + 63) / 64;
@@ -217,26 +245,31 @@ int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* bt
         // grid.y is limited to 65535: process in slabs of images.
         for (int n0 = 0; n0 < N; n0 += 65535) {
             const int nn = (N - n0 < 65535) ? (N - n0) : 65535;
-            int rc = quantize_dispatch(x + (long long)n0 * pixels * C, ths + n0,
+            int rc = quantize_dispatch(reinterpret_cast<const char*>(x) + (long long)n0 * pixels * C * (in16 ? 2 : 4), ths + n0,
                                        qx + (long long)n0 * wpi * bits, btn ? btn + n0 : nullptr,
-                                       bits, nn, H, W, C, stream, n0 == 0 ? extras : nullptr);
+                                       bits, nn, H, W, C, stream, n0 == 0 ? extras : nullptr, in16);
             if (rc != TAB_OK) return rc;
         }
         return TAB_OK;
     }
-    const bool fast = (C % 64 == 0) && ((reinterpret_cast<uintptr_t>(x) & 31) == 0);
+    const bool fast = (C % 64 == 0) && ((reinterpret_cast<uintptr_t>(x) & (in16 ? 15 : 31)) == 0);
     uint64_t* q = reinterpret_cast<uint64_t*>(qx);
     if (fast) {
         // CTAs per image: every CTA the same whole number of 128-word steps (a ragged last step, or a nearly empty extra
         // wave, costs a whole step's time), at most about six waves of eight CTAs per SM over all images
-        const long long steps = (wpi + QWORDS_PER_ITER - 1) / QWORDS_PER_ITER;
+        const long long words_per_step = in16 ? 2 * QWORDS_PER_ITER : QWORDS_PER_ITER;
+        const long long steps = (wpi + words_per_step - 1) / words_per_step;
         const long long cap = 148LL * 8 * 6;
         const long long iters = ((long long)N * steps + cap - 1) / cap;    // steps per CTA
         long long per_image = (steps + iters - 1) / iters;
         if (per_image < 1) per_image = 1;
         dim3 grid((unsigned)per_image, (unsigned)N);
-        if (bits == 2) return launch_pdl(quantize_c64_kernel<2>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
-        return launch_pdl(quantize_c64_kernel<1>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
+        if (in16) {
+            if (bits == 2) return launch_pdl(quantize_c64_kernel<2, true>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
+            return launch_pdl(quantize_c64_kernel<1, true>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
+        }
+        if (bits == 2) return launch_pdl(quantize_c64_kernel<2, false>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
+        return launch_pdl(quantize_c64_kernel<1, false>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, wpi, ex);
     } else {
         long long steps = (wpi + (QTHREADS / 32) - 1) / (QTHREADS / 32);
         long long per_image = steps;
@@ -247,8 +280,12 @@ int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* bt
             if (per_image > steps) per_image = steps;
         }
         dim3 grid((unsigned)per_image, (unsigned)N);
-        if (bits == 2) return launch_pdl(quantize_generic_kernel<2>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
-        return launch_pdl(quantize_generic_kernel<1>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
+        if (in16) {
+            if (bits == 2) return launch_pdl(quantize_generic_kernel<2, true>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
+            return launch_pdl(quantize_generic_kernel<1, true>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
+        }
+        if (bits == 2) return launch_pdl(quantize_generic_kernel<2, false>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
+        return launch_pdl(quantize_generic_kernel<1, false>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
     }
 }
 

@@ -140,6 +140,21 @@ torch::Tensor TAB_ExpandWeights(torch::Tensor QW, int bitwidth, int KN, int KH, 
     return W8;
 }
 
+// QuantizeI16: Quantize on the int16 tensor Conv2dBits(..., out_int16 = true) returned; returns QX only.
+torch::Tensor TAB_QuantizeI16(torch::Tensor X16, torch::Tensor thresholds, int bitwidth, int N, int H, int W, int C) {
+    CHECK_INPUT(X16);
+    CHECK_INPUT(thresholds);
+    TORCH_CHECK(X16.scalar_type() == torch::kInt16, "X16 must have dtype torch.int16");
+    TORCH_CHECK(thresholds.scalar_type() == torch::kFloat32, "thresholds must have dtype torch.float32");
+    TORCH_CHECK(N >= 0 && H >= 0 && W >= 0 && C >= 1 && bitwidth >= 1, "Quantize: sizes must be non-negative, C >= 1 and bitwidth >= 1");
+    TORCH_CHECK(X16.numel() == (int64_t)N * H * W * C && thresholds.numel() == N, "X16 / thresholds do not match N*H*W*C / N");
+    const c10::cuda::CUDAGuard guard(X16.device());
+    auto QX = torch::empty({N, H, W, (C + 63) / 64, bitwidth == 1 ? 1 : 2}, torch::device(X16.device()).dtype(torch::kInt64));
+    check_rc(tab_quantize_i16_launch(X16.data_ptr<int16_t>(), thresholds.data_ptr<float>(), QX.data_ptr<int64_t>(), bitwidth, N, H, W, C, current_stream()),
+             "tab_quantize_i16_launch");
+    return QX;
+}
+
 // NewState: the zeroed block Conv2dBits needs when it is asked for thresholds.
 torch::Tensor TAB_NewState(torch::Tensor like, int N) {
     CHECK_CUDA(like);
@@ -147,12 +162,14 @@ torch::Tensor TAB_NewState(torch::Tensor like, int N) {
 }
 
 // Conv2dBits: the GEMM stage of Conv2d on activations Quantize wrote (bitwidth 2 for types 0,1; 1 for types 2,3) and
-// weights from ExpandWeights; residual / state may be None; threshold_scale <= 0 skips the thresholds.
+// weights from ExpandWeights; residual / state may be None; threshold_scale <= 0 skips the thresholds; out_int16: Y as int16
+// (no residual; the values are integers of magnitude at most KH*KW*C), for QuantizeI16.
 // Returns {Y, next_thresholds (empty when skipped)}.
 std::vector<torch::Tensor> TAB_Conv2dBits(torch::Tensor QX, torch::Tensor W8, int type,
                                           int padding1, int padding2, int stride1, int stride2,
                                           int N, int H, int W, int C, int KN, int KH, int KW,
-                                          c10::optional<torch::Tensor> residual, c10::optional<torch::Tensor> state, double threshold_scale) {
+                                          c10::optional<torch::Tensor> residual, c10::optional<torch::Tensor> state, double threshold_scale,
+                                          bool out_int16) {
     CHECK_INPUT(QX);
     CHECK_INPUT(W8);
     TORCH_CHECK(QX.scalar_type() == torch::kInt64, "QX must have dtype torch.int64");
@@ -180,8 +197,17 @@ std::vector<torch::Tensor> TAB_Conv2dBits(torch::Tensor QX, torch::Tensor W8, in
         TORCH_CHECK((size_t)state->numel() * state->element_size() >= tab_conv2d_state_bytes(N), "state block too small");
         sptr = state->data_ptr();
     }
-    auto Y = torch::empty({N, KN, OH, OW}, torch::device(QX.device()).dtype(torch::kFloat32));
     auto next = torch::empty({want ? N : 0}, torch::device(QX.device()).dtype(torch::kFloat32));
+    if (out_int16) {
+        TORCH_CHECK(rptr == nullptr, "out_int16 cannot be combined with a residual");
+        auto Y16 = torch::empty({N, KN, OH, OW}, torch::device(QX.device()).dtype(torch::kInt16));
+        check_rc(tab_conv2d_bits_i16_launch(QX.data_ptr<int64_t>(), W8.data_ptr<int8_t>(), Y16.data_ptr<int16_t>(), type, padding1, padding2, stride1, stride2,
+                                            N, H, W, C, KN, KH, KW, sptr, (want && N > 0) ? next.data_ptr<float>() : nullptr, (float)threshold_scale,
+                                            current_stream()),
+                 "tab_conv2d_bits_i16_launch");
+        return {Y16, next};
+    }
+    auto Y = torch::empty({N, KN, OH, OW}, torch::device(QX.device()).dtype(torch::kFloat32));
     check_rc(tab_conv2d_bits_launch(QX.data_ptr<int64_t>(), W8.data_ptr<int8_t>(), Y.data_ptr<float>(), type, padding1, padding2, stride1, stride2,
                                     N, H, W, C, KN, KH, KW, rptr, sptr, (want && N > 0) ? next.data_ptr<float>() : nullptr, (float)threshold_scale,
                                     current_stream()),
@@ -192,6 +218,7 @@ std::vector<torch::Tensor> TAB_Conv2dBits(torch::Tensor QX, torch::Tensor W8, in
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("Conv2dFused", &TAB_Conv2dFused, "Conv2d + residual + next-layer thresholds (extension)");
     m.def("ExpandWeights", &TAB_ExpandWeights, "Packed weights -> int8 for the tensor-core GEMM stage (extension)");
+    m.def("QuantizeI16", &TAB_QuantizeI16, "Quantize on the int16 output of Conv2dBits(out_int16=True) (extension)");
     m.def("NewState", &TAB_NewState, "Zeroed state block for Conv2dBits thresholds (extension)");
     m.def("Conv2dBits", &TAB_Conv2dBits, "GEMM stage of Conv2d on Quantize's bit-planes and ExpandWeights' bytes (extension)");
     m.def("Quantize", &TAB_Quantize, "Ternarization or binarization of fp32 data in NHWC format");

@@ -51,9 +51,9 @@ struct QuantExtras {
     int wbits = 2, PC = 1, C = 64;       // of the weights
 };
 
-// quantize_sm100.cu: bits is 1 or 2; btn may be null; btn must already be zero.
-int quantize_dispatch(const float* x, const float* ths, int64_t* qx, int32_t* btn, int bits,
-                      int N, int H, int W, int C, cudaStream_t stream, const QuantExtras* extras = nullptr);
+// quantize_sm100.cu: bits is 1 or 2; btn may be null; btn must already be zero.  in16: x holds int16 instead of float.
+int quantize_dispatch(const void* x, const float* ths, int64_t* qx, int32_t* btn, int bits,
+                      int N, int H, int W, int C, cudaStream_t stream, const QuantExtras* extras = nullptr, bool in16 = false);
 int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream);
 
 // conv_sm100.cu: implicit-im2col popcount GEMM on packed activations.  csa: carry-save popcount tree (else one POPC per word).

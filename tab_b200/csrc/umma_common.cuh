@@ -47,6 +47,7 @@ struct TcConvParams {
     const uint64_t* qx;      // activation bit-planes
     const int8_t* w8;        // byte weights
     float* y;                // [M][KN]
+    int16_t* y16;            // when not null the result goes here as int16 instead (no residual; |y| <= KH*KW*C must fit)
     const float* residual;   // [M][KN] added to the result, or null
     double* abs_sums;        // [N]: += sum |y| per image, or null
     int N, H, W, C, PC, KN, KH, KW, OH, OW, p1, p2, s1, s2;

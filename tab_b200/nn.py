@@ -85,19 +85,27 @@ class TABConv2d(torch.nn.Module):
 
     # ---- the two stages -----------------------------------------------------------------------------------------
     def quantize(self, x, thresholds=None):
-        """fp32 NHWC ``[N,H,W,C]`` -> bit-planes at the activation bitwidth of this convolution's type."""
+        """NHWC ``[N,H,W,C]`` activations -> bit-planes at the activation bitwidth of this convolution's type.  ``x`` is fp32,
+        or the int16 a previous ``conv_bits(..., out_int16=True)`` returned (then ``thresholds`` must be given)."""
         N, H, W = (int(v) for v in x.shape[:3])
+        if x.dtype == torch.int16:
+            if thresholds is None:
+                raise ValueError("int16 activations come with the thresholds their convolution produced")
+            return ops.quantize_i16(x, thresholds, act_bitwidth(self.conv_type), N, H, W, self.C)
         if thresholds is None:
             thresholds = ops.residual_threshold(x.reshape(N, -1), None, self.threshold_scale)
         return ops.Quantize(x, thresholds, act_bitwidth(self.conv_type), N, H, W, self.C)[0]
 
-    def conv_bits(self, QX, N, H, W, residual=None, next_threshold_scale=None, state=None):
-        """GEMM stage on quantised activations.  Returns ``(Y, next_thresholds_or_None)``."""
+    def conv_bits(self, QX, N, H, W, residual=None, next_threshold_scale=None, state=None, out_int16=False):
+        """GEMM stage on quantised activations.  Returns ``(Y, next_thresholds_or_None)``.  ``out_int16``: ``Y`` as int16
+        where that is possible (no residual, KH*KW*C <= 32767, a shape the tensor-core kernel covers), else fp32 as usual:
+        look at ``Y.dtype``."""
         if next_threshold_scale is not None and state is None:
             state = self.state(N, QX.device)
+        compact = out_int16 and residual is None and self.KH * self.KW * self.C <= 32767
         try:
             return ops.conv2d_bits(QX, self.W8, self.conv_type, *self.geometry(N, H, W), residual=residual,
-                                   threshold_scale=next_threshold_scale, state=state)
+                                   threshold_scale=next_threshold_scale, state=state, out_int16=compact)
         except _cabi.TabError as exc:
             if exc.code != -5:
                 raise

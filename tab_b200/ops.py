@@ -169,12 +169,29 @@ def new_state(N, device):
     return torch.zeros((max(_cabi.lib().tab_conv2d_state_bytes(int(N)), 8),), dtype=torch.uint8, device=device)
 
 
+def quantize_i16(X16, thresholds, bitwidth, N, H, W, C):
+    """``Quantize`` on the compact int16 output of ``conv2d_bits(..., out_int16=True)``: returns ``QX`` only."""
+    _check_input(X16, "X16", torch.int16)
+    _check_input(thresholds, "thresholds", torch.float32)
+    N, H, W, C = int(N), int(H), int(W), int(C)
+    if X16.numel() != N * H * W * C or thresholds.numel() != N:
+        raise RuntimeError("X16 / thresholds do not match N*H*W*C / N")
+    bits = 1 if int(bitwidth) == 1 else 2
+    with torch.cuda.device(X16.device):
+        QX = torch.empty((N, H, W, (C + 63) // 64, bits), dtype=torch.int64, device=X16.device)
+        rc = _cabi.lib().tab_quantize_i16_launch(X16.data_ptr(), thresholds.data_ptr(), QX.data_ptr(), int(bitwidth), N, H, W, C,
+                                                 _stream_ptr(X16.device))
+    _cabi.check(rc, "tab_quantize_i16_launch")
+    return QX
+
+
 def conv2d_bits(QX, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW,
-                residual=None, threshold_scale=None, state=None):
+                residual=None, threshold_scale=None, state=None, out_int16=False):
     """The GEMM stage on the tensor cores: activations as ``Quantize`` wrote them (bitwidth 2 for types 0,1; 1 for
     types 2,3), weights from ``expand_weights``.  Returns ``(Y, next_thresholds_or_None)``; ``Y = conv + residual``.
-    ``threshold_scale`` needs ``state`` (``new_state``).  Raises ``TabError`` (TAB_E_TOO_LARGE) for shapes the
-    tensor-core kernel does not cover."""
+    ``threshold_scale`` needs ``state`` (``new_state``).  ``out_int16``: ``Y`` as int16 (no residual; the values are
+    integers of magnitude at most KH*KW*C) for ``quantize_i16``.  Raises ``TabError`` (TAB_E_TOO_LARGE) for shapes
+    the tensor-core kernel does not cover."""
     _check_input(QX, "QX", torch.int64)
     _check_input(W8, "W8", torch.int8)
     conv_type = int(type)
@@ -193,9 +210,20 @@ def conv2d_bits(QX, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, 
             raise RuntimeError("residual has %d elements, expected %d" % (residual.numel(), N * KN * OH * OW))
     if threshold_scale is not None and state is None:
         raise RuntimeError("threshold_scale needs a state block (new_state)")
+    if out_int16 and residual is not None:
+        raise RuntimeError("out_int16 cannot be combined with a residual")
     with torch.cuda.device(QX.device):
-        Y = torch.empty((N, KN, OH, OW), dtype=torch.float32, device=QX.device)
+        Y = torch.empty((N, KN, OH, OW), dtype=torch.int16 if out_int16 else torch.float32, device=QX.device)
         nxt = torch.empty((N,), dtype=torch.float32, device=QX.device) if threshold_scale is not None else None
+        if out_int16:
+            rc = _cabi.lib().tab_conv2d_bits_i16_launch(QX.data_ptr(), W8.data_ptr(), Y.data_ptr(), conv_type, p1, p2, s1, s2,
+                                                        N, H, W, C, KN, KH, KW,
+                                                        state.data_ptr() if nxt is not None else None,
+                                                        nxt.data_ptr() if nxt is not None else None,
+                                                        float(threshold_scale) if threshold_scale is not None else 0.0,
+                                                        _stream_ptr(QX.device))
+            _cabi.check(rc, "tab_conv2d_bits_i16_launch")
+            return Y, nxt
         rc = _cabi.lib().tab_conv2d_bits_launch(QX.data_ptr(), W8.data_ptr(), Y.data_ptr(), conv_type, p1, p2, s1, s2,
                                                 N, H, W, C, KN, KH, KW,
                                                 residual.data_ptr() if residual is not None else None,

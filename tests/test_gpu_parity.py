@@ -304,6 +304,17 @@ def test_bits_stage_entry_point(cuda, geom):
         assert np.array_equal(y2.cpu().numpy(), y2o)
         assert np.array_equal(nxt.cpu().numpy(), OracleOps.residual_threshold(y2o.copy(), None, 0.7))
         assert not state.any().item()
+        # the compact form for chained layers: the same integers as int16, and the quantiser that reads them
+        y16, nxt16 = TAB.ops.conv2d_bits(qx, w8, t, *geom, threshold_scale=0.7, state=state, out_int16=True)
+        assert y16.dtype == torch.int16 and np.array_equal(y16.cpu().numpy().astype(np.float32), yo)
+        assert np.array_equal(nxt16.cpu().numpy(), OracleOps.residual_threshold(yo.copy(), None, 0.7))
+        OH, OW = yo.shape[2], yo.shape[3]
+        if OH * OW:
+            for bw in (2, 1):
+                q16 = TAB.ops.quantize_i16(y16, nxt16, bw, N, OH, OW, KN)
+                qf, _ = TAB.Quantize(dev_t(yo, cuda), nxt16, bw, N, OH, OW, KN)
+                assert torch.equal(q16, qf)
+                assert np.array_equal(q16.cpu().numpy(), O.quantize(yo.reshape(N, OH, OW, KN), nxt16.cpu().numpy(), bw, N, OH, OW, KN)[0])
         assert _cabi.lib().tab_device_status() == 0
 
 
