@@ -14,7 +14,7 @@
 //     two patches ahead of the MMAs, across tile boundaries.
 //   * warp 2: TMA copies of the filter slice (TN x 128 B per tap and channel pair) into a ring of SB stages, or - when
 //     the filters of all taps fit beside the patches (BRES) - once per CTA.
-//   * warps 1 and 3 (even and odd tiles): tcgen05.mma.cta_group::1.kind::i8, 128 x TN x 32 per instruction.  Tap (kh, kw) of the 128 rows of an MMA
+//   * warps 1 and 3 (row block 0 and row block 1 of a tile): tcgen05.mma.cta_group::1.kind::i8, 128 x TN x 32 per instruction.  Tap (kh, kw) of the 128 rows of an MMA
 //     is 128 consecutive patch rows starting (kh/s1)*VW + kw/s2 rows into the patch: the A descriptor simply starts
 //     there (the 128-byte swizzle is a function of absolute shared-memory address bits).  Two TMEM accumulator buffers.
 //   * warps 4-11: epilogue of the other accumulator buffer: tcgen05.ld, transposition through a private shared-memory
@@ -35,6 +35,29 @@ namespace tab {
 constexpr int PTHREADS = 512;                                              // 16 warps
 constexpr int NXT = 160;                                                   // expander threads (5 warps)
 constexpr int XUNROLL = 4;                                                 // (pixel, word) items a thread has in flight
+
+// Build-time diagnostic (-DTAB_PROF, never in the shipped library): cycles one representative warp of each role spends
+// in each kind of wait and in its work, summed over CTAs into g_prof, read back by tab_prof_read.
+#ifdef TAB_PROF
+__device__ unsigned long long g_prof[32];
+#define PROF_T0 const long long prof_t0 = clock64()
+#define PROF_ADD(slot, on) do { if (on) atomicAdd(&g_prof[slot], (unsigned long long)(clock64() - prof_t0)); } while (0)
+#define PROF_MAX(slot, on) do { if (on) atomicMax(&g_prof[slot], (unsigned long long)(clock64() - prof_t0)); } while (0)
+__device__ __forceinline__ unsigned long long prof_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define PROF_GT(slot_min, slot_max, on) do { if (on) { const unsigned long long g = prof_gtime(); atomicMin(&g_prof[slot_min], g); atomicMax(&g_prof[slot_max], g); } } while (0)
+#else
+#define PROF_MAX(slot, on) do { } while (0)
+#define PROF_GT(slot_min, slot_max, on) do { } while (0)
+#define PROF_T0 do { } while (0)
+#define PROF_ADD(slot, on) do { } while (0)
+#endif
+template <int SLOT>
+__device__ __forceinline__ bool mbar_wait_prof(bool on, uint32_t addr, uint32_t parity) {
+    PROF_T0;
+    const bool ok = mbar_wait_warp(addr, parity);
+    PROF_ADD(SLOT, on);
+    return ok;
+}
 
 // Called by every thread of every CTA at the end of the kernel, after the CTA's last atomic on abs_sums.
 __device__ __forceinline__ void fused_finish(const TcConvParams& p) {
@@ -422,6 +445,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     const uint32_t sStage = sbase + tail + 1024;                           // [8 epilogue warps][4 KB, or 2 x 4 KB with TEPI]; 1024-byte aligned
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    PROF_GT(16, 17, tid == 0);                                             // kernel entry
     const int s1 = p.s1, s2 = p.s2;
     const bool UNIT = s1 == 1 && s2 == 1;                                  // one plane: flat tap loops
     const int PA = p.PA, PB = p.PB, VW = p.VW;
@@ -448,6 +472,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     // output is read.  The next kernel may be scheduled when every CTA has finished its tiles (not earlier: a grid
     // waiting in griddepcontrol.wait was measured to slow the MMA warp of the tiles still running).
     pdl_wait();
+    PROF_GT(18, 19, tid == 0);                                             // dependencies resolved
+    PROF_T0;
 
     // In every role the whole warp runs the loops and the waits and one elected lane issues the copies, MMAs and
     // commits.  All roles walk the same nest: tile, channel pair cp, plane (a, b), taps of that plane.
@@ -456,6 +482,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         //      issued a whole patch earlier than they are used (they need registers, not the patch buffer), so that their
         //      latency - long when the epilogue's stores fill the memory system - is off the critical path. -----------------
         const int xt = (warp == 0 ? 0 : warp - 11) * 32 + lane;
+        const bool prof_on = warp == 0 && lane == 0;
+        (void)prof_on;
         const int planes = PA * PB, step = (int)gridDim.x;
         PatchIter cur = {(int)blockIdx.x, 0, 0};
         unsigned q = 0;
@@ -463,8 +491,9 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         // One patch: wait for its buffer, expand the words loaded earlier (mine), hand the patch to the MMA warp.
         auto stage_patch = [&](const RawItems& mine) {
             const unsigned pb = q & 1;
-            if (q >= 2 && !mbar_wait_warp(emptyP + 8 * pb, ((q >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 11); *deadp = 1; } return; }
+            if (q >= 2 && !mbar_wait_prof<0>(prof_on, emptyP + 8 * pb, ((q >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 11); *deadp = 1; } return; }
             const uint32_t buf = sPatch + (uint32_t)(pb * prow) * IROW;
+            PROF_T0;
             store_items(p, mine, buf, nrows, cur.cp, 0, xt);
             const int items = nrows * ((2 * cur.cp + 1 < p.PC) ? 2 : 1);
             if (items > NXT * XUNROLL) {                                   // long patches (large halo): the rest, chunk by chunk
@@ -478,6 +507,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             }
             fence_async_smem();
             mbar_arrive(fullP + 8 * pb);
+            PROF_ADD(1, prof_on);
             q++;
         };
         auto load_patch = [&](RawItems& into, const PatchIter& at) {
@@ -510,6 +540,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         } else {
             unsigned g = 0;
             bool dead = false;
+            const bool prof_on = lane == 0;
+            (void)prof_on;
             for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x) {
                 const int n0 = (t % tiles_n) * TNI;
                 for (int cp = 0; cp < ncp && !dead; cp++) {
@@ -519,7 +551,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                     for (int kh = pa; kh < p.KH && !dead; kh += s1)
                     for (int kw = pbb; kw < p.KW; kw += s2, g++) {
                         const unsigned slot = g % SB;
-                        if (g >= (unsigned)SB && !mbar_wait_warp(emptyB + 8 * slot, ((g / SB) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 12); *deadp = 1; } break; }
+                        if (g >= (unsigned)SB && !mbar_wait_prof<2>(prof_on, emptyB + 8 * slot, ((g / SB) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 12); *deadp = 1; } break; }
                         if (elect_one()) {
                             mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
                             tma_load_2d(sRing + slot * BSTAGE, &tmB, ((kh * p.KW + kw) * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
@@ -539,13 +571,16 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         constexpr uint32_t IDESC = umma_idesc(TNI);
         constexpr uint32_t MB_UNITS = (UTM * IROW) >> 4;                   // next 128-row block of the patch, in 16-byte units
         const int mw = warp == 1 ? 0 : 1;
+        const bool prof_on = warp == 1 && lane == 0;
+        (void)prof_on;
+        PROF_T0;
         const int mb_lo = MT == 2 ? mw : 0, mb_hi = MT == 2 ? mw + 1 : 1;  // this warp's row blocks
         unsigned g = 0, q = 0, a = 0;
         bool dead = MT == 1 && mw == 1;                                    // nothing to do for the second warp
-        if (BRES && !dead && !mbar_wait_warp(fullB, 0)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } }
+        if (BRES && !dead && !mbar_wait_prof<5>(prof_on, fullB, 0)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } }
         for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
             const unsigned buf = a & 1;
-            if (a >= 2 && !mbar_wait_warp(accEmpty + 8 * buf, ((a >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 13); *deadp = 1; } break; }
+            if (a >= 2 && !mbar_wait_prof<3>(prof_on, accEmpty + 8 * buf, ((a >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 13); *deadp = 1; } break; }
             tc_fence_after();
             const uint32_t acc = tmem_base + buf * ACOLS;
             uint32_t accumulate = 0;                                       // 0 for the tile's first MMAs
@@ -566,7 +601,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 };
                 if (UNIT) {
                     const unsigned pb = q & 1;
-                    if (!mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
+                    if (!mbar_wait_prof<4>(prof_on, fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
                     tc_fence_after();
                     uint32_t arow = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;   // descriptor address of the tap's first patch row
                     int kw = 0;
@@ -584,7 +619,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                     } else {
                         for (int tap = 0; tap < T; tap++, g++) {
                             const unsigned slot = g % SB;
-                            if (!mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
+                            if (!mbar_wait_prof<5>(prof_on, fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
                             tc_fence_after();
                             if (elect_one()) {
                                 issue_tap(((uint64_t)UMMA_DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4)),
@@ -604,7 +639,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 for (int pa = 0; pa < PA && !dead; pa++)
                 for (int pbb = 0; pbb < PB && !dead; pbb++, q++) {
                     const unsigned pb = q & 1;
-                    if (!mbar_wait_warp(fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
+                    if (!mbar_wait_prof<4>(prof_on, fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
                     tc_fence_after();
                     const uint32_t patch = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;    // descriptor address of the patch
                     const bool last_group = cp == ncp - 1 && pa == PA - 1 && pbb == PB - 1;
@@ -615,7 +650,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                         if (BRES) bsm = sRing + (uint32_t)(cp * T + kh * p.KW + kw) * BSTAGE;
                         else {
                             const unsigned slot = g % SB;
-                            if (!mbar_wait_warp(fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
+                            if (!mbar_wait_prof<5>(prof_on, fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
                             tc_fence_after();
                             bsm = sRing + slot * BSTAGE;
                         }
@@ -635,9 +670,12 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 }
             }
         }
+        PROF_ADD(9, prof_on);
     } else if (TEPI) {
         // ---- epilogue warps 4-11 through TMA (TMEM lane quarter = warp % 4) -------------------------------------------
         const int ew = warp - 4, wg = ew >> 2, step = (int)gridDim.x;
+        const bool prof_on = warp == 4 && lane == 0;
+        (void)prof_on;
         const uint32_t sbuf = sStage + (uint32_t)ew * 8192u;               // two 4 KB block buffers
         const uint32_t mres = resB + 16u * (uint32_t)ew;                   // their "residual arrived" barriers
         const int emb = MT == 2 ? wg : 0, ec0 = MT == 2 ? 0 : wg * (TNI / 2), ec1 = MT == 2 ? TNI : (wg + 1) * (TNI / 2);
@@ -674,7 +712,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                     if (bx.live) tma_prefetch_4d(&tmR, bx.c0, bx.c1, bx.c2, bx.c3);
                 }
             }
-            if (!mbar_wait_warp(accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
+            if (!mbar_wait_prof<6>(prof_on, accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * ACOLS + (uint32_t)(emb * TNI) + ((uint32_t)((warp & 3) * 32) << 16);
 #pragma unroll 1
@@ -694,7 +732,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                         if (nx.t < ntiles)
                             tepi_request_residual(&tmR, tepi_box(p, slab_row(nx.t), (nx.t % tiles_n) * TNI + nx.cb), sbuf + (k ^ 1u) * 4096u, mres + 8u * (k ^ 1u));
                     }
-                    if (!mbar_wait_warp(mres + 8u * k, (blk >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 17); *deadp = 1; } break; }
+                    if (!mbar_wait_prof<7>(prof_on, mres + 8u * k, (blk >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 17); *deadp = 1; } break; }
 #pragma unroll
                     for (int q = 0; q < 8; q++) {
                         const int4 rv = lds_v4(sb + (uint32_t)lane * 128u + ((uint32_t)(q ^ (lane & 7)) << 4));
@@ -779,6 +817,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         unsigned a = 0;
         bool dead = false;
         PendingSums pending;
+        const bool prof_on = warp == 4 && lane == 0;
+        (void)prof_on;
         for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
             const unsigned buf = a & 1;
             const int R0 = (t / tiles_n) * (UTM * MT), n0 = (t % tiles_n) * TNI;
@@ -794,18 +834,23 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 slab_load_residual(p, sr, n0 + ec0, lane, res);
                 res_loaded = true;
             }
-            if (!mbar_wait_warp(accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
+            if (!mbar_wait_prof<6>(prof_on, accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
             tc_fence_after();
+            PROF_T0;
             slab_columns<FUSED>(p, tmem_base + buf * ACOLS + (uint32_t)(emb * TNI) + ((uint32_t)((warp & 3) * 32) << 16), sr, n0, ec0, ec1,
                                 lane, sStage + (warp - 4) * 4096, res, res_loaded, pending);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(accEmpty + 8 * buf);
+            PROF_ADD(8, prof_on);
             if (FUSED) flush_pending(p, pending, lane);                    // the |y| atomics, off the buffer's critical path
         }
     }
     tc_fence_before();
     __syncthreads();
+    PROF_ADD(12, tid == 0);
+    PROF_MAX(13, tid == 0);
+    PROF_GT(20, 21, tid == 0);                                             // tiles done
     if (*deadp != 0) {
         // a wait ran out in this CTA: give copies and MMAs that may still be in flight time to land before this
         // CTA frees its tensor memory and its shared memory goes to another CTA (never taken when the protocol is intact)
@@ -815,7 +860,20 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     pdl_launch_dependents();
     if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(2 * ACOLS));
     if (FUSED) fused_finish(p);
+    PROF_GT(22, 23, tid == 0);                                             // exit
 }
+
+#ifdef TAB_PROF
+extern "C" int tab_prof_read(unsigned long long* out, int clear) {
+    if (cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return -1;
+    if (clear) {
+        unsigned long long z[32] = {0};
+        z[16] = z[18] = z[20] = z[22] = ~0ull;
+        cudaMemcpyToSymbol(g_prof, z, sizeof(z));
+    }
+    return 0;
+}
+#endif
 
 // ---- host side -----------------------------------------------------------------------------------------------------------
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda).

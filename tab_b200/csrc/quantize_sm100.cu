@@ -118,7 +118,10 @@ template <int BITS, bool IN16>
 __global__ void __launch_bounds__(QTHREADS)
 quantize_c64_kernel(const void* __restrict__ x, const float* __restrict__ ths,
                     uint64_t* __restrict__ qx, int* __restrict__ btn, long long words_per_image, const QuantExtras ex) {
-    const int n = blockIdx.y;
+    // Last image first, and within an image the last chunk first: the tensor usually was written front to back by the
+    // kernel before this one, so its end is what the L2 still holds.
+    const int n = (int)(gridDim.y - 1u - blockIdx.y);
+    const unsigned bx = gridDim.x - 1u - blockIdx.x;
     quant_prologue(ex, n);
     const float t = __ldg(ths + n);
     const float nt = -t;
@@ -132,7 +135,7 @@ quantize_c64_kernel(const void* __restrict__ x, const float* __restrict__ ths,
     // 16-bit input halves the bytes of a load: twice as many loads in flight keep the same bytes in flight
     constexpr int UN = IN16 ? 2 * QUNROLL : QUNROLL;
     constexpr int WORDS = (QTHREADS / 8) * UN;
-    for (long long w0 = (long long)blockIdx.x * WORDS; w0 < words_per_image; w0 += (long long)gridDim.x * WORDS) {
+    for (long long w0 = (long long)bx * WORDS; w0 < words_per_image; w0 += (long long)gridDim.x * WORDS) {
         f8 v[IN16 ? 1 : UN];
         u4 raw[IN16 ? UN : 1];                                 // 16-bit input: converted only when used, after every load is issued
         long long w[UN];
