@@ -51,10 +51,10 @@ __device__ __forceinline__ unsigned long long prof_gtime() { unsigned long long 
 #define PROF_T0 do { } while (0)
 #define PROF_ADD(slot, on) do { } while (0)
 #endif
-template <int SLOT>
+template <int SLOT, bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait_prof(bool on, uint32_t addr, uint32_t parity) {
     PROF_T0;
-    const bool ok = mbar_wait_warp(addr, parity);
+    const bool ok = CLUSTER ? mbar_wait_cluster_warp(addr, parity) : mbar_wait_warp(addr, parity);
     PROF_ADD(SLOT, on);
     return ok;
 }
@@ -420,12 +420,18 @@ __device__ __forceinline__ void tepi_request_residual(const void* tmR, const Tep
 // memory; otherwise it streams through a ring of SB stages, one stage per tap and channel pair.
 // TEPI: the epilogue moves the output (and the residual) with TMA boxes; needs the aligned virtual grid (p.tepi).
 // Counters g (ring stages), q (patches) and a (accumulator buffers) run across tiles; barrier parities follow from them.
-template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI>
+// PAIR: the kernel runs as clusters of two CTAs (see umma_common.cuh): a tile is 256 virtual rows x TNI filters, each CTA
+// stages the patch of its own 128 rows and fetches TNI/2 filters of every slice; the even CTA's MMA warp issues the pair's
+// MMAs and its commits arrive on the "empty" / "accumulator full" barriers of both CTAs, while the "full" / "accumulator
+// empty" barriers it waits on live in the even CTA and collect the arrivals of both.
+template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI, bool PAIR = false>
 __global__ void __launch_bounds__(PTHREADS, 1)
 conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmR,
                          const TcConvParams p, int* __restrict__ status,
                          const int prow, const int nrows, const int nst, const int tiles_m, const int tiles_n) {
-    constexpr int BSTAGE = TNI * IROW;
+    static_assert(!PAIR || (MT == 1 && !BRES && !TEPI), "CTA pairs: one row block per CTA, streamed filters, transposing epilogue");
+    constexpr int BROWS = PAIR ? TNI / 2 : TNI;                            // filters of a slice this CTA holds
+    constexpr int BSTAGE = BROWS * IROW;
     constexpr int ACOLS = MT * TNI;                                        // columns of one accumulator buffer
     static_assert(2 * ACOLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
     static_assert(SB <= 8, "eight ring barriers are laid out");
@@ -451,21 +457,27 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     const int PA = p.PA, PB = p.PB, VW = p.VW;
     const int T = p.KH * p.KW, ncp = (p.PC + 1) >> 1;
     const int ntiles = tiles_m * tiles_n;
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;                  // 0: the CTA whose MMA warp works for the pair
+    const int cta0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // first tile of this CTA (pair)
+    const int cstep = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;       // tiles between two of its tiles
+    // first virtual row of this CTA's part of tile t
+    auto tile_row0 = [&](int t) { return PAIR ? ((t / tiles_n) * 2 + (int)crank) * UTM : (t / tiles_n) * (UTM * MT); };
 
     if (tid == 0) {
         *deadp = 0;
         for (int s = 0; s < 8; s++) mbar_init(fullB + 8 * s, 1);
-        mbar_init(fullP, NXT); mbar_init(fullP + 8, NXT);                  // one arrival per expander thread
+        mbar_init(fullP, (PAIR ? 2 : 1) * NXT); mbar_init(fullP + 8, (PAIR ? 2 : 1) * NXT);   // one arrival per expander thread (of both CTAs)
         for (int s = 0; s < 8; s++) mbar_init(emptyB + 8 * s, MT);          // one commit per MMA warp (MT = 2: two warps)
         mbar_init(emptyP, MT); mbar_init(emptyP + 8, MT);
         mbar_init(accFull, MT); mbar_init(accFull + 8, MT);
-        mbar_init(accEmpty, 8); mbar_init(accEmpty + 8, 8);                // one arrival per epilogue warp
+        mbar_init(accEmpty, PAIR ? 16 : 8); mbar_init(accEmpty + 8, PAIR ? 16 : 8);   // one arrival per epilogue warp (of both CTAs)
         if (TEPI) for (int i = 0; i < 16; i++) mbar_init(resB + 8 * i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tslot, (uint32_t)(2 * ACOLS));
+    if (warp == 1) { if (PAIR) tmem_alloc_pair(tslot, (uint32_t)(2 * ACOLS)); else tmem_alloc(tslot, (uint32_t)(2 * ACOLS)); }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();                                          // both CTAs' barriers exist before either arrives on the other's
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // Programmatic launch: the set-up above overlapped the tail of the previous kernel (the quantiser); from here on its
@@ -484,20 +496,20 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         const int xt = (warp == 0 ? 0 : warp - 11) * 32 + lane;
         const bool prof_on = warp == 0 && lane == 0;
         (void)prof_on;
-        const int planes = PA * PB, step = (int)gridDim.x;
-        PatchIter cur = {(int)blockIdx.x, 0, 0};
+        const int planes = PA * PB, step = cstep;
+        PatchIter cur = {cta0, 0, 0};
         unsigned q = 0;
         bool dead = false;
         // One patch: wait for its buffer, expand the words loaded earlier (mine), hand the patch to the MMA warp.
         auto stage_patch = [&](const RawItems& mine) {
             const unsigned pb = q & 1;
-            if (q >= 2 && !mbar_wait_prof<0>(prof_on, emptyP + 8 * pb, ((q >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 11); *deadp = 1; } return; }
+            if (q >= 2 && !mbar_wait_prof<0, PAIR>(prof_on, emptyP + 8 * pb, ((q >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 11); *deadp = 1; } return; }
             const uint32_t buf = sPatch + (uint32_t)(pb * prow) * IROW;
             PROF_T0;
             store_items(p, mine, buf, nrows, cur.cp, 0, xt);
             const int items = nrows * ((2 * cur.cp + 1 < p.PC) ? 2 : 1);
             if (items > NXT * XUNROLL) {                                   // long patches (large halo): the rest, chunk by chunk
-                const int R0 = (cur.t / tiles_n) * (UTM * MT);
+                const int R0 = tile_row0(cur.t);
                 const int pa = UNIT ? 0 : cur.pl / PB;
                 for (int base = NXT * XUNROLL; base < items; base += NXT * XUNROLL) {
                     RawItems more;
@@ -506,13 +518,13 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 }
             }
             fence_async_smem();
-            mbar_arrive(fullP + 8 * pb);
+            if (PAIR) mbar_arrive_cluster(fullP + 8 * pb, 0u); else mbar_arrive(fullP + 8 * pb);
             PROF_ADD(1, prof_on);
             q++;
         };
         auto load_patch = [&](RawItems& into, const PatchIter& at) {
             const int pa = UNIT ? 0 : at.pl / PB;
-            if (at.t < ntiles) load_items(p, into, (at.t / tiles_n) * (UTM * MT), nrows, at.cp, pa, UNIT ? 0 : at.pl - pa * PB, 0, xt);
+            if (at.t < ntiles) load_items(p, into, tile_row0(at.t), nrows, at.cp, pa, UNIT ? 0 : at.pl - pa * PB, 0, xt);
         };
         // The words of the next patch are loaded before this one is expanded.  (The hand-over raw = ahead comes after the
         // expansion, when those loads have long arrived: a move of a register whose load is in flight would wait for it.)
@@ -532,9 +544,15 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         if (BRES) {
             if (elect_one()) {
                 mbar_expect_tx(fullB, (uint32_t)(nst * BSTAGE));
-                for (int cp = 0; cp < ncp; cp++)
-                    for (int tap = 0; tap < T; tap++)
-                        tma_load_2d(sRing + (cp * T + tap) * BSTAGE, &tmB, (tap * p.PC + 2 * cp) * 64, 0, fullB);
+                if (p.PC == 1) {
+                    // one 64-byte word per tap: a 128-byte-wide slot holds taps 2j and 2j + 1 (the box of the last slot of
+                    // an odd tap count ends beyond the row and is zero-filled there)
+                    for (int j = 0; j < nst; j++) tma_load_2d(sRing + j * BSTAGE, &tmB, j * 128, 0, fullB);
+                } else {
+                    for (int cp = 0; cp < ncp; cp++)
+                        for (int tap = 0; tap < T; tap++)
+                            tma_load_2d(sRing + (cp * T + tap) * BSTAGE, &tmB, (tap * p.PC + 2 * cp) * 64, 0, fullB);
+                }
             }
             __syncwarp();
         } else {
@@ -542,8 +560,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             bool dead = false;
             const bool prof_on = lane == 0;
             (void)prof_on;
-            for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x) {
-                const int n0 = (t % tiles_n) * TNI;
+            for (int t = cta0; t < ntiles && !dead; t += cstep) {
+                const int n0 = (t % tiles_n) * TNI + (PAIR ? (int)crank * BROWS : 0);
                 for (int cp = 0; cp < ncp && !dead; cp++) {
                     // same tap order as the MMA warp: plane by plane
                     for (int pa = 0; pa < PA && !dead; pa++)
@@ -551,10 +569,15 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                     for (int kh = pa; kh < p.KH && !dead; kh += s1)
                     for (int kw = pbb; kw < p.KW; kw += s2, g++) {
                         const unsigned slot = g % SB;
-                        if (g >= (unsigned)SB && !mbar_wait_prof<2>(prof_on, emptyB + 8 * slot, ((g / SB) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 12); *deadp = 1; } break; }
+                        if (g >= (unsigned)SB && !mbar_wait_prof<2, PAIR>(prof_on, emptyB + 8 * slot, ((g / SB) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 12); *deadp = 1; } break; }
                         if (elect_one()) {
-                            mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
-                            tma_load_2d(sRing + slot * BSTAGE, &tmB, ((kh * p.KW + kw) * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
+                            if (PAIR) {                                    // both halves are counted on the even CTA's barrier
+                                if (crank == 0) mbar_expect_tx(fullB + 8 * slot, 2u * (uint32_t)BSTAGE);
+                                tma_load_2d_pair(sRing + slot * BSTAGE, &tmB, ((kh * p.KW + kw) * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
+                            } else {
+                                mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
+                                tma_load_2d(sRing + slot * BSTAGE, &tmB, ((kh * p.KW + kw) * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
+                            }
                         }
                         __syncwarp();
                     }
@@ -568,7 +591,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         //      accumulators, the same operands and the same barrier phases (both warps follow every stage, so a parity
         //      wait never sees a phase other than the current or the previous one); the "empty" and "accumulator full"
         //      barriers then count one commit from each.  With one row block warp 3 idles. -----------------------------------
-        constexpr uint32_t IDESC = umma_idesc(TNI);
+        constexpr uint32_t IDESC = PAIR ? umma_idesc_pair(TNI) : umma_idesc(TNI);
         constexpr uint32_t MB_UNITS = (UTM * IROW) >> 4;                   // next 128-row block of the patch, in 16-byte units
         const int mw = warp == 1 ? 0 : 1;
         const bool prof_on = warp == 1 && lane == 0;
@@ -576,11 +599,20 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         PROF_T0;
         const int mb_lo = MT == 2 ? mw : 0, mb_hi = MT == 2 ? mw + 1 : 1;  // this warp's row blocks
         unsigned g = 0, q = 0, a = 0;
-        bool dead = MT == 1 && mw == 1;                                    // nothing to do for the second warp
-        if (BRES && !dead && !mbar_wait_prof<5>(prof_on, fullB, 0)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } }
-        for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
+        bool dead = (MT == 1 && mw == 1) || (PAIR && crank != 0);          // nothing to do for the second warp, nor in the odd CTA of a pair
+        if (BRES && !dead && !mbar_wait_prof<5, PAIR>(prof_on, fullB, 0)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } }
+        // descriptor address of the resident filter slice of (channel pair, tap); with one channel word two taps share a slot
+        auto resident_b = [&](int cp, int tap) -> uint32_t {
+            return p.PC == 1 ? ((sRing + (uint32_t)(tap >> 1) * BSTAGE) >> 4) + (uint32_t)(tap & 1) * 4u
+                             : (sRing + (uint32_t)(cp * T + tap) * BSTAGE) >> 4;
+        };
+        auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t acc_flag) {
+            if (PAIR) umma_i8_pair(d, da, db, IDESC, acc_flag); else umma_i8(d, da, db, IDESC, acc_flag);
+        };
+        auto commit = [&](uint32_t bar) { if (PAIR) umma_commit_pair(bar); else umma_commit(bar); };
+        for (int t = cta0; t < ntiles && !dead; t += cstep, a++) {
             const unsigned buf = a & 1;
-            if (a >= 2 && !mbar_wait_prof<3>(prof_on, accEmpty + 8 * buf, ((a >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 13); *deadp = 1; } break; }
+            if (a >= 2 && !mbar_wait_prof<3, PAIR>(prof_on, accEmpty + 8 * buf, ((a >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 13); *deadp = 1; } break; }
             tc_fence_after();
             const uint32_t acc = tmem_base + buf * ACOLS;
             uint32_t accumulate = 0;                                       // 0 for the tile's first MMAs
@@ -591,17 +623,17 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                     for (int mb = mb_lo; mb < mb_hi; mb++) {
                         const uint32_t d = acc + mb * TNI;
                         const uint64_t dam = da + mb * MB_UNITS;
-                        umma_i8(d, dam, db, IDESC, acc_first);
-                        umma_i8(d, dam + 2, db + 2, IDESC, 1u);
+                        mma(d, dam, db, acc_first);
+                        mma(d, dam + 2, db + 2, 1u);
                         if (four) {
-                            umma_i8(d, dam + 4, db + 4, IDESC, 1u);
-                            umma_i8(d, dam + 6, db + 6, IDESC, 1u);
+                            mma(d, dam + 4, db + 4, 1u);
+                            mma(d, dam + 6, db + 6, 1u);
                         }
                     }
                 };
                 if (UNIT) {
                     const unsigned pb = q & 1;
-                    if (!mbar_wait_prof<4>(prof_on, fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
+                    if (!mbar_wait_prof<4, PAIR>(prof_on, fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
                     tc_fence_after();
                     uint32_t arow = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;   // descriptor address of the tap's first patch row
                     int kw = 0;
@@ -609,25 +641,25 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                         if (elect_one()) {                                 // nothing to wait for between taps: one issue burst
                             for (int tap = 0; tap < T; tap++) {
                                 issue_tap(((uint64_t)UMMA_DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4)),
-                                          ((uint64_t)UMMA_DESC_HI << 32) | ((sRing + (uint32_t)(cp * T + tap) * BSTAGE) >> 4), (cp > 0 || tap > 0) ? 1u : 0u);
+                                          ((uint64_t)UMMA_DESC_HI << 32) | resident_b(cp, tap), (cp > 0 || tap > 0) ? 1u : 0u);
                                 if (++kw == p.KW) { kw = 0; arow += (uint32_t)VW * (IROW >> 4); }
                             }
-                            umma_commit(emptyP + 8 * pb);
-                            if (cp == ncp - 1) umma_commit(accFull + 8 * buf);
+                            commit(emptyP + 8 * pb);
+                            if (cp == ncp - 1) commit(accFull + 8 * buf);
                         }
                         __syncwarp();
                     } else {
                         for (int tap = 0; tap < T; tap++, g++) {
                             const unsigned slot = g % SB;
-                            if (!mbar_wait_prof<5>(prof_on, fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
+                            if (!mbar_wait_prof<5, PAIR>(prof_on, fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
                             tc_fence_after();
                             if (elect_one()) {
                                 issue_tap(((uint64_t)UMMA_DESC_HI << 32) | (arow + (uint32_t)kw * (IROW >> 4)),
                                           ((uint64_t)UMMA_DESC_HI << 32) | ((sRing + slot * BSTAGE) >> 4), (cp > 0 || tap > 0) ? 1u : 0u);
-                                umma_commit(emptyB + 8 * slot);
+                                commit(emptyB + 8 * slot);
                                 if (tap == T - 1) {
-                                    umma_commit(emptyP + 8 * pb);
-                                    if (cp == ncp - 1) umma_commit(accFull + 8 * buf);
+                                    commit(emptyP + 8 * pb);
+                                    if (cp == ncp - 1) commit(accFull + 8 * buf);
                                 }
                             }
                             __syncwarp();
@@ -639,28 +671,27 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 for (int pa = 0; pa < PA && !dead; pa++)
                 for (int pbb = 0; pbb < PB && !dead; pbb++, q++) {
                     const unsigned pb = q & 1;
-                    if (!mbar_wait_prof<4>(prof_on, fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
+                    if (!mbar_wait_prof<4, PAIR>(prof_on, fullP + 8 * pb, (q >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 14); *deadp = 1; } break; }
                     tc_fence_after();
                     const uint32_t patch = (sPatch + (uint32_t)(pb * prow) * IROW) >> 4;    // descriptor address of the patch
                     const bool last_group = cp == ncp - 1 && pa == PA - 1 && pbb == PB - 1;
                     for (int kh = pa, ih = 0; kh < p.KH && !dead; kh += s1, ih++)
                     for (int kw = pbb, iw = 0; kw < p.KW; kw += s2, iw++) {
                         const bool last_tap = kh + s1 >= p.KH && kw + s2 >= p.KW;
-                        uint32_t bsm;
-                        if (BRES) bsm = sRing + (uint32_t)(cp * T + kh * p.KW + kw) * BSTAGE;
-                        else {
+                        uint32_t bsm = 0;
+                        if (!BRES) {
                             const unsigned slot = g % SB;
-                            if (!mbar_wait_prof<5>(prof_on, fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
+                            if (!mbar_wait_prof<5, PAIR>(prof_on, fullB + 8 * slot, (g / SB) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 15); *deadp = 1; } break; }
                             tc_fence_after();
                             bsm = sRing + slot * BSTAGE;
                         }
                         if (elect_one()) {
                             issue_tap(((uint64_t)UMMA_DESC_HI << 32) | (patch + (uint32_t)(ih * VW + iw) * (IROW >> 4)),
-                                      ((uint64_t)UMMA_DESC_HI << 32) | (bsm >> 4), accumulate);
-                            if (!BRES) umma_commit(emptyB + 8 * (g % SB));
+                                      ((uint64_t)UMMA_DESC_HI << 32) | (BRES ? resident_b(cp, kh * p.KW + kw) : (bsm >> 4)), accumulate);
+                            if (!BRES) commit(emptyB + 8 * (g % SB));
                             if (last_tap) {
-                                umma_commit(emptyP + 8 * pb);
-                                if (last_group) umma_commit(accFull + 8 * buf);
+                                commit(emptyP + 8 * pb);
+                                if (last_group) commit(accFull + 8 * buf);
                             }
                         }
                         __syncwarp();
@@ -673,7 +704,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         PROF_ADD(9, prof_on);
     } else if (TEPI) {
         // ---- epilogue warps 4-11 through TMA (TMEM lane quarter = warp % 4) -------------------------------------------
-        const int ew = warp - 4, wg = ew >> 2, step = (int)gridDim.x;
+        const int ew = warp - 4, wg = ew >> 2, step = cstep;
         const bool prof_on = warp == 4 && lane == 0;
         (void)prof_on;
         const uint32_t sbuf = sStage + (uint32_t)ew * 8192u;               // two 4 KB block buffers
@@ -688,11 +719,11 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         bool dead = false;
         PendingSums pending;
         if (has_res && lane == 0) {                                        // the residual of the warp's first block
-            TepiIter first = {(int)blockIdx.x, ec0};
+            TepiIter first = {cta0, ec0};
             first.settle(ec0, step, ntiles, tiles_n, TNI, p.KN);
             if (first.t < ntiles) tepi_request_residual(&tmR, tepi_box(p, slab_row(first.t), (first.t % tiles_n) * TNI + first.cb), sbuf, mres);
         }
-        for (int t = blockIdx.x; t < ntiles && !dead; t += step, a++) {
+        for (int t = cta0; t < ntiles && !dead; t += step, a++) {
             const unsigned buf = a & 1;
             const int n0 = (t % tiles_n) * TNI, Rw = slab_row(t);
             // the lane's own row, for the |y| sums: lanes of image wimg0 and of wimg0 + 1 are totalled separately ("fast":
@@ -819,9 +850,9 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         PendingSums pending;
         const bool prof_on = warp == 4 && lane == 0;
         (void)prof_on;
-        for (int t = blockIdx.x; t < ntiles && !dead; t += gridDim.x, a++) {
+        for (int t = cta0; t < ntiles && !dead; t += cstep, a++) {
             const unsigned buf = a & 1;
-            const int R0 = (t / tiles_n) * (UTM * MT), n0 = (t % tiles_n) * TNI;
+            const int R0 = tile_row0(t), n0 = (t % tiles_n) * TNI;
             // two warps per TMEM lane quarter: they split the row blocks of a two-block tile, else the columns.  Row data
             // and the first block's residual are fetched before the accumulator is waited for.
             const int wg = (warp - 4) >> 2;
@@ -834,14 +865,14 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 slab_load_residual(p, sr, n0 + ec0, lane, res);
                 res_loaded = true;
             }
-            if (!mbar_wait_prof<6>(prof_on, accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
+            if (!mbar_wait_prof<6, PAIR>(prof_on, accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
             tc_fence_after();
             PROF_T0;
             slab_columns<FUSED>(p, tmem_base + buf * ACOLS + (uint32_t)(emb * TNI) + ((uint32_t)((warp & 3) * 32) << 16), sr, n0, ec0, ec1,
                                 lane, sStage + (warp - 4) * 4096, res, res_loaded, pending);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(accEmpty + 8 * buf);
+            if (lane == 0) { if (PAIR) mbar_arrive_cluster(accEmpty + 8 * buf, 0u); else mbar_arrive(accEmpty + 8 * buf); }
             PROF_ADD(8, prof_on);
             if (FUSED) flush_pending(p, pending, lane);                    // the |y| atomics, off the buffer's critical path
         }
@@ -857,8 +888,9 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         for (int i = 0; i < 200; i++) __nanosleep(1000);
     }
     __syncthreads();
+    if (PAIR) cluster_sync_all();                                          // the other CTA no longer reads this one's memory nor arrives on its barriers
     pdl_launch_dependents();
-    if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)(2 * ACOLS));
+    if (warp == 1) { if (PAIR) tmem_dealloc_pair(tmem_base, (uint32_t)(2 * ACOLS)); else tmem_dealloc(tmem_base, (uint32_t)(2 * ACOLS)); }
     if (FUSED) fused_finish(p);
     PROF_GT(22, 23, tid == 0);                                             // exit
 }
@@ -1013,22 +1045,27 @@ static bool set_virtual_grid(TcConvParams& p, bool aligned) {
     return true;
 }
 
-// A tile shape and what it needs.
-struct TcPlan { int mt, tn, sb; bool resident; int prow, nrows, nst, smem; long long tiles_m, tiles_n; };
+// Whether this device runs the pair kernel: two CTAs of its size per cluster, asked of the occupancy calculator once.
+static bool pair_launch_possible();
 
-static bool plan_shape(const TcConvParams& p, int mt, int tn, int sb, TcPlan* out) {
+// A tile shape and what it needs.
+struct TcPlan { int mt, tn, sb; bool resident, pair; int prow, nrows, nst, smem; long long tiles_m, tiles_n; };
+
+// pair: clusters of two CTAs; a tile is 256 rows (128 per CTA) x tn filters, a ring stage holds tn/2 filters per CTA.
+static bool plan_shape(const TcConvParams& p, int mt, int tn, int sb, TcPlan* out, bool pair = false) {
     const long long halo = (long long)((p.KH - 1) / p.s1) * p.VW + (p.KW - 1) / p.s2;
     const long long nrows = 128LL * mt + halo, prow = (nrows + 7) / 8 * 8;
     const long long fixed = 2 * prow * IROW + 1024 + 8 * (p.tepi ? 8192 : 4096) + 1024;   // patches, barriers, epilogue buffers, alignment
-    const long long nres = (long long)p.KH * p.KW * ((p.PC + 1) / 2);
+    const long long nres = p.PC == 1 ? ((long long)p.KH * p.KW + 1) / 2 : (long long)p.KH * p.KW * ((p.PC + 1) / 2);   // slots of resident filters
     TcPlan pl;
-    pl.mt = mt; pl.tn = tn; pl.sb = sb;
-    pl.resident = p.KN <= tn && fixed + nres * tn * IROW <= UMMA_SMEM_MAX;
-    const long long smem = pl.resident ? fixed + nres * tn * IROW : fixed + (long long)sb * tn * IROW;
+    pl.mt = mt; pl.tn = tn; pl.sb = sb; pl.pair = pair;
+    pl.resident = !pair && p.KN <= tn && fixed + nres * tn * IROW <= UMMA_SMEM_MAX;
+    const long long smem = pl.resident ? fixed + nres * tn * IROW : fixed + (long long)sb * (pair ? tn / 2 : tn) * IROW;
     if (smem > UMMA_SMEM_MAX) return false;
     pl.prow = (int)prow; pl.nrows = (int)nrows; pl.nst = pl.resident ? (int)nres : sb; pl.smem = (int)smem;
     const long long Mv = (long long)(p.N - 1) * p.VH * p.VW + (long long)(p.OH - 1) * p.VW + p.OW;   // last useful virtual row + 1
     pl.tiles_m = (Mv + 128LL * mt - 1) / (128LL * mt);
+    if (pair) pl.tiles_m = (pl.tiles_m + 1) / 2;
     pl.tiles_n = (p.KN + tn - 1) / tn;
     if (pl.tiles_m * pl.tiles_n >= (1LL << 31)) return false;
     *out = pl;
@@ -1043,6 +1080,14 @@ static bool plan_shape(const TcConvParams& p, int mt, int tn, int sb, TcPlan* ou
 static bool tc_plan(const TcConvParams& p, int sms, TcPlan* best) {
     static const int cands[5][3] = {{1, 256, 4}, {2, 128, 4}, {1, 128, 6}, {2, 64, 6}, {1, 64, 6}};
     const int tn0 = p.KN <= 64 ? 64 : (p.KN <= 128 ? 128 : 256);
+    // Wide filter blocks on CTA pairs: a lone CTA would have to take in a 32 KB filter slice per 512 cycles of MMAs, which is
+    // all an SM can take in from the L2; a pair splits every slice between its two CTAs.  (Strided layers, bound by their
+    // four or more patches per tile, and layers with a residual, bound by their epilogue, measured no faster on pairs.)
+    TcPlan lone;
+    const bool fits_whole = plan_shape(p, 1, 256, 4, &lone) && lone.resident;      // a block that stays in shared memory is fetched once anyway
+    if (tn0 == 256 && !p.tepi && !fits_whole && p.PA * p.PB == 1 && p.KH * p.KW > 1 && p.residual == nullptr && pair_launch_possible() &&
+        plan_shape(p, 1, 256, 8, best, true) &&
+        best->tiles_m * best->tiles_n * 4 > sms) return true;
     bool found = false;
     for (const auto& c : cands) {
         if (c[1] > tn0) continue;
@@ -1083,7 +1128,7 @@ static bool tc_prepare(TcConvParams& p, int sms, TcPlan* pl) {
     return true;
 }
 
-template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI>
+template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI, bool PAIR = false>
 static int launch_persist_u(const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcConvParams& p, const TcPlan& pl,
                             int sms, int* status, cudaStream_t stream) {
     static std::mutex mu;
@@ -1094,14 +1139,20 @@ static int launch_persist_u(const CUtensorMap& tmB, const CUtensorMap& tmY, cons
     {
         std::lock_guard<std::mutex> lock(mu);
         if (dev < 0 || dev >= 64 || !configured[dev]) {
-            e = cudaFuncSetAttribute(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
+            e = cudaFuncSetAttribute(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX);
             if (e != cudaSuccess) return record_cuda_error(e);
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
     }
     const long long ntiles = pl.tiles_m * pl.tiles_n;
+    if (PAIR) {
+        const long long pairs = sms / 2;
+        const unsigned grid = 2u * (unsigned)(ntiles < pairs ? ntiles : pairs);
+        return launch_pdl_cluster(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS), (size_t)pl.smem, stream, 2u,
+                                  tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
+    }
     const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
-    return launch_pdl(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI>, dim3(grid), dim3(PTHREADS), (size_t)pl.smem, stream,
+    return launch_pdl(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS), (size_t)pl.smem, stream,
                       tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
 }
 
@@ -1111,12 +1162,44 @@ static int launch_persist(const CUtensorMap& tmB, const CUtensorMap& tmY, const 
     const int fused = p.residual ? 2 : (p.abs_sums ? 1 : 0);
     const bool tepi = p.tepi != 0;
 #define TAB_LAUNCH(BR, FU, TE) return launch_persist_u<MT, TNI, SB, BR, FU, TE>(tmB, tmY, tmR, p, pl, sms, status, stream)
+    if (pl.pair) {
+        if constexpr (MT == 1 && TNI == 256) {
+            if (fused == 2) return TAB_E_TOO_LARGE;                        // the planner does not pair layers with a residual
+            if (fused == 1) return launch_persist_u<1, 256, SB, false, 1, false, true>(tmB, tmY, tmR, p, pl, sms, status, stream);
+            return launch_persist_u<1, 256, SB, false, 0, false, true>(tmB, tmY, tmR, p, pl, sms, status, stream);
+        } else {
+            return TAB_E_TOO_LARGE;
+        }
+    }
 #define TAB_LAUNCH_F(BR, TE) do { if (fused == 2) TAB_LAUNCH(BR, 2, TE); if (fused == 1) TAB_LAUNCH(BR, 1, TE); TAB_LAUNCH(BR, 0, TE); } while (0)
     if (pl.resident) { if (tepi) TAB_LAUNCH_F(true, true); TAB_LAUNCH_F(true, false); }
     if (tepi) TAB_LAUNCH_F(false, true);
     TAB_LAUNCH_F(false, false);
 #undef TAB_LAUNCH_F
 #undef TAB_LAUNCH
+}
+
+static bool pair_launch_possible() {
+    static std::mutex mu;
+    static int known[64] = {};                                             // 0 unknown, 1 yes, 2 no
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!known[dev]) {
+        auto kernel = conv_umma_persist_kernel<1, 256, 8, false, 0, false, true>;
+        int clusters = 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2); cfg.blockDim = dim3(PTHREADS); cfg.dynamicSmemBytes = UMMA_SMEM_MAX;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        const bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX) == cudaSuccess &&
+                        cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1;
+        if (!ok) cudaGetLastError();
+        known[dev] = ok ? 1 : 2;
+    }
+    return known[dev] == 1;
 }
 
 static thread_local char g_last_kernel[112] = "none";
@@ -1143,7 +1226,7 @@ int tc_conv_dispatch(TcConvParams p, cudaStream_t stream) {
     TcPlan pl;
     if (!encode_tiled_fn() || !operands_aligned(p) || !tc_prepare(p, sms, &pl)) return TAB_E_TOO_LARGE;
     alignas(64) CUtensorMap tmB, tmY, tmR;
-    if (!make_map_2d(&tmB, p.w8, (unsigned long long)p.Kw * 64, (unsigned long long)p.KN, (unsigned)pl.tn)) return TAB_E_TOO_LARGE;
+    if (!make_map_2d(&tmB, p.w8, (unsigned long long)p.Kw * 64, (unsigned long long)p.KN, (unsigned)(pl.pair ? pl.tn / 2 : pl.tn))) return TAB_E_TOO_LARGE;
     tmY = tmB; tmR = tmB;                                                   // placeholders when the epilogue does not use them
     if (p.tepi) {
         const int bw = p.VW >= 32 ? 32 : p.VW, bh = 32 / bw;
@@ -1151,8 +1234,9 @@ int tc_conv_dispatch(TcConvParams p, cudaStream_t stream) {
         if (p.residual && !make_map_4d(&tmR, p.residual, p.KN, p.OW, p.OH, p.N, bw, bh)) return TAB_E_TOO_LARGE;
     }
     int* status = umma_status_ptr();
-    snprintf(g_last_kernel, sizeof(g_last_kernel), "conv_umma_persist_kernel<%d,%d,%d,%d,%d,%d> grid %dx%d", pl.mt, pl.tn, pl.sb, (int)pl.resident,
-             p.residual ? 2 : (p.abs_sums ? 1 : 0), p.tepi, p.VH, p.VW);
+    snprintf(g_last_kernel, sizeof(g_last_kernel), "conv_umma_persist_kernel<%d,%d,%d,%d,%d,%d%s> grid %dx%d", pl.mt, pl.tn, pl.sb, (int)pl.resident,
+             p.residual ? 2 : (p.abs_sums ? 1 : 0), p.tepi, pl.pair ? ",pair" : "", p.VH, p.VW);
+    if (pl.pair) return launch_persist<1, 256, 8>(tmB, tmY, tmR, p, pl, sms, status, stream);
     if (pl.tn == 64) return pl.mt == 2 ? launch_persist<2, 64, 6>(tmB, tmY, tmR, p, pl, sms, status, stream) : launch_persist<1, 64, 6>(tmB, tmY, tmR, p, pl, sms, status, stream);
     if (pl.tn == 128) return pl.mt == 2 ? launch_persist<2, 128, 4>(tmB, tmY, tmR, p, pl, sms, status, stream) : launch_persist<1, 128, 6>(tmB, tmY, tmR, p, pl, sms, status, stream);
     return launch_persist<1, 256, 4>(tmB, tmY, tmR, p, pl, sms, status, stream);

@@ -172,6 +172,67 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// ---- CTA pairs (thread-block clusters of two, tcgen05 cta_group::2) ----------------------------------------------------
+// One MMA instruction, issued by the even CTA of the pair, multiplies 256 rows - 128 from each CTA's shared memory, at the
+// same offset in both - by N filters of which each CTA holds N/2 (same offset again); each CTA's tensor memory receives the
+// accumulators of its own 128 rows.  A CTA thus fetches half of every filter slice.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// All threads of all CTAs of the cluster (every thread must execute it).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at this shared-memory offset in CTA `rank` of the cluster (may be the caller's own).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t mbar, uint32_t rank) {
+    asm volatile("{\n\t.reg .b32 ra;\n\t"
+                 "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+                 "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(mbar), "r"(rank) : "memory");
+}
+// Bounded wait, by a whole warp, on a barrier that threads of the other CTA arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster_warp(uint32_t addr, uint32_t parity) {
+    bool ok = false;
+    for (uint32_t i = 0; i < UMMA_WAIT_LIMIT && !ok; i++) {
+        uint32_t r;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(r) : "r"(addr), "r"(parity) : "memory");
+        ok = r != 0;
+    }
+    return __all_sync(0xFFFFFFFFu, ok);
+}
+// This CTA's half of a filter slice; the bytes are counted on the even CTA's barrier (bit 24 of a shared::cluster
+// address is the CTA's rank within the pair).  No multicast: each CTA copies its own half.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int x, int y, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"(tmap), "r"(mbar & 0xFEFFFFFFu), "r"(x), "r"(y) : "memory");
+}
+__host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)((2 * UTM) >> 4) << 24);
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives, when the pair's MMAs issued so far have completed, on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(mbar), "h"((uint16_t)3) : "memory");
+}
+// Executed by the same warp of both CTAs.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t tmem_base, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(cols) : "memory");
+}
+
 __device__ __forceinline__ void sts_v4(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }

@@ -3,7 +3,8 @@ profilers and quick measurements).
 
     python -m tab_b200.run_case conv     --type 0 --N 64 --H 56 --C 64 --KN 64 --K 3 --stride 1 --pad 1
     python -m tab_b200.run_case packed   ...        # the popcount convolution alone on pre-packed activations
-    python -m tab_b200.run_case bits     ...        # the tensor-core GEMM stage alone (bit-planes + prepared byte weights)
+    python -m tab_b200.run_case bits     ...        # the tensor-core GEMM stage alone (bit-planes + prepared byte weights);
+                                                    # --chain / --residual / --int16 select its epilogue
     python -m tab_b200.run_case quantize --bitwidth 2 --N 256 --H 56 --C 256
 
 Prints one JSON line: milliseconds per call (CUDA events, after warm-up) and the derived TOPS or GB/s.
@@ -33,6 +34,9 @@ def main():
     ap.add_argument("--pad", type=int, default=1)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--residual", action="store_true", help="bits: add a residual tensor in the epilogue")
+    ap.add_argument("--chain", action="store_true", help="bits: per-image sums of |y| and the next layer's thresholds in the epilogue")
+    ap.add_argument("--int16", action="store_true", help="bits: 16-bit integer output (the hand-over to the next quantiser)")
     ap.add_argument("--path", type=int, default=0, help="conv: 0 tensor cores, 1 popcount kernel, 2 popcount kernel, one POPC per word")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
@@ -77,7 +81,10 @@ def main():
             qx, _ = ops.Quantize(x, ths, 1 if t in (2, 3) else 2, N, H, W, C)
             if a.op == "bits":
                 w8 = ops.expand_weights(qw, 1 if t in (1, 3) else 2, KN, K, K, C)
-                fn = lambda: ops.conv2d_bits(qx, w8, t, p, p, s, s, N, H, W, C, KN, K, K)
+                res = torch.round(torch.randn(N, KN, oh, oh, device=dev) * 8) if a.residual else None
+                state = ops.new_state(N, dev) if a.chain else None
+                fn = lambda: ops.conv2d_bits(qx, w8, t, p, p, s, s, N, H, W, C, KN, K, K, residual=res,
+                                             threshold_scale=0.7 if a.chain else None, state=state, out_int16=a.int16)
             else:
                 fn = lambda: ops.conv2d_packed(qx, qw, btn, t, p, p, s, s, N, H, W, C, KN, K, K)
     for _ in range(a.warmup):

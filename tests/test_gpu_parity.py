@@ -318,6 +318,43 @@ def test_bits_stage_entry_point(cuda, geom):
         assert _cabi.lib().tab_device_status() == 0
 
 
+@pytest.mark.parametrize("t", range(4))
+@pytest.mark.parametrize("geom", [
+    # p1 p2 s1 s2  N   H   W   C   KN KH KW
+    (1, 1, 1, 1, 48, 14, 14, 256, 320, 3, 3),    # two filter blocks, the second ragged
+    (0, 0, 1, 1, 40, 16, 16, 100, 256, 3, 3),    # no padding, one ragged channel word
+    (1, 1, 1, 1, 97, 7, 7, 192, 512, 3, 3),      # odd number of 128-row blocks: the last pair's second CTA has no rows
+])
+def test_cta_pair_kernel(cuda, t, geom, conv_path):
+    """Wide filter blocks with many tiles run on clusters of two CTAs (tcgen05 cta_group::2): plain and with next thresholds
+    and 16-bit output, against the oracle; the same shapes with a residual."""
+    if conv_path != "tensor":
+        pytest.skip("tensor-core path only")
+    p1, p2, s1, s2, N, H, W, C, KN, KH, KW = geom
+    x, ths = make_input(61, N, H, W, C)
+    w, wths = make_input(62, KN, KH, KW, C)
+    ab, wb = O.act_bits(t), O.weight_bits(t)
+    qw, btn = O.quantize(w, wths, wb, KN, KH, KW, C)
+    qx, _ = TAB.Quantize(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C)
+    w8 = TAB.ops.expand_weights(dev_t(qw, cuda), wb, KN, KH, KW, C)
+    yo = c_oracle.conv2d(x, qw, ths, btn, t, *geom)
+    state = TAB.ops.new_state(N, cuda)
+    y, _ = TAB.ops.conv2d_bits(qx, w8, t, *geom)
+    assert ",pair>" in _cabi.lib().tab_last_conv_kernel().decode()
+    assert np.array_equal(y.cpu().numpy(), yo)
+    r = torch.round(torch.randn(*yo.shape, device=cuda) * 5)
+    y2, nxt = TAB.ops.conv2d_bits(qx, w8, t, *geom, residual=r, threshold_scale=0.7, state=state)   # (a residual layer runs on single CTAs)
+    y2o = yo + r.cpu().numpy()
+    assert np.array_equal(y2.cpu().numpy(), y2o)
+    assert np.array_equal(nxt.cpu().numpy(), OracleOps.residual_threshold(y2o.copy(), None, 0.7))
+    y16, nxt16 = TAB.ops.conv2d_bits(qx, w8, t, *geom, threshold_scale=0.7, state=state, out_int16=True)
+    assert ",pair>" in _cabi.lib().tab_last_conv_kernel().decode()
+    assert y16.dtype == torch.int16 and np.array_equal(y16.cpu().numpy().astype(np.float32), yo)
+    assert np.array_equal(nxt16.cpu().numpy(), OracleOps.residual_threshold(yo.copy(), None, 0.7))
+    assert not state.any().item()
+    assert _cabi.lib().tab_device_status() == 0
+
+
 @pytest.mark.parametrize("t", [0, 3])
 @pytest.mark.parametrize("geom", [
     # p1 p2 s1 s2  N   H    W    C   KN KH KW
