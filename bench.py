@@ -298,6 +298,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")       # stdout carries the one JSON line and nothing else
         dist.init_process_group("nccl", device_id=dev)
     lib = _cabi.lib()
     import TAB_CUDA  # the reference-facing extension module (built in-tree by Setup_CUDA.py)
