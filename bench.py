@@ -325,7 +325,11 @@ def main():
 
         def conv_bits(self, *a, **k):
             launches[0] += 1
-            return super().conv_bits(*a, **k)
+            out = super().conv_bits(*a, **k)
+            # the quantised hand-over to the next layer comes from the same kernel ("+next") or from a quantiser launch behind it
+            if k.get("next_bitwidth") is not None and "+next" not in lib.tab_last_conv_kernel().decode():
+                launches[0] += 1
+            return out
 
     class ModuleConv:
         """The same prepared convolution through the TAB_CUDA extension module."""
@@ -354,8 +358,8 @@ def main():
 
     class NhwcConv(CountingConv):
         def conv_bits(self, *a, **k):
-            y, nxt = super().conv_bits(*a, **k)
-            return nhwc(y), nxt
+            out = super().conv_bits(*a, **k)
+            return (nhwc(out[0]),) + tuple(out[1:])
 
     convs = {}
     for name, (w, t) in weights.items():
@@ -373,7 +377,7 @@ def main():
         if count:
             launches[0] += 2
         ths = tab_ops.residual_threshold(x_in.reshape(nb, -1), None, chain.THRESHOLD_SCALE)      # reduce + finalise kernels
-        y, _, _, _ = chain.forward_prepared(cset, x_in, ths, nb, compact_mid=True)
+        y, _, _, _ = chain.forward_prepared(cset, x_in, ths, nb, compact_mid=True, fused_quant=cset is convs)
         return y, ths
 
     def barrier():
@@ -698,7 +702,7 @@ def main():
     popc_achieved = sums["ops"] / (sums["popc_ms"] * 1e-3) / 1e12 if sums["popc_ms"] else None
     l1_images = n_local
     roofline = {
-        "kernel": "whole step: %d launches (quantize_c64_kernel x16, conv_umma_persist_kernel x19, threshold kernels x2)" % launches_per_step,
+        "kernel": "whole step: %d launches (conv_umma_persist_kernel x19, quantize_c64_kernel x%d - the other convolutions' inputs are quantised by the kernel that wrote them -, threshold kernels x2)" % (launches_per_step, launches_per_step - 21),
         "bound": "hbm", "achieved": step_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": step_gbs / hbm_peak, "peak_source": hbm_src,
         "algorithmic_bytes_per_step": step_bytes, "images_per_gpu": n_local,
         "traffic": (L1_TRAFFIC_PER_IMAGE * l1_images) if L1_TRAFFIC_PER_IMAGE else None,

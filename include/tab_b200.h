@@ -180,6 +180,20 @@ int tab_conv2d_bits_i16_launch(const int64_t* qx, const int8_t* w8, int16_t* y16
                                void* state, float* next_ths, float next_scale, tab_stream_t stream);
 int tab_quantize_i16_launch(const int16_t* x, const float* ths, int64_t* qx, int bitwidth, int N, int H, int W, int C,
                             tab_stream_t stream);
+/*
+ * A chained layer that also hands the next convolution its input: after the GEMM stage (tab_conv2d_bits_launch, or the int16
+ * form when y_is_int16) the same launch computes the next thresholds and quantises the result against them into next_qx,
+ * [N][OH][OW][ceil(KN/64)][next_bitwidth] 64-bit words - exactly what tab_quantize_launch(y, next_ths, next_qx, ...) writes
+ * (TerOnlyKernel / BinOnlyKernel, TAB_GEMM.cu:163-247), without that launch and while most of y is still in the L2.  The CTAs of
+ * the grid meet at a counter in the state block in between (a bounded wait; all of them are resident, at most one per SM, as
+ * long as no other work holds SMs of the device for as long as the wait's limit of some tenths of a second).  When KN is not a
+ * multiple of 64, N > 8192 or next_qx is not 16-byte aligned, the quantiser runs as a launch of its own behind the GEMM stage;
+ * the result is the same.  state, next_ths, next_qx are required; residual only with fp32 output.
+ */
+int tab_conv2d_bits_next_launch(const int64_t* qx, const int8_t* w8, void* y, int y_is_int16, int type, int p1, int p2, int s1, int s2,
+                                int N, int H, int W, int C, int KN, int KH, int KW,
+                                const float* residual, void* state, float* next_ths, float next_scale,
+                                int64_t* next_qx, int next_bitwidth, tab_stream_t stream);
 
 /*
  * tab_conv2d_launch without a workspace argument.  No counterpart in the reference (its host code calls

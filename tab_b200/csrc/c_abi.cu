@@ -226,16 +226,19 @@ int tab_expand_weights_launch(const int64_t* qw, int8_t* w8, int bitwidth, int K
     return expand_weights_dispatch(qw, w8, bitwidth == 1 ? 1 : 2, KN, KH, KW, C, reinterpret_cast<cudaStream_t>(stream));
 }
 
-size_t tab_conv2d_state_bytes(int N) { return N < 0 ? 0 : round256((size_t)N * 8 + 8); }
+size_t tab_conv2d_state_bytes(int N) { return N < 0 ? 0 : round256((size_t)N * 8 + 16); }   // sums, completion counter, two grid-barrier words
 
 // Shared by the two GEMM-stage entry points: y (float) or y16 (int16) receives the result.
+// next_qx (optional, with next_ths): the result quantised at next_bits against next_ths, as tab_quantize_launch would write it.
 static int bits_impl(const int64_t* qx, const int8_t* w8, float* y, int16_t* y16, int type, int p1, int p2, int s1, int s2,
                      int N, int H, int W, int C, int KN, int KH, int KW,
-                     const float* residual, void* state, float* next_ths, float next_scale, tab_stream_t stream) {
+                     const float* residual, void* state, float* next_ths, float next_scale, tab_stream_t stream,
+                     int64_t* next_qx = nullptr, int next_bits = 0) {
     int rc = conv_args_ok(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW);
     if (rc != TAB_OK) return rc;
     const long long oh = ((long long)H + 2LL * p1 - KH + 1) / s1, ow = ((long long)W + 2LL * p2 - KW + 1) / s2;
     if (next_ths && !state) return TAB_E_NULL_POINTER;
+    if (next_qx && (!next_ths || next_bits < 1)) return TAB_E_BAD_ARGUMENT;
     if (N == 0) return TAB_OK;
     if (KN == 0 || oh <= 0 || ow <= 0) {                            // empty output: mean |y| of nothing is 0
         if (next_ths) {
@@ -246,7 +249,7 @@ static int bits_impl(const int64_t* qx, const int8_t* w8, float* y, int16_t* y16
     }
     if (!qx || !w8 || (!y && !y16)) return TAB_E_NULL_POINTER;
     if (misaligned(qx, 15) || misaligned(w8, 15) || misaligned(y, 15) || misaligned(y16, 15) || misaligned(residual, 15) || misaligned(state, 7) ||
-        misaligned(next_ths, 3))
+        misaligned(next_ths, 3) || misaligned(next_qx, 7))
         return TAB_E_ALIGNMENT;
     if (y16 && (long long)KH * KW * C > 32767) return TAB_E_TOO_LARGE;   // |y| <= KH*KW*C must fit 16 bits
     TcConvParams p = tc_geometry(type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, oh, ow);
@@ -256,8 +259,22 @@ static int bits_impl(const int64_t* qx, const int8_t* w8, float* y, int16_t* y16
         p.done_counter = reinterpret_cast<unsigned*>(reinterpret_cast<double*>(state) + N);
         p.ths_out = next_ths; p.ths_scale = next_scale; p.self_clean = 1;
     }
+    // The grid quantises its own result when the words line up with the filter count, the thresholds fit its shared memory
+    // and the result is small (up to 8M values); otherwise the quantiser runs as a launch of its own behind it.  Same bits
+    // either way.  Measured on B200 (GEMM stage + quantiser, us, in-kernel / separate launch): results of 0.1-0.8M values
+    // 23-29 / 32-49; 6.4M values 46-57 / 45-57; 12.8M 54-87 / 52-83; 51M 124-189 / 116-161 - the quantiser's own grid has
+    // twice the warps per SM of the GEMM kernel's 16 and streams large tensors faster than the launch it saves.
+    const bool in_kernel = next_qx && (KN % 64) == 0 && N <= 8192 && (long long)N * oh * ow * KN <= (1LL << 23) && !misaligned(next_qx, 15) &&
+                           !misaligned(y, 31);
+    if (in_kernel) {
+        p.next_qx = reinterpret_cast<uint64_t*>(next_qx); p.next_bits = next_bits == 1 ? 1 : 2;
+        p.grid_bar = p.done_counter + 1;
+    }
     tc_forget_last_kernel();
-    return tc_conv_dispatch(p, reinterpret_cast<cudaStream_t>(stream));
+    rc = tc_conv_dispatch(p, reinterpret_cast<cudaStream_t>(stream));
+    if (rc != TAB_OK || !next_qx || in_kernel) return rc;
+    return quantize_dispatch(y16 ? static_cast<const void*>(y16) : static_cast<const void*>(y), next_ths, next_qx, nullptr, next_bits == 1 ? 1 : 2,
+                             N, (int)oh, (int)ow, KN, reinterpret_cast<cudaStream_t>(stream), nullptr, y16 != nullptr);
 }
 
 int tab_conv2d_bits_launch(const int64_t* qx, const int8_t* w8, float* y, int type, int p1, int p2, int s1, int s2,
@@ -270,6 +287,16 @@ int tab_conv2d_bits_i16_launch(const int64_t* qx, const int8_t* w8, int16_t* y16
                                int N, int H, int W, int C, int KN, int KH, int KW,
                                void* state, float* next_ths, float next_scale, tab_stream_t stream) {
     return bits_impl(qx, w8, nullptr, y16, type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, nullptr, state, next_ths, next_scale, stream);
+}
+
+int tab_conv2d_bits_next_launch(const int64_t* qx, const int8_t* w8, void* y, int y_is_int16, int type, int p1, int p2, int s1, int s2,
+                                int N, int H, int W, int C, int KN, int KH, int KW,
+                                const float* residual, void* state, float* next_ths, float next_scale,
+                                int64_t* next_qx, int next_bitwidth, tab_stream_t stream) {
+    if (!next_qx || !next_ths || !state) return TAB_E_NULL_POINTER;
+    if (y_is_int16 && residual) return TAB_E_BAD_ARGUMENT;
+    return bits_impl(qx, w8, y_is_int16 ? nullptr : static_cast<float*>(y), y_is_int16 ? static_cast<int16_t*>(y) : nullptr,
+                     type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, residual, state, next_ths, next_scale, stream, next_qx, next_bitwidth);
 }
 
 int tab_quantize_i16_launch(const int16_t* x, const float* ths, int64_t* qx, int bitwidth, int N, int H, int W, int C, tab_stream_t stream) {

@@ -78,6 +78,163 @@ __device__ __forceinline__ void fused_finish(const TcConvParams& p) {
     }
 }
 
+// ---- second phase: the grid quantises its own result for the next convolution ------------------------------------------
+// Replaces, for a chained layer, the quantiser launch of the next convolution (TerOnlyKernel / BinOnlyKernel,
+// TAB_GEMM.cu:163-247, same encoding).  Every CTA first reports in at a grid-wide counter - all CTAs of the launch are
+// resident (one per SM at most), so the wait is for CTAs that are running; it is bounded all the same - then computes the
+// thresholds of all images from the complete |y| sums (the arithmetic of fused_finish), and the CTAs share the words of
+// the result, last word first (the end of the tensor is what was written last).  Data written by other SMs in this
+// launch is read with L2-coherent loads.
+constexpr uint32_t GRID_WAIT_LIMIT = 1u << 22;                             // x ~100 ns
+
+__device__ __forceinline__ float4 ld_cg_f4(const float* ptr) {
+    float4 r;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(ptr));
+    return r;
+}
+struct F8 { float v[8]; };
+__device__ __forceinline__ F8 ld_cg_f8(const float* ptr) {                         // two 128-bit loads
+    F8 r;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]) : "l"(ptr));
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7]) : "l"(ptr + 4));
+    return r;
+}
+__device__ __forceinline__ uint4 ld_cg_u4(const void* ptr) {
+    uint4 r;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(ptr));
+    return r;
+}
+
+// Eight consecutive channels -> one byte per plane, stored at byte `byte` of the word's planes.
+__device__ __forceinline__ void quantize8(const float (&v)[8], float t, int bits, unsigned char* word_out, int byte) {
+    if (bits == 2) {
+        const float nt = -t;
+        unsigned pos = 0, neg = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            pos |= (v[i] > t) ? (1u << i) : 0u;
+            neg |= (v[i] < nt) ? (1u << i) : 0u;
+        }
+        neg &= ~pos;                                                       // the "+1" branch is tested first (TAB_GEMM.cu:184-192)
+        word_out[byte] = (unsigned char)neg;                               // sign plane
+        word_out[8 + byte] = (unsigned char)(pos | neg);                   // magnitude plane
+    } else {
+        unsigned b = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) b |= (v[i] < t) ? (1u << i) : 0u;      // TAB_GEMM.cu:231
+        word_out[byte] = (unsigned char)b;
+    }
+}
+
+// What the second phase needs of the kernel's parameter block, handed over by value: taking the block's address for a
+// call would move the whole block, which every role reads all the time, from registers and constant memory to the stack.
+struct QuantTailArgs {
+    const float* y; const int16_t* y16; double* abs_sums; float* ths_out; uint64_t* next_qx; unsigned* grid_bar;
+    double per_image; float ths_scale; int self_clean, next_bits, N, M, KN, OH, OW;
+};
+__device__ __forceinline__ QuantTailArgs quant_tail_args(const TcConvParams& p) {
+    QuantTailArgs a;
+    a.y = p.y; a.y16 = p.y16; a.abs_sums = p.abs_sums; a.ths_out = p.ths_out; a.next_qx = p.next_qx; a.grid_bar = p.grid_bar;
+    a.per_image = p.per_image; a.ths_scale = p.ths_scale; a.self_clean = p.self_clean; a.next_bits = p.next_bits;
+    a.N = p.N; a.M = p.M; a.KN = p.KN; a.OH = p.OH; a.OW = p.OW;
+    return a;
+}
+__device__ __noinline__ void quantize_tail(const QuantTailArgs p, float* ths_smem, int* status) {
+    const int tid = threadIdx.x;
+    const unsigned G = gridDim.x;
+    __threadfence();                                                       // this thread's stores and atomics, device-wide
+    __syncthreads();
+    int flag = 0;
+    if (tid == 0) {
+        __threadfence();
+        atomicAdd(p.grid_bar, 1u);
+        bool ok = false;
+        for (uint32_t i = 0; i < GRID_WAIT_LIMIT && !ok; i++) {
+            unsigned seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.grid_bar) : "memory");
+            ok = seen >= G;
+            if (!ok) __nanosleep(100);
+        }
+        if (!ok && status) atomicExch(status, 21);
+        flag = ok ? 1 : 0;
+    }
+    if (!__syncthreads_or(flag)) return;                                   // the result of the launch is void; the status says so
+    for (int n = tid; n < p.N; n += (int)blockDim.x) {
+        const double sum = __ldcg(p.abs_sums + n);
+        const float t = (float)((double)p.ths_scale * (sum / p.per_image));
+        ths_smem[n] = t;
+        if (blockIdx.x == 0 && p.ths_out) p.ths_out[n] = t;
+    }
+    __syncthreads();
+    // the CTA that gets here last knows that every CTA has read the sums: it leaves the state block zero again
+    flag = 0;
+    if (tid == 0) flag = (atomicAdd(p.grid_bar + 1, 1u) == G - 1u) ? 1 : 0;
+    if (__syncthreads_or(flag)) {
+        if (p.self_clean) for (int n = tid; n < p.N; n += (int)blockDim.x) p.abs_sums[n] = 0.0;
+        if (tid == 0) { p.grid_bar[0] = 0u; p.grid_bar[1] = 0u; }
+    }
+    // words of the result: word w = 64 consecutive channels = elements [64 w, 64 w + 64) of y; 8 lanes per word, 64 words
+    // per pass of the CTA, UN passes per step with all loads of a step issued before the first is used (addresses are one
+    // base register plus constants)
+    const int PC2 = p.KN >> 6, bits = p.next_bits, byte = tid & 7;
+    const uint32_t grp = (uint32_t)tid >> 3;
+    const uint32_t words = (uint32_t)((long long)p.M * PC2);               // < 2^31, checked on the host
+    const FastDiv dimg = make_fastdiv_dev((uint32_t)(p.OH * p.OW * PC2));
+    unsigned char* out = reinterpret_cast<unsigned char*>(p.next_qx);
+    const size_t obytes = (size_t)8 * bits;                                // bytes of a word's planes
+    if (p.y16 != nullptr) {
+        constexpr int UN = 16;                                             // 16 x 16 bytes in flight per thread
+        constexpr uint32_t SPAN = 64u * UN;
+        const long long nsteps = ((long long)words + SPAN - 1) / SPAN;
+        for (long long s = nsteps - 1 - (long long)blockIdx.x; s >= 0; s -= G) {
+            const uint32_t w0 = (uint32_t)s * SPAN + grp;
+            const int16_t* src = p.y16 + (size_t)w0 * 64 + byte * 8;
+            const bool full = (uint32_t)s * SPAN + SPAN <= words;
+            uint4 raw[UN];
+            if (full) {
+#pragma unroll
+                for (int u = 0; u < UN; u++) raw[u] = ld_cg_u4(src + u * 4096);
+            } else {
+#pragma unroll
+                for (int u = 0; u < UN; u++) if (w0 + 64u * u < words) raw[u] = ld_cg_u4(src + u * 4096);
+            }
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const uint32_t w = w0 + 64u * u;
+                if (!full && w >= words) continue;
+                const uint32_t q[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 4; i++) { v[2 * i] = (float)(int16_t)(q[i] & 0xFFFFu); v[2 * i + 1] = (float)(int16_t)(q[i] >> 16); }
+                quantize8(v, ths_smem[dimg.div(w)], bits, out + (size_t)w * obytes, byte);
+            }
+        }
+    } else {
+        constexpr int UN = 8;                                              // 8 x 32 bytes in flight per thread
+        constexpr uint32_t SPAN = 64u * UN;
+        const long long nsteps = ((long long)words + SPAN - 1) / SPAN;
+        for (long long s = nsteps - 1 - (long long)blockIdx.x; s >= 0; s -= G) {
+            const uint32_t w0 = (uint32_t)s * SPAN + grp;
+            const float* src = p.y + (size_t)w0 * 64 + byte * 8;
+            const bool full = (uint32_t)s * SPAN + SPAN <= words;
+            F8 v[UN];
+            if (full) {
+#pragma unroll
+                for (int u = 0; u < UN; u++) v[u] = ld_cg_f8(src + u * 4096);
+            } else {
+#pragma unroll
+                for (int u = 0; u < UN; u++) if (w0 + 64u * u < words) v[u] = ld_cg_f8(src + u * 4096);
+            }
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const uint32_t w = w0 + 64u * u;
+                if (!full && w >= words) continue;
+                quantize8(v[u].v, ths_smem[dimg.div(w)], bits, out + (size_t)w * obytes, byte);
+            }
+        }
+    }
+}
+
 // ---- expander: bit-planes -> int8 patch rows ---------------------------------------------------------------------------
 // Four quantised values from the low four bits of a magnitude and a sign nibble: bytes 0x00 / 0x01 / 0xFF.
 __device__ __forceinline__ uint32_t expand4(uint32_t mnib, uint32_t snib) {
@@ -891,7 +1048,10 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     if (PAIR) cluster_sync_all();                                          // the other CTA no longer reads this one's memory nor arrives on its barriers
     pdl_launch_dependents();
     if (warp == 1) { if (PAIR) tmem_dealloc_pair(tmem_base, (uint32_t)(2 * ACOLS)); else tmem_dealloc(tmem_base, (uint32_t)(2 * ACOLS)); }
-    if (FUSED) fused_finish(p);
+    if (FUSED) {
+        if (p.next_qx != nullptr) quantize_tail(quant_tail_args(p), reinterpret_cast<float*>(smem), status);   // the patch area is free now
+        else fused_finish(p);
+    }
     PROF_GT(22, 23, tid == 0);                                             // exit
 }
 
@@ -1234,8 +1394,8 @@ int tc_conv_dispatch(TcConvParams p, cudaStream_t stream) {
         if (p.residual && !make_map_4d(&tmR, p.residual, p.KN, p.OW, p.OH, p.N, bw, bh)) return TAB_E_TOO_LARGE;
     }
     int* status = umma_status_ptr();
-    snprintf(g_last_kernel, sizeof(g_last_kernel), "conv_umma_persist_kernel<%d,%d,%d,%d,%d,%d%s> grid %dx%d", pl.mt, pl.tn, pl.sb, (int)pl.resident,
-             p.residual ? 2 : (p.abs_sums ? 1 : 0), p.tepi, pl.pair ? ",pair" : "", p.VH, p.VW);
+    snprintf(g_last_kernel, sizeof(g_last_kernel), "conv_umma_persist_kernel<%d,%d,%d,%d,%d,%d%s> grid %dx%d%s", pl.mt, pl.tn, pl.sb, (int)pl.resident,
+             p.residual ? 2 : (p.abs_sums ? 1 : 0), p.tepi, pl.pair ? ",pair" : "", p.VH, p.VW, p.next_qx ? " +next" : "");
     if (pl.pair) return launch_persist<1, 256, 8>(tmB, tmY, tmR, p, pl, sms, status, stream);
     if (pl.tn == 64) return pl.mt == 2 ? launch_persist<2, 64, 6>(tmB, tmY, tmR, p, pl, sms, status, stream) : launch_persist<1, 64, 6>(tmB, tmY, tmR, p, pl, sms, status, stream);
     if (pl.tn == 128) return pl.mt == 2 ? launch_persist<2, 128, 4>(tmB, tmY, tmR, p, pl, sms, status, stream) : launch_persist<1, 128, 6>(tmB, tmY, tmR, p, pl, sms, status, stream);

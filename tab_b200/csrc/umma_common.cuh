@@ -18,6 +18,18 @@ struct FastDiv {
     __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : __umulhi(n, mul) >> shr; }
 #endif
 };
+#ifdef __CUDACC__
+__device__ __forceinline__ FastDiv make_fastdiv_dev(uint32_t d) {
+    FastDiv f = {0u, 0u, d};
+    if (d > 1) {
+        const uint32_t l = 32u - (uint32_t)__clz((int)(d - 1));           // ceil(log2 d)
+        const uint32_t p = 31 + l;
+        f.mul = (uint32_t)(((1ull << p) + d - 1) / d);
+        f.shr = p - 32;
+    }
+    return f;
+}
+#endif
 inline FastDiv make_fastdiv(uint32_t d) {
     FastDiv f = {0u, 0u, d};
     if (d > 1) {
@@ -63,6 +75,13 @@ struct TcConvParams {
     double per_image;
     unsigned* done_counter;  // zero before the launch
     int self_clean;
+    // Optional second phase (needs abs_sums and ths_scale): when every CTA has finished its tiles, the grid quantises the
+    // result it has just written (y, or y16) against those thresholds into next_qx, bit-planes [M][KN/64][next_bits] as
+    // tab_quantize_launch would write them - the next convolution's input, without a kernel of its own and read back
+    // while most of it is still in the L2.  KN % 64 == 0.  grid_bar: two words, zero before the launch, zero again after.
+    uint64_t* next_qx;
+    int next_bits;
+    unsigned* grid_bar;
 };
 
 #ifdef __CUDACC__

@@ -96,16 +96,19 @@ class TABConv2d(torch.nn.Module):
             thresholds = ops.residual_threshold(x.reshape(N, -1), None, self.threshold_scale)
         return ops.Quantize(x, thresholds, act_bitwidth(self.conv_type), N, H, W, self.C)[0]
 
-    def conv_bits(self, QX, N, H, W, residual=None, next_threshold_scale=None, state=None, out_int16=False):
+    def conv_bits(self, QX, N, H, W, residual=None, next_threshold_scale=None, state=None, out_int16=False, next_bitwidth=None):
         """GEMM stage on quantised activations.  Returns ``(Y, next_thresholds_or_None)``.  ``out_int16``: ``Y`` as int16
         where that is possible (no residual, KH*KW*C <= 32767, a shape the tensor-core kernel covers), else fp32 as usual:
-        look at ``Y.dtype``."""
+        look at ``Y.dtype``.  ``next_bitwidth`` (with ``next_threshold_scale``): a third value is returned, ``Y`` quantised
+        against the next thresholds at that bitwidth - the next convolution's ``QX`` - from the same launch."""
         if next_threshold_scale is not None and state is None:
             state = self.state(N, QX.device)
+        if next_bitwidth is not None and next_threshold_scale is None:
+            raise ValueError("next_bitwidth needs next_threshold_scale")
         compact = out_int16 and residual is None and self.KH * self.KW * self.C <= 32767
         try:
             return ops.conv2d_bits(QX, self.W8, self.conv_type, *self.geometry(N, H, W), residual=residual,
-                                   threshold_scale=next_threshold_scale, state=state, out_int16=compact)
+                                   threshold_scale=next_threshold_scale, state=state, out_int16=compact, next_bitwidth=next_bitwidth)
         except _cabi.TabError as exc:
             if exc.code != -5:
                 raise
@@ -116,6 +119,9 @@ class TABConv2d(torch.nn.Module):
             nxt = ops.residual_threshold(Y, residual, next_threshold_scale if next_threshold_scale is not None else 0.0)
             if next_threshold_scale is None:
                 nxt = None
+        if next_bitwidth is not None:
+            OH, OW = self.out_size(H, W)
+            return Y, nxt, ops.Quantize(Y, nxt, next_bitwidth, N, OH, OW, self.KN)[0]
         return Y, nxt
 
     def forward(self, x, thresholds=None):

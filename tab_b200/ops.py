@@ -186,12 +186,14 @@ def quantize_i16(X16, thresholds, bitwidth, N, H, W, C):
 
 
 def conv2d_bits(QX, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW,
-                residual=None, threshold_scale=None, state=None, out_int16=False):
+                residual=None, threshold_scale=None, state=None, out_int16=False, next_bitwidth=None):
     """The GEMM stage on the tensor cores: activations as ``Quantize`` wrote them (bitwidth 2 for types 0,1; 1 for
     types 2,3), weights from ``expand_weights``.  Returns ``(Y, next_thresholds_or_None)``; ``Y = conv + residual``.
     ``threshold_scale`` needs ``state`` (``new_state``).  ``out_int16``: ``Y`` as int16 (no residual; the values are
-    integers of magnitude at most KH*KW*C) for ``quantize_i16``.  Raises ``TabError`` (TAB_E_TOO_LARGE) for shapes
-    the tensor-core kernel does not cover."""
+    integers of magnitude at most KH*KW*C) for ``quantize_i16``.  ``next_bitwidth`` (needs ``threshold_scale``): the same
+    launch also quantises ``Y`` against the next thresholds at that bitwidth and a third value is returned, ``QX`` of the
+    next convolution (``[N,OH,OW,ceil(KN/64),bits]`` int64, what ``Quantize(Y, next_thresholds, ...)`` gives).
+    Raises ``TabError`` (TAB_E_TOO_LARGE) for shapes the tensor-core kernel does not cover."""
     _check_input(QX, "QX", torch.int64)
     _check_input(W8, "W8", torch.int8)
     conv_type = int(type)
@@ -212,9 +214,21 @@ def conv2d_bits(QX, W8, type, padding1, padding2, stride1, stride2, N, H, W, C, 
         raise RuntimeError("threshold_scale needs a state block (new_state)")
     if out_int16 and residual is not None:
         raise RuntimeError("out_int16 cannot be combined with a residual")
+    if next_bitwidth is not None and threshold_scale is None:
+        raise RuntimeError("next_bitwidth needs threshold_scale (the thresholds the result is quantised against)")
     with torch.cuda.device(QX.device):
         Y = torch.empty((N, KN, OH, OW), dtype=torch.int16 if out_int16 else torch.float32, device=QX.device)
         nxt = torch.empty((N,), dtype=torch.float32, device=QX.device) if threshold_scale is not None else None
+        if next_bitwidth is not None:
+            nb = 1 if int(next_bitwidth) == 1 else 2
+            QN = torch.empty((N, OH, OW, (KN + 63) // 64, nb), dtype=torch.int64, device=QX.device)
+            rc = _cabi.lib().tab_conv2d_bits_next_launch(QX.data_ptr(), W8.data_ptr(), Y.data_ptr(), 1 if out_int16 else 0, conv_type,
+                                                         p1, p2, s1, s2, N, H, W, C, KN, KH, KW,
+                                                         residual.data_ptr() if residual is not None else None,
+                                                         state.data_ptr(), nxt.data_ptr(), float(threshold_scale),
+                                                         QN.data_ptr(), nb, _stream_ptr(QX.device))
+            _cabi.check(rc, "tab_conv2d_bits_next_launch")
+            return Y, nxt, QN
         if out_int16:
             rc = _cabi.lib().tab_conv2d_bits_i16_launch(QX.data_ptr(), W8.data_ptr(), Y.data_ptr(), conv_type, p1, p2, s1, s2,
                                                         N, H, W, C, KN, KH, KW,

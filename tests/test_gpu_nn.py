@@ -65,20 +65,23 @@ def test_prepared_chain_matches_oracle(cuda, t):
     class Nhwc:
         def __init__(self, c):
             self.c = c
+            self.conv_type = c.conv_type
 
         def quantize(self, xx, th):
             return self.c.quantize(xx, th)
 
         def conv_bits(self, *a, **k):
-            y, nxt = self.c.conv_bits(*a, **k)
-            return y.view(y.shape[0], y.shape[2], y.shape[3], y.shape[1]), nxt
+            out = self.c.conv_bits(*a, **k)
+            y = out[0]
+            return (y.view(y.shape[0], y.shape[2], y.shape[3], y.shape[1]),) + tuple(out[1:])
 
     xd = torch.from_numpy(x).to(cuda)
     thd = TAB.ops.residual_threshold(xd.reshape(N, -1), None, chain.THRESHOLD_SCALE)
     qo = chain.quantize_weights(weights, t, OracleOps.Quantize)
     yo, _, _, _ = chain.forward(OracleOps, x, thd.cpu().numpy(), qo, t, N)
     for compact in (False, True):                                      # fp32 everywhere / int16 between a block's two convolutions
-        yd, oh, ow, kn = chain.forward_prepared({k: Nhwc(v) for k, v in convs.items()}, xd, thd, N, compact_mid=compact)
-        assert (oh, ow, kn) == (7, 7, 512)
-        assert np.array_equal(yd.cpu().numpy().reshape(-1), np.asarray(yo).reshape(-1)), compact
+        for fused_quant in (False, True):                              # quantiser launches / every convolution hands on its quantised result
+            yd, oh, ow, kn = chain.forward_prepared({k: Nhwc(v) for k, v in convs.items()}, xd, thd, N, compact_mid=compact, fused_quant=fused_quant)
+            assert (oh, ow, kn) == (7, 7, 512)
+            assert np.array_equal(yd.cpu().numpy().reshape(-1), np.asarray(yo).reshape(-1)), (compact, fused_quant)
     assert _cabi.lib().tab_device_status() == 0

@@ -282,6 +282,8 @@ def test_expand_weights(cuda):
     (0, 0, 2, 2, 5, 14, 14, 64, 128, 1, 1),
     (3, 3, 1, 1, 2, 6, 5, 64, 16, 3, 3),         # padding wider than the kernel reaches: the grid does not share padding
     (0, 0, 1, 1, 2, 9, 9, 200, 300, 3, 3),
+    (1, 1, 1, 1, 5, 10, 12, 64, 192, 3, 3),       # filter count a multiple of 64: the grid quantises its own result
+    (1, 1, 2, 2, 4, 12, 12, 128, 64, 3, 3),
 ])
 def test_bits_stage_entry_point(cuda, geom):
     """Quantize -> expand_weights -> conv2d_bits (the tensor-core GEMM stage on its own, prepared weights) equals the
@@ -311,6 +313,14 @@ def test_bits_stage_entry_point(cuda, geom):
         OH, OW = yo.shape[2], yo.shape[3]
         if OH * OW:
             for bw in (2, 1):
+                # the same launch handing on the quantised result (in the kernel where KN is a multiple of 64, else behind it)
+                for kw in (dict(residual=r), dict(out_int16=True)):
+                    ya, na, qa = TAB.ops.conv2d_bits(qx, w8, t, *geom, threshold_scale=0.7, state=state, next_bitwidth=bw, **kw)
+                    yb, nb_ = TAB.ops.conv2d_bits(qx, w8, t, *geom, threshold_scale=0.7, state=state, **kw)
+                    assert torch.equal(ya, yb) and torch.equal(na, nb_) and not state.any().item()
+                    want = (TAB.ops.quantize_i16(yb, nb_, bw, N, OH, OW, KN) if yb.dtype == torch.int16
+                            else TAB.Quantize(yb, nb_, bw, N, OH, OW, KN)[0])
+                    assert torch.equal(qa.reshape(-1), want.reshape(-1))
                 q16 = TAB.ops.quantize_i16(y16, nxt16, bw, N, OH, OW, KN)
                 qf, _ = TAB.Quantize(dev_t(yo, cuda), nxt16, bw, N, OH, OW, KN)
                 assert torch.equal(q16, qf)
@@ -352,6 +362,12 @@ def test_cta_pair_kernel(cuda, t, geom, conv_path):
     assert y16.dtype == torch.int16 and np.array_equal(y16.cpu().numpy().astype(np.float32), yo)
     assert np.array_equal(nxt16.cpu().numpy(), OracleOps.residual_threshold(yo.copy(), None, 0.7))
     assert not state.any().item()
+    # the pairs' grid quantising its own result
+    OH, OW = yo.shape[2], yo.shape[3]
+    ya, na, qa = TAB.ops.conv2d_bits(qx, w8, t, *geom, threshold_scale=0.7, state=state, out_int16=True, next_bitwidth=ab)
+    assert ",pair>" in _cabi.lib().tab_last_conv_kernel().decode()
+    assert torch.equal(ya, y16) and torch.equal(na, nxt16) and not state.any().item()
+    assert np.array_equal(qa.cpu().numpy().reshape(-1), O.quantize(yo.reshape(N, OH, OW, KN), nxt16.cpu().numpy(), ab, N, OH, OW, KN)[0].reshape(-1))
     assert _cabi.lib().tab_device_status() == 0
 
 
