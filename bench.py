@@ -185,7 +185,7 @@ def run_reference_arm(args):
         "e2e": {"value": val, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def oracle_chain_images(x_images, ths_images):
@@ -277,8 +277,27 @@ def step_algorithmic_bytes(n_images):
     return total
 
 
+_JSON_FD = None
+
+
+def emit(line):
+    """The one JSON line, on the real stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
+
+
 def main():
+    global _JSON_FD
     args = parse_args()
+    # stdout carries the JSON line and nothing else: whatever libraries print there from native code (NCCL announces its
+    # version on stdout) is sent to stderr
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -298,7 +317,6 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")       # stdout carries the one JSON line and nothing else
         dist.init_process_group("nccl", device_id=dev)
     lib = _cabi.lib()
     import TAB_CUDA  # the reference-facing extension module (built in-tree by Setup_CUDA.py)
@@ -507,6 +525,13 @@ def main():
     ms_e2e = timed(step_e2e, args.steps)
     barrier()
     ms_e2e = max_over_ranks(ms_e2e)
+    # the timed regions last a few milliseconds: keep the same steps running (untimed) until the sampler, which needs a
+    # moment to start when several ranks query at once, has seen the GPU under this load
+    t_load = time.time()
+    while time.time() - t_load < 0.8:
+        for _ in range(20):
+            step_value(False)
+        torch.cuda.synchronize()
     clocks = sampler.stop()
     gpu_launches = launches_per_step * args.steps
 
@@ -753,7 +778,7 @@ def main():
         line["ms_per_step_no_gather"] = ms_nogather / args.steps
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.cpu_sample_images)
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
