@@ -58,9 +58,12 @@ C0 = 64
 CONV_TYPE = 0
 WEIGHT_SEED = 5000
 INPUT_SEED = 5
-# dram__bytes_read.sum + dram__bytes_write.sum per image of conv_umma_persist_kernel on the 56x56x64->64 layer, from the
-# ncu capture summarised under profiles/ (taken at 64 images; the kernel's traffic is proportional to the images it processes)
-L1_TRAFFIC_PER_IMAGE = None
+# dram__bytes_read.sum + dram__bytes_write.sum per image of the step's largest launch, conv_umma_persist_kernel<2,64,6,1,2,1>
+# (56x56x64 -> 64 with residual and next thresholds), from the ncu capture summarised under profiles/: 54.72 MB read +
+# 10.07 MB written at 64 images.  The bytes read (residual + bit-planes) are proportional to the images; of the 51.4 MB of
+# output only 10 MB had left the 126 MB L2 when that small launch ended, so the scaled figure is a lower bound for a launch
+# whose output exceeds the L2 (algorithmic: 3.21 MB per image, of which 0.80 MB output).
+L1_TRAFFIC_PER_IMAGE = (54.720256e6 + 10.072832e6) / 64
 
 
 def parse_args():
@@ -731,9 +734,11 @@ def main():
         "bound": "hbm", "achieved": step_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": step_gbs / hbm_peak, "peak_source": hbm_src,
         "algorithmic_bytes_per_step": step_bytes, "images_per_gpu": n_local,
         "traffic": (L1_TRAFFIC_PER_IMAGE * l1_images) if L1_TRAFFIC_PER_IMAGE else None,
-        "traffic_note": "ncu dram bytes read + written of the step's largest launch (conv_umma_persist_kernel, 56x56x64 -> 64), captured at 64 images and "
-                        "scaled to this rank's %d images; its algorithmic bytes are %.1fe6 (bit-planes + byte weights + fp32 output)"
-                        % (l1_images, (l1_images * 56 * 56 * 16 + 64 * 9 * 64 + 4 * l1_images * 56 * 56 * 64) / 1e6),
+        "traffic_note": "ncu dram bytes read + written of the step's largest launch (conv_umma_persist_kernel<2,64,6,1,2,1>, 56x56x64 -> 64 with "
+                        "residual), captured at 64 images and scaled to this rank's %d images - a lower bound: at 64 images four fifths of the "
+                        "output were still in the L2 when the launch ended; its algorithmic bytes are %.1fe6 (bit-planes + byte weights + fp32 "
+                        "residual read + fp32 output)"
+                        % (l1_images, (l1_images * 56 * 56 * 16 + 64 * 9 * 64 + 8 * l1_images * 56 * 56 * 64) / 1e6),
         "gemm_stage": {
             "kernel": "conv_umma_persist_kernel (persistent tcgen05.mma kind::i8 on bit-plane activations), %d launches per step, each timed alone" % len(layer_rows),
             "bound": "tensor", "achieved": gemm_achieved, "peak": umma_tops, "unit": "TOP/s",
@@ -756,6 +761,18 @@ def main():
     }
     if roofline["quantize_in_step"]["achieved"]:
         roofline["quantize_in_step"]["frac"] = roofline["quantize_in_step"]["achieved"] / hbm_peak
+    # the launch with the largest share of the step (two per step): the 56x56x64 -> 64 convolution with residual, HBM-bound
+    dom = [r for r in layer_rows if r["layer"] in ("s1b0.b", "s1b1.b")]
+    if dom:
+        dom_ms = sum(r["gemm_ms"] for r in dom) / len(dom)
+        dom_bytes = l1_images * 56 * 56 * 16 + 64 * 9 * 64 + 8 * l1_images * 56 * 56 * 64
+        roofline["dominant_kernel"] = {
+            "kernel": dom[0]["gemm_kernel"], "launches_per_step": len(dom), "bound": "hbm",
+            "algorithmic_bytes_per_launch": dom_bytes, "avg_launch_ms": dom_ms,
+            "achieved": dom_bytes / (dom_ms * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+            "frac": dom_bytes / (dom_ms * 1e-3) / 1e9 / hbm_peak,
+            "traffic": (L1_TRAFFIC_PER_IMAGE * l1_images) if L1_TRAFFIC_PER_IMAGE else None,
+            "note": "bit-planes and fp32 residual read, fp32 output written; timed alone with CUDA events, L2 flushed before the launch"}
 
     config = workload_config(world)
     config["parity_check"] = parity
