@@ -62,7 +62,7 @@ INPUT_SEED = 5
 # (56x56x64 -> 64 with residual and next thresholds), from the ncu capture summarised under profiles/: 54.72 MB read +
 # 10.07 MB written at 64 images.  The bytes read (residual + bit-planes) are proportional to the images; of the 51.4 MB of
 # output only 10 MB had left the 126 MB L2 when that small launch ended, so the scaled figure is a lower bound for a launch
-# whose output exceeds the L2 (algorithmic: 3.21 MB per image, of which 0.80 MB output).
+# whose output exceeds the L2 (algorithmic: 1.66 MB per image, of which 0.80 MB output).
 L1_TRAFFIC_PER_IMAGE = (54.720256e6 + 10.072832e6) / 64
 
 
