@@ -23,14 +23,25 @@ residual_abs_sum_kernel(float* __restrict__ y, const float* __restrict__ r, doub
         const long long n4 = per_image >> 2;
         float4* y4 = reinterpret_cast<float4*>(yi);
         const float4* r4 = reinterpret_cast<const float4*>(ri);
-        for (long long i = (long long)blockIdx.x * RTHREADS + threadIdx.x; i < n4; i += stride) {
-            float4 v = y4[i];
-            if (ADD) {
-                const float4 q = __ldg(r4 + i);
-                v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
-                y4[i] = v;
+        // four loads in flight per thread (a streaming pass lives on the bytes it has in flight); the sum takes the
+        // elements in the same order as a one-at-a-time loop
+        for (long long i0 = (long long)blockIdx.x * RTHREADS + threadIdx.x; i0 < n4; i0 += 4 * stride) {
+            float4 v[4], q[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const long long i = i0 + u * stride;
+                if (i < n4) { v[u] = y4[i]; if (ADD) q[u] = __ldg(r4 + i); }
             }
-            acc += ((double)fabsf(v.x) + (double)fabsf(v.y)) + ((double)fabsf(v.z) + (double)fabsf(v.w));
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const long long i = i0 + u * stride;
+                if (i >= n4) break;
+                if (ADD) {
+                    v[u].x += q[u].x; v[u].y += q[u].y; v[u].z += q[u].z; v[u].w += q[u].w;
+                    y4[i] = v[u];
+                }
+                acc += ((double)fabsf(v[u].x) + (double)fabsf(v[u].y)) + ((double)fabsf(v[u].z) + (double)fabsf(v[u].w));
+            }
         }
     } else {
         for (long long i = (long long)blockIdx.x * RTHREADS + threadIdx.x; i < per_image; i += stride) {
