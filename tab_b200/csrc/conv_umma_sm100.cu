@@ -26,6 +26,7 @@
 #include <cuda.h>
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include "tab_kernels.cuh"
 #include "umma_common.cuh"
@@ -1243,11 +1244,23 @@ static bool tc_plan(const TcConvParams& p, int sms, TcPlan* best) {
     // Wide filter blocks on CTA pairs: a lone CTA would have to take in a 32 KB filter slice per 512 cycles of MMAs, which is
     // all an SM can take in from the L2; a pair splits every slice between its two CTAs.  (Strided layers, bound by their
     // four or more patches per tile, and layers with a residual, bound by their epilogue, measured no faster on pairs.)
+#ifdef TAB_TUNE
+    // Build-time diagnostic (-DTAB_TUNE, never in the shipped library): the tile is taken from the environment, "mt,tn,pair".
+    if (const char* env = getenv("TAB_TILE")) {
+        int mt = 0, tn = 0, pair = 0;
+        if (sscanf(env, "%d,%d,%d", &mt, &tn, &pair) == 3) {
+            if (pair) return tn == 256 && mt == 1 && !p.tepi && p.residual == nullptr && plan_shape(p, 1, 256, 8, best, true);
+            for (const auto& c : cands)
+                if (c[0] == mt && c[1] == tn) return plan_shape(p, mt, tn, c[2], best);
+            return false;
+        }
+    }
+#endif
     TcPlan lone;
     const bool fits_whole = plan_shape(p, 1, 256, 4, &lone) && lone.resident;      // a block that stays in shared memory is fetched once anyway
     if (tn0 == 256 && !p.tepi && !fits_whole && p.PA * p.PB == 1 && p.KH * p.KW > 1 && p.residual == nullptr && pair_launch_possible() &&
         plan_shape(p, 1, 256, 8, best, true) &&
-        best->tiles_m * best->tiles_n * 4 > sms) return true;
+        best->tiles_m * best->tiles_n * 2 > sms) return true;              // with a round of tiles for the pairs or less, single CTAs measured faster
     bool found = false;
     for (const auto& c : cands) {
         if (c[1] > tn0) continue;

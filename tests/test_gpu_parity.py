@@ -332,8 +332,8 @@ def test_bits_stage_entry_point(cuda, geom):
 @pytest.mark.parametrize("geom", [
     # p1 p2 s1 s2  N   H   W   C   KN KH KW
     (1, 1, 1, 1, 48, 14, 14, 256, 320, 3, 3),    # two filter blocks, the second ragged
-    (0, 0, 1, 1, 40, 16, 16, 100, 256, 3, 3),    # no padding, one ragged channel word
-    (1, 1, 1, 1, 97, 7, 7, 192, 512, 3, 3),      # odd number of 128-row blocks: the last pair's second CTA has no rows
+    (0, 0, 1, 1, 80, 16, 16, 100, 256, 3, 3),    # no padding, one ragged channel word
+    (1, 1, 1, 1, 153, 7, 7, 192, 512, 3, 3),     # odd number of 128-row blocks: the last pair's second CTA has no rows
 ])
 def test_cta_pair_kernel(cuda, t, geom, conv_path):
     """Wide filter blocks with many tiles run on clusters of two CTAs (tcgen05 cta_group::2): plain and with next thresholds
