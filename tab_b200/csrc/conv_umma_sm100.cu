@@ -1286,7 +1286,10 @@ static bool tc_prepare(TcConvParams& p, int sms, TcPlan* pl) {
     if ((long long)p.KH * p.KW * p.PC >= (1LL << 20)) return false;
     const bool tepi_ok = (p.KN & 3) == 0 && !(reinterpret_cast<uintptr_t>(p.y) & 15) && !(reinterpret_cast<uintptr_t>(p.residual) & 15) &&
                          (long long)p.KN * p.OW * p.OH * 4 < (1LL << 40);
-    const bool tepi_pays = p.residual != nullptr && p.y16 == nullptr && p.KN <= 64 && (long long)p.KH * p.KW * p.C <= 1024;
+    bool tepi_pays = p.residual != nullptr && p.y16 == nullptr && p.KN <= 64 && (long long)p.KH * p.KW * p.C <= 1024;
+#ifdef TAB_TUNE
+    if (const char* env = getenv("TAB_TEPI")) tepi_pays = p.residual != nullptr && p.y16 == nullptr && atoi(env) != 0;
+#endif
     bool have = false;
     if (tepi_ok && tepi_pays) {
         TcConvParams q = p;
