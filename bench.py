@@ -359,6 +359,7 @@ def main():
             wb = tab_nn.weight_bitwidth(conv.conv_type)
             self.W8 = TAB_CUDA.ExpandWeights(conv.QW, wb, conv.KN, conv.KH, conv.KW, conv.C)
             self.state = None
+            self.conv_type = conv.conv_type
 
         def quantize(self, x, thresholds):
             n, h, w = (int(v) for v in x.shape[:3])
@@ -367,12 +368,15 @@ def main():
                 return TAB_CUDA.QuantizeI16(x, thresholds, ab, n, h, w, self.c.C)
             return TAB_CUDA.Quantize(x, thresholds, ab, n, h, w, self.c.C)[0]
 
-        def conv_bits(self, QX, n, h, w, residual, scale, out_int16=False):
+        def conv_bits(self, QX, n, h, w, residual, scale, out_int16=False, next_bitwidth=None):
             if scale is not None and (self.state is None or self.state.numel() < lib.tab_conv2d_state_bytes(n)):
                 self.state = TAB_CUDA.NewState(QX, n)
-            y, nxt = TAB_CUDA.Conv2dBits(QX, self.W8, self.c.conv_type, *self.c.geometry(n, h, w), residual,
-                                         self.state if scale is not None else None, scale if scale is not None else 0.0, bool(out_int16))
-            return y.view(n, y.shape[2], y.shape[3], y.shape[1]), (nxt if scale is not None else None)
+            out = TAB_CUDA.Conv2dBits(QX, self.W8, self.c.conv_type, *self.c.geometry(n, h, w), residual,
+                                      self.state if scale is not None else None, scale if scale is not None else 0.0, bool(out_int16),
+                                      int(next_bitwidth or 0))
+            y = out[0]
+            res = (y.view(n, y.shape[2], y.shape[3], y.shape[1]), (out[1] if scale is not None else None))
+            return res + (out[2],) if next_bitwidth else res
 
     def nhwc(y):                                             # Conv2d's {N,KN,OH,OW} label over the [N][OH][OW][KN] buffer
         return y.view(y.shape[0], y.shape[2], y.shape[3], y.shape[1])
@@ -398,7 +402,7 @@ def main():
         if count:
             launches[0] += 2
         ths = tab_ops.residual_threshold(x_in.reshape(nb, -1), None, chain.THRESHOLD_SCALE)      # reduce + finalise kernels
-        y, _, _, _ = chain.forward_prepared(cset, x_in, ths, nb, compact_mid=True, fused_quant=cset is convs)
+        y, _, _, _ = chain.forward_prepared(cset, x_in, ths, nb, compact_mid=True, fused_quant=True)
         return y, ths
 
     def barrier():
@@ -448,13 +452,23 @@ def main():
     # End-to-end step: the shard is processed in NCH chunks of images (every image is independent), so that the
     # host-to-device copy of chunk i+1 overlaps the forward of chunk i: input buffers / graphs in rotation,
     # copies on their own streams.
+    # (Half-size chunks at the end, to shorten the forward that follows the last copy, measured slower: a forward of 16
+    # images takes 0.8 of the time of one of 32.)
     NCH = 8 if n_local % 8 == 0 and n_local >= 64 else (4 if n_local % 4 == 0 and n_local >= 16 else 1)
     nb_e2e = n_local // NCH
-    x_chunk = [torch.empty((nb_e2e, H0, W0, C0), dtype=torch.float32, device=dev) for _ in range(3 if NCH > 2 else NCH)]
+    chunk_sizes = [nb_e2e] * NCH
+    chunk_lo = [sum(chunk_sizes[:i]) for i in range(len(chunk_sizes))]
+    NBUF = 3 if len(chunk_sizes) > 2 else len(chunk_sizes)
+    x_chunk = [torch.empty((nb_e2e, H0, W0, C0), dtype=torch.float32, device=dev) for _ in range(NBUF)]
     y_local = torch.empty(n_local * per_img_out, dtype=torch.float32, device=dev)
     g_dev = make_graph(convs, x_dev, n_local)
-    g_e2e = [make_graph(mconvs, xb, nb_e2e) for xb in x_chunk]
-    use_graph = g_dev[0] is not None and all(g[0] is not None for g in g_e2e)
+    # one graph per (input buffer, chunk size) pair the schedule uses
+    g_e2e = {}
+    for i, sz in enumerate(chunk_sizes):
+        k = i % NBUF
+        if (k, sz) not in g_e2e:
+            g_e2e[(k, sz)] = make_graph(mconvs, x_chunk[k][:sz], sz)
+    use_graph = g_dev[0] is not None and all(g[0] is not None for g in g_e2e.values())
     h2d_stream = torch.cuda.Stream(dev)
     d2h_stream = torch.cuda.Stream(dev)
     launches[0] = 0
@@ -478,20 +492,20 @@ def main():
         main_s = torch.cuda.current_stream(dev)
         h2d_stream.wait_stream(main_s)               # the step starts where the caller's stream is
         ev_in, ev_done = [], []
-        for i in range(NCH):
-            k = i % len(x_chunk)
+        for i, sz in enumerate(chunk_sizes):
+            k = i % NBUF
             with torch.cuda.stream(h2d_stream):
-                if i >= len(x_chunk):
-                    h2d_stream.wait_event(ev_done[i - len(x_chunk)])     # the buffer's previous chunk has been consumed
-                x_chunk[k].copy_(x_host[i * nb_e2e:(i + 1) * nb_e2e], non_blocking=True)
+                if i >= NBUF:
+                    h2d_stream.wait_event(ev_done[i - NBUF])             # the buffer's previous chunk has been consumed
+                x_chunk[k][:sz].copy_(x_host[chunk_lo[i]:chunk_lo[i] + sz], non_blocking=True)
                 e = torch.cuda.Event(); e.record(h2d_stream); ev_in.append(e)
             main_s.wait_event(ev_in[i])
             if use_graph:
-                g_e2e[k][0].replay()
-                yk = g_e2e[k][1]
+                g_e2e[(k, sz)][0].replay()
+                yk = g_e2e[(k, sz)][1]
             else:
-                yk = forward(mconvs, x_chunk[k], nb_e2e, count=False)[0]
-            lo_, hi_ = i * nb_e2e * per_img_out, (i + 1) * nb_e2e * per_img_out
+                yk = forward(mconvs, x_chunk[k][:sz], sz, count=False)[0]
+            lo_, hi_ = chunk_lo[i] * per_img_out, (chunk_lo[i] + sz) * per_img_out
             y_local[lo_:hi_].copy_(yk.reshape(-1), non_blocking=True)
             e = torch.cuda.Event(); e.record(main_s); ev_done.append(e)
             if world == 1:                               # single GPU: a chunk's result goes back while the next one computes
@@ -783,7 +797,7 @@ def main():
         "config": config,
         "e2e": {"value": e2e_value, "unit": "TOPS", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(N * per_img_out * 4),
-                "api": "TAB_CUDA.Quantize / Conv2dBits (extension module, prepared weights) + pinned-host copies, %d chunks of images pipelined; bytes are rank 0's" % NCH},
+                "api": "TAB_CUDA.Quantize / Conv2dBits (extension module, prepared weights) + pinned-host copies, %d chunks of images pipelined; bytes are rank 0's" % len(chunk_sizes)},
         "gpu_launches": gpu_launches, "launches_per_step": launches_per_step, "cuda_graph": bool(use_graph),
         "clocks": clocks,
         "roofline": roofline,

@@ -164,12 +164,14 @@ torch::Tensor TAB_NewState(torch::Tensor like, int N) {
 // Conv2dBits: the GEMM stage of Conv2d on activations Quantize wrote (bitwidth 2 for types 0,1; 1 for types 2,3) and
 // weights from ExpandWeights; residual / state may be None; threshold_scale <= 0 skips the thresholds; out_int16: Y as int16
 // (no residual; the values are integers of magnitude at most KH*KW*C), for QuantizeI16.
-// Returns {Y, next_thresholds (empty when skipped)}.
+// next_bitwidth 1 or 2 (needs threshold_scale > 0): the same call also quantises Y against the next thresholds, as
+// Quantize(Y, next_thresholds, next_bitwidth, N, OH, OW, KN) would, and returns it as a third tensor.
+// Returns {Y, next_thresholds (empty when skipped)[, next_QX]}.
 std::vector<torch::Tensor> TAB_Conv2dBits(torch::Tensor QX, torch::Tensor W8, int type,
                                           int padding1, int padding2, int stride1, int stride2,
                                           int N, int H, int W, int C, int KN, int KH, int KW,
                                           c10::optional<torch::Tensor> residual, c10::optional<torch::Tensor> state, double threshold_scale,
-                                          bool out_int16) {
+                                          bool out_int16, int next_bitwidth) {
     CHECK_INPUT(QX);
     CHECK_INPUT(W8);
     TORCH_CHECK(QX.scalar_type() == torch::kInt64, "QX must have dtype torch.int64");
@@ -198,6 +200,18 @@ std::vector<torch::Tensor> TAB_Conv2dBits(torch::Tensor QX, torch::Tensor W8, in
         sptr = state->data_ptr();
     }
     auto next = torch::empty({want ? N : 0}, torch::device(QX.device()).dtype(torch::kFloat32));
+    if (next_bitwidth > 0) {
+        TORCH_CHECK(want, "next_bitwidth needs threshold_scale > 0 (the thresholds the result is quantised against)");
+        TORCH_CHECK(!(out_int16 && rptr), "out_int16 cannot be combined with a residual");
+        auto Yn = torch::empty({N, KN, OH, OW}, torch::device(QX.device()).dtype(out_int16 ? torch::kInt16 : torch::kFloat32));
+        auto QN = torch::empty({N, OH, OW, (KN + 63) / 64, next_bitwidth == 1 ? 1 : 2}, torch::device(QX.device()).dtype(torch::kInt64));
+        if (N > 0)
+            check_rc(tab_conv2d_bits_next_launch(QX.data_ptr<int64_t>(), W8.data_ptr<int8_t>(), Yn.data_ptr(), out_int16 ? 1 : 0, type,
+                                                 padding1, padding2, stride1, stride2, N, H, W, C, KN, KH, KW, rptr, sptr, next.data_ptr<float>(),
+                                                 (float)threshold_scale, QN.data_ptr<int64_t>(), next_bitwidth, current_stream()),
+                     "tab_conv2d_bits_next_launch");
+        return {Yn, next, QN};
+    }
     if (out_int16) {
         TORCH_CHECK(rptr == nullptr, "out_int16 cannot be combined with a residual");
         auto Y16 = torch::empty({N, KN, OH, OW}, torch::device(QX.device()).dtype(torch::kInt16));
@@ -220,7 +234,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("ExpandWeights", &TAB_ExpandWeights, "Packed weights -> int8 for the tensor-core GEMM stage (extension)");
     m.def("QuantizeI16", &TAB_QuantizeI16, "Quantize on the int16 output of Conv2dBits(out_int16=True) (extension)");
     m.def("NewState", &TAB_NewState, "Zeroed state block for Conv2dBits thresholds (extension)");
-    m.def("Conv2dBits", &TAB_Conv2dBits, "GEMM stage of Conv2d on Quantize's bit-planes and ExpandWeights' bytes (extension)");
+    m.def("Conv2dBits", &TAB_Conv2dBits, "GEMM stage of Conv2d on Quantize's bit-planes and ExpandWeights' bytes (extension)",
+          pybind11::arg("QX"), pybind11::arg("W8"), pybind11::arg("type"), pybind11::arg("padding1"), pybind11::arg("padding2"),
+          pybind11::arg("stride1"), pybind11::arg("stride2"), pybind11::arg("N"), pybind11::arg("H"), pybind11::arg("W"), pybind11::arg("C"),
+          pybind11::arg("KN"), pybind11::arg("KH"), pybind11::arg("KW"), pybind11::arg("residual"), pybind11::arg("state"),
+          pybind11::arg("threshold_scale"), pybind11::arg("out_int16") = false, pybind11::arg("next_bitwidth") = 0);
     m.def("Quantize", &TAB_Quantize, "Ternarization or binarization of fp32 data in NHWC format");
     m.def("Conv2d", &TAB_Conv2d, "Conv2d of all TAB series CNNs (0 TNN, 1 TBN, 2 BTN, 3 BNN)");
     m.def("TAB_Quantize", &TAB_Quantize, "Alias of Quantize");

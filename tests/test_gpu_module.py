@@ -58,3 +58,32 @@ def test_notebook_demo_shapes(cuda):
         yo = c_oracle.conv2d(x[5].cpu().numpy(), qw.cpu().numpy(), xt[5:6].cpu().numpy(), btn.cpu().numpy(), t,
                              1, 1, 1, 1, 1, H, W, C, KN, K, K)
         assert np.array_equal(y.reshape(N, -1)[5].cpu().numpy(), yo.reshape(-1))
+
+
+def test_module_prepared_stages(cuda):
+    """ExpandWeights / NewState / Conv2dBits / QuantizeI16 of the module: the GEMM stage on prepared weights, with the next
+    thresholds, 16-bit output and the next layer's quantised input from the same call, against the oracle."""
+    import TAB_CUDA as TAB
+    N, H, W, C, KN, K = 3, 12, 10, 64, 128, 3
+    x, ths = make_input(13, N, H, W, C)
+    w, wths = make_input(14, KN, K, K, C)
+    xd, td = torch.from_numpy(x).to(cuda), torch.from_numpy(ths).to(cuda)
+    for t in (0, 3):
+        ab, wb = O.act_bits(t), O.weight_bits(t)
+        qo, bo = O.quantize(w, wths, wb, KN, K, K, C)
+        qw, _ = TAB.Quantize(torch.from_numpy(w).to(cuda), torch.from_numpy(wths).to(cuda), wb, KN, K, K, C)
+        w8 = TAB.ExpandWeights(qw, wb, KN, K, K, C)
+        qx = TAB.Quantize(xd, td, ab, N, H, W, C)[0]
+        yo = c_oracle.conv2d(x, qo, ths, bo, t, 1, 1, 1, 1, N, H, W, C, KN, K, K)
+        state = TAB.NewState(qx, N)
+        y, nxt = TAB.Conv2dBits(qx, w8, t, 1, 1, 1, 1, N, H, W, C, KN, K, K, None, state, 0.7)
+        assert np.array_equal(y.cpu().numpy(), yo)
+        to = (np.float64(np.float32(0.7)) * (np.abs(yo).astype(np.float64).reshape(N, -1).sum(1) / yo[0].size)).astype(np.float32)
+        assert np.array_equal(nxt.cpu().numpy(), to)
+        for nb in (2, 1):
+            y16, n16, qn = TAB.Conv2dBits(qx, w8, t, 1, 1, 1, 1, N, H, W, C, KN, K, K, None, state, 0.7, True, nb)
+            assert y16.dtype == torch.int16 and np.array_equal(y16.cpu().numpy().astype(np.float32), yo) and torch.equal(n16, nxt)
+            want = O.quantize(yo.reshape(N, H, W, KN), to, nb, N, H, W, KN)[0]
+            assert np.array_equal(qn.cpu().numpy(), want)
+            assert torch.equal(TAB.QuantizeI16(y16.view(N, H, W, KN), n16, nb, N, H, W, KN), qn)
+        assert not state.any().item()
