@@ -50,12 +50,13 @@ class OraclePreparedConv:
 
     def __init__(self, qw, btn, conv_type, cs):
         self.qw, self.btn, self.t, self.cs = qw, btn, conv_type, cs
+        self.conv_type = conv_type
 
     def quantize(self, x, ths):
         N, H, W = x.shape[:3]
         return (np.ascontiguousarray(x, dtype=np.float32), np.asarray(ths, dtype=np.float32), N, H, W)     # the oracle quantises inside conv2d
 
-    def conv_bits(self, qx, N, H, W, residual=None, next_threshold_scale=None, out_int16=False):
+    def conv_bits(self, qx, N, H, W, residual=None, next_threshold_scale=None, out_int16=False, next_bitwidth=None):
         x, ths, _, _, _ = qx
         cs = self.cs
         y = c_oracle.conv2d(x.reshape(-1), self.qw, ths, self.btn, self.t, cs.pad, cs.pad, cs.stride, cs.stride, N, H, W, cs.C, cs.KN, cs.K, cs.K)
@@ -65,4 +66,7 @@ class OraclePreparedConv:
                 y += np.asarray(residual, dtype=np.float32).reshape(y.shape)
             return y, None
         nxt = OracleOps.residual_threshold(y, residual, next_threshold_scale)
-        return (y.astype(np.int16) if out_int16 and residual is None else y), nxt
+        out = (y.astype(np.int16) if out_int16 and residual is None else y), nxt
+        if next_bitwidth is not None:                          # the next layer's "quantised input": (values, thresholds) for the oracle's conv2d
+            out = out + ((np.ascontiguousarray(y, dtype=np.float32), nxt, N, y.shape[1], y.shape[2]),)
+        return out

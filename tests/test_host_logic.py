@@ -55,8 +55,9 @@ def test_chain_on_the_cpu_oracle_matches_layer_by_layer_dense_math():
     specs = {cs.name: cs for cs in chain.conv_specs()}
     convs = {k: OraclePreparedConv(v[0], v[1], 0, specs[k]) for k, v in qw.items()}
     for compact in (False, True):
-        yp, oh2, ow2, kn2 = chain.forward_prepared(convs, x, ths, N, compact_mid=compact)
-        assert (oh2, ow2, kn2) == (7, 7, 512) and np.array_equal(np.asarray(yp).reshape(-1), np.asarray(y).reshape(-1))
+        for fused_quant in (False, True):                     # every convolution hands on its quantised result itself
+            yp, oh2, ow2, kn2 = chain.forward_prepared(convs, x, ths, N, compact_mid=compact, fused_quant=fused_quant)
+            assert (oh2, ow2, kn2) == (7, 7, 512) and np.array_equal(np.asarray(yp).reshape(-1), np.asarray(y).reshape(-1))
 
 
 @pytest.mark.parametrize("N,world", [(8, 1), (8, 2), (5, 2), (3, 4), (256, 8), (0, 2)])
