@@ -1206,8 +1206,11 @@ static bool set_virtual_grid(TcConvParams& p, bool aligned) {
     return true;
 }
 
-// Whether this device runs the pair kernel: two CTAs of its size per cluster, asked of the occupancy calculator once.
-static bool pair_launch_possible();
+// How many clusters of two CTAs of the pair kernel's size the device holds at once (0: none), asked of the occupancy
+// calculator once per device.  The launch never asks for more: all its CTAs are resident, which the second phase's
+// grid-wide counter relies on.
+static int pair_clusters();
+static bool pair_launch_possible() { return pair_clusters() >= 1; }
 
 // A tile shape and what it needs.
 struct TcPlan { int mt, tn, sb; bool resident, pair; int prow, nrows, nst, smem; long long tiles_m, tiles_n; };
@@ -1322,7 +1325,7 @@ static int launch_persist_u(const CUtensorMap& tmB, const CUtensorMap& tmY, cons
     }
     const long long ntiles = pl.tiles_m * pl.tiles_n;
     if (PAIR) {
-        const long long pairs = sms / 2;
+        const long long pairs = std::min<long long>(sms / 2, pair_clusters());
         const unsigned grid = 2u * (unsigned)(ntiles < pairs ? ntiles : pairs);
         return launch_pdl_cluster(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS), (size_t)pl.smem, stream, 2u,
                                   tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
@@ -1355,11 +1358,11 @@ static int launch_persist(const CUtensorMap& tmB, const CUtensorMap& tmY, const 
 #undef TAB_LAUNCH
 }
 
-static bool pair_launch_possible() {
+static int pair_clusters() {
     static std::mutex mu;
-    static int known[64] = {};                                             // 0 unknown, 1 yes, 2 no
+    static int known[64] = {};                                             // 0 unknown, else clusters + 1
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
     std::lock_guard<std::mutex> lock(mu);
     if (!known[dev]) {
         auto kernel = conv_umma_persist_kernel<1, 256, 8, false, 0, false, true>;
@@ -1373,9 +1376,9 @@ static bool pair_launch_possible() {
         const bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_SMEM_MAX) == cudaSuccess &&
                         cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1;
         if (!ok) cudaGetLastError();
-        known[dev] = ok ? 1 : 2;
+        known[dev] = ok ? clusters + 1 : 1;
     }
-    return known[dev] == 1;
+    return known[dev] - 1;
 }
 
 static thread_local char g_last_kernel[112] = "none";
