@@ -181,6 +181,16 @@ int tab_conv2d_bits_i16_launch(const int64_t* qx, const int8_t* w8, int16_t* y16
 int tab_quantize_i16_launch(const int16_t* x, const float* ths, int64_t* qx, int bitwidth, int N, int H, int W, int C,
                             tab_stream_t stream);
 /*
+ * Quantize with the thresholds every caller of the reference computes first, ths[n] = scale * mean|x[n]| (the notebook does it
+ * with framework reductions before calling Quantize, TAB_GPU.cpp:53-58 takes them as an argument): one launch sums |x| per
+ * image, meets at a counter in the state block (a bounded wait, as in tab_conv2d_bits_next_launch), writes the thresholds
+ * to ths [N] and the bit-planes to qx, [N][H][W][ceil(C/64)][bitwidth] as tab_quantize_launch does (no btn output).  state:
+ * tab_conv2d_state_bytes(N) bytes, zero before the call and zero again after it.  C not a multiple of 64 or x not 32-byte
+ * aligned: the same result from three launches.  x is only read.
+ */
+int tab_quantize_auto_launch(const float* x, float scale, void* state, float* ths, int64_t* qx, int bitwidth,
+                             int N, int H, int W, int C, tab_stream_t stream);
+/*
  * A chained layer that also hands the next convolution its input: after the GEMM stage (tab_conv2d_bits_launch, or the int16
  * form when y_is_int16) the same launch computes the next thresholds and quantises the result against them into next_qx,
  * [N][OH][OW][ceil(KN/64)][next_bitwidth] 64-bit words - exactly what tab_quantize_launch(y, next_ths, next_qx, ...) writes

@@ -31,6 +31,7 @@ SYMBOLS = {
     "tab_conv2d_bits_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p] * 3 + [_c.c_float, _c.c_void_p]),
     "tab_conv2d_bits_i16_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 12 + [_c.c_void_p] * 2 + [_c.c_float, _c.c_void_p]),
     "tab_conv2d_bits_next_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 13 + [_c.c_void_p] * 3 + [_c.c_float, _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "tab_quantize_auto_launch": (_c.c_int, [_c.c_void_p, _c.c_float, _c.c_void_p, _c.c_void_p, _c.c_void_p] + [_c.c_int] * 5 + [_c.c_void_p]),
     "tab_quantize_i16_launch": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int] * 5 + [_c.c_void_p]),
     "tab_last_conv_kernel": (_c.c_char_p, []),
     "tab_device_status": (_c.c_int, []),

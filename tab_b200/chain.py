@@ -142,7 +142,7 @@ def forward(ops, x, ths, qweights, conv_type: int, N: int, H: int = 56, W: int =
     return x, h, w, resnet18_blocks()[-1].conv_b.KN
 
 
-def forward_prepared(convs, x, ths, N: int, H: int = 56, W: int = 56, compact_mid: bool = False, fused_quant: bool = False):
+def forward_prepared(convs, x, ths, N: int, H: int = 56, W: int = 56, compact_mid: bool = False, fused_quant: bool = False, qx0=None):
     """The same chain on prepared convolutions: ``convs`` maps a layer name to an object with
     ``quantize(x, thresholds) -> QX`` and ``conv_bits(QX, N, H, W, residual, next_threshold_scale) -> (Y, next_ths)``
     (``tab_b200.nn.TABConv2d``: weights quantised and expanded once).  Every convolution input is quantised once:
@@ -152,13 +152,14 @@ def forward_prepared(convs, x, ths, N: int, H: int = 56, W: int = 56, compact_mi
     ``conv_bits(..., out_int16=True)`` and int16 input to ``quantize``.
     ``fused_quant``: every convolution that feeds another one also hands it its quantised input
     (``conv_bits(..., next_bitwidth=bits) -> (Y, next_ths, next_QX)``; the objects need a ``conv_type``), so that only the
-    chain's input is quantised by a launch of its own.
+    chain's input is quantised by a launch of its own; ``qx0``: that quantised input, when the caller already has it
+    (``quantize_auto`` gives it together with ``ths``).
     Returns ``(y, OH, OW, KN)`` like ``forward``; the results are identical."""
     h, w = H, W
     if fused_quant:
         blocks = resnet18_blocks()
         act_bits = lambda conv: 1 if conv.conv_type in (2, 3) else 2
-        qx = convs[blocks[0].conv_a.name].quantize(x, ths)
+        qx = qx0 if qx0 is not None else convs[blocks[0].conv_a.name].quantize(x, ths)
         for i, b in enumerate(blocks):
             a, bb, sc = convs[b.conv_a.name], convs[b.conv_b.name], (convs[b.shortcut.name] if b.shortcut else None)
             oh, ow = (h + 2 * b.conv_a.pad - b.conv_a.K + 1) // b.conv_a.stride, (w + 2 * b.conv_a.pad - b.conv_a.K + 1) // b.conv_a.stride

@@ -299,6 +299,34 @@ int tab_conv2d_bits_next_launch(const int64_t* qx, const int8_t* w8, void* y, in
                      type, p1, p2, s1, s2, N, H, W, C, KN, KH, KW, residual, state, next_ths, next_scale, stream, next_qx, next_bitwidth);
 }
 
+int tab_quantize_auto_launch(const float* x, float scale, void* state, float* ths, int64_t* qx, int bitwidth, int N, int H, int W, int C,
+                             tab_stream_t stream) {
+    if (!dims_ok(N, H, W, C) || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
+    if (N == 0) return TAB_OK;
+    if (!ths || !state) return TAB_E_NULL_POINTER;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const long long per_image = (long long)H * W * C;
+    if (per_image == 0) {
+        cudaError_t e = cudaMemsetAsync(ths, 0, sizeof(float) * (size_t)N, s);
+        return e == cudaSuccess ? TAB_OK : record_cuda_error(e);
+    }
+    if (!x || !qx) return TAB_E_NULL_POINTER;
+    if (misaligned(x, 3) || misaligned(ths, 3) || misaligned(qx, 7) || misaligned(state, 7)) return TAB_E_ALIGNMENT;
+    if ((long long)H * W >= (1LL << 31)) return TAB_E_TOO_LARGE;
+    double* sums = reinterpret_cast<double*>(state);
+    unsigned* bar = reinterpret_cast<unsigned*>(sums + N) + 1;
+    int rc = quantize_auto_dispatch(x, scale, sums, bar, ths, qx, bitwidth == 1 ? 1 : 2, N, H, W, C, device_status_word(), s);
+    if (rc != TAB_E_TOO_LARGE) return rc;
+    // shapes the one-launch form does not take: sums, thresholds, quantiser as launches of their own (x is not modified)
+    rc = residual_abs_sum_dispatch(const_cast<float*>(x), nullptr, sums, N, per_image, s);
+    if (rc != TAB_OK) return rc;
+    rc = tab_threshold_from_sums_launch(sums, ths, scale, N, per_image, stream);
+    if (rc != TAB_OK) return rc;
+    cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(double) * (size_t)N, s);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    return quantize_dispatch(x, ths, qx, nullptr, bitwidth == 1 ? 1 : 2, N, H, W, C, s, nullptr, false);
+}
+
 int tab_quantize_i16_launch(const int16_t* x, const float* ths, int64_t* qx, int bitwidth, int N, int H, int W, int C, tab_stream_t stream) {
     if (!dims_ok(N, H, W, C) || bitwidth < 1) return TAB_E_BAD_ARGUMENT;
     if ((long long)N * H * W == 0) return TAB_OK;

@@ -1168,6 +1168,8 @@ static int* umma_status_ptr() {
     return addr[dev];
 }
 
+int* device_status_word() { return umma_status_ptr(); }
+
 // Reads (and clears) the record of expired waits on the current device; synchronises the device.
 int umma_status_read_and_clear() {
     int v = -1, zero = 0;

@@ -17,6 +17,7 @@
 // Inside a convolution call the same launch also does the call's small set-up jobs (QuantExtras), so that they cost no
 // launch of their own: all CTAs share the expansion of the packed weights to the bytes the tensor-core kernel
 // multiplies, and the first CTA of every image clears that image's |y| sum (the first of all the completion counter).
+#include <mutex>
 #include "tab_kernels.cuh"
 
 namespace tab {
@@ -318,6 +319,161 @@ int quantize_dispatch(const void* x, const float* ths, int64_t* qx, int32_t* btn
         if (bits == 2) return launch_pdl(quantize_generic_kernel<2, false>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
         return launch_pdl(quantize_generic_kernel<1, false>, grid, dim3(QTHREADS), 0, stream, x, ths, q, btn, pixels, C, PC, ex);
     }
+}
+
+// ---- thresholds and bit-planes of a tensor in one launch ----------------------------------------------------------------
+// What every caller of Quantize does first - thresholds[n] = scale * mean|x[n]| (the reference leaves it to framework ops) -
+// and the quantisation against them, as two phases of one persistent grid: per-image sums of |x| (double atomics), a
+// grid-wide counter (all CTAs are resident: the grid is sized by the occupancy calculator; the wait is bounded and
+// reports in *status), then every CTA quantises, last unit first, the units it has just summed - the end of its share is
+// what the L2 still holds.  A unit is one CTA step of 128 words of one image.
+constexpr uint32_t QA_WAIT_LIMIT = 1u << 22;
+
+template <int BITS>
+__global__ void __launch_bounds__(QTHREADS)
+quantize_auto_kernel(const float* __restrict__ x, float scale, double* __restrict__ sums, unsigned* __restrict__ bar,
+                     float* __restrict__ ths_out, uint64_t* __restrict__ qx, long long words_per_image, int steps_per_image,
+                     long long units, int N, int* __restrict__ status) {
+    pdl_wait();
+    const int byte = threadIdx.x & 7, grp = threadIdx.x >> 3;
+    const double per_image = (double)words_per_image * 64.0;
+    __shared__ double wsum[QTHREADS / 32];
+    __shared__ float s_t;
+    // phase 1: sums
+    for (long long u = blockIdx.x; u < units; u += gridDim.x) {
+        const long long n = u / steps_per_image;
+        const long long w0 = (u - n * steps_per_image) * QWORDS_PER_ITER;
+        const float* xi = x + n * words_per_image * 64;
+        f8 v[QUNROLL];
+        bool live[QUNROLL];
+#pragma unroll
+        for (int k = 0; k < QUNROLL; k++) {
+            const long long w = w0 + k * (QTHREADS / 8) + grp;
+            live[k] = w < words_per_image;
+            if (live[k]) v[k] = ld_stream_f8(xi + w * 64 + byte * 8);
+        }
+        double acc = 0.0;
+#pragma unroll
+        for (int k = 0; k < QUNROLL; k++)
+            if (live[k]) {
+                const float* q = v[k].v;
+                acc += (((double)fabsf(q[0]) + (double)fabsf(q[1])) + ((double)fabsf(q[2]) + (double)fabsf(q[3]))) +
+                       (((double)fabsf(q[4]) + (double)fabsf(q[5])) + ((double)fabsf(q[6]) + (double)fabsf(q[7])));
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        __syncthreads();                                      // wsum of the previous unit has been read
+        if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+#pragma unroll
+            for (int i = 0; i < QTHREADS / 32; i++) t += wsum[i];
+            atomicAdd(sums + n, t);
+        }
+    }
+    // grid-wide counter
+    __threadfence();
+    __syncthreads();
+    int flag = 0;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(bar, 1u);
+        bool ok = false;
+        for (uint32_t i = 0; i < QA_WAIT_LIMIT && !ok; i++) {
+            unsigned seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar) : "memory");
+            ok = seen >= gridDim.x;
+            if (!ok) __nanosleep(100);
+        }
+        if (!ok && status) atomicExch(status, 22);
+        flag = ok ? 1 : 0;
+    }
+    if (!__syncthreads_or(flag)) return;
+    if (blockIdx.x == 0 && ths_out)
+        for (int n = threadIdx.x; n < N; n += QTHREADS) ths_out[n] = (float)((double)scale * (__ldcg(sums + n) / per_image));
+    // phase 2: the CTA's units again, last first
+    const long long mine = units > blockIdx.x ? (units - 1 - blockIdx.x) / gridDim.x : -1;      // index of its last unit
+    for (long long k = mine; k >= 0; k--) {
+        const long long u = blockIdx.x + k * gridDim.x;
+        const long long n = u / steps_per_image;
+        const long long w0 = (u - n * steps_per_image) * QWORDS_PER_ITER;
+        __syncthreads();
+        if (threadIdx.x == 0) s_t = (float)((double)scale * (__ldcg(sums + n) / per_image));
+        __syncthreads();
+        const float t = s_t, nt = -t;
+        const float* xi = x + n * words_per_image * 64;
+        unsigned char* qi = reinterpret_cast<unsigned char*>(qx + n * words_per_image * BITS);
+        f8 v[QUNROLL];
+        long long w[QUNROLL];
+#pragma unroll
+        for (int q = 0; q < QUNROLL; q++) {
+            w[q] = w0 + q * (QTHREADS / 8) + grp;
+            if (w[q] < words_per_image) v[q] = ld_stream_f8(xi + w[q] * 64 + byte * 8);
+        }
+#pragma unroll
+        for (int q = 0; q < QUNROLL; q++) {
+            if (w[q] >= words_per_image) continue;
+            if (BITS == 2) {
+                unsigned pos = 0, neg = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    pos |= (v[q].v[i] > t) ? (1u << i) : 0u;
+                    neg |= (v[q].v[i] < nt) ? (1u << i) : 0u;
+                }
+                neg &= ~pos;
+                unsigned char* o = qi + w[q] * 16 + byte;
+                o[0] = (unsigned char)neg;
+                o[8] = (unsigned char)(pos | neg);
+            } else {
+                unsigned b = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) b |= (v[q].v[i] < t) ? (1u << i) : 0u;
+                qi[w[q] * 8 + byte] = (unsigned char)b;
+            }
+        }
+    }
+    // the CTA that gets here last leaves the state block zero again (every CTA has read the sums it needs)
+    __syncthreads();
+    flag = 0;
+    if (threadIdx.x == 0) flag = (atomicAdd(bar + 1, 1u) == gridDim.x - 1u) ? 1 : 0;
+    if (__syncthreads_or(flag)) {
+        for (int n = threadIdx.x; n < N; n += QTHREADS) sums[n] = 0.0;
+        if (threadIdx.x == 0) { bar[0] = 0u; bar[1] = 0u; }
+    }
+    pdl_launch_dependents();
+}
+
+// TAB_E_TOO_LARGE: the caller runs the separate launches instead (C not a multiple of 64, unaligned x).
+int quantize_auto_dispatch(const float* x, float scale, double* sums, unsigned* bar, float* ths_out, int64_t* qx, int bits,
+                           int N, int H, int W, int C, int* status, cudaStream_t stream) {
+    const long long wpi = (long long)H * W * (C / 64);
+    if (C % 64 != 0 || (reinterpret_cast<uintptr_t>(x) & 31) || wpi == 0 || N == 0) return TAB_E_TOO_LARGE;
+    const long long spi = (wpi + QWORDS_PER_ITER - 1) / QWORDS_PER_ITER;
+    if (spi >= (1LL << 31)) return TAB_E_TOO_LARGE;
+    const long long units = spi * N;
+    static std::mutex mu;
+    static int capacity[64][2] = {};                          // resident CTAs per device, per bitwidth
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TAB_E_TOO_LARGE;
+    int cap = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        int& c = capacity[dev][bits == 2 ? 1 : 0];
+        if (!c) {
+            int per_sm = 0, sms = 0;
+            cudaError_t e = bits == 2 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_auto_kernel<2>, QTHREADS, 0)
+                                      : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_auto_kernel<1>, QTHREADS, 0);
+            if (e != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return record_cuda_error(cudaGetLastError());
+            c = per_sm * sms;
+        }
+        cap = c;
+    }
+    if (cap < 1) return TAB_E_TOO_LARGE;
+    const unsigned grid = (unsigned)(units < cap ? units : cap);
+    uint64_t* q = reinterpret_cast<uint64_t*>(qx);
+    if (bits == 2) return launch_pdl(quantize_auto_kernel<2>, dim3(grid), dim3(QTHREADS), 0, stream, x, scale, sums, bar, ths_out, q, wpi, (int)spi, units, N, status);
+    return launch_pdl(quantize_auto_kernel<1>, dim3(grid), dim3(QTHREADS), 0, stream, x, scale, sums, bar, ths_out, q, wpi, (int)spi, units, N, status);
 }
 
 int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream) {

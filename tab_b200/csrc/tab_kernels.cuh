@@ -70,6 +70,12 @@ struct QuantExtras {
 int quantize_dispatch(const void* x, const float* ths, int64_t* qx, int32_t* btn, int bits,
                       int N, int H, int W, int C, cudaStream_t stream, const QuantExtras* extras = nullptr, bool in16 = false);
 int expand_weights_dispatch(const int64_t* qw, int8_t* w8, int wbits, int KN, int KH, int KW, int C, cudaStream_t stream);
+// Thresholds scale * mean|x[n]| and the bit-planes against them in one launch (sums: N doubles, bar: two words, all zero
+// before and after); TAB_E_TOO_LARGE when the shape needs the separate launches.
+int quantize_auto_dispatch(const float* x, float scale, double* sums, unsigned* bar, float* ths_out, int64_t* qx, int bits,
+                           int N, int H, int W, int C, int* status, cudaStream_t stream);
+// Device word that records a bounded wait that ran out (shared with the tensor-core kernel); null if unavailable.
+int* device_status_word();
 
 // conv_sm100.cu: implicit-im2col popcount GEMM on packed activations.  csa: carry-save popcount tree (else one POPC per word).
 int conv_packed_dispatch(const int64_t* qx, const int64_t* qw, const int32_t* btn, float* y, int type,

@@ -93,8 +93,14 @@ class TABConv2d(torch.nn.Module):
                 raise ValueError("int16 activations come with the thresholds their convolution produced")
             return ops.quantize_i16(x, thresholds, act_bitwidth(self.conv_type), N, H, W, self.C)
         if thresholds is None:
-            thresholds = ops.residual_threshold(x.reshape(N, -1), None, self.threshold_scale)
+            return self.quantize_auto(x)[0]
         return ops.Quantize(x, thresholds, act_bitwidth(self.conv_type), N, H, W, self.C)[0]
+
+    def quantize_auto(self, x):
+        """``quantize`` of fp32 activations against ``threshold_scale * mean|x[n]|``, both from one launch.  Returns
+        ``(QX, thresholds)``."""
+        N, H, W = (int(v) for v in x.shape[:3])
+        return ops.quantize_auto(x, self.threshold_scale, act_bitwidth(self.conv_type), N, H, W, self.C, self.state(N, x.device))
 
     def conv_bits(self, QX, N, H, W, residual=None, next_threshold_scale=None, state=None, out_int16=False, next_bitwidth=None):
         """GEMM stage on quantised activations.  Returns ``(Y, next_thresholds_or_None)``.  ``out_int16``: ``Y`` as int16

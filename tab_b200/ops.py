@@ -169,6 +169,26 @@ def new_state(N, device):
     return torch.zeros((max(_cabi.lib().tab_conv2d_state_bytes(int(N)), 8),), dtype=torch.uint8, device=device)
 
 
+def quantize_auto(X, scale, bitwidth, N, H, W, C, state=None):
+    """``Quantize`` with the thresholds computed on the way: ``thresholds[n] = scale * mean|X[n]|``.  One launch (sums, a
+    grid-wide meeting point, quantisation) where C is a multiple of 64, else the three launches it replaces.  Returns
+    ``(QX, thresholds)``.  ``state``: a block from ``new_state(N, device)`` to reuse (zero before and after)."""
+    _check_input(X, "X", torch.float32)
+    N, H, W, C = int(N), int(H), int(W), int(C)
+    if X.numel() != N * H * W * C:
+        raise RuntimeError("X has %d elements, expected N*H*W*C = %d" % (X.numel(), N * H * W * C))
+    bits = 1 if int(bitwidth) == 1 else 2
+    with torch.cuda.device(X.device):
+        if state is None:
+            state = new_state(N, X.device)
+        QX = torch.empty((N, H, W, (C + 63) // 64, bits), dtype=torch.int64, device=X.device)
+        ths = torch.empty((N,), dtype=torch.float32, device=X.device)
+        rc = _cabi.lib().tab_quantize_auto_launch(X.data_ptr(), float(scale), state.data_ptr(), ths.data_ptr(), QX.data_ptr(), int(bitwidth),
+                                                  N, H, W, C, _stream_ptr(X.device))
+    _cabi.check(rc, "tab_quantize_auto_launch")
+    return QX, ths
+
+
 def quantize_i16(X16, thresholds, bitwidth, N, H, W, C):
     """``Quantize`` on the compact int16 output of ``conv2d_bits(..., out_int16=True)``: returns ``QX`` only."""
     _check_input(X16, "X16", torch.int16)

@@ -428,6 +428,31 @@ def test_residual_threshold(cuda):
         assert np.array_equal(yd.cpu().numpy(), yo) and np.array_equal(t1.cpu().numpy(), to)
 
 
+@pytest.mark.parametrize("bw", [2, 1])
+@pytest.mark.parametrize("shape", [(3, 5, 7, 64), (16, 9, 4, 128), (2, 56, 56, 64), (5, 3, 3, 70), (300, 2, 2, 64)])
+def test_quantize_auto(cuda, bw, shape):
+    """Thresholds scale * mean|x[n]| and the bit-planes against them from one call: the thresholds equal the double-precision
+    reference (integer-valued data: every summation order gives the same sum), the bit-planes are the oracle's for those
+    thresholds, and the state block comes back zeroed; also with real-valued data against the device's own thresholds."""
+    N, H, W, C = shape
+    rng = np.random.default_rng(N + C)
+    state = TAB.ops.new_state(N, cuda)
+    for integer in (True, False):
+        x = rng.standard_normal((N, H, W, C)).astype(np.float32)
+        if integer:
+            x = np.round(x * 40).astype(np.float32)
+        for rep in range(2):                                           # twice through the same state block
+            qx, ths = TAB.ops.quantize_auto(dev_t(x, cuda), 0.7, bw, N, H, W, C, state)
+            t = ths.cpu().numpy()
+            if integer:
+                assert np.array_equal(t, OracleOps.residual_threshold(x.reshape(N, -1).copy(), None, 0.7))
+            else:
+                assert np.allclose(t, 0.7 * np.abs(x).reshape(N, -1).mean(1), rtol=1e-6)
+            assert np.array_equal(qx.cpu().numpy(), O.quantize(x, t, bw, N, H, W, C)[0])
+            assert not state.any().item()
+    assert _cabi.lib().tab_device_status() == 0
+
+
 def test_fused_conv_matches_unfused(cuda):
     """tab_conv2d_fused_launch: residual and per-image |y| statistics in the epilogue == separate passes."""
     rng = np.random.default_rng(11)
