@@ -439,7 +439,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- CUDA graph of one forward (the step is ~37 short launches: replaying a graph removes the launch
+    # ---- CUDA graph of one forward (the step is ~32 short launches: replaying a graph removes the launch
     #      gaps; the library's launches take a stream and never allocate or synchronise, so they capture) ----
     def make_graph(cset, x_static, nb):
         try:
@@ -773,7 +773,7 @@ def main():
                            "no epilogue); 2 x MEASURED_PEAKS.json bf16_tflops would be %.0f TOP/s (%s); s8 mma.sync ceiling measured in this run: %.0f TOP/s"
                            % (2.0 * bf16_peak, peak_src, imma_sync_tops)},
         "quantize_in_step": {
-            "kernel": "quantize_c64_kernel, the 16 launches of the step, each timed alone", "bound": "hbm",
+            "kernel": "quantize_c64_kernel on the 16 convolution inputs of the step, each timed alone (inside the step 12 of them are launches of their own; the chain's input goes through quantize_auto_kernel, the small ones are quantised by the kernel that wrote them)", "bound": "hbm",
             "achieved": (sums["quant_bytes"] / (sums["quant_ms"] * 1e-3) / 1e9) if sums["quant_ms"] else None, "peak": hbm_peak, "unit": "GB/s"},
         "quantize": quant,
         "popcount": {
