@@ -453,6 +453,28 @@ def test_quantize_auto(cuda, bw, shape):
     assert _cabi.lib().tab_device_status() == 0
 
 
+@pytest.mark.parametrize("C", [64, 70])
+def test_quantize_i16_threshold_edge_values(cuda, C):
+    """The 16-bit quantiser must agree with the fp32 quantiser (and the oracle) for every kind of threshold: fractions, exact
+    integers, negative, zero, beyond the 16-bit range, infinities and NaN - on values that include the extremes and every
+    integer around the thresholds."""
+    ths = np.array([0.0, -0.0, 0.5, 5.0, 5.5, -3.0, -3.2, 32766.5, 32767.0, 40000.0, -40000.0, 1e30, -1e30, np.inf, -np.inf, np.nan, 1e-30, 7.999999],
+                   dtype=np.float32)
+    N, H, W = len(ths), 4, 8
+    rng = np.random.default_rng(C)
+    v = rng.integers(-12, 13, size=(N, H, W, C)).astype(np.int16)
+    v[:, 0, 0, :8] = np.array([-32767, 32767, -32766, 32766, 0, 1, -1, 8], dtype=np.int16)
+    v[:, 0, 1, :6] = np.array([5, 6, -5, -6, -3, -4], dtype=np.int16)
+    vd = torch.from_numpy(v).to(cuda)
+    td = torch.from_numpy(ths).to(cuda)
+    xf = v.astype(np.float32)
+    for bw in (2, 1):
+        q16 = TAB.ops.quantize_i16(vd, td, bw, N, H, W, C)
+        qf, _ = TAB.Quantize(torch.from_numpy(xf).to(cuda), td, bw, N, H, W, C)
+        assert torch.equal(q16, qf)
+        assert np.array_equal(q16.cpu().numpy(), O.quantize(xf, ths, bw, N, H, W, C)[0])
+
+
 def test_fused_conv_matches_unfused(cuda):
     """tab_conv2d_fused_launch: residual and per-image |y| statistics in the epilogue == separate passes."""
     rng = np.random.default_rng(11)
