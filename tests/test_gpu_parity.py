@@ -453,6 +453,26 @@ def test_quantize_auto(cuda, bw, shape):
     assert _cabi.lib().tab_device_status() == 0
 
 
+def test_next_layer_quantisation_with_many_images(cuda):
+    """More images than the kernel's second phase keeps thresholds for (8192): the quantiser runs behind the GEMM stage and the
+    call returns the same three results."""
+    N, H, W, C, KN = 8200, 2, 2, 64, 64
+    x, ths = make_input(71, N, H, W, C)
+    w, wths = make_input(72, KN, 1, 1, C)
+    qw, btn = O.quantize(w, wths, 2, KN, 1, 1, C)
+    qx, _ = TAB.Quantize(dev_t(x, cuda), dev_t(ths, cuda), 2, N, H, W, C)
+    w8 = TAB.ops.expand_weights(dev_t(qw, cuda), 2, KN, 1, 1, C)
+    state = TAB.ops.new_state(N, cuda)
+    y, nxt, qn = TAB.ops.conv2d_bits(qx, w8, 0, 0, 0, 1, 1, N, H, W, C, KN, 1, 1, threshold_scale=0.7, state=state, next_bitwidth=2)
+    assert "+next" not in _cabi.lib().tab_last_conv_kernel().decode()
+    yo = c_oracle.conv2d(x, qw, ths, btn, 0, 0, 0, 1, 1, N, H, W, C, KN, 1, 1)
+    assert np.array_equal(y.cpu().numpy(), yo)
+    to = OracleOps.residual_threshold(yo.copy(), None, 0.7)
+    assert np.array_equal(nxt.cpu().numpy(), to)
+    assert np.array_equal(qn.cpu().numpy(), O.quantize(yo.reshape(N, H, W, KN), to, 2, N, H, W, KN)[0])
+    assert not state.any().item() and _cabi.lib().tab_device_status() == 0
+
+
 @pytest.mark.parametrize("C", [64, 70])
 def test_quantize_i16_threshold_edge_values(cuda, C):
     """The 16-bit quantiser must agree with the fp32 quantiser (and the oracle) for every kind of threshold: fractions, exact
