@@ -14,15 +14,20 @@
 //     two patches ahead of the MMAs, across tile boundaries.
 //   * warp 2: TMA copies of the filter slice (TN x 128 B per tap and channel pair) into a ring of SB stages, or - when
 //     the filters of all taps fit beside the patches (BRES) - once per CTA.
-//   * warps 1 and 3 (row block 0 and row block 1 of a tile): tcgen05.mma.cta_group::1.kind::i8, 128 x TN x 32 per instruction.  Tap (kh, kw) of the 128 rows of an MMA
-//     is 128 consecutive patch rows starting (kh/s1)*VW + kw/s2 rows into the patch: the A descriptor simply starts
-//     there (the 128-byte swizzle is a function of absolute shared-memory address bits).  Two TMEM accumulator buffers.
-//   * warps 4-11: epilogue of the other accumulator buffer: tcgen05.ld, transposition through a private shared-memory
-//     block so that stores are coalesced, int -> float, residual, per-image sums of |y|, stores.
-//   * the CTA that finishes last turns the sums into the next layer's thresholds.
+//   * warps 1 and 3 (row block 0 and row block 1 of a tile): tcgen05.mma.cta_group::1.kind::i8, 128 x TN x 32 per
+//     instruction.  Tap (kh, kw) of the 128 rows of an MMA is 128 consecutive patch rows starting (kh/s1)*VW + kw/s2 rows
+//     into the patch: the A descriptor simply starts there (the 128-byte swizzle is a function of absolute shared-memory
+//     address bits).  Two TMEM accumulator buffers.
+//   * warps 4-11: epilogue of the other accumulator buffer: tcgen05.ld, then either a transposition through a private
+//     shared-memory block so that stores are coalesced, or (TEPI) TMA loads of the residual and TMA stores of the result;
+//     int -> float, residual, per-image sums of |y|.
+//   * the CTA that finishes last turns the sums into the next layer's thresholds - or, second phase, the whole grid meets
+//     at a counter and quantises the result it has just written for the next convolution (quantize_tail).
+//   * PAIR: the same roles on clusters of two CTAs with one tcgen05.mma.cta_group::2 stream for both (see the kernel).
 // Every mbarrier wait is a bounded try_wait loop; on expiry the role records a code in *status and stops, the other
 // roles run into their own limits, every thread still reaches the final barrier, TMEM is freed and the kernel returns.
-// No kernel here waits on another CTA or GPU, and no copy is multicast.
+// The grid-wide counter of the second phase is the only place where a CTA waits for other CTAs (all resident, at most one
+// per SM; bounded as well); no kernel here waits on another GPU, and no copy is multicast.
 #include <cuda.h>
 #include <algorithm>
 #include <cstdio>
