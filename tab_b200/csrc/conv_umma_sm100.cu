@@ -39,7 +39,8 @@
 namespace tab {
 
 constexpr int PTHREADS = 512;                                              // 16 warps
-constexpr int NXT = 160;                                                   // expander threads (5 warps)
+constexpr int NXT = 160;                                                   // expander threads: 5 warps, and a sixth (192) where the
+                                                                           // second MMA warp has nothing to issue (one row block per tile)
 constexpr int XUNROLL = 4;                                                 // (pixel, word) items a thread has in flight
 
 // Build-time diagnostic (-DTAB_PROF, never in the shipped library): cycles one representative warp of each role spends
@@ -258,14 +259,14 @@ struct RawItems { uint64_t sg[XUNROLL], mg[XUNROLL]; };
 // 2*cp + 1.  Item = (row, word); the two words of a pixel go to neighbouring threads (32 contiguous bytes).  Padding
 // positions are not loaded: they are zero words (ternary: 0; binary: +1 in the real channels).  Binary activations
 // have one plane: its word is the sign, the magnitude is all ones.
-__device__ __forceinline__ void load_items(const TcConvParams& p, RawItems& raw, int Rbase, int nrows, int cp, int pa, int pb, int base, int xt) {
+__device__ __forceinline__ void load_items(const TcConvParams& p, RawItems& raw, int Rbase, int nrows, int cp, int pa, int pb, int base, int xt, int nxt) {
     const bool UNIT = p.s1 == 1 && p.s2 == 1;
     const int nw = (2 * cp + 1 < p.PC) ? 2 : 1;
     const int items = nrows * nw;
     const int VHW = p.VH * p.VW;
 #pragma unroll
     for (int u = 0; u < XUNROLL; u++) {
-        const int it = base + u * NXT + xt;
+        const int it = base + u * nxt + xt;
         raw.sg[u] = 0;
         raw.mg[u] = p.abits == 1 ? ~0ull : 0ull;
         if (it < items) {
@@ -293,12 +294,12 @@ __device__ __forceinline__ void load_items(const TcConvParams& p, RawItems& raw,
 
 // Expands the items load_items fetched into rows of patch buffer `buf` (K-major, 128-byte swizzle: 16-byte unit u of
 // row r lives at r*128 + ((u ^ (r & 7)) << 4); buf is 1024-byte aligned).  Channels beyond C become 0.
-__device__ __forceinline__ void store_items(const TcConvParams& p, const RawItems& raw, uint32_t buf, int nrows, int cp, int base, int xt) {
+__device__ __forceinline__ void store_items(const TcConvParams& p, const RawItems& raw, uint32_t buf, int nrows, int cp, int base, int xt, int nxt) {
     const int nw = (2 * cp + 1 < p.PC) ? 2 : 1;
     const int items = nrows * nw;
 #pragma unroll
     for (int u = 0; u < XUNROLL; u++) {
-        const int it = base + u * NXT + xt;
+        const int it = base + u * nxt + xt;
         if (it < items) {
             const int r = nw == 2 ? it >> 1 : it, w = nw == 2 ? it & 1 : 0;
             const uint32_t rowaddr = buf + (uint32_t)r * IROW;
@@ -596,6 +597,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     constexpr int BROWS = PAIR ? TNI / 2 : TNI;                            // filters of a slice this CTA holds
     constexpr int BSTAGE = BROWS * IROW;
     constexpr int ACOLS = MT * TNI;                                        // columns of one accumulator buffer
+    constexpr int NX = MT == 1 ? NXT + 32 : NXT;                           // expander threads: warp 3 joins them when it has no MMAs to issue
     static_assert(2 * ACOLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
     static_assert(SB <= 8, "eight ring barriers are laid out");
     extern __shared__ unsigned char smem_raw[];
@@ -629,7 +631,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     if (tid == 0) {
         *deadp = 0;
         for (int s = 0; s < 8; s++) mbar_init(fullB + 8 * s, 1);
-        mbar_init(fullP, (PAIR ? 2 : 1) * NXT); mbar_init(fullP + 8, (PAIR ? 2 : 1) * NXT);   // one arrival per expander thread (of both CTAs)
+        mbar_init(fullP, (PAIR ? 2 : 1) * NX); mbar_init(fullP + 8, (PAIR ? 2 : 1) * NX);     // one arrival per expander thread (of both CTAs)
         for (int s = 0; s < 8; s++) mbar_init(emptyB + 8 * s, MT);          // one commit per MMA warp (MT = 2: two warps)
         mbar_init(emptyP, MT); mbar_init(emptyP + 8, MT);
         mbar_init(accFull, MT); mbar_init(accFull + 8, MT);
@@ -652,11 +654,11 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
 
     // In every role the whole warp runs the loops and the waits and one elected lane issues the copies, MMAs and
     // commits.  All roles walk the same nest: tile, channel pair cp, plane (a, b), taps of that plane.
-    if (warp == 0 || warp >= 12) {
+    if (warp == 0 || warp >= 12 || (MT == 1 && warp == 3)) {
         // ---- expanders: up to two patches ahead of the MMAs (across tile boundaries).  The global loads of a patch are
         //      issued a whole patch earlier than they are used (they need registers, not the patch buffer), so that their
         //      latency - long when the epilogue's stores fill the memory system - is off the critical path. -----------------
-        const int xt = (warp == 0 ? 0 : warp - 11) * 32 + lane;
+        const int xt = (warp == 0 ? 0 : (warp == 3 ? 5 : warp - 11)) * 32 + lane;
         const bool prof_on = warp == 0 && lane == 0;
         (void)prof_on;
         const int planes = PA * PB, step = cstep;
@@ -669,15 +671,15 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             if (q >= 2 && !mbar_wait_prof<0, PAIR>(prof_on, emptyP + 8 * pb, ((q >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 11); *deadp = 1; } return; }
             const uint32_t buf = sPatch + (uint32_t)(pb * prow) * IROW;
             PROF_T0;
-            store_items(p, mine, buf, nrows, cur.cp, 0, xt);
+            store_items(p, mine, buf, nrows, cur.cp, 0, xt, NX);
             const int items = nrows * ((2 * cur.cp + 1 < p.PC) ? 2 : 1);
-            if (items > NXT * XUNROLL) {                                   // long patches (large halo): the rest, chunk by chunk
+            if (items > NX * XUNROLL) {                                    // long patches (large halo): the rest, chunk by chunk
                 const int R0 = tile_row0(cur.t);
                 const int pa = UNIT ? 0 : cur.pl / PB;
-                for (int base = NXT * XUNROLL; base < items; base += NXT * XUNROLL) {
+                for (int base = NX * XUNROLL; base < items; base += NX * XUNROLL) {
                     RawItems more;
-                    load_items(p, more, R0, nrows, cur.cp, pa, UNIT ? 0 : cur.pl - pa * PB, base, xt);
-                    store_items(p, more, buf, nrows, cur.cp, base, xt);
+                    load_items(p, more, R0, nrows, cur.cp, pa, UNIT ? 0 : cur.pl - pa * PB, base, xt, NX);
+                    store_items(p, more, buf, nrows, cur.cp, base, xt, NX);
                 }
             }
             fence_async_smem();
@@ -687,7 +689,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         };
         auto load_patch = [&](RawItems& into, const PatchIter& at) {
             const int pa = UNIT ? 0 : at.pl / PB;
-            if (at.t < ntiles) load_items(p, into, tile_row0(at.t), nrows, at.cp, pa, UNIT ? 0 : at.pl - pa * PB, 0, xt);
+            if (at.t < ntiles) load_items(p, into, tile_row0(at.t), nrows, at.cp, pa, UNIT ? 0 : at.pl - pa * PB, 0, xt, NX);
         };
         // The words of the next patch are loaded before this one is expanded.  (The hand-over raw = ahead comes after the
         // expansion, when those loads have long arrived: a move of a register whose load is in flight would wait for it.)
@@ -747,7 +749,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                 }
             }
         }
-    } else if (warp == 1 || warp == 3) {
+    } else if (warp == 1 || (MT == 2 && warp == 3)) {
         // ---- MMA warps.  One thread cannot issue the MMAs of a stage, its commits and the waits between stages as fast
         //      as the tensor pipe executes them (about 300 cycles per handshake and 80 per MMA against 48-128 cycles of
         //      execution).  With two row blocks per tile (MT = 2) warp 1 issues row block 0 and warp 3 row block 1: separate
