@@ -39,6 +39,9 @@
 namespace tab {
 
 constexpr int PTHREADS = 512;                                              // 16 warps
+// Extra expander warps (17, 18): layers without a residual are bound by their expanders, whose warps each run one
+// dependent instruction stream; their epilogue needs fewer registers, so two more warps fit the register file.
+__host__ __device__ constexpr int extra_warps(int fused, bool tepi, int tn) { return (fused <= 1 && !tepi && tn == 64) ? 2 : 0; }
 constexpr int NXT = 160;                                                   // expander threads: 5 warps, and a sixth (192) where the
                                                                            // second MMA warp has nothing to issue (one row block per tile)
 constexpr int XUNROLL = 4;                                                 // (pixel, word) items a thread has in flight
@@ -183,6 +186,7 @@ __device__ __noinline__ void quantize_tail(const QuantTailArgs p, float* ths_sme
     // words of the result: word w = 64 consecutive channels = elements [64 w, 64 w + 64) of y; 8 lanes per word, 64 words
     // per pass of the CTA, UN passes per step with all loads of a step issued before the first is used (addresses are one
     // base register plus constants)
+    if (tid >= 512) return;                                                // 64 words per pass: 512 threads (kernels with extra warps have more)
     const int PC2 = p.KN >> 6, bits = p.next_bits, byte = tid & 7;
     const uint32_t grp = (uint32_t)tid >> 3;
     const uint32_t words = (uint32_t)((long long)p.M * PC2);               // < 2^31, checked on the host
@@ -589,7 +593,7 @@ __device__ __forceinline__ void tepi_request_residual(const void* tmR, const Tep
 // MMAs and its commits arrive on the "empty" / "accumulator full" barriers of both CTAs, while the "full" / "accumulator
 // empty" barriers it waits on live in the even CTA and collect the arrivals of both.
 template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI, bool PAIR = false>
-__global__ void __launch_bounds__(PTHREADS, 1)
+__global__ void __launch_bounds__(PTHREADS + 32 * extra_warps(FUSED, TEPI, TNI), 1)
 conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmR,
                          const TcConvParams p, int* __restrict__ status,
                          const int prow, const int nrows, const int nst, const int tiles_m, const int tiles_n) {
@@ -597,7 +601,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     constexpr int BROWS = PAIR ? TNI / 2 : TNI;                            // filters of a slice this CTA holds
     constexpr int BSTAGE = BROWS * IROW;
     constexpr int ACOLS = MT * TNI;                                        // columns of one accumulator buffer
-    constexpr int NX = MT == 1 ? NXT + 32 : NXT;                           // expander threads: warp 3 joins them when it has no MMAs to issue
+    constexpr int NXW = 5 + extra_warps(FUSED, TEPI, TNI) + (MT == 1 ? 1 : 0);   // expander warps: 0, 12 and up, and warp 3 when it has no MMAs to issue
+    constexpr int NX = 32 * NXW;
     static_assert(2 * ACOLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
     static_assert(SB <= 8, "eight ring barriers are laid out");
     extern __shared__ unsigned char smem_raw[];
@@ -658,7 +663,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         // ---- expanders: up to two patches ahead of the MMAs (across tile boundaries).  The global loads of a patch are
         //      issued a whole patch earlier than they are used (they need registers, not the patch buffer), so that their
         //      latency - long when the epilogue's stores fill the memory system - is off the critical path. -----------------
-        const int xt = (warp == 0 ? 0 : (warp == 3 ? 5 : warp - 11)) * 32 + lane;
+        const int xt = (warp == 0 ? 0 : (warp == 3 ? NXW - 1 : warp - 11)) * 32 + lane;
         const bool prof_on = warp == 0 && lane == 0;
         (void)prof_on;
         const int planes = PA * PB, step = cstep;
@@ -1336,11 +1341,11 @@ static int launch_persist_u(const CUtensorMap& tmB, const CUtensorMap& tmY, cons
     if (PAIR) {
         const long long pairs = std::min<long long>(sms / 2, pair_clusters());
         const unsigned grid = 2u * (unsigned)(ntiles < pairs ? ntiles : pairs);
-        return launch_pdl_cluster(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS), (size_t)pl.smem, stream, 2u,
+        return launch_pdl_cluster(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS + 32 * extra_warps(FUSED, TEPI, TNI)), (size_t)pl.smem, stream, 2u,
                                   tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
     }
     const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
-    return launch_pdl(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS), (size_t)pl.smem, stream,
+    return launch_pdl(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS + 32 * extra_warps(FUSED, TEPI, TNI)), (size_t)pl.smem, stream,
                       tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
 }
 
@@ -1377,7 +1382,7 @@ static int pair_clusters() {
         auto kernel = conv_umma_persist_kernel<1, 256, 8, false, 0, false, true>;
         int clusters = 0;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2); cfg.blockDim = dim3(PTHREADS); cfg.dynamicSmemBytes = UMMA_SMEM_MAX;
+        cfg.gridDim = dim3(2); cfg.blockDim = dim3(PTHREADS + 32 * extra_warps(0, false, 256)); cfg.dynamicSmemBytes = UMMA_SMEM_MAX;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;

@@ -88,8 +88,12 @@ def test_quantize_empty_and_unaligned(cuda):
 
 
 def test_notebook_facts_on_device(cuda):
-    w = torch.rand(64, 3, 3, 256, device=cuda)
+    g = torch.Generator(device=cuda)
+    g.manual_seed(11)
+    w = torch.rand(64, 3, 3, 256, device=cuda, generator=g)
     t = 0.7 * w.reshape(64, -1).mean(dim=1)
+    # a value equal to its threshold is neither "< t" nor "> t": the complement relation below holds for all other values
+    w = torch.where(w == t.reshape(64, 1, 1, 1), w + 0.25, w)
     q2, b2 = TAB.Quantize(w, t, 2, 64, 3, 3, 256)
     q1, b1 = TAB.Quantize(w, t, 1, 64, 3, 3, 256)
     assert tuple(q2.shape) == (64, 3, 3, 4, 2) and q2.dtype == torch.int64 and tuple(b2.shape) == (64,)
