@@ -81,9 +81,12 @@ int tab_conv2d_set_path(int path);
    when the last convolution ran the popcount kernel).  Static storage per thread. */
 const char* tab_last_conv_kernel(void);
 /*
- * Every wait inside the tensor-core kernel is bounded; a wait that ran out makes the kernel record a code and return
- * early, leaving y incomplete.  This call synchronises the current device, returns that code (0 = none) and clears it.
- * A non-zero code invalidates the outputs of every convolution launched on the device since the previous call.
+ * Every wait inside the tensor-core kernel and inside tab_quantize_auto_launch's kernel is bounded; a wait that ran out makes
+ * the kernel record a code and return early, leaving its outputs incomplete.  This call synchronises the current device,
+ * returns that code (0 = none; 11-17: a role of the tensor-core kernel gave up on an mbarrier; 21, 22: the grid-wide
+ * meeting point of tab_conv2d_bits_next_launch / tab_quantize_auto_launch, which needs the launch's CTAs resident together -
+ * other work occupying the device for tenths of a second can cause it) and clears it.  A non-zero code invalidates the
+ * outputs of every launch on the device since the previous call.
  */
 int tab_device_status(void);
 
