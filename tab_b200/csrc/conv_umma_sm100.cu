@@ -906,13 +906,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             const bool fast = want_sum && p.Kw < (1 << 12) && (int)p.dVHW.div((uint32_t)(Rw + 31)) - wimg0 <= 1;
             unsigned isum = 0;
             double dsum = 0.0;
-            if (has_res && lane == 0 && t + step < ntiles) {               // the next tile's residual boxes on their way into L2
-                const int tn_ = t + step, n0n = (tn_ % tiles_n) * TNI;
-                for (int cb = ec0; cb < ec1 && n0n + cb < p.KN; cb += 32) {
-                    const TepiBox bx = tepi_box(p, slab_row(tn_), n0n + cb);
-                    if (bx.live) tma_prefetch_4d(&tmR, bx.c0, bx.c1, bx.c2, bx.c3);
-                }
-            }
+            // (No prefetch of the next tile's residual boxes into the L2: the copy engine, which takes every box row by row, is
+            //  what bounds this epilogue, and the prefetches were half as many requests again - 5 % of the launch.)
             if (!mbar_wait_prof<6>(prof_on, accFull + 8 * buf, (a >> 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 16); *deadp = 1; } break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * ACOLS + (uint32_t)(emb * TNI) + ((uint32_t)((warp & 3) * 32) << 16);
