@@ -387,12 +387,19 @@ __device__ __forceinline__ void slab_rows(const TcConvParams& p, int Rw, int lan
     sr.slow = want_sum && !sr.fast;
 }
 
+// Streaming 128-bit load that leaves no line in L1 (the residual is read once).
+__device__ __forceinline__ float4 ld_stream_f4(const float4* ptr) {
+    float4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(ptr));
+    return r;
+}
+
 // Residual values of the 32-column block at filter nbase, in the transposed layout (res[i] = row 4i + rsub, 4 columns).
 __device__ __forceinline__ void slab_load_residual(const TcConvParams& p, const SlabRows& sr, int nbase, int lane, float4 (&res)[8]) {
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         res[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (sr.mi[i] >= 0) res[i] = __ldg(reinterpret_cast<const float4*>(p.residual + (long long)sr.mi[i] * p.KN + nbase) + (lane & 7));
+        if (sr.mi[i] >= 0) res[i] = ld_stream_f4(reinterpret_cast<const float4*>(p.residual + (long long)sr.mi[i] * p.KN + nbase) + (lane & 7));
     }
 }
 
