@@ -39,9 +39,13 @@
 namespace tab {
 
 constexpr int PTHREADS = 512;                                              // 16 warps
-// Extra expander warps (17, 18): layers without a residual are bound by their expanders, whose warps each run one
-// dependent instruction stream; their epilogue needs fewer registers, so two more warps fit the register file.
-__host__ __device__ constexpr int extra_warps(int fused, bool tepi, int tn) { return (fused <= 1 && !tepi && tn == 64) ? 2 : 0; }
+// Extra expander warps (16 and up): layers without a residual are bound by their expanders.  An expander warp is one
+// dependent instruction stream that takes the patch's items 32 at a time, so what counts is how many rounds of items a
+// thread has per patch: the patches of strided layers (about 290 items) want nine expander warps to be done in one round.
+// The epilogue of these variants fits 96 registers, so up to 21 warps fit the register file.  Measured per filter-block
+// width on the ResNet-18-shaped layers: 2 / 4 / 3 extra warps; one more each changed nothing, and on residual layers the
+// epilogue is the bound and needs the registers.
+__host__ __device__ constexpr int extra_warps(int fused, bool tepi, int tn) { return (fused <= 1 && !tepi) ? (tn == 64 ? 2 : (tn == 128 ? 4 : 3)) : 0; }
 constexpr int NXT = 160;                                                   // expander threads: 5 warps, and a sixth (192) where the
                                                                            // second MMA warp has nothing to issue (one row block per tile)
 constexpr int XUNROLL = 4;                                                 // (pixel, word) items a thread has in flight
