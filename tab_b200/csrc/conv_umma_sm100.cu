@@ -46,6 +46,9 @@ constexpr int PTHREADS = 512;                                              // 16
 // width on the ResNet-18-shaped layers: 2 / 4 / 3 extra warps; one more each changed nothing, and on residual layers the
 // epilogue is the bound and needs the registers.
 __host__ __device__ constexpr int extra_warps(int fused, bool tepi, int tn) { return (fused <= 1 && !tepi) ? (tn == 64 ? 2 : (tn == 128 ? 4 : 3)) : 0; }
+// Kernels that can work a tile as two halves of tn/2 filters (their filter boxes hold tn/2 filters): one row block, the
+// widest tile, streamed filters, transposing epilogue, single CTAs.
+__host__ __device__ constexpr bool split_capable(int mt, int tn, bool resident, bool tepi, bool pair) { return mt == 1 && tn == 256 && !resident && !tepi && !pair; }
 constexpr int NXT = 160;                                                   // expander threads: 5 warps, and a sixth (192) where the
                                                                            // second MMA warp has nothing to issue (one row block per tile)
 constexpr int XUNROLL = 4;                                                 // (pixel, word) items a thread has in flight
@@ -607,8 +610,9 @@ template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI, bool PAIR = 
 __global__ void __launch_bounds__(PTHREADS + 32 * extra_warps(FUSED, TEPI, TNI), 1)
 conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmR,
                          const TcConvParams p, int* __restrict__ status,
-                         const int prow, const int nrows, const int nst, const int tiles_m, const int tiles_n) {
+                         const int prow, const int nrows, const int nst, const int tiles_m, const int tiles_n, const int split_from) {
     static_assert(!PAIR || (MT == 1 && !BRES && !TEPI), "CTA pairs: one row block per CTA, streamed filters, transposing epilogue");
+    constexpr bool SPLIT = split_capable(MT, TNI, BRES, TEPI, PAIR);
     constexpr int BROWS = PAIR ? TNI / 2 : TNI;                            // filters of a slice this CTA holds
     constexpr int BSTAGE = BROWS * IROW;
     constexpr int ACOLS = MT * TNI;                                        // columns of one accumulator buffer
@@ -637,12 +641,17 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     const bool UNIT = s1 == 1 && s2 == 1;                                  // one plane: flat tap loops
     const int PA = p.PA, PB = p.PB, VW = p.VW;
     const int T = p.KH * p.KW, ncp = (p.PC + 1) >> 1;
-    const int ntiles = tiles_m * tiles_n;
+    // SPLIT: the tiles from split_from on (the last, partly filled round of the grid) are worked as two halves of TNI/2
+    // filters each, numbered after the whole tiles: twice as many CTAs share the round and it takes about half as long.
+    const int sfrom = SPLIT ? split_from : tiles_m * tiles_n;
+    const int ntiles = 2 * tiles_m * tiles_n - sfrom;                      // work items: whole tiles, then halves
+    auto tile_of = [&](int v) { return SPLIT && v >= sfrom ? sfrom + ((v - sfrom) >> 1) : v; };
+    auto half_of = [&](int v) { return SPLIT && v >= sfrom ? 1 + ((v - sfrom) & 1) : 0; };    // 0: whole tile, 1 / 2: its halves
     const uint32_t crank = PAIR ? cluster_ctarank() : 0u;                  // 0: the CTA whose MMA warp works for the pair
     const int cta0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // first tile of this CTA (pair)
     const int cstep = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;       // tiles between two of its tiles
     // first virtual row of this CTA's part of tile t
-    auto tile_row0 = [&](int t) { return PAIR ? ((t / tiles_n) * 2 + (int)crank) * UTM : (t / tiles_n) * (UTM * MT); };
+    auto tile_row0 = [&](int t) { return PAIR ? ((t / tiles_n) * 2 + (int)crank) * UTM : (tile_of(t) / tiles_n) * (UTM * MT); };
 
     if (tid == 0) {
         *deadp = 0;
@@ -742,7 +751,8 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             const bool prof_on = lane == 0;
             (void)prof_on;
             for (int t = cta0; t < ntiles && !dead; t += cstep) {
-                const int n0 = (t % tiles_n) * TNI + (PAIR ? (int)crank * BROWS : 0);
+                const int hf = half_of(t);
+                const int n0 = (tile_of(t) % tiles_n) * TNI + (PAIR ? (int)crank * BROWS : 0) + (hf == 2 ? TNI / 2 : 0);
                 for (int cp = 0; cp < ncp && !dead; cp++) {
                     // same tap order as the MMA warp: plane by plane
                     for (int pa = 0; pa < PA && !dead; pa++)
@@ -755,6 +765,11 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
                             if (PAIR) {                                    // both halves are counted on the even CTA's barrier
                                 if (crank == 0) mbar_expect_tx(fullB + 8 * slot, 2u * (uint32_t)BSTAGE);
                                 tma_load_2d_pair(sRing + slot * BSTAGE, &tmB, ((kh * p.KW + kw) * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
+                            } else if (SPLIT) {                            // boxes of TNI/2 filters: two for a whole tile
+                                const int kx = ((kh * p.KW + kw) * p.PC + 2 * cp) * 64;
+                                mbar_expect_tx(fullB + 8 * slot, (uint32_t)(hf ? BSTAGE / 2 : BSTAGE));
+                                tma_load_2d(sRing + slot * BSTAGE, &tmB, kx, n0, fullB + 8 * slot);
+                                if (!hf) tma_load_2d(sRing + slot * BSTAGE + BSTAGE / 2, &tmB, kx, n0 + TNI / 2, fullB + 8 * slot);
                             } else {
                                 mbar_expect_tx(fullB + 8 * slot, (uint32_t)BSTAGE);
                                 tma_load_2d(sRing + slot * BSTAGE, &tmB, ((kh * p.KW + kw) * p.PC + 2 * cp) * 64, n0, fullB + 8 * slot);
@@ -787,8 +802,9 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             return p.PC == 1 ? ((sRing + (uint32_t)(tap >> 1) * BSTAGE) >> 4) + (uint32_t)(tap & 1) * 4u
                              : (sRing + (uint32_t)(cp * T + tap) * BSTAGE) >> 4;
         };
+        uint32_t idesc = IDESC;
         auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t acc_flag) {
-            if (PAIR) umma_i8_pair(d, da, db, IDESC, acc_flag); else umma_i8(d, da, db, IDESC, acc_flag);
+            if (PAIR) umma_i8_pair(d, da, db, IDESC, acc_flag); else umma_i8(d, da, db, SPLIT ? idesc : IDESC, acc_flag);
         };
         auto commit = [&](uint32_t bar) { if (PAIR) umma_commit_pair(bar); else umma_commit(bar); };
         for (int t = cta0; t < ntiles && !dead; t += cstep, a++) {
@@ -796,6 +812,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
             if (a >= 2 && !mbar_wait_prof<3, PAIR>(prof_on, accEmpty + 8 * buf, ((a >> 1) - 1) & 1u)) { dead = true; if (lane == 0) { if (status) atomicExch(status, 13); *deadp = 1; } break; }
             tc_fence_after();
             const uint32_t acc = tmem_base + buf * ACOLS;
+            if (SPLIT) idesc = half_of(t) ? umma_idesc(TNI / 2) : IDESC;
             uint32_t accumulate = 0;                                       // 0 for the tile's first MMAs
             for (int cp = 0; cp < ncp && !dead; cp++) {
                 const bool four = 2 * cp + 1 < p.PC;                       // both 64-channel words of the pair exist
@@ -1028,11 +1045,12 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
         (void)prof_on;
         for (int t = cta0; t < ntiles && !dead; t += cstep, a++) {
             const unsigned buf = a & 1;
-            const int R0 = tile_row0(t), n0 = (t % tiles_n) * TNI;
+            const int hf = half_of(t), wcols = hf ? TNI / 2 : TNI;         // columns of the accumulator in use
+            const int R0 = tile_row0(t), n0 = (tile_of(t) % tiles_n) * TNI + (hf == 2 ? TNI / 2 : 0);
             // two warps per TMEM lane quarter: they split the row blocks of a two-block tile, else the columns.  Row data
             // and the first block's residual are fetched before the accumulator is waited for.
             const int wg = (warp - 4) >> 2;
-            const int emb = MT == 2 ? wg : 0, ec0 = MT == 2 ? 0 : wg * (TNI / 2), ec1 = MT == 2 ? TNI : (wg + 1) * (TNI / 2);
+            const int emb = MT == 2 ? wg : 0, ec0 = MT == 2 ? 0 : wg * (wcols / 2), ec1 = MT == 2 ? TNI : (wg + 1) * (wcols / 2);
             SlabRows sr;
             slab_rows<FUSED>(p, R0 + emb * UTM + (warp & 3) * 32, lane, sr);
             float4 res[8];
@@ -1327,6 +1345,16 @@ static bool tc_prepare(TcConvParams& p, int sms, TcPlan* pl) {
     return true;
 }
 
+// First tile that is worked as two halves (see SPLIT in the kernel), ntiles = none: a last round of the persistent grid
+// that fills at most half of it is split, so that it takes about half as long.
+static long long split_point(long long ntiles, int sms, bool capable) {
+#ifdef TAB_TUNE
+    if (const char* env = getenv("TAB_SPLIT")) if (atoi(env) == 0) return ntiles;      // build-time diagnostic only
+#endif
+    const long long grid = ntiles < sms ? ntiles : sms, rest = grid > 0 ? ntiles % grid : 0;
+    return capable && ntiles > grid && rest != 0 && 2 * rest <= grid ? ntiles - rest : ntiles;
+}
+
 template <int MT, int TNI, int SB, bool BRES, int FUSED, bool TEPI, bool PAIR = false>
 static int launch_persist_u(const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR, const TcConvParams& p, const TcPlan& pl,
                             int sms, int* status, cudaStream_t stream) {
@@ -1348,11 +1376,12 @@ static int launch_persist_u(const CUtensorMap& tmB, const CUtensorMap& tmY, cons
         const long long pairs = std::min<long long>(sms / 2, pair_clusters());
         const unsigned grid = 2u * (unsigned)(ntiles < pairs ? ntiles : pairs);
         return launch_pdl_cluster(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS + 32 * extra_warps(FUSED, TEPI, TNI)), (size_t)pl.smem, stream, 2u,
-                                  tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
+                                  tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n, (int)ntiles);
     }
     const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
+    const long long split_from = split_point(ntiles, sms, split_capable(MT, TNI, BRES, TEPI, PAIR));
     return launch_pdl(conv_umma_persist_kernel<MT, TNI, SB, BRES, FUSED, TEPI, PAIR>, dim3(grid), dim3(PTHREADS + 32 * extra_warps(FUSED, TEPI, TNI)), (size_t)pl.smem, stream,
-                      tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n);
+                      tmB, tmY, tmR, p, status, pl.prow, pl.nrows, pl.nst, (int)pl.tiles_m, (int)pl.tiles_n, (int)split_from);
 }
 
 template <int MT, int TNI, int SB>
@@ -1425,7 +1454,9 @@ int tc_conv_dispatch(TcConvParams p, cudaStream_t stream) {
     TcPlan pl;
     if (!encode_tiled_fn() || !operands_aligned(p) || !tc_prepare(p, sms, &pl)) return TAB_E_TOO_LARGE;
     alignas(64) CUtensorMap tmB, tmY, tmR;
-    if (!make_map_2d(&tmB, p.w8, (unsigned long long)p.Kw * 64, (unsigned long long)p.KN, (unsigned)(pl.pair ? pl.tn / 2 : pl.tn))) return TAB_E_TOO_LARGE;
+    // filter boxes: a pair's CTA and a kernel that can work tiles in halves fetch half a tile's filters per copy
+    const bool half_box = pl.pair || split_capable(pl.mt, pl.tn, pl.resident, p.tepi != 0, pl.pair);
+    if (!make_map_2d(&tmB, p.w8, (unsigned long long)p.Kw * 64, (unsigned long long)p.KN, (unsigned)(half_box ? pl.tn / 2 : pl.tn))) return TAB_E_TOO_LARGE;
     tmY = tmB; tmR = tmB;                                                   // placeholders when the epilogue does not use them
     if (p.tepi) {
         const int bw = p.VW >= 32 ? 32 : p.VW, bh = 32 / bw;
@@ -1433,8 +1464,9 @@ int tc_conv_dispatch(TcConvParams p, cudaStream_t stream) {
         if (p.residual && !make_map_4d(&tmR, p.residual, p.KN, p.OW, p.OH, p.N, bw, bh)) return TAB_E_TOO_LARGE;
     }
     int* status = umma_status_ptr();
-    snprintf(g_last_kernel, sizeof(g_last_kernel), "conv_umma_persist_kernel<%d,%d,%d,%d,%d,%d%s> grid %dx%d%s", pl.mt, pl.tn, pl.sb, (int)pl.resident,
-             p.residual ? 2 : (p.abs_sums ? 1 : 0), p.tepi, pl.pair ? ",pair" : "", p.VH, p.VW, p.next_qx ? " +next" : "");
+    const bool halves = split_point(pl.tiles_m * pl.tiles_n, sms, half_box && !pl.pair) < pl.tiles_m * pl.tiles_n;
+    snprintf(g_last_kernel, sizeof(g_last_kernel), "conv_umma_persist_kernel<%d,%d,%d,%d,%d,%d%s> grid %dx%d%s%s", pl.mt, pl.tn, pl.sb, (int)pl.resident,
+             p.residual ? 2 : (p.abs_sums ? 1 : 0), p.tepi, pl.pair ? ",pair" : "", p.VH, p.VW, halves ? " halves" : "", p.next_qx ? " +next" : "");
     if (pl.pair) return launch_persist<1, 256, 8>(tmB, tmY, tmR, p, pl, sms, status, stream);
     if (pl.tn == 64) return pl.mt == 2 ? launch_persist<2, 64, 6>(tmB, tmY, tmR, p, pl, sms, status, stream) : launch_persist<1, 64, 6>(tmB, tmY, tmR, p, pl, sms, status, stream);
     if (pl.tn == 128) return pl.mt == 2 ? launch_persist<2, 128, 4>(tmB, tmY, tmR, p, pl, sms, status, stream) : launch_persist<1, 128, 6>(tmB, tmY, tmR, p, pl, sms, status, stream);

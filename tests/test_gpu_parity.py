@@ -377,6 +377,49 @@ def test_cta_pair_kernel(cuda, t, geom, conv_path):
 
 @pytest.mark.parametrize("t", [0, 3])
 @pytest.mark.parametrize("geom", [
+    # p1 p2 s1 s2  N   H   W   C   KN KH KW
+    (1, 1, 2, 2, 200, 14, 14, 256, 512, 3, 3),   # strided: 200 tiles, a last round of 52
+    (0, 0, 2, 2, 200, 14, 14, 256, 512, 1, 1),   # 1x1 stride 2: 154 tiles, a last round of 6
+    (1, 1, 1, 1, 200, 7, 7, 128, 512, 3, 3),     # residual layer shape: 200 tiles
+    (1, 1, 1, 1, 48, 14, 14, 192, 320, 3, 3),    # ragged filter count: the second half of the last filter block is empty
+])
+def test_last_round_in_halves(cuda, t, geom, conv_path):
+    """A last round of 256-filter tiles that fills at most half of the persistent grid is worked as halves of 128 filters:
+    plain, with a residual and next thresholds, and with 16-bit output plus the next layer's quantised input, against the
+    oracle."""
+    if conv_path != "tensor":
+        pytest.skip("tensor-core path only")
+    p1, p2, s1, s2, N, H, W, C, KN, KH, KW = geom
+    x, ths = make_input(71, N, H, W, C)
+    w, wths = make_input(72, KN, KH, KW, C)
+    ab, wb = O.act_bits(t), O.weight_bits(t)
+    qw, btn = O.quantize(w, wths, wb, KN, KH, KW, C)
+    qx, _ = TAB.Quantize(dev_t(x, cuda), dev_t(ths, cuda), ab, N, H, W, C)
+    w8 = TAB.ops.expand_weights(dev_t(qw, cuda), wb, KN, KH, KW, C)
+    yo = c_oracle.conv2d(x, qw, ths, btn, t, *geom)
+    OH, OW = yo.shape[2], yo.shape[3]
+    state = TAB.ops.new_state(N, cuda)
+    r = torch.round(torch.randn(*yo.shape, device=cuda) * 5)
+    y2, nxt = TAB.ops.conv2d_bits(qx, w8, t, *geom, residual=r, threshold_scale=0.7, state=state)
+    name = _cabi.lib().tab_last_conv_kernel().decode()
+    if torch.cuda.get_device_properties(cuda).multi_processor_count == 148:
+        assert " halves" in name and ",pair" not in name, name
+    y2o = yo + r.cpu().numpy()
+    assert np.array_equal(y2.cpu().numpy(), y2o)
+    assert np.array_equal(nxt.cpu().numpy(), OracleOps.residual_threshold(y2o.copy(), None, 0.7))
+    if KH * KW == 1 or s1 > 1:                                      # (unit-stride 3x3 layers without a residual run on CTA pairs)
+        y, _ = TAB.ops.conv2d_bits(qx, w8, t, *geom)
+        assert np.array_equal(y.cpu().numpy(), yo)
+        ya, na, qa = TAB.ops.conv2d_bits(qx, w8, t, *geom, threshold_scale=0.7, state=state, out_int16=True, next_bitwidth=ab)
+        tn = OracleOps.residual_threshold(yo.copy(), None, 0.7)
+        assert ya.dtype == torch.int16 and np.array_equal(ya.cpu().numpy().astype(np.float32), yo) and np.array_equal(na.cpu().numpy(), tn)
+        assert np.array_equal(qa.cpu().numpy().reshape(-1), O.quantize(yo.reshape(N, OH, OW, KN), tn, ab, N, OH, OW, KN)[0].reshape(-1))
+    assert not state.any().item()
+    assert _cabi.lib().tab_device_status() == 0
+
+
+@pytest.mark.parametrize("t", [0, 3])
+@pytest.mark.parametrize("geom", [
     # p1 p2 s1 s2  N   H    W    C   KN KH KW
     (3, 3, 2, 2, 2, 224, 224, 3, 64, 7, 7),      # ResNet stem: 49 taps over four parity planes
     (1, 1, 1, 1, 1, 224, 224, 64, 64, 3, 3),     # wide image: the patch only fits with one row block per tile
