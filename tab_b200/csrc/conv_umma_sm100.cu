@@ -432,9 +432,19 @@ __device__ __forceinline__ void slab_columns(const TcConvParams& p, uint32_t tad
         uint32_t v[32];
         tmem_ld32(taddr + (uint32_t)cb, v);
         if (vec4 && nbase + 32 <= p.KN) {
+            // compact output whose rows start on 16-byte boundaries: the block is transposed as 16-bit values (half the
+            // shared-memory traffic; on the 64-filter layers that traffic, next to the MMAs' operand reads, is the bound)
+            const bool pack16 = !has_res && p.y16 != nullptr && (p.KN & 7) == 0;
+            if (pack16) {
 #pragma unroll
-            for (int q = 0; q < 8; q++)
-                sts_v4(stage + lane * 128 + ((q ^ (lane & 7)) << 4), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                for (int q = 0; q < 4; q++)                                // row `lane`: 64 bytes, 16-byte chunk q at (q ^ (lane / 2 % 4))
+                    sts_v4(stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4), __byte_perm(v[8 * q], v[8 * q + 1], 0x5410), __byte_perm(v[8 * q + 2], v[8 * q + 3], 0x5410),
+                           __byte_perm(v[8 * q + 4], v[8 * q + 5], 0x5410), __byte_perm(v[8 * q + 6], v[8 * q + 7], 0x5410));
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    sts_v4(stage + lane * 128 + ((q ^ (lane & 7)) << 4), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            }
             if (sr.fast && !has_res) {                                     // y is the accumulator itself: sum |acc| of the lane's own row
                 unsigned r0 = 0, r1 = 0, r2 = 0, r3 = 0;                   // (row `lane` of the slab), in integers, before the transposition;
 #pragma unroll                                                             // four independent |x| + acc chains (one SAD instruction each)
@@ -446,6 +456,27 @@ __device__ __forceinline__ void slab_columns(const TcConvParams& p, uint32_t tad
             }
             if (has_res && !res_loaded) slab_load_residual(p, sr, nbase, lane, res);
             __syncwarp();
+            if (pack16) {                                                  // four lanes store the 64 bytes of a row, eight rows per instruction
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int r = 8 * i + (lane >> 2), c = lane & 3;
+                    const int4 raw = lds_v4(stage + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+                    const int m = __shfl_sync(0xFFFFFFFFu, sr.m_own, r);
+                    if (m >= 0) {
+                        reinterpret_cast<int4*>(p.y16 + (long long)m * p.KN + nbase)[c] = raw;
+                        if (sr.slow) {
+                            const int img = (int)p.dVHW.div((uint32_t)(sr.Rw + r));
+                            const int q4[4] = {raw.x, raw.y, raw.z, raw.w};
+                            int tot = 0;
+#pragma unroll
+                            for (int j = 0; j < 4; j++) tot += abs((int)(int16_t)(q4[j] & 0xFFFF)) + abs(q4[j] >> 16);
+                            if (img < p.N) atomicAdd(p.abs_sums + img, (double)tot);
+                        }
+                    }
+                }
+                __syncwarp();
+                continue;
+            }
             if (!has_res && p.y16 != nullptr) {                            // compact output: the integers themselves, 16 bits each
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
