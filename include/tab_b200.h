@@ -78,7 +78,10 @@ size_t tab_conv2d_workspace_bytes(int type, int p1, int p2, int s1, int s2,
 enum { TAB_PATH_AUTO = 0, TAB_PATH_POPCOUNT = 1, TAB_PATH_POPCOUNT_PLAIN = 2 };
 int tab_conv2d_set_path(int path);
 /* Name and tile of the kernel the calling thread's most recent tensor-core convolution launched ("none" before the first, or
-   when the last convolution ran the popcount kernel).  Static storage per thread. */
+   when the last convolution ran the popcount kernel), e.g. "conv_umma_persist_kernel<1,256,4,0,2,0> grid 15x15 halves +next":
+   template arguments (row blocks per tile, filters per tile, ring stages, resident filters, fused epilogue, TMA epilogue,
+   ",pair" on clusters of two CTAs), the virtual grid per image, " halves" when the last round of tiles is worked as half-width
+   tiles, " +next" when the launch also quantises its result for the next layer.  Static storage per thread. */
 const char* tab_last_conv_kernel(void);
 /*
  * Every wait inside the tensor-core kernel and inside tab_quantize_auto_launch's kernel is bounded; a wait that ran out makes
