@@ -675,7 +675,7 @@ conv_umma_persist_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_c
     // SPLIT: the tiles from split_from on (the last, partly filled round of the grid) are worked as two halves of TNI/2
     // filters each, numbered after the whole tiles: twice as many CTAs share the round and it takes about half as long.
     const int sfrom = SPLIT ? split_from : tiles_m * tiles_n;
-    const int ntiles = 2 * tiles_m * tiles_n - sfrom;                      // work items: whole tiles, then halves
+    const int ntiles = tiles_m * tiles_n + (tiles_m * tiles_n - sfrom);    // work items: whole tiles, then halves (at most one grid of them)
     auto tile_of = [&](int v) { return SPLIT && v >= sfrom ? sfrom + ((v - sfrom) >> 1) : v; };
     auto half_of = [&](int v) { return SPLIT && v >= sfrom ? 1 + ((v - sfrom) & 1) : 0; };    // 0: whole tile, 1 / 2: its halves
     const uint32_t crank = PAIR ? cluster_ctarank() : 0u;                  // 0: the CTA whose MMA warp works for the pair
@@ -1300,7 +1300,7 @@ static bool plan_shape(const TcConvParams& p, int mt, int tn, int sb, TcPlan* ou
     pl.tiles_m = (Mv + 128LL * mt - 1) / (128LL * mt);
     if (pair) pl.tiles_m = (pl.tiles_m + 1) / 2;
     pl.tiles_n = (p.KN + tn - 1) / tn;
-    if (pl.tiles_m * pl.tiles_n >= (1LL << 31)) return false;
+    if (pl.tiles_m * pl.tiles_n >= (1LL << 31) - 65536) return false;      // tile and work-item indices are ints
     *out = pl;
     return true;
 }
